@@ -1,0 +1,146 @@
+/*
+ * qiyas_b200.h -- C ABI of libqiyas_b200.so: the block-scaled quantized products of Qiyas
+ * (gemv and A.B^T over the GGUF block formats Q8_0, Q4_0, Q4_K, Q6_K) as hand-written
+ * sm_100a CUDA kernels.
+ *
+ * The library replaces, for this path only, Qiyas's run-time PTX generation and its driver
+ * binding (src/Gpu.cs:46-66,142-182,290-301).  Every entry point cites the reference
+ * interface it stands in for.  Conventions shared by all of them:
+ *
+ *  - Device pointers are plain addresses in the current device's primary context (what
+ *    cuMemAlloc_v2 returns to the reference's Gpu.Rent, src/Gpu.cs:227-249).  Operands need
+ *    2-byte alignment only (a 34- or 18-byte block is 2-byte aligned, src/BlockProducts.cs:108);
+ *    f32 arrays need 4-byte alignment.
+ *  - `stream` is a cudaStream_t / CUstream passed as void*; NULL is the legacy default stream,
+ *    which is where the reference launches (src/Gpu.cs:300).  Calls are asynchronous and never
+ *    synchronize; the caller orders them as it orders the reference's launches.
+ *  - Return value: 0 success; < 0 an argument error (the reference throws NotSupportedException
+ *    or ArgumentException there); > 0 a cudaError_t (the reference throws
+ *    InvalidOperationException, src/Gpu.cs:74-79).  qb200_last_error() gives the text.
+ *  - Nothing is retained from the caller's buffers; outputs are overwritten whole.
+ *  - No entry point falls back to a CPU path: without a usable sm_100 device they fail.
+ */
+#ifndef QIYAS_B200_H
+#define QIYAS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Format ids.  Names and layouts: src/Blocks.cs:10-17 and the type structs at :261-331. */
+#define QB200_Q8_0 0   /* 32 values / 34 bytes: f16 d, 32 int8                          */
+#define QB200_Q4_0 1   /* 32 values / 18 bytes: f16 d, 16 bytes of nibbles, value d(q-8) */
+#define QB200_Q4_K 2   /* 256 values / 144 bytes                                          */
+#define QB200_Q6_K 3   /* 256 values / 210 bytes                                          */
+#define QB200_F32 100  /* plain float32 lanes                                             */
+
+/* Argument errors (negative returns). */
+#define QB200_E_FORMAT (-1)     /* format not taken by this entry point                    */
+#define QB200_E_SHAPE (-2)      /* columns / k not in whole blocks, or a dimension <= 0     */
+#define QB200_E_POINTER (-3)    /* null or misaligned pointer                               */
+#define QB200_E_WORKSPACE (-4)  /* workspace missing or too small                           */
+#define QB200_E_DEVICE (-5)     /* no sm_100 device / library not initialised               */
+#define QB200_E_LIMIT (-6)      /* a size beyond what the kernels take (see each call)      */
+
+/* Operations, for qb200_lane_name. */
+#define QB200_OP_GEMV 0
+#define QB200_OP_MATMUL 1
+
+typedef struct qb200_caps {
+    int device;              /* ordinal the library is bound to                              */
+    int sm_major, sm_minor;  /* compute capability                                           */
+    int sm_count;            /* multiprocessors                                              */
+    int tcgen05;             /* 1 when the int8 tcgen05 product can run (sm_100)             */
+    int max_shared_bytes;    /* opt-in shared memory per block                               */
+    int64_t l2_bytes;        /* L2 cache size                                                */
+    int64_t global_bytes;    /* device memory                                                */
+} qb200_caps_t;
+
+/* Binds the library to `device` (the reference always takes ordinal 0, src/Gpu.cs:94-96) and
+ * sets the kernels' attributes.  Must be called once before any other call. */
+int qb200_init(int device);
+int qb200_caps(qb200_caps_t *out);
+
+/* Text of the last error on the calling thread ("" if none). */
+const char *qb200_last_error(void);
+
+/* GpuOps.BlockProductAvailable (src/MatMulBlocks.cs:392): 1 when the tensor product can run. */
+int qb200_block_product_available(void);
+
+/* The lane-name string the reference's operators return (src/BlockProducts.cs:185,
+ * src/MatMulBlocks.cs:402): "s8dp blocks" for gemv, "s8 tcgen05 blocks" for A.B^T. */
+const char *qb200_lane_name(int op, int fmt_a);
+
+/* Reads and clears the device-side status word.  0 = every kernel so far ran to the end;
+ * non-zero = a bounded wait inside a kernel gave up (bit 0: gemv ring, bit 1: A.B^T pipeline).
+ * Synchronizes the device. */
+int qb200_device_status(int *status);
+
+/* ---- gemv -------------------------------------------------------------------------------
+ * GpuOps.GemvBlocks<TN>(a, x, y, rows, cols) (src/BlockProducts.cs:178-186; kernel it replaces:
+ * Ptx.GemvBlocks, :78-172):  y[r] = sum over blocks of (dA*dX) * (sum_32 qA*qX), f32 lanes.
+ *   fmt_a: Q8_0, Q4_0 (the reference's two) or Q4_K, Q6_K (no block product in the reference:
+ *          its gemv decodes them to f32, src/GpuOps.cs:287-300).
+ *   fmt_x: Q8_0 or Q4_0 blocks (the reference passes x in a's format), or QB200_F32: x is then
+ *          encoded to Q8_0 inside the kernel exactly as lanes_to_q8_0 encodes it
+ *          (src/Ptx.Blocks.cs:52-73), and the product is taken on those blocks.
+ *          With fmt_a Q4_K / Q6_K, fmt_x is Q8_0 or F32.
+ *   cols must be whole blocks of a's format, and at most 65536.  rows >= 0. */
+int qb200_gemv_blocks(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, void *stream);
+
+/* As qb200_gemv_blocks, and also writes the exact s32 sum of every 32-value block,
+ * sums[r * (cols/32) + b] (Q8_0 / Q4_0: sum qA*qX with Q4_0's q-8; Q4_K: sum q*qX per sub-block;
+ * Q6_K: scA*sum16 + scB*sum16 with q-32).  For parity checks of the integer part. */
+int qb200_gemv_block_sums(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols,
+                          void *stream);
+
+/* The same product on HOST buffers: copies a and x to the device, runs the kernel, copies y
+ * back and waits (what Checks.GemvRun does around the operator, src/Checks.cs:1983-1997:
+ * Rent, Upload, op, Synchronize, Download).  Device staging is kept by the library and grows
+ * on demand. */
+int qb200_gemv_blocks_host(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols);
+
+/* ---- A.B^T ------------------------------------------------------------------------------
+ * GpuOps.MatMulBlocks<TN>(a, b, cLanes, m, n, k) (src/MatMulBlocks.cs:395-403; kernel it
+ * replaces: Ptx.MatMulBlocks, :178-386):  C[i,j] = sum over k-blocks of
+ * fma(float(D_kb[i,j]), sA[i,kb]*sB[j,kb], acc), kb ascending, D_kb the exact s32 of 32 products.
+ *   fmt_a, fmt_b: Q8_0 or Q4_0 each (the reference takes one format for both).
+ *   k whole blocks of 32; m, n >= 1.
+ *   workspace: device scratch of qb200_matmul_workspace_bytes(...) bytes, 256-byte aligned,
+ *   private to the call until it completes on `stream` (the operands are re-laid there for
+ *   the tensor cores).  Pass NULL/0 to use a scratch buffer the library keeps and grows. */
+size_t qb200_matmul_workspace_bytes(int fmt_a, int fmt_b, int m, int n, int k);
+int qb200_matmul_blocks(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int m, int n, int k, void *workspace,
+                        size_t workspace_bytes, void *stream);
+
+/* As qb200_matmul_blocks for a tiny shape, also writing every exact block sum
+ * sums[(i*n + j)*(k/32) + kb]; m*n*(k/32) must be at most 2^24. */
+int qb200_matmul_block_sums(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int32_t *sums, int m, int n, int k,
+                            void *stream);
+
+/* ---- codecs -----------------------------------------------------------------------------
+ * qb200_encode: Ptx.LanesToBlock, the `Back` step (src/Ptx.Blocks.cs:11-331, src/GpuOps.cs:964-975):
+ * n f32 lanes -> whole blocks of fmt, zeros read past n; byte-for-byte the CPU encoder
+ * (src/Blocks.cs:37-45,58-70,98-148,175-215) with the device's rounding for Q4_0.
+ * qb200_decode: Ptx.Widen (src/Ptx.Attention.cs:202-219, src/Ptx.cs:151-277): value i of a block
+ * array as f32, bit-for-bit Blocks.Decode* (src/Blocks.cs:31-35,48-56,79-96,151-173). */
+int qb200_encode(int fmt, const float *lanes, void *blocks, int64_t n, void *stream);
+int qb200_decode(int fmt, const void *blocks, float *lanes, int64_t n, void *stream);
+
+/* ---- plain device memory for hosts without a CUDA binding of their own (tests, bench) ---- */
+int qb200_malloc(void **ptr, size_t bytes);
+int qb200_free(void *ptr);
+int qb200_malloc_host(void **ptr, size_t bytes);   /* pinned host memory */
+int qb200_free_host(void *ptr);
+int qb200_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream);
+int qb200_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream);
+int qb200_memset(void *dst, int value, size_t bytes, void *stream);
+int qb200_synchronize(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

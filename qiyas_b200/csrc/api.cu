@@ -1,0 +1,303 @@
+// The C ABI of libqiyas_b200.so (declared in include/qiyas_b200.h): argument checks in the reference's terms,
+// error text, device binding, and the launches.  No entry point has a CPU path: on a machine without an sm_100 device
+// qb200_init fails and every other call returns QB200_E_DEVICE.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+#include "launch.h"
+
+namespace {
+
+thread_local char t_error[512] = "";
+bool g_ready = false;
+qb200_caps_t g_caps;
+
+// grow-only device buffers the library keeps: staging for the host-buffer calls, scratch for A.B^T without a workspace
+struct Kept {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
+Kept g_stage_a, g_stage_x, g_stage_y, g_scratch;
+int *g_status = nullptr;      // device word the kernels OR their STATUS_* bits into
+
+int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_error, sizeof t_error, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char *what)
+{
+    snprintf(t_error, sizeof t_error, "%s: %s", what, cudaGetErrorString(e));
+    return (int)e;
+}
+
+int finish(int rc, const char *what)
+{
+    if (rc > 0) return cuda_fail((cudaError_t)rc, what);
+    if (rc == QB200_E_LIMIT) return fail(rc, "%s: the shape is beyond what the kernel's shared memory takes", what);
+    if (rc < 0) return fail(rc, "%s: argument error %d", what, rc);
+    return 0;
+}
+
+const char *fmt_name(int fmt)
+{
+    switch (fmt) {
+    case QB200_Q8_0: return "q8_0";
+    case QB200_Q4_0: return "q4_0";
+    case QB200_Q4_K: return "q4_k";
+    case QB200_Q6_K: return "q6_k";
+    case QB200_F32: return "f32";
+    default: return "?";
+    }
+}
+
+int keep(Kept &k, size_t bytes)
+{
+    if (k.bytes >= bytes) return 0;
+    if (k.ptr) cudaFree(k.ptr);
+    k.ptr = nullptr;
+    k.bytes = 0;
+    size_t want = bytes + bytes / 4 + 4096;
+    cudaError_t e = cudaMalloc(&k.ptr, want);
+    if (e) return cuda_fail(e, "cudaMalloc");
+    k.bytes = want;
+    return 0;
+}
+
+int check_gemv(int fmt_a, int fmt_x, const void *a, const void *x, const float *y, int rows, int cols)
+{
+    if (!g_ready) return fail(QB200_E_DEVICE, "qb200_init has not succeeded");
+    const int bv = qb::block_values(fmt_a);
+    if (!bv) return fail(QB200_E_FORMAT, "%s: the block product takes Q8_0, Q4_0, Q4_K or Q6_K rows", fmt_name(fmt_a));
+    const bool k_quant = fmt_a == QB200_Q4_K || fmt_a == QB200_Q6_K;
+    if (!(fmt_x == QB200_Q8_0 || fmt_x == QB200_F32 || (fmt_x == QB200_Q4_0 && !k_quant)))
+        return fail(QB200_E_FORMAT, "%s x %s: x comes in Q8_0 or f32 (or Q4_0 against Q8_0 / Q4_0 rows)", fmt_name(fmt_a), fmt_name(fmt_x));
+    if (rows < 0 || cols <= 0 || cols % bv != 0)
+        return fail(QB200_E_SHAPE, "%s: the block product takes columns in whole blocks of %d (rows %d, cols %d)", fmt_name(fmt_a), bv, rows, cols);
+    if (cols > 65536) return fail(QB200_E_LIMIT, "cols %d: at most 65536 columns", cols);
+    if (rows == 0) return 0;
+    if (!a || !x || !y) return fail(QB200_E_POINTER, "null operand");
+    if (((uintptr_t)a & 1) || ((uintptr_t)x & (fmt_x == QB200_F32 ? 3 : 1)) || ((uintptr_t)y & 3)) return fail(QB200_E_POINTER, "misaligned operand");
+    return 0;
+}
+
+int check_matmul(int fmt_a, int fmt_b, const void *a, const void *b, const float *c, int m, int n, int k)
+{
+    if (!g_ready) return fail(QB200_E_DEVICE, "qb200_init has not succeeded");
+    if ((fmt_a != QB200_Q8_0 && fmt_a != QB200_Q4_0) || (fmt_b != QB200_Q8_0 && fmt_b != QB200_Q4_0))
+        return fail(QB200_E_FORMAT, "%s x %s: the block product takes Q8_0 or Q4_0 with k in whole blocks", fmt_name(fmt_a), fmt_name(fmt_b));
+    if (m <= 0 || n <= 0 || k <= 0 || k % 32 != 0)
+        return fail(QB200_E_SHAPE, "the block product takes Q8_0 or Q4_0 with k in whole blocks (m %d, n %d, k %d)", m, n, k);
+    if (!g_caps.tcgen05) return fail(QB200_E_DEVICE, "the block product needs the s8 tensor instruction (tcgen05, sm_100)");
+    if (!a || !b || !c) return fail(QB200_E_POINTER, "null operand");
+    if (((uintptr_t)a & 1) || ((uintptr_t)b & 1) || ((uintptr_t)c & 3)) return fail(QB200_E_POINTER, "misaligned operand");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int qb200_init(int device)
+{
+    g_ready = false;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e) return cuda_fail(e, "cudaGetDeviceCount");
+    if (device < 0 || device >= count) return fail(QB200_E_DEVICE, "device %d of %d", device, count);
+    if ((e = cudaSetDevice(device))) return cuda_fail(e, "cudaSetDevice");
+    cudaDeviceProp prop;
+    if ((e = cudaGetDeviceProperties(&prop, device))) return cuda_fail(e, "cudaGetDeviceProperties");
+    memset(&g_caps, 0, sizeof g_caps);
+    g_caps.device = device;
+    g_caps.sm_major = prop.major;
+    g_caps.sm_minor = prop.minor;
+    g_caps.sm_count = prop.multiProcessorCount;
+    g_caps.tcgen05 = prop.major == 10 ? 1 : 0;
+    g_caps.max_shared_bytes = (int)prop.sharedMemPerBlockOptin;
+    g_caps.l2_bytes = prop.l2CacheSize;
+    g_caps.global_bytes = (int64_t)prop.totalGlobalMem;
+    if (prop.major != 10) return fail(QB200_E_DEVICE, "device %d is sm_%d%d: the kernels are built for sm_100a only", device, prop.major, prop.minor);
+    if (!g_status) {
+        if ((e = cudaMalloc((void **)&g_status, 256))) return cuda_fail(e, "cudaMalloc status");
+    }
+    if ((e = cudaMemset(g_status, 0, 256))) return cuda_fail(e, "cudaMemset status");
+    if ((e = qb::gemv_init(g_caps.sm_count, g_caps.max_shared_bytes, g_status))) return cuda_fail(e, "gemv attributes");
+    if ((e = qb::matmul_init(g_caps.sm_count, g_caps.max_shared_bytes, g_status))) return cuda_fail(e, "matmul attributes");
+    g_stage_a = g_stage_x = g_stage_y = g_scratch = Kept();
+    g_ready = true;
+    t_error[0] = 0;
+    return 0;
+}
+
+int qb200_caps(qb200_caps_t *out)
+{
+    if (!g_ready) return fail(QB200_E_DEVICE, "qb200_init has not succeeded");
+    if (!out) return fail(QB200_E_POINTER, "null caps");
+    *out = g_caps;
+    return 0;
+}
+
+const char *qb200_last_error(void) { return t_error; }
+
+int qb200_block_product_available(void) { return g_ready && g_caps.tcgen05 ? 1 : 0; }
+
+const char *qb200_lane_name(int op, int fmt_a)
+{
+    (void)fmt_a;
+    return op == QB200_OP_MATMUL ? "s8 tcgen05 blocks" : "s8dp blocks";
+}
+
+int qb200_device_status(int *status)
+{
+    if (!g_ready) return fail(QB200_E_DEVICE, "qb200_init has not succeeded");
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e) return cuda_fail(e, "cudaDeviceSynchronize");
+    int value = 0, zero = 0;
+    if ((e = cudaMemcpy(&value, g_status, sizeof value, cudaMemcpyDeviceToHost))) return cuda_fail(e, "status read");
+    if (value && (e = cudaMemcpy(g_status, &zero, sizeof zero, cudaMemcpyHostToDevice))) return cuda_fail(e, "status clear");
+    if (status) *status = value;
+    return 0;
+}
+
+int qb200_gemv_blocks(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, void *stream)
+{
+    int rc = check_gemv(fmt_a, fmt_x, a, x, y, rows, cols);
+    if (rc) return rc;
+    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, nullptr, rows, cols, (cudaStream_t)stream), "gemv_blocks");
+}
+
+int qb200_gemv_block_sums(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols, void *stream)
+{
+    int rc = check_gemv(fmt_a, fmt_x, a, x, y, rows, cols);
+    if (rc) return rc;
+    if (rows > 0 && (!sums || ((uintptr_t)sums & 3))) return fail(QB200_E_POINTER, "null or misaligned sums");
+    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, sums, rows, cols, (cudaStream_t)stream), "gemv_block_sums");
+}
+
+int qb200_gemv_blocks_host(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols)
+{
+    if (!g_ready) return fail(QB200_E_DEVICE, "qb200_init has not succeeded");
+    const int bv = qb::block_values(fmt_a);
+    if (!bv || rows < 0 || cols <= 0 || cols % bv) return fail(QB200_E_SHAPE, "the block product takes columns in whole blocks");
+    if (rows == 0) return 0;
+    if (!a || !x || !y) return fail(QB200_E_POINTER, "null operand");
+    const size_t a_bytes = (size_t)rows * (cols / bv) * qb::block_bytes(fmt_a);
+    const size_t x_bytes = fmt_x == QB200_F32 ? (size_t)cols * 4 : (size_t)(cols / 32) * qb::block_bytes(fmt_x);
+    int rc;
+    if ((rc = keep(g_stage_a, a_bytes)) || (rc = keep(g_stage_x, x_bytes)) || (rc = keep(g_stage_y, (size_t)rows * 4))) return rc;
+    cudaError_t e;
+    if ((e = cudaMemcpyAsync(g_stage_a.ptr, a, a_bytes, cudaMemcpyHostToDevice, 0))) return cuda_fail(e, "upload a");
+    if ((e = cudaMemcpyAsync(g_stage_x.ptr, x, x_bytes, cudaMemcpyHostToDevice, 0))) return cuda_fail(e, "upload x");
+    if ((rc = qb200_gemv_blocks(fmt_a, fmt_x, g_stage_a.ptr, g_stage_x.ptr, (float *)g_stage_y.ptr, rows, cols, nullptr))) return rc;
+    if ((e = cudaMemcpyAsync(y, g_stage_y.ptr, (size_t)rows * 4, cudaMemcpyDeviceToHost, 0))) return cuda_fail(e, "download y");
+    if ((e = cudaStreamSynchronize(0))) return cuda_fail(e, "synchronize");
+    return 0;
+}
+
+size_t qb200_matmul_workspace_bytes(int fmt_a, int fmt_b, int m, int n, int k)
+{
+    if (m <= 0 || n <= 0 || k <= 0 || k % 32) return 0;
+    return qb::matmul_workspace_bytes(fmt_a, fmt_b, m, n, k);
+}
+
+int qb200_matmul_blocks(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int m, int n, int k, void *workspace,
+                        size_t workspace_bytes, void *stream)
+{
+    int rc = check_matmul(fmt_a, fmt_b, a, b, c, m, n, k);
+    if (rc) return rc;
+    const size_t need = qb::matmul_workspace_bytes(fmt_a, fmt_b, m, n, k);
+    if (workspace) {
+        if (workspace_bytes < need) return fail(QB200_E_WORKSPACE, "workspace of %zu bytes, %zu needed", workspace_bytes, need);
+        if ((uintptr_t)workspace & 255) return fail(QB200_E_WORKSPACE, "workspace not 256-byte aligned");
+    } else {
+        if ((rc = keep(g_scratch, need))) return rc;
+        workspace = g_scratch.ptr;
+    }
+    return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, c, nullptr, m, n, k, workspace, (cudaStream_t)stream), "matmul_blocks");
+}
+
+int qb200_matmul_block_sums(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int32_t *sums, int m, int n, int k, void *stream)
+{
+    int rc = check_matmul(fmt_a, fmt_b, a, b, c, m, n, k);
+    if (rc) return rc;
+    if (!sums || ((uintptr_t)sums & 3)) return fail(QB200_E_POINTER, "null or misaligned sums");
+    if ((int64_t)m * n * (k / 32) > (1 << 24)) return fail(QB200_E_LIMIT, "block sums are for small shapes: m*n*(k/32) at most 2^24");
+    if ((rc = keep(g_scratch, qb::matmul_workspace_bytes(fmt_a, fmt_b, m, n, k)))) return rc;
+    return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, c, sums, m, n, k, g_scratch.ptr, (cudaStream_t)stream), "matmul_block_sums");
+}
+
+int qb200_encode(int fmt, const float *lanes, void *blocks, int64_t n, void *stream)
+{
+    if (!g_ready) return fail(QB200_E_DEVICE, "qb200_init has not succeeded");
+    if (!qb::block_values(fmt)) return fail(QB200_E_FORMAT, "%s: not a block format", fmt_name(fmt));
+    if (n < 0 || n > 2147483647LL) return fail(QB200_E_SHAPE, "count %lld", (long long)n);
+    if (n && (!lanes || !blocks || ((uintptr_t)lanes & 3))) return fail(QB200_E_POINTER, "null or misaligned operand");
+    return finish(qb::encode_launch(fmt, lanes, blocks, n, (cudaStream_t)stream), "encode");
+}
+
+int qb200_decode(int fmt, const void *blocks, float *lanes, int64_t n, void *stream)
+{
+    if (!g_ready) return fail(QB200_E_DEVICE, "qb200_init has not succeeded");
+    if (!qb::block_values(fmt)) return fail(QB200_E_FORMAT, "%s: not a block format", fmt_name(fmt));
+    if (n < 0 || n > 2147483647LL) return fail(QB200_E_SHAPE, "count %lld", (long long)n);
+    if (n && (!lanes || !blocks || ((uintptr_t)lanes & 3))) return fail(QB200_E_POINTER, "null or misaligned operand");
+    return finish(qb::decode_launch(fmt, blocks, lanes, n, (cudaStream_t)stream), "decode");
+}
+
+int qb200_malloc(void **ptr, size_t bytes)
+{
+    if (!ptr) return fail(QB200_E_POINTER, "null out pointer");
+    cudaError_t e = cudaMalloc(ptr, bytes ? bytes : 1);
+    return e ? cuda_fail(e, "cudaMalloc") : 0;
+}
+
+int qb200_free(void *ptr)
+{
+    cudaError_t e = cudaFree(ptr);
+    return e ? cuda_fail(e, "cudaFree") : 0;
+}
+
+int qb200_malloc_host(void **ptr, size_t bytes)
+{
+    if (!ptr) return fail(QB200_E_POINTER, "null out pointer");
+    cudaError_t e = cudaMallocHost(ptr, bytes ? bytes : 1);
+    return e ? cuda_fail(e, "cudaMallocHost") : 0;
+}
+
+int qb200_free_host(void *ptr)
+{
+    cudaError_t e = cudaFreeHost(ptr);
+    return e ? cuda_fail(e, "cudaFreeHost") : 0;
+}
+
+int qb200_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream)
+{
+    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream);
+    return e ? cuda_fail(e, "cudaMemcpyAsync h2d") : 0;
+}
+
+int qb200_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream)
+{
+    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    return e ? cuda_fail(e, "cudaMemcpyAsync d2h") : 0;
+}
+
+int qb200_memset(void *dst, int value, size_t bytes, void *stream)
+{
+    cudaError_t e = cudaMemsetAsync(dst, value, bytes, (cudaStream_t)stream);
+    return e ? cuda_fail(e, "cudaMemsetAsync") : 0;
+}
+
+int qb200_synchronize(void)
+{
+    cudaError_t e = cudaDeviceSynchronize();
+    return e ? cuda_fail(e, "cudaDeviceSynchronize") : 0;
+}
+
+}  // extern "C"

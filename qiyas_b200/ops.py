@@ -1,0 +1,200 @@
+"""Host-side mirror of the reference's operator surface for the block-scaled products.
+
+``GpuOps`` keeps the names, argument meaning and error behaviour of the reference's C# class for
+this path (src/BlockProducts.cs:175-187, src/MatMulBlocks.cs:389-443, src/GpuOps.cs:277-285) and
+forwards every call through the C ABI of ``libqiyas_b200.so``.  Operands are device pointers
+(ints, as the reference's ``ulong``) or CUDA ``torch`` tensors, whose ``data_ptr()`` is taken:
+torch is used for device memory and streams only.
+
+Errors follow the reference: a format or shape the block product does not take raises
+``NotImplementedError`` (the reference's NotSupportedException); a CUDA failure raises
+``RuntimeError`` (its InvalidOperationException).  Nothing here computes on the CPU.
+"""
+import ctypes as C
+from dataclasses import dataclass
+
+from . import _lib
+from .blocks import BLOCK_VALUES, F32, NAMES, Q4_0, Q8_0, fmt_id, nbytes
+
+OP_GEMV, OP_MATMUL = 0, 1
+
+
+@dataclass(frozen=True)
+class ProductView:
+    """A product on views (src/Products.cs:15): C = op(A).op(B); the block product takes A.B^T, batch 1."""
+    M: int
+    N: int
+    K: int
+    TransA: bool = False
+    TransB: bool = True
+    Batch: int = 1
+
+    @property
+    def ValuesC(self):
+        return self.M * self.N
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    return x.data_ptr()
+
+
+def _stream(stream):
+    if stream is None:
+        return None
+    if isinstance(stream, int):
+        return stream or None
+    return stream.cuda_stream or None
+
+
+class Gpu:
+    """The device binding for this path (stands where src/Gpu.cs stands in the reference): one device, bound once."""
+
+    def __init__(self, device=0):
+        self.lib = _lib.load()
+        rc = self.lib.qb200_init(int(device))
+        if rc:
+            raise RuntimeError(f"qb200_init({device}): {self.error()}")
+        self.device = int(device)
+        caps = _lib.Caps()
+        self.check(self.lib.qb200_caps(C.byref(caps)), "qb200_caps")
+        self.caps = caps
+
+    def error(self):
+        return self.lib.qb200_last_error().decode()
+
+    def check(self, rc, what):
+        """Maps a return code as the C# shim maps it: < 0 not supported, > 0 a CUDA failure."""
+        if rc == 0:
+            return
+        if rc in (-1, -2, -6):
+            raise NotImplementedError(self.error())
+        if rc < 0:
+            raise ValueError(self.error())
+        raise RuntimeError(f"{what}: {self.error()}")
+
+    def Synchronize(self):
+        self.check(self.lib.qb200_synchronize(), "synchronize")
+
+    def status(self):
+        """Device status word (0 = every bounded wait inside the kernels completed); synchronizes."""
+        value = C.c_int(0)
+        self.check(self.lib.qb200_device_status(C.byref(value)), "device_status")
+        return value.value
+
+
+class GpuOps:
+    """GemvBlocks / MatMulBlocks / Gemv / MatMulViewBlocks / MatMulView on block formats, as the reference names them."""
+
+    def __init__(self, gpu=None, device=0):
+        self.gpu = gpu if gpu is not None else Gpu(device)
+        self.lib = self.gpu.lib
+        self.BlockProducts = None          # the gate's override (src/MatMulBlocks.cs:406): True forces the block product
+        self._scratch = {}
+
+    # -- availability -------------------------------------------------------------------------
+    @property
+    def BlockProductAvailable(self):
+        return bool(self.lib.qb200_block_product_available())
+
+    def lane_name(self, op, fmt):
+        return self.lib.qb200_lane_name(op, fmt_id(fmt)).decode()
+
+    # -- gemv ----------------------------------------------------------------------------------
+    def GemvBlocks(self, fmt, a, x, y, rows, cols, fmt_x=None, stream=None):
+        """y (f32 lanes) = A.x; `fmt` names A's block type; x is in the same format unless `fmt_x` says otherwise."""
+        fa = fmt_id(fmt)
+        fx = fa if fmt_x is None else fmt_id(fmt_x)
+        rc = self.lib.qb200_gemv_blocks(fa, fx, _ptr(a), _ptr(x), _ptr(y), int(rows), int(cols), _stream(stream))
+        self.gpu.check(rc, "GemvBlocks")
+        return self.lane_name(OP_GEMV, fa)
+
+    def GemvBlockSums(self, fmt, a, x, y, sums, rows, cols, fmt_x=None, stream=None):
+        fa = fmt_id(fmt)
+        fx = fa if fmt_x is None else fmt_id(fmt_x)
+        rc = self.lib.qb200_gemv_block_sums(fa, fx, _ptr(a), _ptr(x), _ptr(y), _ptr(sums), int(rows), int(cols), _stream(stream))
+        self.gpu.check(rc, "GemvBlockSums")
+        return self.lane_name(OP_GEMV, fa)
+
+    def Gemv(self, fmt, a, x, y, rows, cols, transposed=False, stream=None):
+        """The public gemv's block branch (src/GpuOps.cs:277-285): f32 lanes, then `Back` into y's block format."""
+        fa = fmt_id(fmt)
+        if fa not in (Q8_0, Q4_0) or transposed or cols % 32:
+            raise NotImplementedError(f"{NAMES.get(fa, fa)}: only the block-scaled branch of Gemv is built here")
+        lanes = self._rent(rows * 4)
+        lane = self.GemvBlocks(fa, a, x, lanes, rows, cols, stream=stream)
+        self.Back(fa, lanes, y, rows, stream=stream)
+        return lane
+
+    # -- A.B^T ---------------------------------------------------------------------------------
+    def MatMulBlocks(self, fmt, a, b, c_lanes, m, n, k, fmt_b=None, workspace=None, workspace_bytes=0, stream=None):
+        """C (f32 lanes, m x n) = A.B^T; `fmt` names A's block type and B's unless `fmt_b` is given."""
+        fa = fmt_id(fmt)
+        fb = fa if fmt_b is None else fmt_id(fmt_b)
+        rc = self.lib.qb200_matmul_blocks(fa, fb, _ptr(a), _ptr(b), _ptr(c_lanes), int(m), int(n), int(k), _ptr(workspace),
+                                          int(workspace_bytes), _stream(stream))
+        self.gpu.check(rc, "MatMulBlocks")
+        return self.lane_name(OP_MATMUL, fa)
+
+    def MatMulBlockSums(self, fmt, a, b, c_lanes, sums, m, n, k, fmt_b=None, stream=None):
+        fa = fmt_id(fmt)
+        fb = fa if fmt_b is None else fmt_id(fmt_b)
+        rc = self.lib.qb200_matmul_block_sums(fa, fb, _ptr(a), _ptr(b), _ptr(c_lanes), _ptr(sums), int(m), int(n), int(k), _stream(stream))
+        self.gpu.check(rc, "MatMulBlockSums")
+        return self.lane_name(OP_MATMUL, fa)
+
+    def workspace_bytes(self, fmt, m, n, k, fmt_b=None):
+        fa = fmt_id(fmt)
+        return int(self.lib.qb200_matmul_workspace_bytes(fa, fa if fmt_b is None else fmt_id(fmt_b), int(m), int(n), int(k)))
+
+    def BlockView(self, fmt, v):
+        """src/MatMulBlocks.cs:410-411."""
+        return (fmt_id(fmt) in (Q8_0, Q4_0) and v.Batch == 1 and not v.TransA and v.TransB and v.K % 32 == 0
+                and self.BlockProductAvailable)
+
+    def MatMulViewBlocks(self, fmt, v, a, b, c, stream=None):
+        """The block product for the view, C encoded to the type by blocks (src/MatMulBlocks.cs:414-424)."""
+        lanes = self._rent(v.M * v.N * 4)
+        lane = self.MatMulBlocks(fmt, a, b, lanes, v.M, v.N, v.K, stream=stream)
+        self.Back(fmt, lanes, c, v.M * v.N, stream=stream)
+        return lane
+
+    def MatMulView(self, fmt, v, a, b, c, stream=None):
+        """src/GpuOps.Products.cs:15-19: the block product where the view allows it.  The decoded route is not part of
+        this library, so a view outside the block path, or `BlockProducts = False`, is not supported."""
+        if self.BlockView(fmt, v) and self.BlockProducts is not False:
+            return self.MatMulViewBlocks(fmt, v, a, b, c, stream=stream)
+        raise NotImplementedError("only A.B^T of two Q8_0 / Q4_0 operands with k in whole blocks is built here")
+
+    # -- codecs --------------------------------------------------------------------------------
+    def Back(self, fmt, lanes, stored, count, stream=None):
+        """f32 lanes -> blocks (src/GpuOps.cs:964-975)."""
+        self.gpu.check(self.lib.qb200_encode(fmt_id(fmt), _ptr(lanes), _ptr(stored), int(count), _stream(stream)), "Back")
+
+    def Lanes(self, fmt, stored, lanes, count, stream=None):
+        """blocks -> f32 lanes, the Widen kernel (src/GpuOps.cs:948-962)."""
+        self.gpu.check(self.lib.qb200_decode(fmt_id(fmt), _ptr(stored), _ptr(lanes), int(count), _stream(stream)), "Lanes")
+
+    # -- host-buffer form (upload, product, download), for callers that hold numpy arrays ---------
+    def GemvBlocksHost(self, fmt, a, x, y, rows, cols, fmt_x=None):
+        fa = fmt_id(fmt)
+        fx = fa if fmt_x is None else fmt_id(fmt_x)
+        rc = self.lib.qb200_gemv_blocks_host(fa, fx, a.ctypes.data, x.ctypes.data, y.ctypes.data, int(rows), int(cols))
+        self.gpu.check(rc, "GemvBlocksHost")
+        return self.lane_name(OP_GEMV, fa)
+
+    # -- the reference's Rent: a kept f32 lane buffer per size class -------------------------------
+    def _rent(self, nbytes_):
+        import torch
+        size = max(256, (int(nbytes_) + 255) // 256 * 256)
+        buf = self._scratch.get("lanes")
+        if buf is None or buf.numel() < size:
+            buf = torch.empty(size, dtype=torch.uint8, device=f"cuda:{self.gpu.device}")
+            self._scratch["lanes"] = buf
+        return buf
+
+
+__all__ = ["Gpu", "GpuOps", "ProductView", "OP_GEMV", "OP_MATMUL", "BLOCK_VALUES", "F32", "nbytes"]

@@ -1,0 +1,141 @@
+"""Parity of the CUDA gemv with the C oracle, through the C ABI.
+
+Gates, in the order the task states them: every block's s32 sum bit-exact; f32 outputs within 1e-5
+(relative to the row's sum of |terms| and, norm-wise, to max|y|) of the reference's device-order
+block product (src/BlockProducts.cs:158-161) and of its CPU order (src/BlockProducts.cs:50); and an
+error against float64 on the stored values (Program.cs:946-952) no larger than the reference's.
+"""
+import numpy as np
+import pytest
+
+from qiyas_b200 import blocks as B
+
+from . import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+REL = 1e-5     # the tolerance the task states for f32 lanes
+
+
+def check_q(oracle, fmt_a, fmt_x, rows, cols, seed, offset_a=0, strict_f64=True):
+    a = B.make_weights(fmt_a, rows, cols, seed)
+    xf = B.make_activations(cols, seed + 1)
+    x = H.x_for(fmt_x, oracle, xf)
+    y, sums, lane = H.gemv_gpu(fmt_a, fmt_x, a, x, rows, cols, want_sums=True, offset_a=offset_a)
+    y_plain, _ = H.gemv_gpu(fmt_a, fmt_x, a, x, rows, cols, offset_a=offset_a)
+    assert lane == "s8dp blocks"
+    assert np.array_equal(y.view(np.uint32), y_plain.view(np.uint32))      # the sums variant changes nothing in y
+    ref_dev, ref_sums, mag = oracle.gemv_blocks(fmt_a, fmt_x, a, x, rows, cols, order=1, want_sums=True, want_abs=True)
+    ref_cpu = oracle.gemv_blocks(fmt_a, fmt_x, a, x, rows, cols, order=0)
+    assert np.array_equal(sums, ref_sums)
+    for ref in (ref_dev, ref_cpu):
+        assert np.all(np.abs(y.astype(np.float64) - ref) <= REL * mag + 1e-30)
+        assert np.max(np.abs(y.astype(np.float64) - ref)) <= REL * np.max(np.abs(ref))
+    y64 = oracle.gemv_f64(fmt_a, a, H.x_values(fmt_x, oracle, x, cols), rows, cols)
+    err_gpu, err_ref = np.abs(y - y64), np.abs(ref_dev - y64)
+    if strict_f64 and rows * cols >= 1 << 20:
+        assert np.sqrt(np.mean(err_gpu ** 2)) <= np.sqrt(np.mean(err_ref ** 2))
+        assert np.max(err_gpu) <= np.max(err_ref)
+    else:
+        assert np.max(err_gpu) <= max(np.max(err_ref), REL * np.max(np.abs(y64)))
+
+
+@pytest.mark.parametrize("fmt_a", [B.Q8_0, B.Q4_0])
+@pytest.mark.parametrize("fmt_x", ["same", B.Q8_0, B.F32])
+def test_gate_shape_37x64(oracle, fmt_a, fmt_x):
+    # the reference's own gemv gate shape (src/Checks.cs:1251-1256)
+    check_q(oracle, fmt_a, fmt_a if fmt_x == "same" else fmt_x, 37, 64, 44)
+
+
+@pytest.mark.parametrize("fmt_a", [B.Q8_0, B.Q4_0])
+@pytest.mark.parametrize("rows,cols", [(1, 32), (3, 64), (2, 96), (37, 320), (61, 2080), (131, 4064), (257, 8160), (64, 11008), (5, 65536)])
+def test_small_and_ragged_shapes(oracle, fmt_a, rows, cols):
+    check_q(oracle, fmt_a, B.F32, rows, cols, 7 + rows)
+
+
+@pytest.mark.parametrize("offset", [2, 6, 14, 18])
+@pytest.mark.parametrize("fmt_a", [B.Q8_0, B.Q4_0])
+def test_operand_alignment_of_two_bytes(oracle, fmt_a, offset):
+    check_q(oracle, fmt_a, B.F32, 67, 1056, 21, offset_a=offset)
+
+
+def test_config_q8_0_4096(oracle):
+    check_q(oracle, B.Q8_0, B.F32, 4096, 4096, 100)
+
+
+def test_config_q8_0_odd_4093x4064(oracle):
+    check_q(oracle, B.Q8_0, B.F32, 4093, 4064, 101)
+
+
+def test_config_q4_0_8192(oracle):
+    check_q(oracle, B.Q4_0, B.F32, 8192, 8192, 102)
+
+
+def test_config_q4_0_odd_8191x8160(oracle):
+    check_q(oracle, B.Q4_0, B.F32, 8191, 8160, 103)
+
+
+def test_reference_signature_same_format(oracle):
+    # GemvBlocks<TN>(a, x, y, rows, cols): x in a's format (src/BlockProducts.cs:178)
+    for fmt in (B.Q8_0, B.Q4_0):
+        check_q(oracle, fmt, fmt, 515, 2048, 55)
+
+
+def test_zero_rows_and_errors():
+    import torch
+    o = H.ops()
+    y = H.empty(4, torch.float32)
+    a = H.empty(64, torch.uint8)
+    assert o.GemvBlocks("q8_0", a, a, y, 0, 32) == "s8dp blocks"
+    with pytest.raises(NotImplementedError):
+        o.GemvBlocks("q8_0", a, a, y, 1, 33)                # columns not in whole blocks
+    with pytest.raises(NotImplementedError):
+        o.GemvBlocks("f32", a, a, y, 1, 32)                 # not a block format
+    with pytest.raises(NotImplementedError):
+        o.GemvBlocks("q4_k", a, a, y, 1, 256, fmt_x="q4_0")  # K-quant rows take Q8_0 or f32 x
+
+
+def test_repeatable_bit_for_bit(oracle):
+    a = B.make_weights(B.Q4_0, 1000, 4096, 9)
+    x = B.make_activations(4096, 10)
+    first, _ = H.gemv_gpu(B.Q4_0, B.F32, a, x, 1000, 4096)
+    for _ in range(5):
+        again, _ = H.gemv_gpu(B.Q4_0, B.F32, a, x, 1000, 4096)
+        assert np.array_equal(first.view(np.uint32), again.view(np.uint32))
+
+
+# ---- Q4_K / Q6_K: no block product in the reference (its gemv decodes them, src/GpuOps.cs:287-300) ----
+
+def check_k(oracle, fmt_a, rows, cols, seed, fmt_x=B.F32):
+    a = B.make_weights(fmt_a, rows, cols, seed)
+    xf = B.make_activations(cols, seed + 1)
+    x = H.x_for(fmt_x, oracle, xf)
+    y, sums, _ = H.gemv_gpu(fmt_a, fmt_x, a, x, rows, cols, want_sums=True)
+    xq_blocks = oracle.encode(B.Q8_0, xf).reshape(-1, 34)
+    xq = xq_blocks[:, 2:].copy().view(np.int8).reshape(-1)
+    assert np.array_equal(sums, oracle.k_block_sums(fmt_a, a, xq, rows, cols))
+    xv = H.x_values(fmt_x, oracle, x, cols)
+    y64 = oracle.gemv_f64(fmt_a, a, xv, rows, cols)
+    decoded = oracle.gemv_decoded_f32(fmt_a, a, xv, rows, cols)          # the reference's route on the same stored values
+    scale = np.max(np.abs(y64))
+    assert np.max(np.abs(y - y64)) <= REL * scale
+    assert np.max(np.abs(y - decoded)) <= REL * scale
+    if rows * cols >= 1 << 20:
+        assert np.max(np.abs(y - y64)) <= np.max(np.abs(decoded - y64)) * 1.0 + 0.0
+
+
+@pytest.mark.parametrize("fmt_a", [B.Q4_K, B.Q6_K])
+@pytest.mark.parametrize("rows,cols", [(1, 256), (5, 512), (37, 1280), (129, 2304), (33, 11008)])
+def test_k_quants_small(oracle, fmt_a, rows, cols):
+    check_k(oracle, fmt_a, rows, cols, 31 + rows)
+
+
+@pytest.mark.parametrize("fmt_a", [B.Q4_K, B.Q6_K])
+@pytest.mark.parametrize("rows,cols", [(4096, 4096), (11008, 4096), (4096, 11008)])
+def test_k_quants_layer_shapes(oracle, fmt_a, rows, cols):
+    check_k(oracle, fmt_a, rows, cols, 200)
+
+
+def test_k_quants_take_q8_0_x(oracle):
+    check_k(oracle, B.Q4_K, 65, 1024, 77, fmt_x=B.Q8_0)
+    check_k(oracle, B.Q6_K, 65, 1024, 78, fmt_x=B.Q8_0)

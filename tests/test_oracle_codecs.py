@@ -1,0 +1,160 @@
+"""The C oracle's codecs against the reference's own known answers.
+
+The hand-laid blocks and expected values are the formulas of the reference's codec gate
+(src/Checks.cs:264-355, BlockSpecifications); the round trip is its 1001-value gate
+(src/Checks.cs:189-207) with this repository's generator in place of .NET's Random.
+"""
+import numpy as np
+import pytest
+
+from qiyas_b200 import blocks as B
+
+
+def f16(v):
+    return np.array([v], np.float16).view(np.uint8)
+
+
+def test_half_conversions_match_ieee(oracle):
+    # every half widens exactly; every float rounds to nearest even like numpy's float16
+    for h in range(0, 65536, 7):
+        want = np.array([h], np.uint16).view(np.float16).astype(np.float32)[0]
+        got = oracle.half_to_float(h)
+        assert (np.isnan(want) and np.isnan(got)) or got == want
+    rng = np.random.default_rng(5)
+    values = np.concatenate([rng.standard_normal(4000).astype(np.float32) * 10.0 ** rng.integers(-9, 6, 4000),
+                             np.array([0.0, -0.0, 65504.0, 65519.9, 65520.0, 1e-8, 5.9604645e-08, 2.9802322e-08,
+                                       2.98023259e-08, 6.1035156e-05, 6.0975552e-05, 1e30, -1e30], np.float32)])
+    with np.errstate(over="ignore"):
+        want = values.astype(np.float16).view(np.uint16)
+    for v, w in zip(values, want):
+        assert oracle.float_to_half(v) == int(w), v
+    # ties: halfway between two halves goes to the even one
+    assert oracle.float_to_half(np.float32(1.0 + 2.0 ** -11)) == 0x3C00
+    assert oracle.float_to_half(np.float32(1.0 + 3 * 2.0 ** -11)) == 0x3C02
+
+
+def test_q8_0_specification(oracle):
+    # d = 0.5, q_i = i - 16 -> value_i = 0.5 (i - 16)   (src/Checks.cs:269-281)
+    block = np.zeros(34, np.uint8)
+    block[0:2] = f16(0.5)
+    block[2:] = (np.arange(32) - 16).astype(np.int8).view(np.uint8)
+    v = oracle.decode(B.Q8_0, block, 32)
+    assert np.array_equal(v, 0.5 * (np.arange(32) - 16).astype(np.float32))
+    back = oracle.encode(B.Q8_0, v)
+    d = back[0:2].view(np.float16).astype(np.float32)[0]
+    again = oracle.decode(B.Q8_0, back, 32)
+    assert np.all(np.abs(again - v) <= 0.5 * d + 1e-6)
+
+
+def test_q4_0_specification(oracle):
+    # d = 0.25; byte 2+j holds value j low, value j+16 high   (src/Checks.cs:283-293)
+    block = np.zeros(18, np.uint8)
+    block[0:2] = f16(0.25)
+    j = np.arange(16)
+    block[2:] = (j | ((15 - j) << 4)).astype(np.uint8)
+    v = oracle.decode(B.Q4_0, block, 32)
+    assert np.array_equal(v[:16], 0.25 * (j - 8).astype(np.float32))
+    assert np.array_equal(v[16:], 0.25 * (15 - j - 8).astype(np.float32))
+
+
+def test_q4_k_specification(oracle):
+    # d = 1, dmin = 0.5; scales 1..8, mins 0..7; sub-block j value i = (i + j) & 15   (src/Checks.cs:295-321)
+    ls, lm = np.arange(1, 9), np.arange(0, 8)
+    block = np.zeros(144, np.uint8)
+    block[0:2] = f16(1.0)
+    block[2:4] = f16(0.5)
+    sc = block[4:16]
+    for jj in range(8):
+        if jj < 4:
+            sc[jj] = ls[jj]
+            sc[jj + 4] = lm[jj]
+        else:
+            sc[jj + 4] = (ls[jj] & 15) | ((lm[jj] & 15) << 4)
+            sc[jj - 4] |= (ls[jj] >> 4) << 6
+            sc[jj] |= (lm[jj] >> 4) << 6
+    assert np.array_equal(B.pack_q4_k_scales(ls, lm), sc)
+    qs = block[16:]
+    for jj in range(8):
+        for i in range(32):
+            q, at = (i + jj) & 15, jj // 2 * 32 + i
+            qs[at] = (qs[at] & 0xF0) | q if jj % 2 == 0 else (qs[at] & 0x0F) | (q << 4)
+    v = oracle.decode(B.Q4_K, block, 256)
+    for jj in range(8):
+        want = np.float32(1.0) * ls[jj] * ((np.arange(32) + jj) & 15) - np.float32(0.5) * lm[jj]
+        assert np.array_equal(v[jj * 32:(jj + 1) * 32], want.astype(np.float32))
+
+
+def test_q6_k_specification(oracle):
+    # d = 0.125; scales j - 8; q = (3 i + j) & 63 laid into ql / qh   (src/Checks.cs:323-351)
+    block = np.zeros(210, np.uint8)
+    block[208:210] = f16(0.125)
+    block[192:208] = (np.arange(16) - 8).astype(np.int8).view(np.uint8)
+    q = np.array([[(i * 3 + jj) & 63 for i in range(16)] for jj in range(16)], np.uint8).reshape(256)
+    for half in range(2):
+        for l in range(32):
+            q1, q2, q3, q4 = (int(q[half * 128 + l + 32 * g]) for g in range(4))
+            block[half * 64 + l] = (q1 & 15) | ((q3 & 15) << 4)
+            block[half * 64 + l + 32] = (q2 & 15) | ((q4 & 15) << 4)
+            block[128 + half * 32 + l] = ((q1 >> 4) & 3) | (((q2 >> 4) & 3) << 2) | (((q3 >> 4) & 3) << 4) | (((q4 >> 4) & 3) << 6)
+    ql, qh = B.pack_q6_k_codes(q)
+    assert np.array_equal(ql, block[:128]) and np.array_equal(qh, block[128:192])
+    v = oracle.decode(B.Q6_K, block, 256)
+    for jj in range(16):
+        want = np.float32(0.125) * np.float32(jj - 8) * (((np.arange(16) * 3 + jj) & 63) - 32).astype(np.float32)
+        assert np.array_equal(v[jj * 16:(jj + 1) * 16], want)
+
+
+@pytest.mark.parametrize("fmt,mant", [(B.Q8_0, 6), (B.Q4_0, 2), (B.Q4_K, 2), (B.Q6_K, 4)])
+def test_round_trip_within_block_steps(oracle, fmt, mant):
+    # 1001 values in [-4, 4], every seventh scaled by 0.01; encode then decode within 1.5 block steps
+    # (src/Checks.cs:189-207; mantissas src/Bench/Registry.cs:150-154)
+    n = 1001
+    rng = np.random.default_rng(99)
+    values = ((rng.random(n) * 8 - 4) * np.where(np.arange(n) % 7 == 0, 0.01, 1.0)).astype(np.float32)
+    stored = oracle.encode(fmt, values)
+    assert stored.size == B.nbytes(fmt, n)
+    back = oracle.decode(fmt, stored, n)
+    bv = B.BLOCK_VALUES[fmt]
+    worst = 0.0
+    for i in range(n):
+        lo = i // bv * bv
+        bmax = np.max(np.abs(values[lo:min(n, lo + bv)]))
+        worst = max(worst, abs(float(back[i]) - float(values[i])) / (bmax * 2.0 ** -mant + 1e-30))
+    assert worst <= 1.5
+
+
+def test_q8_0_encoder_by_formula(oracle):
+    # d = amax/127 -> f16 -> back; q = clamp(round_half_even(v/d), -127, 127)   (src/Blocks.cs:37-45)
+    rng = np.random.default_rng(3)
+    v = rng.standard_normal(32 * 50).astype(np.float32)
+    v[0:32] = 0                               # an all-zero block: d = 0, id = 0, codes 0
+    v[32 + 5] = 2.5 * 127 / 127               # exact tie candidates survive the f16 round trip or not, either way by formula
+    got = oracle.encode(B.Q8_0, v).reshape(-1, 34)
+    for b in range(50):
+        x = v[b * 32:(b + 1) * 32]
+        d = np.float32(np.max(np.abs(x)) / np.float32(127)).astype(np.float16)
+        df = d.astype(np.float32)
+        idv = np.float32(0) if df == 0 else np.float32(1) / df
+        q = np.clip(np.rint(x * idv), -127, 127).astype(np.int8)
+        assert np.array_equal(got[b, 0:2], np.array([d]).view(np.uint8))
+        assert np.array_equal(got[b, 2:].view(np.int8), q)
+
+
+def test_q4_0_encoder_by_formula_and_device_rounding(oracle):
+    # d = (value of largest magnitude)/-8; q = clamp(trunc(v/d + 8.5), 0, 15)   (src/Blocks.cs:58-70)
+    rng = np.random.default_rng(4)
+    v = rng.standard_normal(32 * 64).astype(np.float32)
+    cpu = oracle.encode(B.Q4_0, v).reshape(-1, 18)
+    dev = oracle.encode(B.Q4_0, v, device_rounding=True).reshape(-1, 18)
+    for b in range(64):
+        x = v[b * 32:(b + 1) * 32]
+        mx = x[np.argmax(np.abs(x))]
+        d = np.float32(mx / np.float32(-8)).astype(np.float16)
+        df = d.astype(np.float32)
+        idv = np.float32(1) / df
+        t = (x * idv).astype(np.float32) + np.float32(8.5)
+        q = np.clip(np.trunc(t), 0, 15).astype(np.uint8)
+        assert np.array_equal(cpu[b, 0:2], np.array([d]).view(np.uint8))
+        assert np.array_equal(cpu[b, 2:], q[:16] | (q[16:] << 4))
+    # the fused device rounding differs from the CPU's at most where v/d + 8.5 sits on an integer boundary
+    assert np.mean(cpu != dev) < 1e-3
