@@ -10,7 +10,8 @@ namespace qb {
 
 __device__ __forceinline__ uint16_t f2h_bits(float v) { return __half_as_ushort(__float2half_rn(v)); }
 __device__ __forceinline__ float h2f_bits(uint16_t h) { return __half2float(__ushort_as_half(h)); }
-__device__ __forceinline__ void put16(uint8_t *p, uint16_t v) { p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); }
+// blocks are 2-byte aligned and every f16 field sits at an even offset: one 16-bit store
+__device__ __forceinline__ void put16(uint8_t *p, uint16_t v) { *reinterpret_cast<volatile uint16_t *>(p) = v; }
 __device__ __forceinline__ uint16_t get16(const uint8_t *p) { return (uint16_t)(p[0] | p[1] << 8); }
 __device__ __forceinline__ int round_clamp(float x, int lo, int hi) { return max(lo, min(hi, __float2int_rn(x))); }
 
