@@ -18,7 +18,7 @@ struct Kept {
     void *ptr = nullptr;
     size_t bytes = 0;
 };
-Kept g_stage_a, g_stage_x, g_stage_y, g_scratch;
+Kept g_stage_a, g_stage_x, g_stage_y, g_scratch, g_xprep;
 int *g_status = nullptr;      // device word the kernels OR their STATUS_* bits into
 
 int fail(int code, const char *fmt, ...)
@@ -129,7 +129,9 @@ int qb200_init(int device)
     if ((e = cudaMemset(g_status, 0, 256))) return cuda_fail(e, "cudaMemset status");
     if ((e = qb::gemv_init(g_caps.sm_count, g_caps.max_shared_bytes, g_status))) return cuda_fail(e, "gemv attributes");
     if ((e = qb::matmul_init(g_caps.sm_count, g_caps.max_shared_bytes, g_status))) return cuda_fail(e, "matmul attributes");
-    g_stage_a = g_stage_x = g_stage_y = g_scratch = Kept();
+    g_stage_a = g_stage_x = g_stage_y = g_scratch = g_xprep = Kept();
+    // x in the gemv's own layout: sized once for the widest x the kernels take, so no gemv call allocates
+    { int rc = keep(g_xprep, qb::gemv_scratch_bytes(65536)); if (rc) return rc; }
     g_ready = true;
     t_error[0] = 0;
     return 0;
@@ -169,7 +171,7 @@ int qb200_gemv_blocks(int fmt_a, int fmt_x, const void *a, const void *x, float 
 {
     int rc = check_gemv(fmt_a, fmt_x, a, x, y, rows, cols);
     if (rc) return rc;
-    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, nullptr, rows, cols, (cudaStream_t)stream), "gemv_blocks");
+    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, nullptr, rows, cols, g_xprep.ptr, (cudaStream_t)stream), "gemv_blocks");
 }
 
 int qb200_gemv_block_sums(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols, void *stream)
@@ -177,7 +179,7 @@ int qb200_gemv_block_sums(int fmt_a, int fmt_x, const void *a, const void *x, fl
     int rc = check_gemv(fmt_a, fmt_x, a, x, y, rows, cols);
     if (rc) return rc;
     if (rows > 0 && (!sums || ((uintptr_t)sums & 3))) return fail(QB200_E_POINTER, "null or misaligned sums");
-    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, sums, rows, cols, (cudaStream_t)stream), "gemv_block_sums");
+    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, sums, rows, cols, g_xprep.ptr, (cudaStream_t)stream), "gemv_block_sums");
 }
 
 int qb200_gemv_blocks_host(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols)

@@ -4,9 +4,15 @@
 // Here the matrix is one flat byte stream: a producer warp moves whole groups of rows ("units") into a ring of
 // shared-memory slots with untiled TMA bulk copies (16-byte aligned middle part; the ragged head and tail bytes by
 // plain 2-byte loads), and consumer warps unpack the raw block bytes in registers, take each block's integer dot with
-// dp4a in s32, apply the f16 block scales in f32 and reduce each row with warp shuffles.  x is turned once per block of
-// threads into int8 values + f32 scales (+ per-block sums) in shared memory, in the reference's Q8_0 encoding when it
-// arrives as f32 (src/Ptx.Blocks.cs:52-73).
+// dp4a in s32, apply the f16 block scales in f32 and reduce each row with warp shuffles.  x is first turned, by a small
+// kernel of its own, into int8 values + f32 scales + per-block sums in a scratch buffer (in the reference's Q8_0
+// encoding when it arrives as f32, src/Ptx.Blocks.cs:52-73), laid out so that every lane of the gemv fetches the blocks
+// it meets in every row with a few coalesced 16-byte loads and keeps them in registers.  The gemv is launched as a
+// programmatic dependent of that kernel: its weight copies start at once and only the read of x waits for it.
+//
+// A consumer warp owns a fixed column segment of every row (runs of 64 blocks), so its share of x stays in registers
+// for the whole kernel; the warps of a row group split a row between them, write one partial sum per row and segment
+// to shared memory, and the block adds the segments in ascending order once at the end (no barrier per unit).
 //
 // Per block the arithmetic is the reference kernel's: scale = dA*dX (rounded), acc = fma(scale, float(dot), acc)
 // (src/BlockProducts.cs:158-161).  The order in which a row's blocks are added differs (lanes, then a shuffle tree,
@@ -18,23 +24,27 @@ namespace qb {
 
 struct GemvArgs {
     const uint8_t *a;
-    const void *x;
+    const uint8_t *xprep; // x as prepare_x_kernel lays it out
     float *y;
     int32_t *sums;
     int *status;         // device word for STATUS_* bits
-    int rows, cols, fmt_x;
+    long long *timeline; // optional: 8 timestamps (ns) a block, for tuning; null in normal use
+    int probe;           // tuning aid: 1 = consumers skip the arithmetic, 2 = the producer skips the copies; 0 in normal use
+    int rows, cols;
     uint32_t row_bytes;
     int nw;              // consumer warps; the producer is warp nw
     int cs, rg;          // column segments x row groups = nw
     int stage_rows;      // rows per unit = rg * RW
     int units;           // ceil(rows / stage_rows)
-    int stages;          // ring depth
-    uint32_t stage_stride;
-    uint32_t off_xq, off_xm, off_part, off_ring;   // shared-memory offsets
+    int slots;           // ring depth in chunks (a chunk = the RW rows of one row group), at least rg
+    int flush_units;     // units whose partial sums fit the partials area before they are added up
+    uint32_t slot_stride;
+    uint32_t row_flip;   // 1 when a row is 2 (mod 4) bytes long: rows alternate between the two 4-byte alignments
+    uint32_t off_part, off_ring;   // shared-memory offsets
 };
 
-constexpr int MAX_STAGES = 16;
-constexpr uint32_t SMEM_HEADER = 512;   // full[16], empty[16], red[16] barriers and the abort word
+constexpr int MAX_SLOTS = 60;
+constexpr uint32_t SMEM_HEADER = 1024;  // full[60] and empty[60] barriers and the abort word
 
 __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c)
 {
@@ -128,38 +138,46 @@ __device__ __forceinline__ void load_x_block(const void *x, int fmt_x, int b, ui
     for (int i = 0; i < 8; i++) sum = dp4a_s8s8(w[i], 0x01010101u, sum);
 }
 
-// PAIRED layout (Q8_0 / Q4_0 rows): a lane of the consumer handles blocks 2l and 2l+1 of every run of 64 blocks, so
-// the 64 bytes of a pair are stored as four 16-byte pieces at [(run*4 + piece)*32 + lane] (consecutive lanes read
-// consecutive 16 bytes), and a pair's {d0, d1, sum0, sum1} as one 16-byte record at [pair].
-// NATURAL layout (Q4_K / Q6_K rows): int8 values in order, then per block a {d, sum} record.
+// Prepared x.  PAIRED (Q8_0 / Q4_0 rows): a lane of the gemv handles blocks 2l and 2l+1 of every run of 64 blocks, so the
+// 64 bytes of a pair are stored as four 16-byte pieces at [(run*4 + piece)*32 + lane] (consecutive lanes, consecutive 16
+// bytes), followed by one 16-byte record {d0, d1, sum0, sum1} a pair.  NATURAL (Q4_K / Q6_K rows): the int8 values in
+// order, followed by one 8-byte record {d, sum} a block.  `codes_bytes` is where the records start.
+__host__ __device__ inline uint32_t xprep_codes_bytes(int cols) { return ((uint32_t)cols + 2047u) / 2048u * 2048u; }
+__host__ __device__ inline uint32_t xprep_bytes(int cols) { return xprep_codes_bytes(cols) + ((uint32_t)(cols / 32 + 2) * 8u + 255u) / 256u * 256u; }
+
 template <bool PAIRED>
-__device__ __forceinline__ void stage_x(const GemvArgs &p, uint8_t *smem, int tid, int threads)
+__global__ void __launch_bounds__(128) prepare_x_kernel(const void *x, int fmt_x, int cols, uint8_t *out)
 {
-    const int blocks = p.cols / 32;
-    uint4 *xq = (uint4 *)(smem + p.off_xq);
-    for (int b = tid; b < blocks; b += threads) {
-        uint32_t w[8];
-        float d;
-        int sum;
-        load_x_block(p.x, p.fmt_x, b, w, d, sum);
-        if (PAIRED) {
-            int run = b >> 6, lane = (b & 63) >> 1, half = b & 1;
-            xq[(run * 4 + half * 2) * 32 + lane] = make_uint4(w[0], w[1], w[2], w[3]);
-            xq[(run * 4 + half * 2 + 1) * 32 + lane] = make_uint4(w[4], w[5], w[6], w[7]);
-            uint32_t *m = (uint32_t *)(smem + p.off_xm) + (b >> 1) * 4;
-            m[half] = __float_as_uint(d);
-            m[2 + half] = (uint32_t)sum;
-        } else {
-            xq[b * 2] = make_uint4(w[0], w[1], w[2], w[3]);
-            xq[b * 2 + 1] = make_uint4(w[4], w[5], w[6], w[7]);
-            uint2 *m = (uint2 *)(smem + p.off_xm);
-            m[b] = make_uint2(__float_as_uint(d), (uint32_t)sum);
+    // the gemv that follows may start now: it waits for this grid's end only where it first reads `out`
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // x may be the output of the kernel before this one, and `out` may still be read by the gemv before it
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int blocks = cols / 32, b = blockIdx.x * blockDim.x + threadIdx.x;
+    uint8_t *meta = out + xprep_codes_bytes(cols);
+    if (b >= blocks) {
+        if (PAIRED && b == blocks && (blocks & 1)) {      // the missing partner of a last odd block reads as zero
+            uint32_t *m = (uint32_t *)meta + (size_t)(b >> 1) * 4;
+            m[1] = 0;
+            m[3] = 0;
         }
+        return;
     }
-    if (PAIRED && (blocks & 1) && tid == 0) {           // the missing partner of a last odd block reads as zero
-        uint32_t *m = (uint32_t *)(smem + p.off_xm) + (blocks >> 1) * 4;
-        m[1] = 0;
-        m[3] = 0;
+    uint32_t w[8];
+    float d;
+    int sum;
+    load_x_block(x, fmt_x, b, w, d, sum);
+    uint4 *xq = (uint4 *)out;
+    if (PAIRED) {
+        const int run = b >> 6, lane = (b & 63) >> 1, half = b & 1;
+        xq[(run * 4 + half * 2) * 32 + lane] = make_uint4(w[0], w[1], w[2], w[3]);
+        xq[(run * 4 + half * 2 + 1) * 32 + lane] = make_uint4(w[4], w[5], w[6], w[7]);
+        uint32_t *m = (uint32_t *)meta + (size_t)(b >> 1) * 4;
+        m[half] = __float_as_uint(d);
+        m[2 + half] = (uint32_t)sum;
+    } else {
+        xq[b * 2] = make_uint4(w[0], w[1], w[2], w[3]);
+        xq[b * 2 + 1] = make_uint4(w[4], w[5], w[6], w[7]);
+        ((uint2 *)meta)[b] = make_uint2(__float_as_uint(d), (uint32_t)sum);
     }
 }
 
@@ -188,6 +206,28 @@ __device__ __forceinline__ void load_block(const uint8_t *q, uint32_t (&w)[NWORD
     }
 }
 
+// The same with the alignment known at compile time: Q4 = the block starts on a 4-byte boundary (its codes do not).
+template <int NWORDS, bool Q4>
+__device__ __forceinline__ void load_block_at(const uint8_t *q, uint32_t (&w)[NWORDS], uint32_t &hscale)
+{
+    if (Q4) {
+        const uint32_t *t = (const uint32_t *)q;
+        uint32_t prev = t[0];
+        hscale = prev & 0xFFFFu;
+#pragma unroll
+        for (int i = 0; i < NWORDS; i++) {
+            uint32_t next = t[i + 1];
+            w[i] = __funnelshift_r(prev, next, 16);
+            prev = next;
+        }
+    } else {
+        hscale = *(const uint16_t *)q;
+        const uint32_t *t = (const uint32_t *)(q + 2);
+#pragma unroll
+        for (int i = 0; i < NWORDS; i++) w[i] = t[i];
+    }
+}
+
 // 32 bits at a 2-byte aligned shared address.
 __device__ __forceinline__ uint32_t ld32_a2(const uint8_t *q)
 {
@@ -196,317 +236,453 @@ __device__ __forceinline__ uint32_t ld32_a2(const uint8_t *q)
     return __funnelshift_r(t[0], t[1], sh);
 }
 
-// ---------------------------------------------------------------------------------- consumers, one per format
+// ---------------------------------------------------------------------------------- a warp's share of x, in registers
 
-// Q8_0 / Q4_0: RW rows at once over this warp's column runs; a lane takes blocks 2l, 2l+1 of each run of 64.
-template <int FMT, int RW, bool SUMS>
-__device__ __forceinline__ void consume_q(const GemvArgs &p, const uint8_t *smem, const uint8_t *rows, int nvalid, int row0,
-                                          int seg, int lane, float (&acc)[RW])
+// Q8_0 / Q4_0 rows: per run of 64 blocks a lane holds blocks 2l and 2l+1 of x.
+struct XPair {
+    uint32_t a[8], b[8];     // int8 values of the two blocks
+    float d0, d1;            // their scales
+    int s0, s1;              // the sums of their values (for Q4_0 rows: sum (q-8)*x = sum q*x - 8*sum x)
+    int count;               // how many of the two blocks exist (a row can end inside a run)
+    int first;               // index of block 2l of this run
+};
+
+__device__ __forceinline__ void load_x(XPair &x, const GemvArgs &p, int run, int lane)
+{
+    const int blocks = p.cols / 32;
+    x.first = run * 64 + lane * 2;
+    x.count = max(0, min(2, blocks - x.first));
+    x.d0 = x.d1 = 0.f;
+    x.s0 = x.s1 = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) x.a[i] = x.b[i] = 0;
+    if (x.count == 0) return;
+    const uint4 *xq = (const uint4 *)p.xprep;
+    const uint4 x0 = xq[(run * 4 + 0) * 32 + lane], x1 = xq[(run * 4 + 1) * 32 + lane];
+    const uint4 x2 = xq[(run * 4 + 2) * 32 + lane], x3 = xq[(run * 4 + 3) * 32 + lane];
+    const uint4 meta = ((const uint4 *)(p.xprep + xprep_codes_bytes(p.cols)))[x.first >> 1];
+    x.a[0] = x0.x; x.a[1] = x0.y; x.a[2] = x0.z; x.a[3] = x0.w; x.a[4] = x1.x; x.a[5] = x1.y; x.a[6] = x1.z; x.a[7] = x1.w;
+    x.b[0] = x2.x; x.b[1] = x2.y; x.b[2] = x2.z; x.b[3] = x2.w; x.b[4] = x3.x; x.b[5] = x3.y; x.b[6] = x3.z; x.b[7] = x3.w;
+    x.d0 = __uint_as_float(meta.x); x.d1 = __uint_as_float(meta.y);
+    x.s0 = (int)meta.z; x.s1 = (int)meta.w;
+}
+
+// Q4_K rows: eight lanes a super-block, four super-blocks a run; a lane holds 16 values of sub-block 2p and 16 of 2p+1.
+struct XK4 {
+    uint32_t lo[4], hi[4];
+    float da, db;
+    int sa, sb;              // whole sub-block sums of x (the min term), used by the even lane of a pair
+    int xb;                  // x block of sub-block 2p
+    bool valid;
+};
+
+__device__ __forceinline__ void load_x(XK4 &x, const GemvArgs &p, int run, int lane)
+{
+    const int sb = run * 4 + (lane >> 3), part = lane & 7;
+    x.valid = sb < p.cols / 256;
+    x.xb = sb * 8 + (part >> 1) * 2;
+    if (!x.valid) return;
+    const uint8_t *xq = p.xprep + (size_t)x.xb * 32 + (part & 1) * 16;
+    const uint4 l = *(const uint4 *)xq, h = *(const uint4 *)(xq + 32);
+    const uint2 *meta = (const uint2 *)(p.xprep + xprep_codes_bytes(p.cols));
+    const uint2 ma = meta[x.xb], mb = meta[x.xb + 1];
+    x.lo[0] = l.x; x.lo[1] = l.y; x.lo[2] = l.z; x.lo[3] = l.w;
+    x.hi[0] = h.x; x.hi[1] = h.y; x.hi[2] = h.z; x.hi[3] = h.w;
+    x.da = __uint_as_float(ma.x); x.db = __uint_as_float(mb.x);
+    x.sa = (int)ma.y; x.sb = (int)mb.y;
+}
+
+// Q6_K rows: sixteen lanes a super-block, two super-blocks a run; a lane holds four values of each of four runs of 32.
+struct XK6 {
+    uint32_t w[4];
+    float d[4];
+    int ones[4];             // sums of the four values (the -32 offset)
+    int sb;
+    bool valid;
+};
+
+__device__ __forceinline__ void load_x(XK6 &x, const GemvArgs &p, int run, int lane)
+{
+    x.sb = run * 2 + (lane >> 4);
+    x.valid = x.sb < p.cols / 256;
+    if (!x.valid) return;
+    const int half = (lane >> 3) & 1, t = lane & 7;
+    const uint2 *meta = (const uint2 *)(p.xprep + xprep_codes_bytes(p.cols));
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        x.w[g] = *(const uint32_t *)(p.xprep + (size_t)x.sb * 256 + half * 128 + g * 32 + t * 4);
+        x.d[g] = __uint_as_float(meta[x.sb * 8 + half * 4 + g].x);
+        x.ones[g] = dp4a_s8s8(x.w[g], 0x01010101u, 0);
+    }
+}
+
+template <int FMT> struct XOf { typedef XPair type; };
+template <> struct XOf<QB200_Q4_K> { typedef XK4 type; };
+template <> struct XOf<QB200_Q6_K> { typedef XK6 type; };
+
+// ---------------------------------------------------------------------------------- one row against one run of x
+
+// Q8_0 / Q4_0: the lane's two blocks of this run.
+template <int FMT, bool SUMS>
+__device__ __forceinline__ float row_dot(const XPair &x, const uint8_t *row, int lane, int32_t *sums_row, float acc)
 {
     constexpr int BB = block_bytes(FMT), NWORDS = FMT == QB200_Q8_0 ? 8 : 4;
-    const int blocks = p.cols / 32;
-    const uint4 *xq = (const uint4 *)(smem + p.off_xq);
-    const uint4 *xm = (const uint4 *)(smem + p.off_xm);
-    for (int run = seg; run * 64 < blocks; run += p.cs) {
-        const int b0 = run * 64 + lane * 2;
-        if (b0 >= blocks) continue;
-        const bool two = b0 + 1 < blocks;
-        uint4 x0 = xq[(run * 4 + 0) * 32 + lane], x1 = xq[(run * 4 + 1) * 32 + lane];
-        uint4 x2 = xq[(run * 4 + 2) * 32 + lane], x3 = xq[(run * 4 + 3) * 32 + lane];
-        uint4 meta = xm[b0 >> 1];
-        const float dx0 = __uint_as_float(meta.x), dx1 = __uint_as_float(meta.y);
-        const uint32_t xa[8] = { x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w };
-        const uint32_t xb[8] = { x2.x, x2.y, x2.z, x2.w, x3.x, x3.y, x3.z, x3.w };
+    if (x.count == 0) return acc;
+    const uint8_t *q = row + (size_t)x.first * BB;
 #pragma unroll
-        for (int r = 0; r < RW; r++) {
-            if (r >= nvalid) break;
-            const uint8_t *q = rows + (size_t)r * p.row_bytes + (size_t)b0 * BB;
+    for (int h = 0; h < 2; h++) {
+        if (h == 1 && x.count < 2) break;
+        uint32_t w[NWORDS], hs;
+        load_block<NWORDS>(q + h * BB, w, hs);
+        const uint32_t *xw = h ? x.b : x.a;
+        int dot;
+        if (FMT == QB200_Q8_0) {
+            int e = 0, o = 0;
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                if (h == 1 && !two) break;
-                uint32_t w[NWORDS], hs;
-                load_block<NWORDS>(q + h * BB, w, hs);
-                const uint32_t *xw = h ? xb : xa;
-                int dot;
-                if (FMT == QB200_Q8_0) {
-                    dot = 0;
-#pragma unroll
-                    for (int i = 0; i < 8; i++) dot = dp4a_s8s8(w[i], xw[i], dot);
-                } else {
-                    // sum (q-8)*x = sum q*x - 8*sum x; the high nibbles are taken in place (16q), exact after >> 4
-                    int lo = 0, hi = 0;
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        lo = dp4a_u8s8(w[i] & 0x0F0F0F0Fu, xw[i], lo);
-                        hi = dp4a_u8s8(w[i] & 0xF0F0F0F0u, xw[i + 4], hi);
-                    }
-                    dot = lo + (hi >> 4) - 8 * (int)(h ? meta.w : meta.z);
-                }
-                const float scale = __fmul_rn(half_bits_to_float(hs), h ? dx1 : dx0);
-                acc[r] = __fmaf_rn(scale, (float)dot, acc[r]);
-                if (SUMS) p.sums[(size_t)(row0 + r) * blocks + b0 + h] = dot;
+            for (int i = 0; i < 8; i += 2) {
+                e = dp4a_s8s8(w[i], xw[i], e);
+                o = dp4a_s8s8(w[i + 1], xw[i + 1], o);
             }
-        }
-    }
-}
-
-// Q4_K: eight lanes a super-block; a lane takes 16 bytes of nibbles = half of sub-block 2p (low nibbles) and half of
-// sub-block 2p+1 (high nibbles).  value = (d*sc)*q - dmin*m (src/Blocks.cs:79-96), so against x = dx*qx a sub-block gives
-// (d*sc)*dx*sum(q*qx) - (dmin*m)*dx*sum(qx).  The 6-bit fields are unpacked as ScaleMin does (src/Blocks.cs:73-77), four at a time.
-template <int RW, bool SUMS>
-__device__ __forceinline__ void consume_q4k(const GemvArgs &p, const uint8_t *smem, const uint8_t *rows, int nvalid, int row0,
-                                            int seg, int lane, float (&acc)[RW])
-{
-    const int sbs = p.cols / 256;
-    const uint8_t *xq = smem + p.off_xq;
-    const uint2 *xm = (const uint2 *)(smem + p.off_xm);
-    const int part = lane & 7, pr = part >> 1, hsel = part & 1;
-    for (int run = seg; run * 4 < sbs; run += p.cs) {
-        const int sb = run * 4 + (lane >> 3);
-        if (sb >= sbs) continue;
-        const int xb = sb * 8 + pr * 2;                                    // x block of sub-block 2p
-        const uint4 xlo = *(const uint4 *)(xq + (size_t)xb * 32 + hsel * 16);
-        const uint4 xhi = *(const uint4 *)(xq + (size_t)xb * 32 + 32 + hsel * 16);
-        const uint2 ma = xm[xb], mb = xm[xb + 1];
-        const float dxa = __uint_as_float(ma.x), dxb = __uint_as_float(mb.x);
-#pragma unroll
-        for (int r = 0; r < RW; r++) {
-            if (r >= nvalid) break;
-            const uint8_t *blk = rows + (size_t)r * p.row_bytes + (size_t)sb * 144;
-            uint32_t h0, s0, s1, s2, n[4];
-            if (((uint32_t)(uintptr_t)blk & 15u) == 0) {
-                const uint4 hdr = *(const uint4 *)blk;
-                const uint4 nb = *(const uint4 *)(blk + 16 + pr * 32 + hsel * 16);
-                h0 = hdr.x; s0 = hdr.y; s1 = hdr.z; s2 = hdr.w;
-                n[0] = nb.x; n[1] = nb.y; n[2] = nb.z; n[3] = nb.w;
-            } else {
-                h0 = ld32_a2(blk); s0 = ld32_a2(blk + 4); s1 = ld32_a2(blk + 8); s2 = ld32_a2(blk + 12);
-#pragma unroll
-                for (int i = 0; i < 4; i++) n[i] = ld32_a2(blk + 16 + pr * 32 + hsel * 16 + 4 * i);
-            }
-            const float d = half_bits_to_float(h0 & 0xFFFFu), dmin = half_bits_to_float(h0 >> 16);
-            // scales of sub-blocks 0..3 | 4..7 and their mins, a byte each
-            const uint32_t sc_lo = s0 & 0x3F3F3F3Fu, sc_hi = (s2 & 0x0F0F0F0Fu) | (((s0 >> 6) & 0x03030303u) << 4);
-            const uint32_t mn_lo = s1 & 0x3F3F3F3Fu, mn_hi = ((s2 >> 4) & 0x0F0F0F0Fu) | (((s1 >> 6) & 0x03030303u) << 4);
-            const uint32_t scw = (pr < 2 ? sc_lo : sc_hi) >> ((pr & 1) * 16), mnw = (pr < 2 ? mn_lo : mn_hi) >> ((pr & 1) * 16);
-            const int sca = scw & 255, scb = (scw >> 8) & 255, mna = mnw & 255, mnb = (mnw >> 8) & 255;
+            dot = e + o;
+        } else {
+            // sum (q-8)*x = sum q*x - 8*sum x; the high nibbles are taken in place (16q), exact after >> 4
             int lo = 0, hi = 0;
-            const uint32_t xl[4] = { xlo.x, xlo.y, xlo.z, xlo.w }, xh[4] = { xhi.x, xhi.y, xhi.z, xhi.w };
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                lo = dp4a_u8s8(n[i] & 0x0F0F0F0Fu, xl[i], lo);
-                hi = dp4a_u8s8(n[i] & 0xF0F0F0F0u, xh[i], hi);
+                lo = dp4a_u8s8(w[i] & 0x0F0F0F0Fu, xw[i], lo);
+                hi = dp4a_u8s8(w[i] & 0xF0F0F0F0u, xw[i + 4], hi);
             }
-            hi >>= 4;
-            float a = acc[r];
-            a = __fmaf_rn(__fmul_rn(__fmul_rn(d, (float)sca), dxa), (float)lo, a);
-            a = __fmaf_rn(__fmul_rn(__fmul_rn(d, (float)scb), dxb), (float)hi, a);
-            if (hsel == 0) {
-                a = __fmaf_rn(-__fmul_rn(__fmul_rn(dmin, (float)mna), dxa), (float)(int)ma.y, a);
-                a = __fmaf_rn(-__fmul_rn(__fmul_rn(dmin, (float)mnb), dxb), (float)(int)mb.y, a);
-            }
-            acc[r] = a;
-            if (SUMS) {
-                lo += __shfl_xor_sync(__activemask(), lo, 1);
-                hi += __shfl_xor_sync(__activemask(), hi, 1);
-                if (hsel == 0) {
-                    int32_t *o = p.sums + (size_t)(row0 + r) * (p.cols / 32) + xb;
-                    o[0] = lo;
-                    o[1] = hi;
-                }
-            }
+            dot = lo + (hi >> 4) - 8 * (h ? x.s1 : x.s0);
+        }
+        const float scale = __fmul_rn(half_bits_to_float(hs), h ? x.d1 : x.d0);
+        acc = __fmaf_rn(scale, (float)dot, acc);
+        if (SUMS) sums_row[x.first + h] = dot;
+    }
+    (void)lane;
+    return acc;
+}
+
+// The same for a lane whose two blocks both exist, with the first block's alignment known at compile time (the second
+// block, 34 or 18 bytes on, has the other alignment): no branches, so the loads of several rows can be in flight at once.
+template <int FMT, bool Q4>
+__device__ __forceinline__ float row_dot_fast(const XPair &x, const uint8_t *row, float acc)
+{
+    constexpr int BB = block_bytes(FMT), NWORDS = FMT == QB200_Q8_0 ? 8 : 4;
+    const uint8_t *q = row + (size_t)x.first * BB;
+    uint32_t w0[NWORDS], w1[NWORDS], h0, h1;
+    load_block_at<NWORDS, Q4>(q, w0, h0);
+    load_block_at<NWORDS, !Q4>(q + BB, w1, h1);
+    int dot0, dot1;
+    if (FMT == QB200_Q8_0) {
+        int e0 = 0, o0 = 0, e1 = 0, o1 = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            e0 = dp4a_s8s8(w0[i], x.a[i], e0);
+            o0 = dp4a_s8s8(w0[i + 1], x.a[i + 1], o0);
+            e1 = dp4a_s8s8(w1[i], x.b[i], e1);
+            o1 = dp4a_s8s8(w1[i + 1], x.b[i + 1], o1);
+        }
+        dot0 = e0 + o0;
+        dot1 = e1 + o1;
+    } else {
+        int lo0 = 0, hi0 = 0, lo1 = 0, hi1 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            lo0 = dp4a_u8s8(w0[i] & 0x0F0F0F0Fu, x.a[i], lo0);
+            hi0 = dp4a_u8s8(w0[i] & 0xF0F0F0F0u, x.a[i + 4], hi0);
+            lo1 = dp4a_u8s8(w1[i] & 0x0F0F0F0Fu, x.b[i], lo1);
+            hi1 = dp4a_u8s8(w1[i] & 0xF0F0F0F0u, x.b[i + 4], hi1);
+        }
+        dot0 = lo0 + (hi0 >> 4) - 8 * x.s0;
+        dot1 = lo1 + (hi1 >> 4) - 8 * x.s1;
+    }
+    acc = __fmaf_rn(__fmul_rn(half_bits_to_float(h0), x.d0), (float)dot0, acc);
+    acc = __fmaf_rn(__fmul_rn(half_bits_to_float(h1), x.d1), (float)dot1, acc);
+    return acc;
+}
+
+// RW whole rows of a unit against this warp's runs of x; row r's first block has alignment Q4E (even r) or Q4O (odd r).
+template <int FMT, int RW, int RUNS, bool Q4E, bool Q4O>
+__device__ __forceinline__ void rows_fast(const XPair (&xr)[RUNS], const uint8_t *rows, uint32_t row_bytes, float (&acc)[RW])
+{
+#pragma unroll
+    for (int j = 0; j < RUNS; j++) {
+#pragma unroll
+        for (int r = 0; r < RW; r++) {
+            if (r & 1) acc[r] = row_dot_fast<FMT, Q4O>(xr[j], rows + (size_t)r * row_bytes, acc[r]);
+            else acc[r] = row_dot_fast<FMT, Q4E>(xr[j], rows + (size_t)r * row_bytes, acc[r]);
         }
     }
 }
 
-// Q6_K: sixteen lanes a super-block; a lane takes one word of each of ql[64h..], ql[64h+32..] and qh[32h..]: four
-// values of each of four runs of 32 (src/Blocks.cs:157-171).  value = d*sc*(q-32); per 16-value sub-block the integer
-// sum is sc * (sum q*qx - 32*sum qx).
-template <int RW, bool SUMS>
-__device__ __forceinline__ void consume_q6k(const GemvArgs &p, const uint8_t *smem, const uint8_t *rows, int nvalid, int row0,
-                                            int seg, int lane, float (&acc)[RW])
+// Q4_K: value = (d*sc)*q - dmin*m (src/Blocks.cs:79-96), so against x = dx*qx a sub-block gives
+// (d*sc)*dx*sum(q*qx) - (dmin*m)*dx*sum(qx).  The 6-bit fields are unpacked as ScaleMin does (src/Blocks.cs:73-77), four at a time.
+template <int FMT, bool SUMS>
+__device__ __forceinline__ float row_dot(const XK4 &x, const uint8_t *row, int lane, int32_t *sums_row, float acc)
 {
-    const int sbs = p.cols / 256;
-    const uint8_t *xq = smem + p.off_xq;
-    const uint2 *xm = (const uint2 *)(smem + p.off_xm);
-    const int half = (lane >> 3) & 1, t = lane & 7;
-    for (int run = seg; run * 2 < sbs; run += p.cs) {
-        const int sb = run * 2 + (lane >> 4);
-        if (sb >= sbs) continue;
-        uint32_t xw[4];
-        float dx[4];
-        int ones[4];
+    if (!x.valid) return acc;
+    const int part = lane & 7, pr = part >> 1, hsel = part & 1;
+    const uint8_t *blk = row + (size_t)(x.xb >> 3) * 144;
+    uint32_t h0, s0, s1, s2, n[4];
+    if (((uint32_t)(uintptr_t)blk & 15u) == 0) {
+        const uint4 hdr = *(const uint4 *)blk;
+        const uint4 nb = *(const uint4 *)(blk + 16 + pr * 32 + hsel * 16);
+        h0 = hdr.x; s0 = hdr.y; s1 = hdr.z; s2 = hdr.w;
+        n[0] = nb.x; n[1] = nb.y; n[2] = nb.z; n[3] = nb.w;
+    } else {
+        h0 = ld32_a2(blk); s0 = ld32_a2(blk + 4); s1 = ld32_a2(blk + 8); s2 = ld32_a2(blk + 12);
 #pragma unroll
-        for (int g = 0; g < 4; g++) {
-            xw[g] = *(const uint32_t *)(xq + (size_t)sb * 256 + half * 128 + g * 32 + t * 4);
-            dx[g] = __uint_as_float(xm[sb * 8 + half * 4 + g].x);
-            ones[g] = dp4a_s8s8(xw[g], 0x01010101u, 0);
-        }
+        for (int i = 0; i < 4; i++) n[i] = ld32_a2(blk + 16 + pr * 32 + hsel * 16 + 4 * i);
+    }
+    const float d = half_bits_to_float(h0 & 0xFFFFu), dmin = half_bits_to_float(h0 >> 16);
+    // scales of sub-blocks 0..3 | 4..7 and their mins, a byte each
+    const uint32_t sc_lo = s0 & 0x3F3F3F3Fu, sc_hi = (s2 & 0x0F0F0F0Fu) | (((s0 >> 6) & 0x03030303u) << 4);
+    const uint32_t mn_lo = s1 & 0x3F3F3F3Fu, mn_hi = ((s2 >> 4) & 0x0F0F0F0Fu) | (((s1 >> 6) & 0x03030303u) << 4);
+    const uint32_t scw = (pr < 2 ? sc_lo : sc_hi) >> ((pr & 1) * 16), mnw = (pr < 2 ? mn_lo : mn_hi) >> ((pr & 1) * 16);
+    const int sca = scw & 255, scb = (scw >> 8) & 255, mna = mnw & 255, mnb = (mnw >> 8) & 255;
+    int lo = 0, hi = 0;
 #pragma unroll
-        for (int r = 0; r < RW; r++) {
-            if (r >= nvalid) break;
-            const uint8_t *blk = rows + (size_t)r * p.row_bytes + (size_t)sb * 210;
-            const uint32_t A = ld32_a2(blk + half * 64 + t * 4), B = ld32_a2(blk + half * 64 + 32 + t * 4);
-            const uint32_t H = ld32_a2(blk + 128 + half * 32 + t * 4);
-            const float d = half_bits_to_float(*(const uint16_t *)(blk + 208));
-            const int8_t *sc = (const int8_t *)(blk + 192 + half * 8 + (t >> 2));
-            uint32_t q[4];
-            q[0] = (A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u);
-            q[1] = (B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u);
-            q[2] = ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u);
-            q[3] = ((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u);
-            float a = acc[r];
-#pragma unroll
-            for (int g = 0; g < 4; g++) {
-                int isum = (int)sc[2 * g] * (dp4a_u8s8(q[g], xw[g], 0) - 32 * ones[g]);
-                a = __fmaf_rn(__fmul_rn(d, dx[g]), (float)isum, a);
-                if (SUMS) {
-                    isum += __shfl_xor_sync(__activemask(), isum, 1);
-                    isum += __shfl_xor_sync(__activemask(), isum, 2);
-                    isum += __shfl_xor_sync(__activemask(), isum, 4);
-                    if (t == 0) p.sums[(size_t)(row0 + r) * (p.cols / 32) + sb * 8 + half * 4 + g] = isum;
-                }
-            }
-            acc[r] = a;
+    for (int i = 0; i < 4; i++) {
+        lo = dp4a_u8s8(n[i] & 0x0F0F0F0Fu, x.lo[i], lo);
+        hi = dp4a_u8s8(n[i] & 0xF0F0F0F0u, x.hi[i], hi);
+    }
+    hi >>= 4;
+    acc = __fmaf_rn(__fmul_rn(__fmul_rn(d, (float)sca), x.da), (float)lo, acc);
+    acc = __fmaf_rn(__fmul_rn(__fmul_rn(d, (float)scb), x.db), (float)hi, acc);
+    if (hsel == 0) {
+        acc = __fmaf_rn(-__fmul_rn(__fmul_rn(dmin, (float)mna), x.da), (float)x.sa, acc);
+        acc = __fmaf_rn(-__fmul_rn(__fmul_rn(dmin, (float)mnb), x.db), (float)x.sb, acc);
+    }
+    if (SUMS) {
+        lo += __shfl_xor_sync(__activemask(), lo, 1);
+        hi += __shfl_xor_sync(__activemask(), hi, 1);
+        if (hsel == 0) {
+            sums_row[x.xb] = lo;
+            sums_row[x.xb + 1] = hi;
         }
     }
+    return acc;
+}
+
+// Q6_K: a lane takes one word of each of ql[64h..], ql[64h+32..] and qh[32h..] (src/Blocks.cs:157-171).
+// value = d*sc*(q-32); per 16-value sub-block the integer sum is sc * (sum q*qx - 32*sum qx).
+template <int FMT, bool SUMS>
+__device__ __forceinline__ float row_dot(const XK6 &x, const uint8_t *row, int lane, int32_t *sums_row, float acc)
+{
+    if (!x.valid) return acc;
+    const int half = (lane >> 3) & 1, t = lane & 7;
+    const uint8_t *blk = row + (size_t)x.sb * 210;
+    const uint32_t A = ld32_a2(blk + half * 64 + t * 4), B = ld32_a2(blk + half * 64 + 32 + t * 4);
+    const uint32_t H = ld32_a2(blk + 128 + half * 32 + t * 4);
+    const float d = half_bits_to_float(*(const uint16_t *)(blk + 208));
+    const int8_t *sc = (const int8_t *)(blk + 192 + half * 8 + (t >> 2));
+    uint32_t q[4];
+    q[0] = (A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u);
+    q[1] = (B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u);
+    q[2] = ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u);
+    q[3] = ((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u);
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        int isum = (int)sc[2 * g] * (dp4a_u8s8(q[g], x.w[g], 0) - 32 * x.ones[g]);
+        acc = __fmaf_rn(__fmul_rn(d, x.d[g]), (float)isum, acc);
+        if (SUMS) {
+            isum += __shfl_xor_sync(__activemask(), isum, 1);
+            isum += __shfl_xor_sync(__activemask(), isum, 2);
+            isum += __shfl_xor_sync(__activemask(), isum, 4);
+            if (t == 0) sums_row[x.sb * 8 + half * 4 + g] = isum;
+        }
+    }
+    return acc;
 }
 
 // ---------------------------------------------------------------------------------- the kernel
 
-template <int FMT, int RW, bool SUMS>
+// The ring holds `slots` chunks; a chunk is RW consecutive rows, fetched by one bulk copy with its own pair of barriers
+// and consumed by the cs warps of one row group.  A unit is rg consecutive chunks (one a row group); block b takes units
+// b, b + grid, ...  RUNS = runs of x a warp holds (its column segment: runs seg, seg + cs, ...).
+template <int FMT, int RW, int RUNS, bool SUMS>
 __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = (uint64_t *)smem;
-    volatile int *abort_flag = (volatile int *)(smem + 3 * MAX_STAGES * 8);
+    volatile int *abort_flag = (volatile int *)(smem + 2 * MAX_SLOTS * 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t full0 = smem_u32(bars), empty0 = full0 + MAX_STAGES * 8, red0 = full0 + 2 * MAX_STAGES * 8;
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + MAX_SLOTS * 8;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; s++) {
+        for (int s = 0; s < p.slots; s++) {
             mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, p.nw);
-            mbar_init(red0 + 8 * s, p.nw);
+            mbar_init(empty0 + 8 * s, p.cs);
         }
         *abort_flag = 0;
         mbar_fence_init();
     }
     __syncthreads();
 
+    auto stamp = [&](int slot) {
+        if (p.timeline && lane == 0 && warp == 0) {
+            long long t;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+            p.timeline[(size_t)blockIdx.x * 8 + slot] = t;
+        }
+    };
+    stamp(0);
     uint8_t *ring = smem + p.off_ring;
+    const int my_units = p.units > (int)blockIdx.x ? (p.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
 
     if (warp == p.nw) {
-        // ---- producer: one untiled bulk copy a unit, plus the bytes outside its 16-byte aligned middle
-        int issued = 0;
-        for (int i = 0;; i++) {
-            const int u = blockIdx.x + i * gridDim.x;
-            if (u >= p.units) break;
-            const int s = i % p.stages;
-            const uint32_t phase = (uint32_t)(i / p.stages) & 1u;
-            if (i >= p.stages && !mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag, p.status, STATUS_GEMV_WAIT)) break;
-            const int row0 = u * p.stage_rows, nrows = min(p.stage_rows, p.rows - row0);
-            const uint8_t *g0 = p.a + (size_t)row0 * p.row_bytes, *g1 = g0 + (size_t)nrows * p.row_bytes;
-            const uint32_t mis = (uint32_t)(uintptr_t)g0 & 15u;
-            const uint8_t *b0 = (const uint8_t *)(((uintptr_t)g0 + 15) & ~(uintptr_t)15);
-            const uint8_t *b1 = (const uint8_t *)((uintptr_t)g1 & ~(uintptr_t)15);
-            uint8_t *slot = ring + (size_t)s * p.stage_stride + mis;      // g0's byte lands here
-            const uint8_t *head_end, *tail_begin;
-            if (b1 > b0) {
-                if (lane == 0) {
-                    mbar_expect_tx(full0 + 8 * s, (uint32_t)(b1 - b0));
-                    bulk_g2s(smem_u32(slot + (b0 - g0)), b0, (uint32_t)(b1 - b0), full0 + 8 * s);
+        // ---- producer: one untiled bulk copy a chunk, plus the bytes outside its 16-byte aligned middle.  The weights
+        // are read-only for the whole call, so the copies start before the kernel that prepares x has ended.
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        int issued = 0, s = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        for (int i = 0; i < my_units && alive; i++) {
+            const int unit_row = (blockIdx.x + i * gridDim.x) * p.stage_rows;
+            for (int g = 0; g < p.rg; g++) {
+                if (issued >= p.slots && !mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag, p.status, STATUS_GEMV_WAIT)) { alive = false; break; }
+                const int row0 = unit_row + g * RW, nrows = max(0, min(RW, p.rows - row0));
+                const uint8_t *g0 = p.a + (size_t)row0 * p.row_bytes, *g1 = g0 + (size_t)nrows * p.row_bytes;
+                const uint32_t mis = (uint32_t)(uintptr_t)g0 & 15u;
+                const uint8_t *b0 = (const uint8_t *)(((uintptr_t)g0 + 15) & ~(uintptr_t)15);
+                const uint8_t *b1 = (const uint8_t *)((uintptr_t)g1 & ~(uintptr_t)15);
+                uint8_t *slot = ring + (size_t)s * p.slot_stride + mis;      // g0's byte lands here
+                const uint8_t *head_end = g1, *tail_begin = g1;
+                if (b1 > b0 && p.probe != 2) {
+                    if (lane == 0) {
+                        mbar_expect_tx(full0 + 8 * s, (uint32_t)(b1 - b0));
+                        bulk_g2s(smem_u32(slot + (b0 - g0)), b0, (uint32_t)(b1 - b0), full0 + 8 * s);
+                    }
+                    head_end = b0;
+                    tail_begin = b1;
                 }
-                head_end = b0;
-                tail_begin = b1;
-            } else {
-                head_end = g1;
-                tail_begin = g1;
+                // at most 15 halfwords on either side
+                if (lane < 16) {
+                    const uint8_t *src = g0 + 2 * lane;
+                    if (src < head_end) *(uint16_t *)(slot + 2 * lane) = __ldg((const uint16_t *)src);
+                } else {
+                    const uint8_t *src = tail_begin + 2 * (lane - 16);
+                    if (src < g1) *(uint16_t *)(slot + (src - g0)) = __ldg((const uint16_t *)src);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + 8 * s);
+                issued++;
+                if (++s == p.slots) { s = 0; phase ^= 1u; }
             }
-            // at most 15 halfwords on either side
-            if (lane < 16) {
-                const uint8_t *src = g0 + 2 * lane;
-                if (src < head_end) *(uint16_t *)(slot + 2 * lane) = __ldg((const uint16_t *)src);
-            } else {
-                const uint8_t *src = tail_begin + 2 * (lane - 16);
-                if (src < g1) *(uint16_t *)(slot + (src - g0)) = __ldg((const uint16_t *)src);
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full0 + 8 * s);
-            issued = i + 1;
         }
         // after a wait that gave up: let the copies still in flight land before the block exits
         if (*abort_flag && lane == 0) {
-            for (int i = max(0, issued - p.stages); i < issued; i++) {
-                const uint32_t bar = full0 + 8 * (i % p.stages), phase = (uint32_t)(i / p.stages) & 1u;
+            for (int k = max(0, issued - p.slots); k < issued; k++) {
+                const uint32_t bar = full0 + 8 * (k % p.slots), ph = (uint32_t)(k / p.slots) & 1u;
                 long long start = clock64();
-                while (!mbar_try_wait(bar, phase) && clock64() - start < WAIT_CYCLES) { }
+                while (!mbar_try_wait(bar, ph) && clock64() - start < WAIT_CYCLES) { }
             }
         }
         return;
     }
 
-    // ---- consumers
+    // ---- consumers: each warp's column segment of the prepared x into registers
     const int threads = p.nw * 32;
-    if (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) stage_x<true>(p, smem, threadIdx.x, threads);
-    else stage_x<false>(p, smem, threadIdx.x, threads);
-    named_bar_sync(1, threads);
-
     const int seg = warp % p.cs, rgi = warp / p.cs;
+    typename XOf<FMT>::type xr[RUNS];
+    asm volatile("griddepcontrol.wait;" ::: "memory");        // the grid that prepared x has ended and its writes are visible
+#pragma unroll
+    for (int j = 0; j < RUNS; j++) load_x(xr[j], p, seg + j * p.cs, lane);
+    // x is in registers: the next call's kernels may be scheduled as this grid's blocks retire
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // whether every lane of this warp has both blocks of every run (then whole chunks take the branch-free path)
+    bool whole_runs = false;
+    if (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) whole_runs = (seg + (RUNS - 1) * p.cs + 1) * 64 <= p.cols / 32;
+    stamp(1);
+
     float *part = (float *)(smem + p.off_part);
-    for (int i = 0;; i++) {
-        const int u = blockIdx.x + i * gridDim.x;
-        if (u >= p.units) break;
-        const int s = i % p.stages;
-        const uint32_t phase = (uint32_t)(i / p.stages) & 1u;
-        if (!mbar_wait(full0 + 8 * s, phase, abort_flag, p.status, STATUS_GEMV_WAIT)) break;
-        const int row0 = u * p.stage_rows, nrows = min(p.stage_rows, p.rows - row0);
-        const uint32_t mis = (uint32_t)(uintptr_t)(p.a + (size_t)row0 * p.row_bytes) & 15u;
-        const int lr0 = rgi * RW;
-        const uint8_t *rows = ring + (size_t)s * p.stage_stride + mis + (size_t)lr0 * p.row_bytes;
-        const int nvalid = max(0, min(RW, nrows - lr0));
-        float acc[RW];
+    const int blocks32 = p.cols / 32;
+    const uint32_t first_off = (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) ? (uint32_t)(seg * 64 + lane * 2) * (uint32_t)block_bytes(FMT) : 0u;
+    bool alive = true;
+    int s = rgi % p.slots, flush_i = 0;
+    uint32_t phase = (uint32_t)(rgi / p.slots) & 1u;
+    for (int i = 0; i < my_units; i++) {
+        const int row0 = (blockIdx.x + i * gridDim.x) * p.stage_rows + rgi * RW;
+        const int nvalid = max(0, min(RW, p.rows - row0));
+        if (alive) alive = mbar_wait(full0 + 8 * s, phase, abort_flag, p.status, STATUS_GEMV_WAIT);
+        if (i == 0) stamp(2);
+        if (i == 1) stamp(3);
+        if (i == my_units - 1) stamp(4);
+        if (alive) {
+            const uint32_t mis = (uint32_t)(uintptr_t)(p.a + (size_t)row0 * p.row_bytes) & 15u;
+            const uint8_t *rows = ring + (size_t)s * p.slot_stride + mis;
+            float acc[RW];
 #pragma unroll
-        for (int r = 0; r < RW; r++) acc[r] = 0.f;
-        if (FMT == QB200_Q4_K) consume_q4k<RW, SUMS>(p, smem, rows, nvalid, row0 + lr0, seg, lane, acc);
-        else if (FMT == QB200_Q6_K) consume_q6k<RW, SUMS>(p, smem, rows, nvalid, row0 + lr0, seg, lane, acc);
-        else consume_q<FMT, RW, SUMS>(p, smem, rows, nvalid, row0 + lr0, seg, lane, acc);
-#pragma unroll
-        for (int r = 0; r < RW; r++) acc[r] = warp_sum(acc[r]);     // every lane has read its last byte of the slot
-        if (p.cs == 1) {
-            if (lane == 0) mbar_arrive(empty0 + 8 * s);
-#pragma unroll
-            for (int r = 0; r < RW; r++) if (lane == r && r < nvalid) p.y[row0 + lr0 + r] = acc[r];
-        } else {
-            float *mine = part + (size_t)s * p.stage_rows * p.cs;
-            if (lane == 0) {
-#pragma unroll
-                for (int r = 0; r < RW; r++) mine[(lr0 + r) * p.cs + seg] = acc[r];
-                mbar_arrive(red0 + 8 * s);
-                if (warp != 0) mbar_arrive(empty0 + 8 * s);
-            }
-            if (warp == 0) {
-                // the unit's rows (at most 32): segments added in ascending order
-                if (!mbar_wait(red0 + 8 * s, phase, abort_flag, p.status, STATUS_GEMV_WAIT)) break;
-                if (lane < nrows) {
-                    float sum = mine[lane * p.cs];
-                    for (int c = 1; c < p.cs; c++) sum += mine[lane * p.cs + c];
-                    p.y[row0 + lane] = sum;
+            for (int r = 0; r < RW; r++) acc[r] = 0.f;
+            bool done = p.probe == 1;
+            if constexpr ((FMT == QB200_Q8_0 || FMT == QB200_Q4_0) && !SUMS) {
+                if (!done && whole_runs && nvalid == RW) {
+                    const bool q4 = (((uint32_t)(uintptr_t)rows + first_off) & 2u) == 0;
+                    if (!p.row_flip) {
+                        if (q4) rows_fast<FMT, RW, RUNS, true, true>(xr, rows, p.row_bytes, acc);
+                        else rows_fast<FMT, RW, RUNS, false, false>(xr, rows, p.row_bytes, acc);
+                    } else {
+                        if (q4) rows_fast<FMT, RW, RUNS, true, false>(xr, rows, p.row_bytes, acc);
+                        else rows_fast<FMT, RW, RUNS, false, true>(xr, rows, p.row_bytes, acc);
+                    }
+                    done = true;
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty0 + 8 * s);
+            }
+            if (!done) {
+#pragma unroll
+                for (int j = 0; j < RUNS; j++) {
+#pragma unroll
+                    for (int r = 0; r < RW; r++) {
+                        if (r < nvalid)
+                            acc[r] = row_dot<FMT, SUMS>(xr[j], rows + (size_t)r * p.row_bytes, lane,
+                                                        SUMS ? p.sums + (size_t)(row0 + r) * blocks32 : nullptr, acc[r]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < RW; r++) acc[r] = warp_sum(acc[r]);     // every lane has read its last byte of the slot
+            if (lane == 0) mbar_arrive(empty0 + 8 * s);
+            if (p.cs == 1) {
+#pragma unroll
+                for (int r = 0; r < RW; r++) if (lane == r && r < nvalid) p.y[row0 + r] = acc[r];
+            } else if (lane == 0) {
+                float *mine = part + ((size_t)flush_i * p.stage_rows + rgi * RW) * p.cs + seg;
+#pragma unroll
+                for (int r = 0; r < RW; r++) mine[r * p.cs] = acc[r];
             }
         }
+        s += p.rg;
+        while (s >= p.slots) { s -= p.slots; phase ^= 1u; }
+        // the partial sums of the last flush_units units: segments added in ascending order
+        if (p.cs > 1 && (++flush_i == p.flush_units || i + 1 == my_units)) {
+            named_bar_sync(1, threads);
+            const int first = i + 1 - flush_i, count = flush_i * p.stage_rows;
+            for (int idx = threadIdx.x; idx < count; idx += threads) {
+                const int k = idx / p.stage_rows, lr = idx - k * p.stage_rows;
+                const int row = (blockIdx.x + (first + k) * gridDim.x) * p.stage_rows + lr;
+                if (row < p.rows) {
+                    const float *src = part + (size_t)idx * p.cs;
+                    float sum = src[0];
+                    for (int c = 1; c < p.cs; c++) sum += src[c];
+                    p.y[row] = sum;
+                }
+            }
+            flush_i = 0;
+            if (i + 1 < my_units) named_bar_sync(1, threads);
+        }
     }
+    stamp(5);
 }
 
 // ---------------------------------------------------------------------------------- host side: shape -> configuration
 
 static int g_sm_count = 0, g_max_smem = 0;
 static int *g_status = nullptr;
+static long long *g_timeline = nullptr;
+static int g_probe = 0;
 
 struct GemvPlan {
-    int rw, nw, cs, rg, stages, grid;
+    int rw, runs_per_warp, nw, cs, rg, stages, grid;
     uint32_t stage_stride, smem_bytes;
     GemvArgs args;
 };
@@ -517,88 +693,128 @@ static int env_int(const char *name, int fallback)
     return v && *v ? atoi(v) : fallback;
 }
 
+// tuning overrides, read once when the library binds a device
+static struct { int warps, stage_bytes, rw, cs, stages; } g_tune = { 16, 24576, 0, 0, 0 };
+
+static void read_tuning()
+{
+    g_tune.warps = env_int("QB200_GEMV_WARPS", 16);
+    g_tune.stage_bytes = env_int("QB200_GEMV_STAGE_BYTES", 24576);
+    g_tune.rw = env_int("QB200_GEMV_RW", 0);
+    g_tune.cs = env_int("QB200_GEMV_CS", 0);
+    g_tune.stages = env_int("QB200_GEMV_STAGES", 0);
+}
+
 static int cols_per_run(int fmt) { return fmt == QB200_Q4_K ? 1024 : fmt == QB200_Q6_K ? 512 : 2048; }
+static int max_runs_per_warp(int fmt) { return fmt == QB200_Q8_0 || fmt == QB200_Q4_0 ? 2 : 4; }
+static constexpr uint32_t PART_BYTES = 16384;
 
 // Splits the consumer warps into column segments x row groups and sizes the ring.
 static int plan_gemv(int fmt_a, int rows, int cols, GemvPlan &pl)
 {
     const uint32_t row_bytes = (uint32_t)(cols / block_values(fmt_a) * block_bytes(fmt_a));
     const int runs = (cols + cols_per_run(fmt_a) - 1) / cols_per_run(fmt_a);
-    int nw = env_int("QB200_GEMV_WARPS", 8);
-    if (nw != 4 && nw != 8 && nw != 16) nw = 8;
+    int nw = g_tune.warps;
+    if (nw != 4 && nw != 8 && nw != 16) nw = 16;
     const uint32_t budget = (uint32_t)g_max_smem - 1024;
-    const uint32_t xq_bytes = ((uint32_t)cols + 2047u) / 2048u * 2048u;      // whole runs of 64 blocks in the paired layout
-    const uint32_t x_bytes = xq_bytes + (uint32_t)(cols / 32 + 2) * 8u + 64u;
-    const uint32_t target = (uint32_t)env_int("QB200_GEMV_STAGE_BYTES", 20480);
-    // candidates: the fewest idle run slots first, then a unit closest to the target size
-    int best_cs = 1, best_rw = 1;
-    double best_score = 1e30;
-    for (int cs = 1; cs <= nw; cs *= 2) {
-        const int per = (runs + cs - 1) / cs;
-        const double waste = (double)(per * cs) / runs;
-        for (int rw = 4; rw >= 1; rw /= 2) {
-            const int stage_rows = nw / cs * rw;
-            if (cs > 1 && stage_rows > 32) continue;
-            const double bytes = (double)stage_rows * row_bytes;
-            if (bytes + 256 > (budget - x_bytes - SMEM_HEADER) / 2) continue;
-            double size_pen = bytes > target ? bytes / target : target / bytes;
-            double score = waste * 4.0 + size_pen + (rw == 1 ? 0.5 : 0.0);
-            if (score < best_score) { best_score = score; best_cs = cs; best_rw = rw; }
-        }
+    // column segments: no idle warps first, then as many segments as possible (small units, few registers of x)
+    int cs = 0;
+    double best = 1e30;
+    for (int c = 1; c <= nw; c *= 2) {
+        const int per = (runs + c - 1) / c;
+        if (per > max_runs_per_warp(fmt_a)) continue;
+        const double waste = (double)(per * c) / runs;
+        if (waste < best - 1e-9 || (waste < best + 1e-9 && c > cs)) { best = waste; cs = c; }
     }
-    if (best_score > 1e29) return QB200_E_LIMIT;
-    const int force_rw = env_int("QB200_GEMV_RW", 0), force_cs = env_int("QB200_GEMV_CS", 0);
-    if (force_rw == 1 || force_rw == 2 || force_rw == 4) best_rw = force_rw;
-    if (force_cs >= 1 && force_cs <= nw && (nw % force_cs) == 0) best_cs = force_cs;
-    pl.rw = best_rw; pl.nw = nw; pl.cs = best_cs; pl.rg = nw / best_cs;
-    const int stage_rows = pl.rg * pl.rw;
-    if (best_cs > 1 && stage_rows > 32) return QB200_E_LIMIT;
-    pl.stage_stride = ((uint32_t)stage_rows * row_bytes + 48u + 127u) / 128u * 128u;
+    if (g_tune.cs >= 1 && g_tune.cs <= nw && nw % g_tune.cs == 0 && (runs + g_tune.cs - 1) / g_tune.cs <= max_runs_per_warp(fmt_a)) cs = g_tune.cs;
+    if (cs == 0) return QB200_E_LIMIT;
+    const int per = (runs + cs - 1) / cs, rg = nw / cs;
+    // rows a warp takes at once: the unit (rg * rw rows) near the target size, at least one row
+    int rw = 4;
+    while (rw > 1 && (uint64_t)rw * row_bytes > (uint64_t)g_tune.stage_bytes) rw /= 2;
+    if (g_tune.rw == 1 || g_tune.rw == 2 || g_tune.rw == 4) rw = g_tune.rw;
+    pl.rw = rw; pl.runs_per_warp = per <= 1 ? 1 : per <= 2 ? 2 : 4; pl.nw = nw; pl.cs = cs; pl.rg = rg;
+    const int stage_rows = rg * rw;
+    pl.stage_stride = ((uint32_t)rw * row_bytes + 48u + 127u) / 128u * 128u;       // one chunk
     GemvArgs &a = pl.args;
     a.row_bytes = row_bytes;
-    a.nw = nw; a.cs = pl.cs; a.rg = pl.rg; a.stage_rows = stage_rows;
+    a.nw = nw; a.cs = cs; a.rg = rg; a.stage_rows = stage_rows;
     a.units = (rows + stage_rows - 1) / stage_rows;
-    a.off_xq = SMEM_HEADER;
-    a.off_xm = a.off_xq + xq_bytes;
-    a.off_part = a.off_xm + ((uint32_t)(cols / 32 + 2) * 8u + 15u) / 16u * 16u;
-    const uint32_t part_one = (uint32_t)stage_rows * pl.cs * 4u;
-    // ring depth: what fits, at most MAX_STAGES, no more than this block's share of the units needs
-    uint32_t fixed = a.off_part;
-    int stages = MAX_STAGES;
-    while (stages > 1 && fixed + (uint32_t)stages * part_one + 128u + (uint32_t)stages * pl.stage_stride > budget) stages--;
-    const int force_stages = env_int("QB200_GEMV_STAGES", 0);
-    if (force_stages >= 1 && force_stages < stages) stages = force_stages;
-    if (fixed + (uint32_t)stages * part_one + 128u + (uint32_t)stages * pl.stage_stride > budget) return QB200_E_LIMIT;
+    a.row_flip = (row_bytes & 2u) ? 1u : 0u;
+    a.off_part = SMEM_HEADER;
+    a.off_ring = (a.off_part + PART_BYTES + 127u) / 128u * 128u;
+    a.flush_units = (int)(PART_BYTES / ((uint32_t)stage_rows * cs * 4u));
+    if (a.flush_units < 1) return QB200_E_LIMIT;
+    if (a.off_ring + (uint64_t)rg * pl.stage_stride > budget) return QB200_E_LIMIT;
     pl.grid = a.units < g_sm_count ? a.units : g_sm_count;
+    int slots = (int)((budget - a.off_ring) / pl.stage_stride);
+    if (slots > MAX_SLOTS) slots = MAX_SLOTS;
     const int per_block = (a.units + pl.grid - 1) / pl.grid;
-    if (stages > per_block) stages = per_block;
-    pl.stages = stages;
-    a.stages = stages;
-    a.stage_stride = pl.stage_stride;
-    a.off_ring = (fixed + (uint32_t)stages * part_one + 127u) / 128u * 128u;
-    pl.smem_bytes = a.off_ring + (uint32_t)stages * pl.stage_stride;
+    if (slots > per_block * rg) slots = per_block * rg;
+    if (g_tune.stages >= 1 && g_tune.stages * rg < slots) slots = g_tune.stages * rg;
+    if (slots < rg) return QB200_E_LIMIT;
+    pl.stages = slots;
+    a.slots = slots;
+    a.slot_stride = pl.stage_stride;
+    pl.smem_bytes = a.off_ring + (uint32_t)slots * pl.stage_stride;
     return 0;
 }
 
-template <int FMT, bool SUMS>
-static cudaError_t launch_fmt(const GemvPlan &pl, cudaStream_t stream)
+template <int FMT, int RW, int RUNS, bool SUMS>
+static cudaError_t launch_one(const GemvPlan &pl, cudaStream_t stream)
 {
-    const dim3 grid(pl.grid), block((pl.nw + 1) * 32);
-    switch (pl.rw) {
-    case 4: gemv_kernel<FMT, 4, SUMS><<<grid, block, pl.smem_bytes, stream>>>(pl.args); break;
-    case 2: gemv_kernel<FMT, 2, SUMS><<<grid, block, pl.smem_bytes, stream>>>(pl.args); break;
-    default: gemv_kernel<FMT, 1, SUMS><<<grid, block, pl.smem_bytes, stream>>>(pl.args); break;
-    }
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(pl.grid);
+    cfg.blockDim = dim3((pl.nw + 1) * 32);
+    cfg.dynamicSmemBytes = pl.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, RW, RUNS, SUMS>, pl.args);
 }
 
-template <int FMT, bool SUMS>
+template <int FMT, int RW, bool SUMS>
+static cudaError_t launch_runs(const GemvPlan &pl, cudaStream_t stream)
+{
+    if (pl.runs_per_warp == 1) return launch_one<FMT, RW, 1, SUMS>(pl, stream);
+    if (pl.runs_per_warp == 2 || FMT == QB200_Q8_0 || FMT == QB200_Q4_0) return launch_one<FMT, RW, 2, SUMS>(pl, stream);
+    return launch_one<FMT, RW, (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) ? 2 : 4, SUMS>(pl, stream);
+}
+
+template <int FMT>
+static cudaError_t launch_fmt(const GemvPlan &pl, bool sums, cudaStream_t stream)
+{
+    if (sums) return launch_runs<FMT, 1, true>(pl, stream);      // the checking variant: a row at a time
+    switch (pl.rw) {
+    case 4: return launch_runs<FMT, 4, false>(pl, stream);
+    case 2: return launch_runs<FMT, 2, false>(pl, stream);
+    default: return launch_runs<FMT, 1, false>(pl, stream);
+    }
+}
+
+template <int FMT, int RW, bool SUMS>
+static cudaError_t set_attr_runs(int bytes)
+{
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 1, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 2, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+    if (FMT == QB200_Q4_K || FMT == QB200_Q6_K)
+        e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) ? 2 : 4, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    return e;
+}
+
+template <int FMT>
 static cudaError_t set_attr(int bytes)
 {
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, 4, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
-    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, 2, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
-    return cudaFuncSetAttribute(gemv_kernel<FMT, 1, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if ((e = set_attr_runs<FMT, 1, true>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 1, false>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 2, false>(bytes))) return e;
+    return set_attr_runs<FMT, 4, false>(bytes);
 }
 
 cudaError_t gemv_init(int sm_count, int max_smem, int *status)
@@ -606,61 +822,89 @@ cudaError_t gemv_init(int sm_count, int max_smem, int *status)
     g_sm_count = sm_count;
     g_max_smem = max_smem;
     g_status = status;
+    read_tuning();
     cudaError_t e;
-    if ((e = set_attr<QB200_Q8_0, false>(max_smem))) return e;
-    if ((e = set_attr<QB200_Q4_0, false>(max_smem))) return e;
-    if ((e = set_attr<QB200_Q4_K, false>(max_smem))) return e;
-    if ((e = set_attr<QB200_Q6_K, false>(max_smem))) return e;
-    if ((e = set_attr<QB200_Q8_0, true>(max_smem))) return e;
-    if ((e = set_attr<QB200_Q4_0, true>(max_smem))) return e;
-    if ((e = set_attr<QB200_Q4_K, true>(max_smem))) return e;
-    return set_attr<QB200_Q6_K, true>(max_smem);
+    if ((e = set_attr<QB200_Q8_0>(max_smem))) return e;
+    if ((e = set_attr<QB200_Q4_0>(max_smem))) return e;
+    if ((e = set_attr<QB200_Q4_K>(max_smem))) return e;
+    return set_attr<QB200_Q6_K>(max_smem);
 }
 
 // Returns 0, a negative QB200_E_* or a positive cudaError_t.  Arguments are already validated.
-int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols, cudaStream_t stream)
+size_t gemv_scratch_bytes(int cols) { return xprep_bytes(cols); }
+
+int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols, void *scratch,
+                cudaStream_t stream)
 {
     if (rows == 0) return 0;
+    // the last few shapes' plans are kept: a decode loop calls the same shapes over and over
+    static thread_local struct { int fmt, rows, cols, rw; GemvPlan plan; } cache[8];
+    static thread_local int cached = 0, next = 0;
     GemvPlan pl;
-    int rc = plan_gemv(fmt_a, rows, cols, pl);
-    if (rc) return rc;
+    bool hit = false;
+    const int want_rw = sums ? 1 : 0;
+    for (int i = 0; i < cached && !hit; i++)
+        if (cache[i].fmt == fmt_a && cache[i].rows == rows && cache[i].cols == cols && cache[i].rw == want_rw) { pl = cache[i].plan; hit = true; }
+    if (!hit) {
+        const int keep_rw = g_tune.rw;
+        if (sums) g_tune.rw = 1;
+        int rc = plan_gemv(fmt_a, rows, cols, pl);
+        g_tune.rw = keep_rw;
+        if (rc) return rc;
+        cache[next].fmt = fmt_a; cache[next].rows = rows; cache[next].cols = cols; cache[next].rw = want_rw; cache[next].plan = pl;
+        next = (next + 1) % 8;
+        if (cached < 8) cached++;
+    }
     pl.args.a = (const uint8_t *)a;
-    pl.args.x = x;
+    pl.args.xprep = (const uint8_t *)scratch;
     pl.args.y = y;
     pl.args.sums = sums;
     pl.args.status = g_status;
+    pl.args.timeline = g_timeline;
+    pl.args.probe = g_probe;
     pl.args.rows = rows;
     pl.args.cols = cols;
-    pl.args.fmt_x = fmt_x;
     cudaError_t e;
-    if (sums) {
-        switch (fmt_a) {
-        case QB200_Q8_0: e = launch_fmt<QB200_Q8_0, true>(pl, stream); break;
-        case QB200_Q4_0: e = launch_fmt<QB200_Q4_0, true>(pl, stream); break;
-        case QB200_Q4_K: e = launch_fmt<QB200_Q4_K, true>(pl, stream); break;
-        default: e = launch_fmt<QB200_Q6_K, true>(pl, stream); break;
-        }
-    } else {
-        switch (fmt_a) {
-        case QB200_Q8_0: e = launch_fmt<QB200_Q8_0, false>(pl, stream); break;
-        case QB200_Q4_0: e = launch_fmt<QB200_Q4_0, false>(pl, stream); break;
-        case QB200_Q4_K: e = launch_fmt<QB200_Q4_K, false>(pl, stream); break;
-        default: e = launch_fmt<QB200_Q6_K, false>(pl, stream); break;
-        }
+    {
+        const int blocks = cols / 32, threads = 128, grid = (blocks + 1 + threads - 1) / threads;
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof cfg);
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(threads);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        uint8_t *out = (uint8_t *)scratch;
+        if (fmt_a == QB200_Q8_0 || fmt_a == QB200_Q4_0) e = cudaLaunchKernelEx(&cfg, prepare_x_kernel<true>, x, fmt_x, cols, out);
+        else e = cudaLaunchKernelEx(&cfg, prepare_x_kernel<false>, x, fmt_x, cols, out);
+        if (e) return (int)e;
+    }
+    switch (fmt_a) {
+    case QB200_Q8_0: e = launch_fmt<QB200_Q8_0>(pl, sums != nullptr, stream); break;
+    case QB200_Q4_0: e = launch_fmt<QB200_Q4_0>(pl, sums != nullptr, stream); break;
+    case QB200_Q4_K: e = launch_fmt<QB200_Q4_K>(pl, sums != nullptr, stream); break;
+    default: e = launch_fmt<QB200_Q6_K>(pl, sums != nullptr, stream); break;
     }
     return (int)e;
 }
 
-// The plan for a shape, for the bench's report and the tests of the host logic (no device needed once sizes are set).
-void gemv_describe(int fmt_a, int rows, int cols, int *out8)
+// The plan for a shape: {rc, warps, column segments, rows a warp, ring depth, grid, slot bytes, shared bytes, runs a warp}.
+void gemv_describe(int fmt_a, int rows, int cols, int *out9)
 {
     GemvPlan pl;
     memset(&pl, 0, sizeof pl);
     int rc = plan_gemv(fmt_a, rows, cols, pl);
-    out8[0] = rc; out8[1] = pl.nw; out8[2] = pl.cs; out8[3] = pl.rw; out8[4] = pl.stages; out8[5] = pl.grid;
-    out8[6] = (int)pl.stage_stride; out8[7] = (int)pl.smem_bytes;
+    out9[0] = rc; out9[1] = pl.nw; out9[2] = pl.cs; out9[3] = pl.rw; out9[4] = pl.stages; out9[5] = pl.grid;
+    out9[6] = (int)pl.stage_stride; out9[7] = (int)pl.smem_bytes; out9[8] = pl.runs_per_warp;
 }
 
-void gemv_set_device_limits(int sm_count, int max_smem) { g_sm_count = sm_count; g_max_smem = max_smem; }
+// Tuning aid: a device buffer of 8 timestamps a block (or null to stop recording).
+void gemv_set_timeline(long long *buffer) { g_timeline = buffer; }
+void gemv_set_probe(int mode) { g_probe = mode; }
+
+void gemv_set_device_limits(int sm_count, int max_smem) { g_sm_count = sm_count; g_max_smem = max_smem; read_tuning(); }
 
 }  // namespace qb

@@ -12,8 +12,10 @@ namespace qb {
 
 cudaError_t gemv_init(int sm_count, int max_smem, int *status);
 void gemv_set_device_limits(int sm_count, int max_smem);
-int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols, cudaStream_t stream);
-void gemv_describe(int fmt_a, int rows, int cols, int *out8);
+size_t gemv_scratch_bytes(int cols);
+int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols, void *scratch,
+                cudaStream_t stream);
+void gemv_describe(int fmt_a, int rows, int cols, int *out9);
 
 int encode_launch(int fmt, const float *lanes, void *blocks, int64_t n, cudaStream_t stream);
 int decode_launch(int fmt, const void *blocks, float *lanes, int64_t n, cudaStream_t stream);
