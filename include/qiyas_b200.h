@@ -103,6 +103,22 @@ int qb200_gemv_block_sums(int fmt_a, int fmt_x, const void *a, const void *x, fl
  * on demand. */
 int qb200_gemv_blocks_host(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols);
 
+/* No counterpart in the reference.  The same gemv for callers that must not allocate device memory: a host
+ * application that owns all of it through its own pool (the reference's Gpu.Rent / Arena, src/Gpu.cs:227-249, would be
+ * one: an allocation behind its back escapes its accounting and makes the driver synchronize the device), or a
+ * latency-critical loop in which a cudaMalloc stall is not acceptable.  Where qb200_gemv_blocks prepares x in a buffer
+ * the library allocated, this entry point prepares it in a fixed array compiled into the library (20 736 bytes of
+ * every GPU that loads the library, held until the process exits), so it takes at most QB200_NOALLOC_MAX_COLS
+ * columns and returns QB200_E_LIMIT beyond that.  It calls no cudaMalloc / cudaFree and needs no qb200_init.
+ * The first call on each device looks up the array's device address and sets the kernels' attributes on that device:
+ * make that first call outside any stream capture.  All calls on a device share the one array and the one status
+ * word: two calls whose kernels could overlap on the GPU (different streams, no ordering between them) race, and the
+ * caller must order them.  Same arguments, arithmetic and results as qb200_gemv_blocks. */
+#define QB200_NOALLOC_MAX_COLS 16384
+int qb200_gemv_blocks_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, void *stream);
+/* The status word of the no-allocation path on the current device (as qb200_device_status; synchronizes). */
+int qb200_gemv_noalloc_status(int *status);
+
 /* ---- A.B^T ------------------------------------------------------------------------------
  * GpuOps.MatMulBlocks<TN>(a, b, cLanes, m, n, k) (src/MatMulBlocks.cs:395-403; kernel it
  * replaces: Ptx.MatMulBlocks, :178-386):  C[i,j] = sum over k-blocks of

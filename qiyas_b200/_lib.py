@@ -27,6 +27,8 @@ SIGNATURES = {
     "qb200_gemv_blocks": (_I, [_I, _I, _P, _P, _P, _I, _I, _P]),
     "qb200_gemv_block_sums": (_I, [_I, _I, _P, _P, _P, _P, _I, _I, _P]),
     "qb200_gemv_blocks_host": (_I, [_I, _I, _P, _P, _P, _I, _I]),
+    "qb200_gemv_blocks_noalloc": (_I, [_I, _I, _P, _P, _P, _I, _I, _P]),
+    "qb200_gemv_noalloc_status": (_I, [C.POINTER(_I)]),
     "qb200_matmul_workspace_bytes": (_Z, [_I, _I, _I, _I, _I]),
     "qb200_matmul_blocks": (_I, [_I, _I, _P, _P, _P, _I, _I, _I, _P, _Z, _P]),
     "qb200_matmul_block_sums": (_I, [_I, _I, _P, _P, _P, _P, _I, _I, _I, _P]),

@@ -202,6 +202,33 @@ int qb200_gemv_blocks_host(int fmt_a, int fmt_x, const void *a, const void *x, f
     return 0;
 }
 
+// The gemv with its scratch in a static device array (see the header): no allocation, no qb200_init needed.
+int qb200_gemv_blocks_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, void *stream)
+{
+    const int bv = qb::block_values(fmt_a);
+    if (!bv) return fail(QB200_E_FORMAT, "%s: the block product takes Q8_0, Q4_0, Q4_K or Q6_K rows", fmt_name(fmt_a));
+    const bool k_quant = fmt_a == QB200_Q4_K || fmt_a == QB200_Q6_K;
+    if (!(fmt_x == QB200_Q8_0 || fmt_x == QB200_F32 || (fmt_x == QB200_Q4_0 && !k_quant)))
+        return fail(QB200_E_FORMAT, "%s x %s: x comes in Q8_0 or f32 (or Q4_0 against Q8_0 / Q4_0 rows)", fmt_name(fmt_a), fmt_name(fmt_x));
+    if (rows < 0 || cols <= 0 || cols % bv != 0)
+        return fail(QB200_E_SHAPE, "%s: the block product takes columns in whole blocks of %d (rows %d, cols %d)", fmt_name(fmt_a), bv, rows, cols);
+    if (cols > QB200_NOALLOC_MAX_COLS)
+        return fail(QB200_E_LIMIT, "cols %d: the no-allocation gemv holds x for at most %d columns in its static scratch; use qb200_gemv_blocks",
+                    cols, QB200_NOALLOC_MAX_COLS);
+    if (rows == 0) return 0;
+    if (!a || !x || !y) return fail(QB200_E_POINTER, "null operand");
+    if (((uintptr_t)a & 1) || ((uintptr_t)x & (fmt_x == QB200_F32 ? 3 : 1)) || ((uintptr_t)y & 3)) return fail(QB200_E_POINTER, "misaligned operand");
+    const int rc = qb::gemv_launch_noalloc(fmt_a, fmt_x, a, x, y, rows, cols, (cudaStream_t)stream);
+    if (rc == QB200_E_DEVICE) return fail(rc, "gemv_blocks_noalloc: the current device is not sm_100");
+    return finish(rc, "gemv_blocks_noalloc");
+}
+
+int qb200_gemv_noalloc_status(int *status)
+{
+    if (!status) return fail(QB200_E_POINTER, "null status");
+    return finish(qb::gemv_noalloc_status(status), "gemv_noalloc_status");
+}
+
 size_t qb200_matmul_workspace_bytes(int fmt_a, int fmt_b, int m, int n, int k)
 {
     if (m <= 0 || n <= 0 || k <= 0 || k % 32) return 0;

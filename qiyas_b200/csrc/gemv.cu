@@ -891,6 +891,97 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     return (int)e;
 }
 
+// ---------------------------------------------------------------------------------- the variant that allocates nothing
+
+// Scratch of the no-allocation entry point: x in the gemv's own layout (prepare_x_kernel) for up to
+// QB200_NOALLOC_MAX_COLS columns, and a status word.  Both live in every device's image of this library from load to
+// exit.  In host code these names are only handles: the device address comes from cudaGetSymbolAddress.
+constexpr int NOALLOC_MAX_COLS = QB200_NOALLOC_MAX_COLS;
+constexpr uint32_t NOALLOC_SCRATCH_BYTES = (NOALLOC_MAX_COLS + 2047) / 2048 * 2048 + ((NOALLOC_MAX_COLS / 32 + 2) * 8 + 255) / 256 * 256;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+static __device__ int g_noalloc_status;
+
+struct NoAllocDevice {
+    void *scratch;
+    int *status;
+};
+static NoAllocDevice g_noalloc[64];
+
+// First use on the current device: resolves the two symbols' device addresses and gives the kernels their
+// shared-memory attribute on this device.  Allocates nothing.
+static int noalloc_setup(int device, NoAllocDevice **out)
+{
+    if (device < 0 || device >= 64) return QB200_E_DEVICE;
+    NoAllocDevice &d = g_noalloc[device];
+    if (!d.scratch) {
+        cudaError_t e;
+        int major = 0, sms = 0, smem = 0;
+        if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device))) return (int)e;
+        if (major != 10) return QB200_E_DEVICE;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device))) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device))) return (int)e;
+        void *scratch = nullptr, *status = nullptr;
+        if ((e = cudaGetSymbolAddress(&scratch, g_noalloc_scratch))) return (int)e;
+        if ((e = cudaGetSymbolAddress(&status, g_noalloc_status))) return (int)e;
+        if (g_sm_count == 0) { g_sm_count = sms; g_max_smem = smem; read_tuning(); }
+        if ((e = set_attr<QB200_Q8_0>(smem)) || (e = set_attr<QB200_Q4_0>(smem)) || (e = set_attr<QB200_Q4_K>(smem)) || (e = set_attr<QB200_Q6_K>(smem)))
+            return (int)e;
+        d.status = (int *)status;
+        d.scratch = scratch;
+    }
+    *out = &d;
+    return 0;
+}
+
+// y = A.x as gemv_launch computes it, with x prepared in the static array instead of a caller's or the library's
+// allocation.  The status word is cleared by a memset node in the stream before the kernels (it must start at zero;
+// the x scratch needs no clearing: the preparing kernel rewrites every byte the gemv reads).
+int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, cudaStream_t stream)
+{
+    if (cols > NOALLOC_MAX_COLS) return QB200_E_LIMIT;
+    if (rows == 0) return 0;
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e) return (int)e;
+    NoAllocDevice *dev = nullptr;
+    int rc = noalloc_setup(device, &dev);
+    if (rc) return rc;
+    GemvPlan pl;
+    if ((rc = plan_gemv(fmt_a, rows, cols, pl))) return rc;
+    pl.args.a = (const uint8_t *)a;
+    pl.args.xprep = (const uint8_t *)dev->scratch;
+    pl.args.y = y;
+    pl.args.sums = nullptr;
+    pl.args.status = dev->status;
+    pl.args.timeline = nullptr;
+    pl.args.probe = 0;
+    pl.args.rows = rows;
+    pl.args.cols = cols;
+    if ((e = cudaMemsetAsync(dev->status, 0, sizeof(int), stream))) return (int)e;
+    const int blocks = cols / 32, threads = 128, grid = (blocks + 1 + threads - 1) / threads;
+    if (fmt_a == QB200_Q8_0 || fmt_a == QB200_Q4_0) prepare_x_kernel<true><<<grid, threads, 0, stream>>>(x, fmt_x, cols, (uint8_t *)dev->scratch);
+    else prepare_x_kernel<false><<<grid, threads, 0, stream>>>(x, fmt_x, cols, (uint8_t *)dev->scratch);
+    if ((e = cudaGetLastError())) return (int)e;
+    switch (fmt_a) {
+    case QB200_Q8_0: e = launch_fmt<QB200_Q8_0>(pl, false, stream); break;
+    case QB200_Q4_0: e = launch_fmt<QB200_Q4_0>(pl, false, stream); break;
+    case QB200_Q4_K: e = launch_fmt<QB200_Q4_K>(pl, false, stream); break;
+    default: e = launch_fmt<QB200_Q6_K>(pl, false, stream); break;
+    }
+    return (int)e;
+}
+
+// Reads the static status word of the current device (0 = no bounded wait gave up); synchronizes the stream's device.
+int gemv_noalloc_status(int *value)
+{
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e) return (int)e;
+    if (device < 0 || device >= 64 || !g_noalloc[device].status) { *value = 0; return 0; }
+    if ((e = cudaDeviceSynchronize())) return (int)e;
+    return (int)cudaMemcpy(value, g_noalloc[device].status, sizeof(int), cudaMemcpyDeviceToHost);
+}
+
 // The plan for a shape: {rc, warps, column segments, rows a warp, ring depth, grid, slot bytes, shared bytes, runs a warp}.
 void gemv_describe(int fmt_a, int rows, int cols, int *out9)
 {

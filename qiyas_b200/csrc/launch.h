@@ -15,6 +15,8 @@ void gemv_set_device_limits(int sm_count, int max_smem);
 size_t gemv_scratch_bytes(int cols);
 int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols, void *scratch,
                 cudaStream_t stream);
+int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, cudaStream_t stream);
+int gemv_noalloc_status(int *value);
 void gemv_describe(int fmt_a, int rows, int cols, int *out9);
 
 int encode_launch(int fmt, const float *lanes, void *blocks, int64_t n, cudaStream_t stream);
