@@ -63,6 +63,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// The same for a whole warp: lane 0 waits and every lane gets its answer, so the warp stays converged whatever happens
+// (warp-wide instructions follow these waits); the shuffle also orders the lanes' later reads after lane 0's acquire.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort, int *status, int status_bit)
+{
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort, status, status_bit) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // ---------------------------------------------------------------------------------- bulk copies (TMA, untiled)
 // global -> shared, both addresses 16-byte aligned, bytes a multiple of 16; completion counted on the mbarrier.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)

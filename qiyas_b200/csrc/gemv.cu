@@ -604,7 +604,7 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
     for (int i = 0; i < my_units; i++) {
         const int row0 = (blockIdx.x + i * gridDim.x) * p.stage_rows + rgi * RW;
         const int nvalid = max(0, min(RW, p.rows - row0));
-        if (alive) alive = mbar_wait(full0 + 8 * s, phase, abort_flag, p.status, STATUS_GEMV_WAIT);
+        if (alive) alive = mbar_wait_warp(full0 + 8 * s, phase, abort_flag, p.status, STATUS_GEMV_WAIT);
         if (i == 0) stamp(2);
         if (i == 1) stamp(3);
         if (i == my_units - 1) stamp(4);

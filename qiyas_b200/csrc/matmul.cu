@@ -1,8 +1,339 @@
-// placeholder until the tcgen05 product lands
+// Block-scaled A.B^T for sm_100a: C (m x n, f32) = A (m x k) . B (n x k)^T with A and B in Q8_0 / Q4_0 rows.
+//
+// Replaces Ptx.MatMulBlocks (reference src/MatMulBlocks.cs:178-386: 64 x 64 tiles, mma.sync m16n8k32, operands staged
+// by 16-bit loads).  The arithmetic is that kernel's: per k-block of 32 the exact s32 product sum D, then
+//     acc = fma(float(D), sA*sB, acc)        (src/MatMulBlocks.cs:339-347), k-blocks in ascending order,
+// so the f32 result equals the reference's device result bit for bit.
+//
+// Two steps:
+//  1. pack_rows_kernel re-lays each operand in scratch memory for the tensor cores: the scales are stripped out of the
+//     34- / 18-byte blocks into an f32 plane, Q4_0 nibbles are widened to int8 (q - 8), and the int8 codes are stored
+//     tile by tile in the canonical K-major, unswizzled shared-memory layout of tcgen05 (8-row x 16-byte core matrices),
+//     so that a whole (128 rows x several k-blocks) slab is one contiguous run of bytes.
+//  2. matmul_kernel: one 128 x 128 tile of C a block.  A producer warp brings slabs of codes and scales into a ring of
+//     shared-memory stages with untiled TMA bulk copies; one thread issues a tcgen05.mma (kind::i8, M 128, N 128, K 32)
+//     per k-block into one of four 128-column accumulators in tensor memory, with accumulation off, and commits it to
+//     an mbarrier; eight epilogue warps read the s32 sums back with tcgen05.ld, scale them in f32 and add them to
+//     register accumulators while the next k-blocks' products run.
 #include "common.cuh"
 #include "launch.h"
+
 namespace qb {
-cudaError_t matmul_init(int, int, int *) { return cudaSuccess; }
-size_t matmul_workspace_bytes(int, int, int, int, int) { return 256; }
-int matmul_launch(int, int, const void *, const void *, float *, int32_t *, int, int, int, void *, cudaStream_t) { return QB200_E_DEVICE; }
+
+constexpr int TILE = 128;            // rows of A and of B per block tile
+constexpr int KS = 4;                // k-blocks per shared-memory stage
+constexpr int MM_STAGES = 5;
+constexpr int TMEM_STAGES = 4;       // 4 x 128 columns = all 512 columns of tensor memory
+constexpr int SLAB = TILE * 32;      // bytes of codes per tile and k-block
+constexpr int MM_THREADS = 320;      // warp 0 producer, warp 1 MMA, warps 2..9 epilogue
+constexpr uint32_t STAGE_BYTES = KS * (2 * SLAB + 2 * TILE * 4);
+constexpr uint32_t MM_HEADER = 1024;
+constexpr uint32_t MM_SMEM = MM_HEADER + MM_STAGES * STAGE_BYTES;
+
+struct PackedOperand {
+    const uint8_t *codes;    // [tile][kb][2][16][8][16]
+    const float *scales;     // [tile][kb][128]
+};
+
+struct MatmulArgs {
+    PackedOperand a, b;
+    float *c;
+    int32_t *sums;
+    int *status;
+    int m, n, kb;
+};
+
+// ---------------------------------------------------------------------------------- step 1: operands for the tensor cores
+
+// A thread a block: rows of the raw operand are `kb` blocks long; row r of tile t lands at byte
+// (t*kb + b)*4096 + j*2048 + (r/8)*128 + (r%8)*16 for its bytes 16j..16j+15, and its scale at ((t*kb + b)*128 + r).
+// Rows past `rows` (the padding of the last tile) are written as zeros.
+template <int FMT>
+__global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int rows, int kb, uint8_t *codes, float *scales)
+{
+    constexpr int BB = block_bytes(FMT);
+    const int r = blockIdx.x * 32 + (threadIdx.x & 31), b = blockIdx.y * 8 + (threadIdx.x >> 5);
+    if (b >= kb) return;
+    uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+    float d = 0.f;
+    if (r < rows) {
+        const uint16_t *p = (const uint16_t *)(raw + ((size_t)r * kb + b) * BB);
+        d = half_bits_to_float(__ldg(p));
+        uint32_t w[8];
+        if (FMT == QB200_Q8_0) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) w[i] = (uint32_t)__ldg(p + 1 + 2 * i) | (uint32_t)__ldg(p + 2 + 2 * i) << 16;
+        } else {
+            // value i in the low nibble of byte i, value i + 16 in the high nibble, each minus 8 (src/MatMulBlocks.cs:282-299)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t n = (uint32_t)__ldg(p + 1 + 2 * i) | (uint32_t)__ldg(p + 2 + 2 * i) << 16;
+                w[i] = __vsub4(n & 0x0F0F0F0Fu, 0x08080808u);
+                w[i + 4] = __vsub4((n >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+            }
+        }
+        lo = make_uint4(w[0], w[1], w[2], w[3]);
+        hi = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    const int t = r / TILE, rr = r % TILE;
+    uint8_t *slab = codes + ((size_t)t * kb + b) * SLAB + (rr >> 3) * 128 + (rr & 7) * 16;
+    *(uint4 *)slab = lo;
+    *(uint4 *)(slab + SLAB / 2) = hi;
+    scales[((size_t)t * kb + b) * TILE + rr] = d;
 }
+
+// ---------------------------------------------------------------------------------- tcgen05 in inline PTX
+
+__device__ __forceinline__ void tmem_alloc(uint32_t holder_smem, uint32_t columns)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major, no swizzle.  Core matrices are 8 rows x 16 bytes, stored contiguously
+// (128 bytes); LBO = bytes between the two 16-byte k-chunks of a row, SBO = bytes between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo)
+{
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (uint64_t)(lbo >> 4) << 16 | (uint64_t)(sbo >> 4) << 32 | (uint64_t)1 << 46;
+}
+
+// Instruction descriptor of kind::i8: D s32, A and B signed 8-bit, both K-major, dense, M x N.
+__host__ __device__ constexpr uint32_t idesc_s8(int m, int n)
+{
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// D[tmem] = A.B^T for one k-block (K = 32 bytes of int8), accumulation off: each k-block needs its own scale.
+__device__ __forceinline__ void mma_s8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0u)
+        : "memory");
+}
+
+// The mbarrier gets one arrival when every tcgen05.mma this thread issued so far has completed.
+__device__ __forceinline__ void mma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 columns of 32-bit accumulators: thread l of the warp gets row (lane base + l), columns c .. c+31.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, int32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------- step 2: the product
+
+template <bool SUMS>
+__global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs p)
+{
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = smem_u32(smem);
+    const uint32_t full0 = base, empty0 = base + 8 * MM_STAGES, tfull0 = base + 16 * MM_STAGES, tempty0 = tfull0 + 8 * TMEM_STAGES;
+    const uint32_t holder = tempty0 + 8 * TMEM_STAGES;
+    volatile int *abort_flag = (volatile int *)(smem + 512);
+    volatile uint32_t *holder_ptr = (volatile uint32_t *)(smem + (holder - base));
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < MM_STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 9);          // the MMA thread's commit and the eight epilogue warps
+        }
+        for (int s = 0; s < TMEM_STAGES; s++) {
+            mbar_init(tfull0 + 8 * s, 1);
+            mbar_init(tempty0 + 8 * s, 8);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(holder, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *holder_ptr;
+
+    const int tn = blockIdx.x, tm = blockIdx.y;
+    const int stages_total = (p.kb + KS - 1) / KS;
+    uint8_t *ring = smem + MM_HEADER;
+
+    if (warp == 0) {
+        // ---- producer: four contiguous slabs a stage (A codes, B codes, A scales, B scales)
+        if (lane == 0) {
+            int issued = 0;
+            for (int it = 0; it < stages_total; it++) {
+                const int s = it % MM_STAGES;
+                const uint32_t phase = (uint32_t)(it / MM_STAGES) & 1u;
+                if (it >= MM_STAGES && !mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) break;
+                const int kb0 = it * KS, nkb = min(KS, p.kb - kb0);
+                const uint32_t dst = smem_u32(ring + (size_t)s * STAGE_BYTES), bar = full0 + 8 * s;
+                const uint32_t code_bytes = (uint32_t)nkb * SLAB, scale_bytes = (uint32_t)nkb * TILE * 4;
+                mbar_arrive_expect_tx(bar, 2 * code_bytes + 2 * scale_bytes);
+                bulk_g2s(dst, p.a.codes + ((size_t)tm * p.kb + kb0) * SLAB, code_bytes, bar);
+                bulk_g2s(dst + KS * SLAB, p.b.codes + ((size_t)tn * p.kb + kb0) * SLAB, code_bytes, bar);
+                bulk_g2s(dst + 2 * KS * SLAB, p.a.scales + ((size_t)tm * p.kb + kb0) * TILE, scale_bytes, bar);
+                bulk_g2s(dst + 2 * KS * SLAB + KS * TILE * 4, p.b.scales + ((size_t)tn * p.kb + kb0) * TILE, scale_bytes, bar);
+                issued = it + 1;
+            }
+            if (*abort_flag) {          // let the copies still in flight land before the block exits
+                for (int it = max(0, issued - MM_STAGES); it < issued; it++) {
+                    long long start = clock64();
+                    while (!mbar_try_wait(full0 + 8 * (it % MM_STAGES), (uint32_t)(it / MM_STAGES) & 1u) && clock64() - start < WAIT_CYCLES) { }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue: one thread, one instruction a k-block, each into the next of four accumulators
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_s8(TILE, TILE);
+            bool alive = true;
+            for (int it = 0; it < stages_total && alive; it++) {
+                const int s = it % MM_STAGES;
+                if (!mbar_wait(full0 + 8 * s, (uint32_t)(it / MM_STAGES) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) break;
+                tc_fence_after();
+                const uint32_t a_smem = smem_u32(ring + (size_t)s * STAGE_BYTES), b_smem = a_smem + KS * SLAB;
+                const int nkb = min(KS, p.kb - it * KS);
+                for (int kk = 0; kk < nkb; kk++) {
+                    const int i = it * KS + kk, ts = i % TMEM_STAGES, use = i / TMEM_STAGES;
+                    if (use > 0 && !mbar_wait(tempty0 + 8 * ts, (uint32_t)(use - 1) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
+                    tc_fence_after();
+                    mma_s8(tmem + (uint32_t)ts * TILE, smem_desc(a_smem + kk * SLAB, SLAB / 2, 128), smem_desc(b_smem + kk * SLAB, SLAB / 2, 128), idesc);
+                    mma_commit(tfull0 + 8 * ts);
+                }
+                mma_commit(empty0 + 8 * s);      // the stage's codes are free once these products have run
+            }
+        }
+    } else {
+        // ---- epilogue: a warp reads its 32 rows (tensor-memory lanes 32*(warp%4) ..) x 64 columns of each accumulator
+        const int q = warp & 3, ch = (warp - 2) >> 2;
+        const int row = tm * TILE + q * 32 + lane, col0 = tn * TILE + ch * 64;
+        float acc[64];
+#pragma unroll
+        for (int c = 0; c < 64; c++) acc[c] = 0.f;
+        bool alive = true;
+        for (int i = 0; i < p.kb && alive; i++) {
+            const int it = i / KS, kk = i % KS, s = it % MM_STAGES, ts = i % TMEM_STAGES;
+            if (kk == 0 && !mbar_wait_warp(full0 + 8 * s, (uint32_t)(it / MM_STAGES) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
+            if (!mbar_wait_warp(tfull0 + 8 * ts, (uint32_t)(i / TMEM_STAGES) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
+            tc_fence_after();
+            int32_t v0[32], v1[32];
+            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ts * TILE + ch * 64);
+            tmem_ld32(taddr, v0);
+            tmem_ld32(taddr + 32, v1);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * ts);        // the accumulator may be overwritten
+            const float *sa_s = (const float *)(ring + (size_t)s * STAGE_BYTES + 2 * KS * SLAB) + kk * TILE;
+            const float *sb_s = sa_s + KS * TILE + ch * 64;
+            const float sa = sa_s[q * 32 + lane];
+#pragma unroll
+            for (int c4 = 0; c4 < 16; c4++) {
+                const float4 sb = *(const float4 *)(sb_s + 4 * c4);
+                const int32_t *v = c4 < 8 ? v0 + 4 * c4 : v1 + 4 * (c4 - 8);
+                acc[4 * c4 + 0] = __fmaf_rn((float)v[0], __fmul_rn(sa, sb.x), acc[4 * c4 + 0]);
+                acc[4 * c4 + 1] = __fmaf_rn((float)v[1], __fmul_rn(sa, sb.y), acc[4 * c4 + 1]);
+                acc[4 * c4 + 2] = __fmaf_rn((float)v[2], __fmul_rn(sa, sb.z), acc[4 * c4 + 2]);
+                acc[4 * c4 + 3] = __fmaf_rn((float)v[3], __fmul_rn(sa, sb.w), acc[4 * c4 + 3]);
+            }
+            if (SUMS && row < p.m) {
+#pragma unroll
+                for (int c = 0; c < 64; c++)
+                    if (col0 + c < p.n) p.sums[((size_t)row * p.n + col0 + c) * p.kb + i] = c < 32 ? v0[c] : v1[c - 32];
+            }
+            if (kk == KS - 1 || i == p.kb - 1) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * s);      // this warp has read the stage's scales
+            }
+        }
+        if (alive && row < p.m) {
+            float *out = p.c + (size_t)row * p.n + col0;
+            if ((p.n & 3) == 0 && col0 + 64 <= p.n && ((uintptr_t)p.c & 15) == 0) {
+#pragma unroll
+                for (int c4 = 0; c4 < 16; c4++) *(float4 *)(out + 4 * c4) = make_float4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 64; c++) if (col0 + c < p.n) out[c] = acc[c];
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------- host side
+
+static int *g_mm_status = nullptr;
+
+cudaError_t matmul_init(int, int max_smem, int *status)
+{
+    g_mm_status = status;
+    if ((int)MM_SMEM > max_smem) return cudaErrorInvalidValue;
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(matmul_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MM_SMEM))) return e;
+    return cudaFuncSetAttribute(matmul_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MM_SMEM);
+}
+
+static size_t packed_codes_bytes(int rows, int k) { return (size_t)((rows + TILE - 1) / TILE) * (k / 32) * SLAB; }
+static size_t packed_scales_bytes(int rows, int k) { return (size_t)((rows + TILE - 1) / TILE) * (k / 32) * TILE * 4; }
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+// Scratch for both packed operands: codes then scales of A, codes then scales of B, each on a 256-byte boundary.
+size_t matmul_workspace_bytes(int, int, int m, int n, int k)
+{
+    return align256(packed_codes_bytes(m, k)) + align256(packed_scales_bytes(m, k)) + align256(packed_codes_bytes(n, k)) +
+           align256(packed_scales_bytes(n, k));
+}
+
+static cudaError_t pack(int fmt, const void *raw, int rows, int k, uint8_t *codes, float *scales, cudaStream_t stream)
+{
+    const int kb = k / 32, padded = (rows + TILE - 1) / TILE * TILE;
+    const dim3 grid(padded / 32, (kb + 7) / 8);
+    if (fmt == QB200_Q8_0) pack_rows_kernel<QB200_Q8_0><<<grid, 256, 0, stream>>>((const uint8_t *)raw, rows, kb, codes, scales);
+    else pack_rows_kernel<QB200_Q4_0><<<grid, 256, 0, stream>>>((const uint8_t *)raw, rows, kb, codes, scales);
+    return cudaGetLastError();
+}
+
+int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int32_t *sums, int m, int n, int k, void *workspace,
+                  cudaStream_t stream)
+{
+    uint8_t *w = (uint8_t *)workspace;
+    uint8_t *a_codes = w;
+    float *a_scales = (float *)(w += align256(packed_codes_bytes(m, k)));
+    uint8_t *b_codes = (w += align256(packed_scales_bytes(m, k)));
+    float *b_scales = (float *)(w += align256(packed_codes_bytes(n, k)));
+    cudaError_t e;
+    if ((e = pack(fmt_a, a, m, k, a_codes, a_scales, stream))) return (int)e;
+    if ((e = pack(fmt_b, b, n, k, b_codes, b_scales, stream))) return (int)e;
+    MatmulArgs args;
+    args.a.codes = a_codes; args.a.scales = a_scales;
+    args.b.codes = b_codes; args.b.scales = b_scales;
+    args.c = c; args.sums = sums; args.status = g_mm_status;
+    args.m = m; args.n = n; args.kb = k / 32;
+    const dim3 grid((n + TILE - 1) / TILE, (m + TILE - 1) / TILE);
+    if (sums) matmul_kernel<true><<<grid, MM_THREADS, MM_SMEM, stream>>>(args);
+    else matmul_kernel<false><<<grid, MM_THREADS, MM_SMEM, stream>>>(args);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace qb

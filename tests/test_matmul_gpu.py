@@ -1,0 +1,136 @@
+"""Parity of the tcgen05 A.B^T with the C oracle, through the C ABI.
+
+The kernel keeps the reference device kernel's arithmetic (src/MatMulBlocks.cs:339-347: per k-block
+acc = fma(float(D), sA*sB, acc), ascending), so C must equal the oracle's device-order product bit for bit;
+every k-block's s32 sum must be exact; against the reference's CPU order (src/MatMulBlocks.cs:130-148) the
+tolerance is 1e-5; and the error against the double-double float64 reference (Program.cs:995-1019) must not
+exceed the reference's own.
+"""
+import numpy as np
+import pytest
+
+from qiyas_b200 import blocks as B
+
+from . import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def operands(oracle, fmt_a, fmt_b, m, n, k, seed, quantized_a=True):
+    rng = np.random.default_rng(seed)
+    if quantized_a:       # activations drawn then row-quantized by the reference's encoder
+        a = oracle.encode(fmt_a, rng.standard_normal(m * k).astype(np.float32), device_rounding=True)
+    else:
+        a = B.make_weights(fmt_a, m, k, seed + 7)
+    b = B.make_weights(fmt_b, n, k, seed + 1)
+    return a, b
+
+
+def matmul_gpu(fmt_a, fmt_b, a, b, m, n, k, want_sums=False, workspace=False):
+    import torch
+    o = H.ops()
+    da, db = H.dev(a), H.dev(b)
+    c = H.empty(m * n, torch.float32)
+    c.fill_(float("nan"))
+    if want_sums:
+        sums = H.empty(m * n * (k // 32), torch.int32)
+        lane = o.MatMulBlockSums(fmt_a, da, db, c, sums, m, n, k, fmt_b=fmt_b)
+    elif workspace:
+        need = o.workspace_bytes(fmt_a, m, n, k, fmt_b=fmt_b)
+        ws = torch.empty(need + 256, dtype=torch.uint8, device="cuda:0")
+        off = (-ws.data_ptr()) % 256
+        lane = o.MatMulBlocks(fmt_a, da, db, c, m, n, k, fmt_b=fmt_b, workspace=ws.data_ptr() + off, workspace_bytes=need)
+    else:
+        lane = o.MatMulBlocks(fmt_a, da, db, c, m, n, k, fmt_b=fmt_b)
+    assert o.gpu.status() == 0
+    assert lane == "s8 tcgen05 blocks"
+    out = c.cpu().numpy().reshape(m, n)
+    if want_sums:
+        return out, sums.cpu().numpy().reshape(m, n, k // 32)
+    return out
+
+
+def check(oracle, fmt_a, fmt_b, m, n, k, seed, f64=True):
+    a, b = operands(oracle, fmt_a, fmt_b, m, n, k, seed)
+    c, sums = matmul_gpu(fmt_a, fmt_b, a, b, m, n, k, want_sums=True)
+    ref, ref_sums = oracle.matmul_blocks(fmt_a, fmt_b, a, b, m, n, k, order=1, want_sums=True)
+    assert np.array_equal(sums, ref_sums)
+    assert np.array_equal(c.view(np.uint32), ref.view(np.uint32))
+    plain = matmul_gpu(fmt_a, fmt_b, a, b, m, n, k)
+    assert np.array_equal(plain.view(np.uint32), ref.view(np.uint32))
+    cpu = oracle.matmul_blocks(fmt_a, fmt_b, a, b, m, n, k, order=0)
+    assert np.max(np.abs(c - cpu)) <= 1e-5 * np.max(np.abs(cpu))
+    if f64:
+        c64 = oracle.matmul_f64(fmt_a, fmt_b, a, b, m, n, k)
+        assert np.max(np.abs(c - c64)) <= np.max(np.abs(ref - c64))
+
+
+@pytest.mark.parametrize("fmt", [B.Q8_0, B.Q4_0])
+@pytest.mark.parametrize("k", [64, 320])
+def test_gate_shapes_37x29(oracle, fmt, k):
+    # the reference's block product gate: M 37, N 29, K 64 and 320 (src/Checks.cs:1234-1249)
+    check(oracle, fmt, fmt, 37, 29, k, 34)
+
+
+@pytest.mark.parametrize("fmt_a,fmt_b", [(B.Q8_0, B.Q4_0), (B.Q4_0, B.Q8_0)])
+def test_mixed_formats(oracle, fmt_a, fmt_b):
+    check(oracle, fmt_a, fmt_b, 45, 131, 96, 5)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 32), (1, 129, 32), (128, 128, 32), (129, 127, 160), (16, 257, 4096), (257, 384, 1056), (3, 5, 8160)])
+def test_edges(oracle, m, n, k):
+    check(oracle, B.Q8_0, B.Q8_0, m, n, k, 9 + m, f64=m * n * k < 1 << 24)
+
+
+def test_caller_workspace(oracle):
+    m, n, k = 70, 300, 512
+    a, b = operands(oracle, B.Q8_0, B.Q8_0, m, n, k, 3)
+    c = matmul_gpu(B.Q8_0, B.Q8_0, a, b, m, n, k, workspace=True)
+    ref = oracle.matmul_blocks(B.Q8_0, B.Q8_0, a, b, m, n, k, order=1)
+    assert np.array_equal(c.view(np.uint32), ref.view(np.uint32))
+
+
+def sampled_rows_check(oracle, fmt_a, fmt_b, m, n, k, seed, rows=12):
+    """Full-size shapes: C on the GPU; a sample of A's rows through the oracle (a row of C needs that row of A only)."""
+    a, b = operands(oracle, fmt_a, fmt_b, m, n, k, seed)
+    c = matmul_gpu(fmt_a, fmt_b, a, b, m, n, k)
+    pick = np.unique(np.concatenate([[0, m - 1], np.random.default_rng(seed).integers(0, m, rows)]))
+    rb = B.row_bytes(fmt_a, k)
+    a_rows = a.reshape(m, rb)[pick].reshape(-1)
+    ref = oracle.matmul_blocks(fmt_a, fmt_b, a_rows, b, len(pick), n, k, order=1)
+    assert np.array_equal(c[pick].view(np.uint32), ref.view(np.uint32))
+    assert np.isfinite(c).all()
+
+
+@pytest.mark.parametrize("m", [1, 16, 128, 512, 2048])
+def test_prefill_config_q8_0(oracle, m):
+    sampled_rows_check(oracle, B.Q8_0, B.Q8_0, m, 11008, 4096, 300 + m)
+
+
+def test_prefill_config_odd(oracle):
+    sampled_rows_check(oracle, B.Q8_0, B.Q8_0, 509, 11003, 4096, 77)
+
+
+def test_q4_0_weights_q8_0_activations(oracle):
+    sampled_rows_check(oracle, B.Q8_0, B.Q4_0, 64, 28672 // 8, 8192, 78)
+    sampled_rows_check(oracle, B.Q8_0, B.Q4_0, 33, 1021, 8160, 79)
+
+
+def test_view_surface(oracle):
+    import torch
+    from qiyas_b200.ops import ProductView
+    o = H.ops()
+    m, n, k = 37, 29, 320
+    a, b = operands(oracle, B.Q8_0, B.Q8_0, m, n, k, 34)
+    v = ProductView(m, n, k, False, True)
+    assert o.BlockProductAvailable and o.BlockView("q8_0", v)
+    out = H.empty(B.nbytes(B.Q8_0, m * n), torch.uint8)
+    assert o.MatMulView("q8_0", v, H.dev(a), H.dev(b), out) == "s8 tcgen05 blocks"
+    lanes = oracle.matmul_blocks(B.Q8_0, B.Q8_0, a, b, m, n, k, order=1).reshape(-1)
+    assert np.array_equal(out.cpu().numpy(), oracle.encode(B.Q8_0, lanes, device_rounding=True))
+    with pytest.raises(NotImplementedError):
+        o.MatMulView("q8_0", ProductView(m, n, k, True, True), H.dev(a), H.dev(b), out)
+    with pytest.raises(NotImplementedError):
+        o.MatMulBlocks("q8_0", H.dev(a), H.dev(b), out, m, n, 33)
+    with pytest.raises(NotImplementedError):
+        o.MatMulBlocks("q4_k", H.dev(a), H.dev(b), out, m, n, 256)
