@@ -13,8 +13,8 @@
 //  2. matmul_kernel: one 128 x 128 tile of C a block.  A producer warp brings slabs of codes and scales into a ring of
 //     shared-memory stages with untiled TMA bulk copies; one thread issues a tcgen05.mma (kind::i8, M 128, N 128, K 32)
 //     per k-block into one of four 128-column accumulators in tensor memory, with accumulation off, and commits it to
-//     an mbarrier; eight epilogue warps read the s32 sums back with tcgen05.ld, scale them in f32 and add them to
-//     register accumulators while the next k-blocks' products run.
+//     an mbarrier; sixteen epilogue warps read the s32 sums back with tcgen05.ld, scale them in f32 (packed f32x2
+//     instructions) and add them to register accumulators while the next k-blocks' products run.
 #include "common.cuh"
 #include "launch.h"
 
@@ -25,7 +25,8 @@ constexpr int KS = 4;                // k-blocks per shared-memory stage
 constexpr int MM_STAGES = 5;
 constexpr int TMEM_STAGES = 4;       // 4 x 128 columns = all 512 columns of tensor memory
 constexpr int SLAB = TILE * 32;      // bytes of codes per tile and k-block
-constexpr int MM_THREADS = 320;      // warp 0 producer, warp 1 MMA, warps 2..9 epilogue
+constexpr int EPI_WARPS = 16;
+constexpr int MM_THREADS = 32 * (2 + EPI_WARPS);   // warp 0 producer, warp 1 MMA, the rest epilogue
 constexpr uint32_t STAGE_BYTES = KS * (2 * SLAB + 2 * TILE * 4);
 constexpr uint32_t MM_HEADER = 1024;
 constexpr uint32_t MM_SMEM = MM_HEADER + MM_STAGES * STAGE_BYTES;
@@ -41,6 +42,8 @@ struct MatmulArgs {
     int32_t *sums;
     int *status;
     int m, n, kb;
+    long long *dbg;  // tuning aid: cycle counts of block 0's MMA thread; null in normal use
+    int probe;       // tuning aid: 1 = no arithmetic, 2 = no tensor-memory reads, 3 = neither; 0 in normal use
 };
 
 // ---------------------------------------------------------------------------------- step 1: operands for the tensor cores
@@ -143,6 +146,57 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 // ---------------------------------------------------------------------------------- step 2: the product
 
+// Packed f32 pairs (sm_100): one instruction rounds two independent products / fused multiply-adds, each exactly as
+// mul.rn.f32 / fma.rn.f32 would.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+// Two s32 block sums as two floats, exactly, without the conversion unit: |D| <= 32*127*127 < 2^22, so the integer
+// D + 0x4B400000 is the bit pattern of the float 12582912 + D (1.5 * 2^23 has a unit in the last place of 1 and D stays
+// inside its binade), and subtracting 12582912 leaves float(D) with no rounding anywhere.
+__device__ __forceinline__ uint64_t to_float2(int32_t d0, int32_t d1)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(d0 + 0x4B400000), "r"(d1 + 0x4B400000));
+    return add2(r, pack2(-12582912.f, -12582912.f));
+}
+
+// 32 columns of one k-block into the accumulators: acc = fma(float(D), sA*sB, acc) (src/MatMulBlocks.cs:344-346).
+__device__ __forceinline__ void scale_add(const int32_t (&v)[32], float sa, const float *sb, uint64_t (&acc)[16])
+{
+    const uint64_t sa2 = pack2(sa, sa);
+#pragma unroll
+    for (int c4 = 0; c4 < 8; c4++) {
+        const ulonglong2 s = *(const ulonglong2 *)(sb + 4 * c4);
+        acc[2 * c4] = fma2(pack2((float)v[4 * c4], (float)v[4 * c4 + 1]), mul2(sa2, s.x), acc[2 * c4]);
+        acc[2 * c4 + 1] = fma2(pack2((float)v[4 * c4 + 2], (float)v[4 * c4 + 3]), mul2(sa2, s.y), acc[2 * c4 + 1]);
+    }
+}
+
 template <bool SUMS>
 __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs p)
 {
@@ -157,11 +211,11 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
     if (threadIdx.x == 0) {
         for (int s = 0; s < MM_STAGES; s++) {
             mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 9);          // the MMA thread's commit and the eight epilogue warps
+            mbar_init(empty0 + 8 * s, 1 + EPI_WARPS);      // the MMA thread's commit and the epilogue warps
         }
         for (int s = 0; s < TMEM_STAGES; s++) {
             mbar_init(tfull0 + 8 * s, 1);
-            mbar_init(tempty0 + 8 * s, 8);
+            mbar_init(tempty0 + 8 * s, EPI_WARPS);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -205,6 +259,10 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
         // ---- MMA issue: one thread, one instruction a k-block, each into the next of four accumulators
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_s8(TILE, TILE);
+            // descriptors differ from k-block to k-block only in the start address (16-byte units)
+            const uint64_t desc_hi = smem_desc(0, SLAB / 2, 128);
+            int ts = 0, i = 0;
+            uint32_t tphase = 0;                   // parity of "the previous use of this accumulator has been read"
             bool alive = true;
             for (int it = 0; it < stages_total && alive; it++) {
                 const int s = it % MM_STAGES;
@@ -212,67 +270,79 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                 tc_fence_after();
                 const uint32_t a_smem = smem_u32(ring + (size_t)s * STAGE_BYTES), b_smem = a_smem + KS * SLAB;
                 const int nkb = min(KS, p.kb - it * KS);
-                for (int kk = 0; kk < nkb; kk++) {
-                    const int i = it * KS + kk, ts = i % TMEM_STAGES, use = i / TMEM_STAGES;
-                    if (use > 0 && !mbar_wait(tempty0 + 8 * ts, (uint32_t)(use - 1) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
-                    tc_fence_after();
-                    mma_s8(tmem + (uint32_t)ts * TILE, smem_desc(a_smem + kk * SLAB, SLAB / 2, 128), smem_desc(b_smem + kk * SLAB, SLAB / 2, 128), idesc);
+                for (int kk = 0; kk < nkb; kk++, i++) {
+                    if (i >= TMEM_STAGES) {
+                        if (!mbar_wait(tempty0 + 8 * ts, tphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
+                        tc_fence_after();
+                    }
+                    mma_s8(tmem + (uint32_t)ts * TILE, desc_hi | (uint64_t)(((a_smem + kk * SLAB) & 0x3FFFFu) >> 4),
+                           desc_hi | (uint64_t)(((b_smem + kk * SLAB) & 0x3FFFFu) >> 4), idesc);
                     mma_commit(tfull0 + 8 * ts);
+                    if (p.dbg && i == 0 && blockIdx.x == 0 && blockIdx.y == 0) {        // tuning aid: issue -> completion seen, in cycles
+                        long long t0 = clock64();
+                        while (!mbar_try_wait(tfull0, 0u) && clock64() - t0 < 1000000) { }
+                        p.dbg[3] = clock64() - t0;
+                    }
+                    if (++ts == TMEM_STAGES) { ts = 0; if (i >= TMEM_STAGES) tphase ^= 1u; }
                 }
                 mma_commit(empty0 + 8 * s);      // the stage's codes are free once these products have run
             }
         }
     } else {
-        // ---- epilogue: a warp reads its 32 rows (tensor-memory lanes 32*(warp%4) ..) x 64 columns of each accumulator
-        const int q = warp & 3, ch = (warp - 2) >> 2;
-        const int row = tm * TILE + q * 32 + lane, col0 = tn * TILE + ch * 64;
-        float acc[64];
+        // ---- epilogue: a warp owns 32 rows (tensor-memory lanes 32*(warp%4) ..) x 32 columns of every accumulator;
+        // four warps a scheduler cover each other's tensor-memory reads.
+        const int q = warp & 3, cg = (warp - 2) >> 2;
+        const int row = tm * TILE + q * 32 + lane, col0 = tn * TILE + cg * 32;
+        const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cg * 32);
+        uint64_t acc[16];
 #pragma unroll
-        for (int c = 0; c < 64; c++) acc[c] = 0.f;
+        for (int c = 0; c < 16; c++) acc[c] = 0ull;
         bool alive = true;
-        for (int i = 0; i < p.kb && alive; i++) {
-            const int it = i / KS, kk = i % KS, s = it % MM_STAGES, ts = i % TMEM_STAGES;
-            if (kk == 0 && !mbar_wait_warp(full0 + 8 * s, (uint32_t)(it / MM_STAGES) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
-            if (!mbar_wait_warp(tfull0 + 8 * ts, (uint32_t)(i / TMEM_STAGES) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
+        int s = 0, kk = 0, ts = 0;
+        uint32_t sphase = 0, tphase = 0;
+        long long c_wait = 0, c_ld = 0, c_all = clock64();
+        const bool timing = p.dbg && warp == 2 && blockIdx.x == 0 && blockIdx.y == 0;
+        for (int i = 0; i < p.kb; i++) {
+            long long t0 = timing ? clock64() : 0;
+            if (!mbar_wait_warp(tfull0 + 8 * ts, tphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
             tc_fence_after();
-            int32_t v0[32], v1[32];
-            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ts * TILE + ch * 64);
-            tmem_ld32(taddr, v0);
-            tmem_ld32(taddr + 32, v1);
+            long long t1 = timing ? clock64() : 0;
+            c_wait += t1 - t0;
+            int32_t v[32];
+            if (!(p.probe & 2)) tmem_ld32(tlane + (uint32_t)ts * TILE, v);
+            if (kk == 0 && !mbar_wait_warp(full0 + 8 * s, sphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
+            const float *sa_s = (const float *)(ring + (size_t)s * STAGE_BYTES + 2 * KS * SLAB) + kk * TILE;
+            const float sa = sa_s[q * 32 + lane];
             tmem_ld_wait();
+            if (timing) c_ld += clock64() - t1;
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty0 + 8 * ts);        // the accumulator may be overwritten
-            const float *sa_s = (const float *)(ring + (size_t)s * STAGE_BYTES + 2 * KS * SLAB) + kk * TILE;
-            const float *sb_s = sa_s + KS * TILE + ch * 64;
-            const float sa = sa_s[q * 32 + lane];
-#pragma unroll
-            for (int c4 = 0; c4 < 16; c4++) {
-                const float4 sb = *(const float4 *)(sb_s + 4 * c4);
-                const int32_t *v = c4 < 8 ? v0 + 4 * c4 : v1 + 4 * (c4 - 8);
-                acc[4 * c4 + 0] = __fmaf_rn((float)v[0], __fmul_rn(sa, sb.x), acc[4 * c4 + 0]);
-                acc[4 * c4 + 1] = __fmaf_rn((float)v[1], __fmul_rn(sa, sb.y), acc[4 * c4 + 1]);
-                acc[4 * c4 + 2] = __fmaf_rn((float)v[2], __fmul_rn(sa, sb.z), acc[4 * c4 + 2]);
-                acc[4 * c4 + 3] = __fmaf_rn((float)v[3], __fmul_rn(sa, sb.w), acc[4 * c4 + 3]);
-            }
+            if (lane == 0) mbar_arrive(tempty0 + 8 * ts);        // this accumulator may be overwritten
+            if (!(p.probe & 1)) scale_add(v, sa, sa_s + KS * TILE + cg * 32, acc);
             if (SUMS && row < p.m) {
 #pragma unroll
-                for (int c = 0; c < 64; c++)
-                    if (col0 + c < p.n) p.sums[((size_t)row * p.n + col0 + c) * p.kb + i] = c < 32 ? v0[c] : v1[c - 32];
+                for (int c = 0; c < 32; c++)
+                    if (col0 + c < p.n) p.sums[((size_t)row * p.n + col0 + c) * p.kb + i] = v[c];
             }
             if (kk == KS - 1 || i == p.kb - 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * s);      // this warp has read the stage's scales
             }
+            if (++ts == TMEM_STAGES) { ts = 0; tphase ^= 1u; }
+            if (++kk == KS) { kk = 0; if (++s == MM_STAGES) { s = 0; sphase ^= 1u; } }
         }
+        if (timing && lane == 0) { p.dbg[4] = clock64() - c_all; p.dbg[5] = c_wait; p.dbg[6] = c_ld; }
         if (alive && row < p.m) {
             float *out = p.c + (size_t)row * p.n + col0;
-            if ((p.n & 3) == 0 && col0 + 64 <= p.n && ((uintptr_t)p.c & 15) == 0) {
+            float f[32];
 #pragma unroll
-                for (int c4 = 0; c4 < 16; c4++) *(float4 *)(out + 4 * c4) = make_float4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
+            for (int c = 0; c < 16; c++) unpack2(acc[c], f[2 * c], f[2 * c + 1]);
+            if ((p.n & 3) == 0 && col0 + 32 <= p.n && ((uintptr_t)p.c & 15) == 0) {
+#pragma unroll
+                for (int c4 = 0; c4 < 8; c4++) *(float4 *)(out + 4 * c4) = make_float4(f[4 * c4], f[4 * c4 + 1], f[4 * c4 + 2], f[4 * c4 + 3]);
             } else {
 #pragma unroll
-                for (int c = 0; c < 64; c++) if (col0 + c < p.n) out[c] = acc[c];
+                for (int c = 0; c < 32; c++) if (col0 + c < p.n) out[c] = f[c];
             }
         }
     }
@@ -284,6 +354,10 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
 // ---------------------------------------------------------------------------------- host side
 
 static int *g_mm_status = nullptr;
+static int g_mm_probe = 0;
+static long long *g_mm_dbg = nullptr;
+void matmul_set_dbg(long long *p) { g_mm_dbg = p; }
+void matmul_set_probe(int mode) { g_mm_probe = mode; }
 
 cudaError_t matmul_init(int, int max_smem, int *status)
 {
@@ -329,7 +403,7 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, float *c, 
     args.a.codes = a_codes; args.a.scales = a_scales;
     args.b.codes = b_codes; args.b.scales = b_scales;
     args.c = c; args.sums = sums; args.status = g_mm_status;
-    args.m = m; args.n = n; args.kb = k / 32;
+    args.m = m; args.n = n; args.kb = k / 32; args.probe = g_mm_probe; args.dbg = g_mm_dbg;
     const dim3 grid((n + TILE - 1) / TILE, (m + TILE - 1) / TILE);
     if (sums) matmul_kernel<true><<<grid, MM_THREADS, MM_SMEM, stream>>>(args);
     else matmul_kernel<false><<<grid, MM_THREADS, MM_SMEM, stream>>>(args);
