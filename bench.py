@@ -120,6 +120,76 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def sharded_gemv_leg(ops, torch, dist, rank, world, dev):
+    """BASELINE configs[4] at M = 1: Q4_0 28672 x 8192 sharded by output rows over the ranks (strong scaling of one matrix),
+    timed without and with the all-gather of the f32 slices.  Each rank rotates over copies of its shard larger than L2."""
+    from qiyas_b200.shard import ShardPlan, all_gather_rows
+    n, k = 28672, 8192
+    plan = ShardPlan(n, world)
+    rows = plan.count(rank)
+    shard = plan.slice_weights(rank, FMT_A, k, B.make_weights(FMT_A, n, k, 4000))
+    copies = max(2, min(24, int(300e6 // max(1, shard.size)) + 1))
+    ws = [torch.from_numpy(shard).to(dev).clone() for _ in range(copies)]
+    x = torch.from_numpy(B.make_activations(k, 4001)).to(dev)
+    y = torch.empty(max(rows, 1), dtype=torch.float32, device=dev)
+    reps = 5
+
+    def timed(gather):
+        for w in ws[:2]:
+            ops.GemvBlocks(FMT_A, w, x, y, rows, k, fmt_x=FMT_X)
+            if gather:
+                all_gather_rows(plan, rank, y)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for w in ws:
+                ops.GemvBlocks(FMT_A, w, x, y, rows, k, fmt_x=FMT_X)
+                if gather:
+                    all_gather_rows(plan, rank, y)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / (reps * copies)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e-3
+
+    local_s, full_s = timed(False), timed(True)
+    algo = n * (k // 32) * 18 + k * 4 + n * 4
+    return {"workload": f"Q4_0 gemv {n}x{k} sharded by output rows over {world} GPU(s), x f32 replicated", "scaling": "strong",
+            "local_us": local_s * 1e6, "local_GBs": algo / local_s / 1e9,
+            "with_allgather_us": full_s * 1e6, "with_allgather_GBs": algo / full_s / 1e9,
+            "launch": "host-launched (not graph-replayed); max over ranks"}
+
+
+def abt_leg(ops, torch, dev):
+    """BASELINE configs[2]: Q8_0 x Q8_0 A.B^T, M 512, N 11008, K 4096 through qb200_matmul_blocks (repack + tcgen05 product)."""
+    m, n, k = 512, 11008, 4096
+    a = torch.from_numpy(B.make_weights(B.Q8_0, m, k, 5000)).to(dev)
+    b = torch.from_numpy(B.make_weights(B.Q8_0, n, k, 5001)).to(dev)
+    c = torch.empty(m * n, dtype=torch.float32, device=dev)
+    need = ops.workspace_bytes(B.Q8_0, m, n, k)
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    for _ in range(3):
+        ops.MatMulBlocks(B.Q8_0, a, b, c, m, n, k, workspace=ws, workspace_bytes=need)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 20
+    e0.record()
+    for _ in range(reps):
+        ops.MatMulBlocks(B.Q8_0, a, b, c, m, n, k, workspace=ws, workspace_bytes=need)
+    e1.record()
+    torch.cuda.synchronize()
+    s = e0.elapsed_time(e1) * 1e-3 / reps
+    tops = 2.0 * m * n * k / s / 1e12
+    return {"workload": f"Q8_0 x Q8_0 A.B^T M {m} N {n} K {k} (BASELINE configs[2]), operands repacked every call",
+            "us_per_call": s * 1e6, "int8_TOPS": tops,
+            "roofline": {"bound": "tensor", "achieved": tops, "peak": 4500.0, "unit": "TOP/s", "frac": tops / 4500.0,
+                         "peak_kind": "nominal dense int8 (no measured int8 figure exists)"}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -128,6 +198,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the sharded-gemv and A.B^T legs (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -231,6 +302,9 @@ def main():
                "h2d_bytes_per_step": LAYERS * (WEIGHT_BYTES + COLS * 4), "d2h_bytes_per_step": LAYERS * ROWS * 4,
                "steps": e_steps, "ms_per_step": e_s * 1e3 / e_steps}
 
+    sharded = None if args.no_extra else sharded_gemv_leg(ops, torch, dist, rank, world, dev)
+    abt = abt_leg(ops, torch, dev) if (world == 1 and not args.no_extra) else None
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -257,9 +331,13 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": TRAFFIC_BYTES, "peak_kind": f"of {peak_kind}", "kernel": "gemv_kernel<Q4_0>",
                          "launch_us": per_launch_s * 1e6, "algorithmic_bytes_per_launch": ALGO_BYTES},
-            "clocks": clocks, "gpu_launches": launches}
+            "clocks": clocks, "gpu_launches": 2 * launches}      # a call = the kernel that prepares x + the gemv kernel
     if e2e is not None:
         line["e2e"] = e2e
+    if sharded is not None:
+        line["sharded"] = sharded
+    if abt is not None:
+        line["abt"] = abt
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"], _ = cpu_baseline()
     print(json.dumps(line), flush=True)
