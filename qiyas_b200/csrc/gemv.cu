@@ -24,7 +24,9 @@ namespace qb {
 
 struct GemvArgs {
     const uint8_t *a;
-    const uint8_t *xprep; // x as prepare_x_kernel lays it out
+    const uint8_t *xprep; // x as prepare_x_kernel lays it out (used when x is null)
+    const void *x;        // x as the caller gave it: prepared inside the kernel, in shared memory at off_x
+    int fmt_x;
     float *y;
     int32_t *sums;
     int *status;         // device word for STATUS_* bits
@@ -36,15 +38,18 @@ struct GemvArgs {
     int cs, rg;          // column segments x row groups = nw
     int stage_rows;      // rows per unit = rg * RW
     int units;           // ceil(rows / stage_rows)
+    int chunks;          // ceil(rows / RW)
     int slots;           // ring depth in chunks (a chunk = the RW rows of one row group), at least rg
+    int independent;     // 1: nothing this call reads or writes is touched by the launch before it, so no wait on that launch
+    int prefetch;        // chunks a block requests before x has been asked for (the rest wait, so x's reads meet idle queues)
     int flush_units;     // units whose partial sums fit the partials area before they are added up
     uint32_t slot_stride;
     uint32_t row_flip;   // 1 when a row is 2 (mod 4) bytes long: rows alternate between the two 4-byte alignments
-    uint32_t off_part, off_ring;   // shared-memory offsets
+    uint32_t off_x, off_part, off_ring;   // shared-memory offsets
 };
 
 constexpr int MAX_SLOTS = 60;
-constexpr uint32_t SMEM_HEADER = 1024;  // full[60] and empty[60] barriers and the abort word
+constexpr uint32_t SMEM_HEADER = 1024;  // full[60] and empty[60] barriers, the x barrier and the abort word
 
 __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c)
 {
@@ -146,12 +151,14 @@ __host__ __device__ inline uint32_t xprep_codes_bytes(int cols) { return ((uint3
 __host__ __device__ inline uint32_t xprep_bytes(int cols) { return xprep_codes_bytes(cols) + ((uint32_t)(cols / 32 + 2) * 8u + 255u) / 256u * 256u; }
 
 template <bool PAIRED>
-__global__ void __launch_bounds__(128) prepare_x_kernel(const void *x, int fmt_x, int cols, uint8_t *out)
+__global__ void __launch_bounds__(128) prepare_x_kernel(const void *x, int fmt_x, int cols, uint8_t *out, int independent)
 {
     // the gemv that follows may start now: it waits for this grid's end only where it first reads `out`
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // x may be the output of the kernel before this one, and `out` may still be read by the gemv before it
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // x may be the output of the kernel before this one: wait for it, unless the host has established that it is not.
+    // (`out` is free in either case: the gemv before this one lets its dependents start only once all its threads
+    // have x in registers.)
+    if (!independent) asm volatile("griddepcontrol.wait;" ::: "memory");
     const int blocks = cols / 32, b = blockIdx.x * blockDim.x + threadIdx.x;
     uint8_t *meta = out + xprep_codes_bytes(cols);
     if (b >= blocks) {
@@ -179,6 +186,102 @@ __global__ void __launch_bounds__(128) prepare_x_kernel(const void *x, int fmt_x
         xq[b * 2 + 1] = make_uint4(w[4], w[5], w[6], w[7]);
         ((uint2 *)meta)[b] = make_uint2(__float_as_uint(d), (uint32_t)sum);
     }
+}
+
+// The same preparation inside the gemv kernel, by all its consumer threads, into shared memory.  f32 x: four threads a
+// block of 32 values (eight values each, coalesced 32-byte reads); the block's max and sum meet by two shuffles.
+// The arithmetic is quantize32's, value for value.
+template <bool PAIRED>
+__device__ __forceinline__ void prepare_x_in_block(const void *x, int fmt_x, int cols, uint8_t *out, int tid, int threads, uint32_t xbar)
+{
+    const int blocks = cols / 32;
+    uint8_t *meta = out + xprep_codes_bytes(cols);
+    bool told = false;
+    if (fmt_x == QB200_F32 && ((uintptr_t)x & 15) == 0) {
+        const int items = blocks * 4;
+        // two items a thread and pass: both reads are issued before either is used
+        for (int base = 0; base < items; base += 2 * threads) {
+            float v[2][8];
+            bool valid[2];
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int it = base + u * threads + tid;
+                valid[u] = it < items;
+                float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+                if (valid[u]) {
+                    lo = __ldg((const float4 *)x + (size_t)it * 2);
+                    hi = __ldg((const float4 *)x + (size_t)it * 2 + 1);
+                }
+                v[u][0] = lo.x; v[u][1] = lo.y; v[u][2] = lo.z; v[u][3] = lo.w; v[u][4] = hi.x; v[u][5] = hi.y; v[u][6] = hi.z; v[u][7] = hi.w;
+            }
+            if (!told) {            // x's first reads are on their way: the producer may ask for the rest of the matrix
+                told = true;
+                if ((tid & 31) == 0) mbar_arrive(xbar);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int it = base + u * threads + tid, b = it >> 2, part = it & 3;
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[u][i]));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                const float d = __half2float(__float2half_rn(__fdiv_rn(amax, 127.f)));
+                const float id = d == 0.f ? 0.f : __fdiv_rn(1.f, d);
+                uint32_t w0 = 0, w1 = 0;
+                int sum = 0;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int q0 = max(-127, min(127, __float2int_rn(__fmul_rn(v[u][j], id))));
+                    const int q1 = max(-127, min(127, __float2int_rn(__fmul_rn(v[u][4 + j], id))));
+                    sum += q0 + q1;
+                    w0 |= (uint32_t)(q0 & 255) << (8 * j);
+                    w1 |= (uint32_t)(q1 & 255) << (8 * j);
+                }
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                if (!valid[u]) continue;
+                if (PAIRED) {
+                    const int run = b >> 6, lane = (b & 63) >> 1, half = b & 1;
+                    *(uint2 *)(out + ((size_t)((run * 4 + half * 2 + (part >> 1)) * 32 + lane)) * 16 + (part & 1) * 8) = make_uint2(w0, w1);
+                    if (part == 0) {
+                        uint32_t *m = (uint32_t *)meta + (size_t)(b >> 1) * 4;
+                        m[half] = __float_as_uint(d);
+                        m[2 + half] = (uint32_t)sum;
+                    }
+                } else {
+                    *(uint2 *)(out + (size_t)b * 32 + part * 8) = make_uint2(w0, w1);
+                    if (part == 0) ((uint2 *)meta)[b] = make_uint2(__float_as_uint(d), (uint32_t)sum);
+                }
+            }
+        }
+    } else {
+        for (int b = tid; b < blocks; b += threads) {
+            uint32_t w[8];
+            float d;
+            int sum;
+            load_x_block(x, fmt_x, b, w, d, sum);
+            uint4 *xq = (uint4 *)out;
+            if (PAIRED) {
+                const int run = b >> 6, lane = (b & 63) >> 1, half = b & 1;
+                xq[(run * 4 + half * 2) * 32 + lane] = make_uint4(w[0], w[1], w[2], w[3]);
+                xq[(run * 4 + half * 2 + 1) * 32 + lane] = make_uint4(w[4], w[5], w[6], w[7]);
+                uint32_t *m = (uint32_t *)meta + (size_t)(b >> 1) * 4;
+                m[half] = __float_as_uint(d);
+                m[2 + half] = (uint32_t)sum;
+            } else {
+                xq[b * 2] = make_uint4(w[0], w[1], w[2], w[3]);
+                xq[b * 2 + 1] = make_uint4(w[4], w[5], w[6], w[7]);
+                ((uint2 *)meta)[b] = make_uint2(__float_as_uint(d), (uint32_t)sum);
+            }
+        }
+    }
+    if (PAIRED && (blocks & 1) && tid == 0) {
+        uint32_t *m = (uint32_t *)meta + (size_t)(blocks >> 1) * 4;
+        m[1] = 0;
+        m[3] = 0;
+    }
+    if (!told && (tid & 31) == 0) mbar_arrive(xbar);
 }
 
 // ---------------------------------------------------------------------------------- raw blocks out of shared memory
@@ -247,7 +350,7 @@ struct XPair {
     int first;               // index of block 2l of this run
 };
 
-__device__ __forceinline__ void load_x(XPair &x, const GemvArgs &p, int run, int lane)
+__device__ __forceinline__ void load_x(XPair &x, const GemvArgs &p, const uint8_t *xp, int run, int lane)
 {
     const int blocks = p.cols / 32;
     x.first = run * 64 + lane * 2;
@@ -257,10 +360,10 @@ __device__ __forceinline__ void load_x(XPair &x, const GemvArgs &p, int run, int
 #pragma unroll
     for (int i = 0; i < 8; i++) x.a[i] = x.b[i] = 0;
     if (x.count == 0) return;
-    const uint4 *xq = (const uint4 *)p.xprep;
+    const uint4 *xq = (const uint4 *)xp;
     const uint4 x0 = xq[(run * 4 + 0) * 32 + lane], x1 = xq[(run * 4 + 1) * 32 + lane];
     const uint4 x2 = xq[(run * 4 + 2) * 32 + lane], x3 = xq[(run * 4 + 3) * 32 + lane];
-    const uint4 meta = ((const uint4 *)(p.xprep + xprep_codes_bytes(p.cols)))[x.first >> 1];
+    const uint4 meta = ((const uint4 *)(xp + xprep_codes_bytes(p.cols)))[x.first >> 1];
     x.a[0] = x0.x; x.a[1] = x0.y; x.a[2] = x0.z; x.a[3] = x0.w; x.a[4] = x1.x; x.a[5] = x1.y; x.a[6] = x1.z; x.a[7] = x1.w;
     x.b[0] = x2.x; x.b[1] = x2.y; x.b[2] = x2.z; x.b[3] = x2.w; x.b[4] = x3.x; x.b[5] = x3.y; x.b[6] = x3.z; x.b[7] = x3.w;
     x.d0 = __uint_as_float(meta.x); x.d1 = __uint_as_float(meta.y);
@@ -276,15 +379,15 @@ struct XK4 {
     bool valid;
 };
 
-__device__ __forceinline__ void load_x(XK4 &x, const GemvArgs &p, int run, int lane)
+__device__ __forceinline__ void load_x(XK4 &x, const GemvArgs &p, const uint8_t *xp, int run, int lane)
 {
     const int sb = run * 4 + (lane >> 3), part = lane & 7;
     x.valid = sb < p.cols / 256;
     x.xb = sb * 8 + (part >> 1) * 2;
     if (!x.valid) return;
-    const uint8_t *xq = p.xprep + (size_t)x.xb * 32 + (part & 1) * 16;
+    const uint8_t *xq = xp + (size_t)x.xb * 32 + (part & 1) * 16;
     const uint4 l = *(const uint4 *)xq, h = *(const uint4 *)(xq + 32);
-    const uint2 *meta = (const uint2 *)(p.xprep + xprep_codes_bytes(p.cols));
+    const uint2 *meta = (const uint2 *)(xp + xprep_codes_bytes(p.cols));
     const uint2 ma = meta[x.xb], mb = meta[x.xb + 1];
     x.lo[0] = l.x; x.lo[1] = l.y; x.lo[2] = l.z; x.lo[3] = l.w;
     x.hi[0] = h.x; x.hi[1] = h.y; x.hi[2] = h.z; x.hi[3] = h.w;
@@ -301,16 +404,16 @@ struct XK6 {
     bool valid;
 };
 
-__device__ __forceinline__ void load_x(XK6 &x, const GemvArgs &p, int run, int lane)
+__device__ __forceinline__ void load_x(XK6 &x, const GemvArgs &p, const uint8_t *xp, int run, int lane)
 {
     x.sb = run * 2 + (lane >> 4);
     x.valid = x.sb < p.cols / 256;
     if (!x.valid) return;
     const int half = (lane >> 3) & 1, t = lane & 7;
-    const uint2 *meta = (const uint2 *)(p.xprep + xprep_codes_bytes(p.cols));
+    const uint2 *meta = (const uint2 *)(xp + xprep_codes_bytes(p.cols));
 #pragma unroll
     for (int g = 0; g < 4; g++) {
-        x.w[g] = *(const uint32_t *)(p.xprep + (size_t)x.sb * 256 + half * 128 + g * 32 + t * 4);
+        x.w[g] = *(const uint32_t *)(xp + (size_t)x.sb * 256 + half * 128 + g * 32 + t * 4);
         x.d[g] = __uint_as_float(meta[x.sb * 8 + half * 4 + g].x);
         x.ones[g] = dp4a_s8s8(x.w[g], 0x01010101u, 0);
     }
@@ -498,18 +601,20 @@ __device__ __forceinline__ float row_dot(const XK6 &x, const uint8_t *row, int l
 // ---------------------------------------------------------------------------------- the kernel
 
 // The ring holds `slots` chunks; a chunk is RW consecutive rows, fetched by one bulk copy with its own pair of barriers
-// and consumed by the cs warps of one row group.  A unit is rg consecutive chunks (one a row group); block b takes units
-// b, b + grid, ...  RUNS = runs of x a warp holds (its column segment: runs seg, seg + cs, ...).
+// and consumed by the cs warps of one row group.  Block b takes the contiguous chunks [b*C/grid, (b+1)*C/grid) of the
+// C chunks of the matrix (so blocks differ by at most one chunk); its j-th chunk goes to row group j % rg, and the rg
+// chunks dealt in one round are a unit.  RUNS = runs of x a warp holds (its column segment: runs seg, seg + cs, ...).
 template <int FMT, int RW, int RUNS, bool SUMS>
 __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = (uint64_t *)smem;
-    volatile int *abort_flag = (volatile int *)(smem + 2 * MAX_SLOTS * 8);
+    volatile int *abort_flag = (volatile int *)(smem + 2 * MAX_SLOTS * 8 + 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t full0 = smem_u32(bars), empty0 = full0 + MAX_SLOTS * 8;
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + MAX_SLOTS * 8, xbar = empty0 + MAX_SLOTS * 8;
 
     if (threadIdx.x == 0) {
+        mbar_init(xbar, p.nw);
         for (int s = 0; s < p.slots; s++) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, p.cs);
@@ -523,52 +628,60 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
         if (p.timeline && lane == 0 && warp == 0) {
             long long t;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-            p.timeline[(size_t)blockIdx.x * 8 + slot] = t;
+            p.timeline[(size_t)blockIdx.x * 32 + slot] = t;
         }
     };
     stamp(0);
     uint8_t *ring = smem + p.off_ring;
-    const int my_units = p.units > (int)blockIdx.x ? (p.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int chunk0 = (int)((long long)p.chunks * blockIdx.x / gridDim.x), chunk1 = (int)((long long)p.chunks * (blockIdx.x + 1) / gridDim.x);
+    const int my_units = (chunk1 - chunk0 + p.rg - 1) / p.rg;
 
     if (warp == p.nw) {
         // ---- producer: one untiled bulk copy a chunk, plus the bytes outside its 16-byte aligned middle.  The weights
         // are read-only for the whole call, so the copies start before the kernel that prepares x has ended.
+        // Every lane issues its own chunk's copy (a lone thread needs some hundreds of cycles a copy for the address
+        // arithmetic and the barrier calls, which would pace the whole kernel): a pass of the warp issues `step`
+        // consecutive chunks, never more than there are slots, so no lane of a pass waits on another lane of it.
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-        int issued = 0, s = 0;
-        uint32_t phase = 0;
+        const int total = my_units * p.rg, step = min(32, p.slots);
+        int issued = 0;
         bool alive = true;
-        for (int i = 0; i < my_units && alive; i++) {
-            const int unit_row = (blockIdx.x + i * gridDim.x) * p.stage_rows;
-            for (int g = 0; g < p.rg; g++) {
-                if (issued >= p.slots && !mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag, p.status, STATUS_GEMV_WAIT)) { alive = false; break; }
-                const int row0 = unit_row + g * RW, nrows = max(0, min(RW, p.rows - row0));
-                const uint8_t *g0 = p.a + (size_t)row0 * p.row_bytes, *g1 = g0 + (size_t)nrows * p.row_bytes;
-                const uint32_t mis = (uint32_t)(uintptr_t)g0 & 15u;
-                const uint8_t *b0 = (const uint8_t *)(((uintptr_t)g0 + 15) & ~(uintptr_t)15);
-                const uint8_t *b1 = (const uint8_t *)((uintptr_t)g1 & ~(uintptr_t)15);
-                uint8_t *slot = ring + (size_t)s * p.slot_stride + mis;      // g0's byte lands here
-                const uint8_t *head_end = g1, *tail_begin = g1;
-                if (b1 > b0 && p.probe != 2) {
-                    if (lane == 0) {
+        bool gated = p.prefetch < total;
+        for (int base = 0; base < total && alive; base += step) {
+            const int k = base + lane;                       // this lane's chunk, counted within the block
+            bool ok = true;
+            if (gated && base + step > p.prefetch) {
+                // the rest of the matrix is asked for only once the consumers have asked for x
+                ok = mbar_wait_warp(xbar, 0u, abort_flag, p.status, STATUS_GEMV_WAIT);
+                gated = false;
+            }
+            if (ok && lane < step && k < total) {
+                const int s = k % p.slots;
+                const uint32_t phase = (uint32_t)(k / p.slots) & 1u;
+                if (k >= p.slots) ok = mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag, p.status, STATUS_GEMV_WAIT);
+                if (ok) {
+                    const int chunk = chunk0 + k;
+                    const int row0 = chunk * RW, nrows = chunk < chunk1 ? max(0, min(RW, p.rows - row0)) : 0;
+                    const uint8_t *g0 = p.a + (size_t)row0 * p.row_bytes, *g1 = g0 + (size_t)nrows * p.row_bytes;
+                    const uint32_t mis = (uint32_t)(uintptr_t)g0 & 15u;
+                    const uint8_t *b0 = (const uint8_t *)(((uintptr_t)g0 + 15) & ~(uintptr_t)15);
+                    const uint8_t *b1 = (const uint8_t *)((uintptr_t)g1 & ~(uintptr_t)15);
+                    uint8_t *slot = ring + (size_t)s * p.slot_stride + mis;      // g0's byte lands here
+                    const uint8_t *head_end = g1, *tail_begin = g1;
+                    if (b1 > b0 && !(p.probe & 2)) {
                         mbar_expect_tx(full0 + 8 * s, (uint32_t)(b1 - b0));
                         bulk_g2s(smem_u32(slot + (b0 - g0)), b0, (uint32_t)(b1 - b0), full0 + 8 * s);
+                        head_end = b0;
+                        tail_begin = b1;
                     }
-                    head_end = b0;
-                    tail_begin = b1;
+                    // at most 15 halfwords on either side (none when the chunk starts and ends on 16 bytes)
+                    for (const uint8_t *src = g0; src < head_end; src += 2) *(uint16_t *)(slot + (src - g0)) = __ldg((const uint16_t *)src);
+                    for (const uint8_t *src = tail_begin; src < g1; src += 2) *(uint16_t *)(slot + (src - g0)) = __ldg((const uint16_t *)src);
+                    mbar_arrive(full0 + 8 * s);
                 }
-                // at most 15 halfwords on either side
-                if (lane < 16) {
-                    const uint8_t *src = g0 + 2 * lane;
-                    if (src < head_end) *(uint16_t *)(slot + 2 * lane) = __ldg((const uint16_t *)src);
-                } else {
-                    const uint8_t *src = tail_begin + 2 * (lane - 16);
-                    if (src < g1) *(uint16_t *)(slot + (src - g0)) = __ldg((const uint16_t *)src);
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full0 + 8 * s);
-                issued++;
-                if (++s == p.slots) { s = 0; phase ^= 1u; }
             }
+            alive = __all_sync(0xffffffffu, ok);
+            issued = min(total, base + step);
         }
         // after a wait that gave up: let the copies still in flight land before the block exits
         if (*abort_flag && lane == 0) {
@@ -585,36 +698,51 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
     const int threads = p.nw * 32;
     const int seg = warp % p.cs, rgi = warp / p.cs;
     typename XOf<FMT>::type xr[RUNS];
-    asm volatile("griddepcontrol.wait;" ::: "memory");        // the grid that prepared x has ended and its writes are visible
+    // whatever wrote x (or prepared it) has ended and its writes are visible; skipped when the host has established that
+    // the launch before this one (the only one that can still be running) shares no buffer with this call
+    if (!p.independent || !p.x) asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint8_t *xp = p.xprep;
+    stamp(1);
+    if (p.x) {
+        if (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) prepare_x_in_block<true>(p.x, p.fmt_x, p.cols, smem + p.off_x, threadIdx.x, threads, xbar);
+        else prepare_x_in_block<false>(p.x, p.fmt_x, p.cols, smem + p.off_x, threadIdx.x, threads, xbar);
+        stamp(2);
+        named_bar_sync(1, threads);
+        xp = smem + p.off_x;
+    }
 #pragma unroll
-    for (int j = 0; j < RUNS; j++) load_x(xr[j], p, seg + j * p.cs, lane);
+    for (int j = 0; j < RUNS; j++) load_x(xr[j], p, xp, seg + j * p.cs, lane);
+    if (!p.x && lane == 0) mbar_arrive(xbar);
     // x is in registers: the next call's kernels may be scheduled as this grid's blocks retire
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // whether every lane of this warp has both blocks of every run (then whole chunks take the branch-free path)
     bool whole_runs = false;
     if (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) whole_runs = (seg + (RUNS - 1) * p.cs + 1) * 64 <= p.cols / 32;
-    stamp(1);
+    stamp(3);
 
     float *part = (float *)(smem + p.off_part);
     const int blocks32 = p.cols / 32;
     const uint32_t first_off = (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) ? (uint32_t)(seg * 64 + lane * 2) * (uint32_t)block_bytes(FMT) : 0u;
     bool alive = true;
+    long long c_wait = 0, c_dot = 0, c_sum = 0;
     int s = rgi % p.slots, flush_i = 0;
     uint32_t phase = (uint32_t)(rgi / p.slots) & 1u;
     for (int i = 0; i < my_units; i++) {
-        const int row0 = (blockIdx.x + i * gridDim.x) * p.stage_rows + rgi * RW;
-        const int nvalid = max(0, min(RW, p.rows - row0));
+        const int chunk = chunk0 + i * p.rg + rgi;
+        const int row0 = chunk * RW;
+        const int nvalid = chunk < chunk1 ? max(0, min(RW, p.rows - row0)) : 0;
+        long long tq0 = p.timeline ? clock64() : 0;
         if (alive) alive = mbar_wait_warp(full0 + 8 * s, phase, abort_flag, p.status, STATUS_GEMV_WAIT);
-        if (i == 0) stamp(2);
-        if (i == 1) stamp(3);
-        if (i == my_units - 1) stamp(4);
+        long long tq1 = p.timeline ? clock64() : 0;
+        c_wait += tq1 - tq0;
+        if (i == 0) stamp(4);
         if (alive) {
             const uint32_t mis = (uint32_t)(uintptr_t)(p.a + (size_t)row0 * p.row_bytes) & 15u;
             const uint8_t *rows = ring + (size_t)s * p.slot_stride + mis;
             float acc[RW];
 #pragma unroll
             for (int r = 0; r < RW; r++) acc[r] = 0.f;
-            bool done = p.probe == 1;
+            bool done = (p.probe & 1) != 0;
             if constexpr ((FMT == QB200_Q8_0 || FMT == QB200_Q4_0) && !SUMS) {
                 if (!done && whole_runs && nvalid == RW) {
                     const bool q4 = (((uint32_t)(uintptr_t)rows + first_off) & 2u) == 0;
@@ -639,8 +767,11 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
                     }
                 }
             }
+            long long tq2 = p.timeline ? clock64() : 0;
+            c_dot += tq2 - tq1;
 #pragma unroll
             for (int r = 0; r < RW; r++) acc[r] = warp_sum(acc[r]);     // every lane has read its last byte of the slot
+            if (p.timeline) c_sum += clock64() - tq2;
             if (lane == 0) mbar_arrive(empty0 + 8 * s);
             if (p.cs == 1) {
 #pragma unroll
@@ -655,12 +786,17 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
         while (s >= p.slots) { s -= p.slots; phase ^= 1u; }
         // the partial sums of the last flush_units units: segments added in ascending order
         if (p.cs > 1 && (++flush_i == p.flush_units || i + 1 == my_units)) {
+            if (p.timeline && lane == 0 && i + 1 == my_units) {
+                long long t;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+                p.timeline[(size_t)blockIdx.x * 32 + 8 + warp] = t;
+            }
             named_bar_sync(1, threads);
             const int first = i + 1 - flush_i, count = flush_i * p.stage_rows;
             for (int idx = threadIdx.x; idx < count; idx += threads) {
                 const int k = idx / p.stage_rows, lr = idx - k * p.stage_rows;
-                const int row = (blockIdx.x + (first + k) * gridDim.x) * p.stage_rows + lr;
-                if (row < p.rows) {
+                const int ch = chunk0 + (first + k) * p.rg + lr / RW, row = ch * RW + lr % RW;
+                if (ch < chunk1 && row < p.rows) {
                     const float *src = part + (size_t)idx * p.cs;
                     float sum = src[0];
                     for (int c = 1; c < p.cs; c++) sum += src[c];
@@ -672,6 +808,10 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
         }
     }
     stamp(5);
+    if (p.timeline && warp == 0 && lane == 0) {
+        p.timeline[(size_t)blockIdx.x * 32 + 6] = c_wait;
+        p.timeline[(size_t)blockIdx.x * 32 + 7] = (c_dot << 24) | (c_sum & 0xFFFFFF);
+    }
 }
 
 // ---------------------------------------------------------------------------------- host side: shape -> configuration
@@ -694,7 +834,7 @@ static int env_int(const char *name, int fallback)
 }
 
 // tuning overrides, read once when the library binds a device
-static struct { int warps, stage_bytes, rw, cs, stages; } g_tune = { 16, 24576, 0, 0, 0 };
+static struct { int warps, stage_bytes, rw, cs, stages, prekernel, prefetch, always_wait, ctas; } g_tune = { 16, 24576, 0, 0, 0, 0, 0, 0, 1 };
 
 static void read_tuning()
 {
@@ -703,6 +843,10 @@ static void read_tuning()
     g_tune.rw = env_int("QB200_GEMV_RW", 0);
     g_tune.cs = env_int("QB200_GEMV_CS", 0);
     g_tune.stages = env_int("QB200_GEMV_STAGES", 0);
+    g_tune.prekernel = env_int("QB200_GEMV_PREKERNEL", 0);
+    g_tune.prefetch = env_int("QB200_GEMV_PREFETCH", 0);
+    g_tune.always_wait = env_int("QB200_GEMV_ALWAYS_WAIT", 0);
+    g_tune.ctas = env_int("QB200_GEMV_CTAS", 1);
 }
 
 static int cols_per_run(int fmt) { return fmt == QB200_Q4_K ? 1024 : fmt == QB200_Q6_K ? 512 : 2048; }
@@ -716,7 +860,8 @@ static int plan_gemv(int fmt_a, int rows, int cols, GemvPlan &pl)
     const int runs = (cols + cols_per_run(fmt_a) - 1) / cols_per_run(fmt_a);
     int nw = g_tune.warps;
     if (nw != 4 && nw != 8 && nw != 16) nw = 16;
-    const uint32_t budget = (uint32_t)g_max_smem - 1024;
+    const int ctas = g_tune.ctas == 2 ? 2 : 1;                   // blocks meant to share an SM
+    const uint32_t budget = ctas == 2 ? (uint32_t)(g_max_smem + 1024) / 2 - 2048 : (uint32_t)g_max_smem - 1024;
     // column segments: no idle warps first, then as many segments as possible (small units, few registers of x)
     int cs = 0;
     double best = 1e30;
@@ -740,21 +885,29 @@ static int plan_gemv(int fmt_a, int rows, int cols, GemvPlan &pl)
     a.row_bytes = row_bytes;
     a.nw = nw; a.cs = cs; a.rg = rg; a.stage_rows = stage_rows;
     a.units = (rows + stage_rows - 1) / stage_rows;
+    a.chunks = (rows + rw - 1) / rw;
     a.row_flip = (row_bytes & 2u) ? 1u : 0u;
-    a.off_part = SMEM_HEADER;
-    a.off_ring = (a.off_part + PART_BYTES + 127u) / 128u * 128u;
-    a.flush_units = (int)(PART_BYTES / ((uint32_t)stage_rows * cs * 4u));
+    a.off_x = SMEM_HEADER;
+    a.off_part = a.off_x + xprep_bytes(cols);
+    // partial sums: room for every round of a block when that is small, else PART_BYTES with flushes in between
+    const uint32_t round_bytes = (uint32_t)stage_rows * cs * 4u;
+    const int grid_guess = g_sm_count < 1 ? 1 : g_sm_count * ctas;
+    const uint32_t rounds = (uint32_t)(((a.chunks + grid_guess - 1) / grid_guess + rg - 1) / rg) + 1u;
+    const uint32_t part_bytes = rounds * round_bytes < PART_BYTES ? (rounds * round_bytes + 127u) / 128u * 128u : PART_BYTES;
+    a.off_ring = (a.off_part + part_bytes + 127u) / 128u * 128u;
+    a.flush_units = (int)(part_bytes / round_bytes);
     if (a.flush_units < 1) return QB200_E_LIMIT;
     if (a.off_ring + (uint64_t)rg * pl.stage_stride > budget) return QB200_E_LIMIT;
-    pl.grid = a.units < g_sm_count ? a.units : g_sm_count;
+    pl.grid = a.units < g_sm_count * ctas ? a.units : g_sm_count * ctas;
     int slots = (int)((budget - a.off_ring) / pl.stage_stride);
     if (slots > MAX_SLOTS) slots = MAX_SLOTS;
-    const int per_block = (a.units + pl.grid - 1) / pl.grid;
+    const int per_block = ((a.chunks + pl.grid - 1) / pl.grid + rg - 1) / rg;      // rounds of rg chunks a block takes at most
     if (slots > per_block * rg) slots = per_block * rg;
     if (g_tune.stages >= 1 && g_tune.stages * rg < slots) slots = g_tune.stages * rg;
     if (slots < rg) return QB200_E_LIMIT;
     pl.stages = slots;
     a.slots = slots;
+    a.prefetch = g_tune.prefetch > 0 ? g_tune.prefetch : (slots + 1) / 2;
     a.slot_stride = pl.stage_stride;
     pl.smem_bytes = a.off_ring + (uint32_t)slots * pl.stage_stride;
     return 0;
@@ -833,6 +986,18 @@ cudaError_t gemv_init(int sm_count, int max_smem, int *status)
 // Returns 0, a negative QB200_E_* or a positive cudaError_t.  Arguments are already validated.
 size_t gemv_scratch_bytes(int cols) { return xprep_bytes(cols); }
 
+// The buffers of this thread's previous gemv launch.  A gemv is launched as a programmatic dependent, so only the launch
+// directly before it in the stream can still be running when it starts, and only if that launch was one of these
+// kernels (any other kernel, copy or memset completes first).  When this call's x and y are disjoint from everything
+// that launch touched, its kernels need not wait for it.
+struct Touched { const uint8_t *p; size_t n; };
+static thread_local struct { cudaStream_t stream; bool valid; Touched a, x, y; } t_prev = { nullptr, false, {}, {}, {} };
+
+static bool overlap(const Touched &u, const Touched &v)
+{
+    return u.n && v.n && u.p < v.p + v.n && v.p < u.p + u.n;
+}
+
 int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols, void *scratch,
                 cudaStream_t stream)
 {
@@ -857,6 +1022,17 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     }
     pl.args.a = (const uint8_t *)a;
     pl.args.xprep = (const uint8_t *)scratch;
+    pl.args.x = g_tune.prekernel ? nullptr : x;
+    pl.args.fmt_x = fmt_x;
+    {
+        const Touched ta = { (const uint8_t *)a, (size_t)rows * pl.args.row_bytes };
+        const Touched tx = { (const uint8_t *)x, fmt_x == QB200_F32 ? (size_t)cols * 4 : (size_t)(cols / 32) * block_bytes(fmt_x) };
+        const Touched ty = { (const uint8_t *)y, (size_t)rows * 4 };
+        bool independent = !sums && t_prev.valid && t_prev.stream == stream;
+        if (independent) independent = !overlap(tx, t_prev.y) && !overlap(ta, t_prev.y) && !overlap(ty, t_prev.y) && !overlap(ty, t_prev.x) && !overlap(ty, t_prev.a);
+        pl.args.independent = independent && !g_tune.always_wait ? 1 : 0;
+        t_prev.stream = stream; t_prev.valid = !sums; t_prev.a = ta; t_prev.x = tx; t_prev.y = ty;
+    }
     pl.args.y = y;
     pl.args.sums = sums;
     pl.args.status = g_status;
@@ -865,7 +1041,7 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     pl.args.rows = rows;
     pl.args.cols = cols;
     cudaError_t e;
-    {
+    if (g_tune.prekernel) {
         const int blocks = cols / 32, threads = 128, grid = (blocks + 1 + threads - 1) / threads;
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof cfg);
@@ -878,8 +1054,8 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         uint8_t *out = (uint8_t *)scratch;
-        if (fmt_a == QB200_Q8_0 || fmt_a == QB200_Q4_0) e = cudaLaunchKernelEx(&cfg, prepare_x_kernel<true>, x, fmt_x, cols, out);
-        else e = cudaLaunchKernelEx(&cfg, prepare_x_kernel<false>, x, fmt_x, cols, out);
+        if (fmt_a == QB200_Q8_0 || fmt_a == QB200_Q4_0) e = cudaLaunchKernelEx(&cfg, prepare_x_kernel<true>, x, fmt_x, cols, out, pl.args.independent);
+        else e = cudaLaunchKernelEx(&cfg, prepare_x_kernel<false>, x, fmt_x, cols, out, pl.args.independent);
         if (e) return (int)e;
     }
     switch (fmt_a) {
@@ -950,6 +1126,10 @@ int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, floa
     if ((rc = plan_gemv(fmt_a, rows, cols, pl))) return rc;
     pl.args.a = (const uint8_t *)a;
     pl.args.xprep = (const uint8_t *)dev->scratch;
+    pl.args.x = nullptr;
+    pl.args.fmt_x = fmt_x;
+    pl.args.independent = 0;
+    t_prev.valid = false;
     pl.args.y = y;
     pl.args.sums = nullptr;
     pl.args.status = dev->status;
@@ -959,8 +1139,8 @@ int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, floa
     pl.args.cols = cols;
     if ((e = cudaMemsetAsync(dev->status, 0, sizeof(int), stream))) return (int)e;
     const int blocks = cols / 32, threads = 128, grid = (blocks + 1 + threads - 1) / threads;
-    if (fmt_a == QB200_Q8_0 || fmt_a == QB200_Q4_0) prepare_x_kernel<true><<<grid, threads, 0, stream>>>(x, fmt_x, cols, (uint8_t *)dev->scratch);
-    else prepare_x_kernel<false><<<grid, threads, 0, stream>>>(x, fmt_x, cols, (uint8_t *)dev->scratch);
+    if (fmt_a == QB200_Q8_0 || fmt_a == QB200_Q4_0) prepare_x_kernel<true><<<grid, threads, 0, stream>>>(x, fmt_x, cols, (uint8_t *)dev->scratch, 0);
+    else prepare_x_kernel<false><<<grid, threads, 0, stream>>>(x, fmt_x, cols, (uint8_t *)dev->scratch, 0);
     if ((e = cudaGetLastError())) return (int)e;
     switch (fmt_a) {
     case QB200_Q8_0: e = launch_fmt<QB200_Q8_0>(pl, false, stream); break;
@@ -992,7 +1172,7 @@ void gemv_describe(int fmt_a, int rows, int cols, int *out9)
     out9[6] = (int)pl.stage_stride; out9[7] = (int)pl.smem_bytes; out9[8] = pl.runs_per_warp;
 }
 
-// Tuning aid: a device buffer of 8 timestamps a block (or null to stop recording).
+// Tuning aid: a device buffer of 32 timestamps a block (or null to stop recording).
 void gemv_set_timeline(long long *buffer) { g_timeline = buffer; }
 void gemv_set_probe(int mode) { g_probe = mode; }
 
