@@ -33,7 +33,7 @@ LAYERS = 8
 WEIGHT_BYTES = ROWS * (COLS // 32) * 18
 ALGO_BYTES = WEIGHT_BYTES + COLS * 4 + ROWS * 4          # per launch: weights once, x, y
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload's kernel (ncu; profiles/), or None
-TRAFFIC_BYTES = None
+TRAFFIC_BYTES = 37847040 + 256    # profiles/gemv_q4_0_8192x8192.md
 
 
 def measured_peak():
@@ -330,8 +330,8 @@ def main():
                        f"{LAYERS * WEIGHT_BYTES / 1e6:.0f} MB per step", "pct_of_8TBs": 100.0 * value / world / 8000.0},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": TRAFFIC_BYTES, "peak_kind": f"of {peak_kind}", "kernel": "gemv_kernel<Q4_0>",
-                         "launch_us": per_launch_s * 1e6, "algorithmic_bytes_per_launch": ALGO_BYTES},
-            "clocks": clocks, "gpu_launches": 2 * launches}      # a call = the kernel that prepares x + the gemv kernel
+                         "launch_us": per_launch_s * 1e6, "kernels_per_call": 1, "algorithmic_bytes_per_launch": ALGO_BYTES},
+            "clocks": clocks, "gpu_launches": launches}      # one kernel a call: x is encoded inside the gemv kernel
     if e2e is not None:
         line["e2e"] = e2e
     if sharded is not None:
