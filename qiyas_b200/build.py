@@ -23,7 +23,7 @@ def build(force=False, verbose=False):
     if not force and not stale():
         return LIBRARY
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc] + FLAGS + ["-o", LIBRARY] + SOURCES
+    cmd = [nvcc] + FLAGS + os.environ.get("QB200_NVCC_FLAGS", "").split() + ["-o", LIBRARY] + SOURCES
     out = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
     if verbose or out.returncode:
         print(out.stdout + out.stderr)

@@ -72,6 +72,14 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
+// Every lane polls (one warp instruction a poll, no shuffle afterwards); all lanes see the same barrier, so they leave
+// together except in the give-up case, where the abort word makes the stragglers follow within a poll.
+__device__ __forceinline__ bool mbar_wait_lanes(uint32_t bar, uint32_t parity, volatile int *abort, int *status, int status_bit)
+{
+    bool ok = mbar_wait(bar, parity, abort, status, status_bit);
+    return __all_sync(0xffffffffu, ok);
+}
+
 // ---------------------------------------------------------------------------------- bulk copies (TMA, untiled)
 // global -> shared, both addresses 16-byte aligned, bytes a multiple of 16; completion counted on the mbarrier.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)

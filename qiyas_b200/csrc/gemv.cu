@@ -39,7 +39,7 @@ struct GemvArgs {
     int stage_rows;      // rows per unit = rg * RW
     int units;           // ceil(rows / stage_rows)
     int chunks;          // ceil(rows / RW)
-    int slots;           // ring depth in chunks (a chunk = the RW rows of one row group), at least rg
+    int slots;           // ring depth in chunks (a chunk = the RW rows of one row group): a multiple of rg, slots/rg a row group
     int independent;     // 1: nothing this call reads or writes is touched by the launch before it, so no wait on that launch
     int prefetch;        // chunks a block requests before x has been asked for (the rest wait, so x's reads meet idle queues)
     int flush_units;     // units whose partial sums fit the partials area before they are added up
@@ -643,22 +643,21 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
         // arithmetic and the barrier calls, which would pace the whole kernel): a pass of the warp issues `step`
         // consecutive chunks, never more than there are slots, so no lane of a pass waits on another lane of it.
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-        const int total = my_units * p.rg, step = min(32, p.slots);
+        // A slot belongs to one row group for the whole kernel (spg slots a group): the warps that wait on a slot's
+        // barrier are then always the ones that released its previous use, so a phase parity can never be mistaken for the
+        // parity two phases back.
+        const int total = my_units * p.rg, step = min(32, p.slots), spg = p.slots / p.rg;
         int issued = 0;
-        bool alive = true;
-        bool gated = p.prefetch < total;
+        bool alive = true, x_asked = false;
         for (int base = 0; base < total && alive; base += step) {
             const int k = base + lane;                       // this lane's chunk, counted within the block
             bool ok = true;
-            if (gated && base + step > p.prefetch) {
-                // the rest of the matrix is asked for only once the consumers have asked for x
-                ok = mbar_wait_warp(xbar, 0u, abort_flag, p.status, STATUS_GEMV_WAIT);
-                gated = false;
-            }
-            if (ok && lane < step && k < total) {
-                const int s = k % p.slots;
-                const uint32_t phase = (uint32_t)(k / p.slots) & 1u;
-                if (k >= p.slots) ok = mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag, p.status, STATUS_GEMV_WAIT);
+            if (lane < step && k < total) {
+                const int g = k % p.rg, i = k / p.rg, s = g * spg + i % spg;
+                const uint32_t use = (uint32_t)(i / spg);
+                // the matrix beyond the first `prefetch` chunks is asked for only once the consumers have asked for x
+                if (k >= p.prefetch && !x_asked) ok = mbar_wait(xbar, 0u, abort_flag, p.status, STATUS_GEMV_WAIT);
+                if (ok && use > 0) ok = mbar_wait(empty0 + 8 * s, (use - 1u) & 1u, abort_flag, p.status, STATUS_GEMV_WAIT);
                 if (ok) {
                     const int chunk = chunk0 + k;
                     const int row0 = chunk * RW, nrows = chunk < chunk1 ? max(0, min(RW, p.rows - row0)) : 0;
@@ -681,12 +680,14 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
                 }
             }
             alive = __all_sync(0xffffffffu, ok);
+            if (base + step > p.prefetch) x_asked = true;    // every lane beyond the prefetch has seen the x barrier complete
             issued = min(total, base + step);
         }
         // after a wait that gave up: let the copies still in flight land before the block exits
         if (*abort_flag && lane == 0) {
             for (int k = max(0, issued - p.slots); k < issued; k++) {
-                const uint32_t bar = full0 + 8 * (k % p.slots), ph = (uint32_t)(k / p.slots) & 1u;
+                const int g = k % p.rg, i = k / p.rg;
+                const uint32_t bar = full0 + 8 * (g * spg + i % spg), ph = (uint32_t)(i / spg) & 1u;
                 long long start = clock64();
                 while (!mbar_try_wait(bar, ph) && clock64() - start < WAIT_CYCLES) { }
             }
@@ -725,10 +726,11 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
     const uint32_t first_off = (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) ? (uint32_t)(seg * 64 + lane * 2) * (uint32_t)block_bytes(FMT) : 0u;
     bool alive = true;
     long long c_wait = 0, c_dot = 0, c_sum = 0;
-    int s = rgi % p.slots, flush_i = 0;
-    uint32_t phase = (uint32_t)(rgi / p.slots) & 1u;
+    const int spg = p.slots / p.rg;                  // this row group's own slots: rgi*spg .. rgi*spg + spg - 1
+    int sl = 0, flush_i = 0;
+    uint32_t phase = 0;
     for (int i = 0; i < my_units; i++) {
-        const int chunk = chunk0 + i * p.rg + rgi;
+        const int chunk = chunk0 + i * p.rg + rgi, s = rgi * spg + sl;
         const int row0 = chunk * RW;
         const int nvalid = chunk < chunk1 ? max(0, min(RW, p.rows - row0)) : 0;
         long long tq0 = p.timeline ? clock64() : 0;
@@ -782,8 +784,7 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
                 for (int r = 0; r < RW; r++) mine[r * p.cs] = acc[r];
             }
         }
-        s += p.rg;
-        while (s >= p.slots) { s -= p.slots; phase ^= 1u; }
+        if (++sl == spg) { sl = 0; phase ^= 1u; }
         // the partial sums of the last flush_units units: segments added in ascending order
         if (p.cs > 1 && (++flush_i == p.flush_units || i + 1 == my_units)) {
             if (p.timeline && lane == 0 && i + 1 == my_units) {
@@ -904,6 +905,7 @@ static int plan_gemv(int fmt_a, int rows, int cols, GemvPlan &pl)
     const int per_block = ((a.chunks + pl.grid - 1) / pl.grid + rg - 1) / rg;      // rounds of rg chunks a block takes at most
     if (slots > per_block * rg) slots = per_block * rg;
     if (g_tune.stages >= 1 && g_tune.stages * rg < slots) slots = g_tune.stages * rg;
+    slots = slots / rg * rg;                     // every row group owns the same number of slots
     if (slots < rg) return QB200_E_LIMIT;
     pl.stages = slots;
     a.slots = slots;

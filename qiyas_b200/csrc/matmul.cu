@@ -20,6 +20,10 @@
 
 namespace qb {
 
+#ifndef QB_MM_WAIT
+#define QB_MM_WAIT mbar_wait_lanes
+#endif
+
 constexpr int TILE = 128;            // rows of A and of B per block tile
 constexpr int KS = 4;                // k-blocks per shared-memory stage
 constexpr int MM_STAGES = 5;
@@ -48,40 +52,50 @@ struct MatmulArgs {
 
 // ---------------------------------------------------------------------------------- step 1: operands for the tensor cores
 
-// A thread a block: rows of the raw operand are `kb` blocks long; row r of tile t lands at byte
+// A block of 256 threads re-lays 32 rows x 8 k-blocks.  The rows' bytes (8 consecutive blocks of a row are contiguous
+// in the raw operand, 2-byte aligned) are first copied to shared memory with coalesced 2-byte loads; then a thread a
+// block assembles its 32 int8 values and its scale.  Row r of tile t lands at byte
 // (t*kb + b)*4096 + j*2048 + (r/8)*128 + (r%8)*16 for its bytes 16j..16j+15, and its scale at ((t*kb + b)*128 + r).
 // Rows past `rows` (the padding of the last tile) are written as zeros.
 template <int FMT>
 __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int rows, int kb, uint8_t *codes, float *scales)
 {
-    constexpr int BB = block_bytes(FMT);
-    const int r = blockIdx.x * 32 + (threadIdx.x & 31), b = blockIdx.y * 8 + (threadIdx.x >> 5);
+    constexpr int BB = block_bytes(FMT), HALVES = 8 * BB / 2, PITCH = HALVES + 1;      // halfwords a row segment; odd pitch
+    __shared__ uint16_t seg[32 * PITCH];
+    const int r0 = blockIdx.x * 32, b0 = blockIdx.y * 8;
+    const int nb = min(8, kb - b0), halves = nb * BB / 2;
+    for (int idx = threadIdx.x; idx < 32 * HALVES; idx += 256) {
+        const int rr = idx / HALVES, h = idx - rr * HALVES;
+        uint16_t v = 0;
+        if (r0 + rr < rows && h < halves) v = __ldg((const uint16_t *)(raw + ((size_t)(r0 + rr) * kb + b0) * BB) + h);
+        seg[rr * PITCH + h] = v;
+    }
+    __syncthreads();
+    const int rl = threadIdx.x & 31, bl = threadIdx.x >> 5, r = r0 + rl, b = b0 + bl;
     if (b >= kb) return;
-    uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
-    float d = 0.f;
-    if (r < rows) {
-        const uint16_t *p = (const uint16_t *)(raw + ((size_t)r * kb + b) * BB);
-        d = half_bits_to_float(__ldg(p));
-        uint32_t w[8];
-        if (FMT == QB200_Q8_0) {
+    const uint16_t *p = seg + rl * PITCH + bl * (BB / 2);
+    const float d = half_bits_to_float(p[0]);           // zero rows read as scale 0, codes 0 (Q4_0: see below)
+    uint32_t w[8];
+    if (FMT == QB200_Q8_0) {
 #pragma unroll
-            for (int i = 0; i < 8; i++) w[i] = (uint32_t)__ldg(p + 1 + 2 * i) | (uint32_t)__ldg(p + 2 + 2 * i) << 16;
-        } else {
-            // value i in the low nibble of byte i, value i + 16 in the high nibble, each minus 8 (src/MatMulBlocks.cs:282-299)
+        for (int i = 0; i < 8; i++) w[i] = (uint32_t)p[1 + 2 * i] | (uint32_t)p[2 + 2 * i] << 16;
+    } else {
+        // value i in the low nibble of byte i, value i + 16 in the high nibble, each minus 8 (src/MatMulBlocks.cs:282-299)
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint32_t n = (uint32_t)__ldg(p + 1 + 2 * i) | (uint32_t)__ldg(p + 2 + 2 * i) << 16;
-                w[i] = __vsub4(n & 0x0F0F0F0Fu, 0x08080808u);
-                w[i + 4] = __vsub4((n >> 4) & 0x0F0F0F0Fu, 0x08080808u);
-            }
+        for (int i = 0; i < 4; i++) {
+            const uint32_t n = (uint32_t)p[1 + 2 * i] | (uint32_t)p[2 + 2 * i] << 16;
+            w[i] = __vsub4(n & 0x0F0F0F0Fu, 0x08080808u);
+            w[i + 4] = __vsub4((n >> 4) & 0x0F0F0F0Fu, 0x08080808u);
         }
-        lo = make_uint4(w[0], w[1], w[2], w[3]);
-        hi = make_uint4(w[4], w[5], w[6], w[7]);
+        if (r >= rows) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) w[i] = 0;
+        }
     }
     const int t = r / TILE, rr = r % TILE;
     uint8_t *slab = codes + ((size_t)t * kb + b) * SLAB + (rr >> 3) * 128 + (rr & 7) * 16;
-    *(uint4 *)slab = lo;
-    *(uint4 *)(slab + SLAB / 2) = hi;
+    *(uint4 *)slab = make_uint4(w[0], w[1], w[2], w[3]);
+    *(uint4 *)(slab + SLAB / 2) = make_uint4(w[4], w[5], w[6], w[7]);
     scales[((size_t)t * kb + b) * TILE + rr] = d;
 }
 
@@ -188,6 +202,22 @@ __device__ __forceinline__ uint64_t to_float2(int32_t d0, int32_t d1)
 // 32 columns of one k-block into the accumulators: acc = fma(float(D), sA*sB, acc) (src/MatMulBlocks.cs:344-346).
 __device__ __forceinline__ void scale_add(const int32_t (&v)[32], float sa, const float *sb, uint64_t (&acc)[16])
 {
+#ifdef QB_MM_SCALAR
+#pragma unroll
+    for (int c4 = 0; c4 < 8; c4++) {
+        const float4 s = *(const float4 *)(sb + 4 * c4);
+        float a0, a1, a2, a3;
+        unpack2(acc[2 * c4], a0, a1);
+        unpack2(acc[2 * c4 + 1], a2, a3);
+        a0 = __fmaf_rn((float)v[4 * c4], __fmul_rn(sa, s.x), a0);
+        a1 = __fmaf_rn((float)v[4 * c4 + 1], __fmul_rn(sa, s.y), a1);
+        a2 = __fmaf_rn((float)v[4 * c4 + 2], __fmul_rn(sa, s.z), a2);
+        a3 = __fmaf_rn((float)v[4 * c4 + 3], __fmul_rn(sa, s.w), a3);
+        acc[2 * c4] = pack2(a0, a1);
+        acc[2 * c4 + 1] = pack2(a2, a3);
+    }
+    return;
+#endif
     const uint64_t sa2 = pack2(sa, sa);
 #pragma unroll
     for (int c4 = 0; c4 < 8; c4++) {
@@ -300,24 +330,17 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
         bool alive = true;
         int s = 0, kk = 0, ts = 0;
         uint32_t sphase = 0, tphase = 0;
-        long long c_wait = 0, c_ld = 0, c_all = clock64();
-        const bool timing = p.dbg && warp == 2 && blockIdx.x == 0 && blockIdx.y == 0;
         for (int i = 0; i < p.kb; i++) {
-            long long t0 = timing ? clock64() : 0;
-            if (!mbar_wait_warp(tfull0 + 8 * ts, tphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
+            if (!QB_MM_WAIT(tfull0 + 8 * ts, tphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
             tc_fence_after();
-            long long t1 = timing ? clock64() : 0;
-            c_wait += t1 - t0;
             int32_t v[32];
             if (!(p.probe & 2)) tmem_ld32(tlane + (uint32_t)ts * TILE, v);
-            if (kk == 0 && !mbar_wait_warp(full0 + 8 * s, sphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
+            if (kk == 0 && !QB_MM_WAIT(full0 + 8 * s, sphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
             const float *sa_s = (const float *)(ring + (size_t)s * STAGE_BYTES + 2 * KS * SLAB) + kk * TILE;
             const float sa = sa_s[q * 32 + lane];
             tmem_ld_wait();
-            if (timing) c_ld += clock64() - t1;
             tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty0 + 8 * ts);        // this accumulator may be overwritten
+            if (lane == 0) mbar_arrive(tempty0 + 8 * ts);        // this accumulator may be overwritten (the read was warp-wide)
             if (!(p.probe & 1)) scale_add(v, sa, sa_s + KS * TILE + cg * 32, acc);
             if (SUMS && row < p.m) {
 #pragma unroll
@@ -331,7 +354,6 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
             if (++ts == TMEM_STAGES) { ts = 0; tphase ^= 1u; }
             if (++kk == KS) { kk = 0; if (++s == MM_STAGES) { s = 0; sphase ^= 1u; } }
         }
-        if (timing && lane == 0) { p.dbg[4] = clock64() - c_all; p.dbg[5] = c_wait; p.dbg[6] = c_ld; }
         if (alive && row < p.m) {
             float *out = p.c + (size_t)row * p.n + col0;
             float f[32];

@@ -75,6 +75,23 @@ def test_config_q4_0_odd_8191x8160(oracle):
     check_q(oracle, B.Q4_0, B.F32, 8191, 8160, 103)
 
 
+def test_many_chunks_per_block_back_to_back(oracle):
+    # 28672 x 8192 (the sharded configuration's matrix): every block's ring slots are reused many times, and three
+    # launches in a row that share y make each kernel a dependent of the one before
+    import torch
+    rows, cols = 28672, 8192
+    a = B.make_weights(B.Q4_0, rows, cols, 400)
+    xf = B.make_activations(cols, 401)
+    o = H.ops()
+    da, dx = H.dev(a), H.dev(xf)
+    y = H.empty(rows, torch.float32)
+    for _ in range(3):
+        o.GemvBlocks(B.Q4_0, da, dx, y, rows, cols, fmt_x=B.F32)
+    assert o.gpu.status() == 0
+    ref, mag = oracle.gemv_blocks(B.Q4_0, B.F32, a, xf, rows, cols, order=1, want_abs=True)
+    assert np.all(np.abs(y.cpu().numpy().astype(np.float64) - ref) <= REL * mag)
+
+
 def test_reference_signature_same_format(oracle):
     # GemvBlocks<TN>(a, x, y, rows, cols): x in a's format (src/BlockProducts.cs:178)
     for fmt in (B.Q8_0, B.Q4_0):
