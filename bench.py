@@ -132,13 +132,14 @@ def sharded_gemv_leg(ops, torch, dist, rank, world, dev):
     ws = [torch.from_numpy(shard).to(dev).clone() for _ in range(copies)]
     x = torch.from_numpy(B.make_activations(k, 4001)).to(dev)
     y = torch.empty(max(rows, 1), dtype=torch.float32, device=dev)
+    y_full = torch.empty(n, dtype=torch.float32, device=dev)
     reps = 5
 
     def timed(gather):
         for w in ws[:2]:
             ops.GemvBlocks(FMT_A, w, x, y, rows, k, fmt_x=FMT_X)
             if gather:
-                all_gather_rows(plan, rank, y)
+                all_gather_rows(plan, rank, y, out=y_full)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -148,7 +149,7 @@ def sharded_gemv_leg(ops, torch, dist, rank, world, dev):
             for w in ws:
                 ops.GemvBlocks(FMT_A, w, x, y, rows, k, fmt_x=FMT_X)
                 if gather:
-                    all_gather_rows(plan, rank, y)
+                    all_gather_rows(plan, rank, y, out=y_full)
         e1.record()
         torch.cuda.synchronize()
         t = torch.tensor([e0.elapsed_time(e1) / (reps * copies)], dtype=torch.float64, device=dev)

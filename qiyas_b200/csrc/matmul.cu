@@ -25,7 +25,7 @@ namespace qb {
 #endif
 
 constexpr int TILE = 128;            // rows of A and of B per block tile
-constexpr int KS = 4;                // k-blocks per shared-memory stage
+constexpr int KS = 4;                // k-blocks per shared-memory stage (even: pairs of k-blocks never straddle stages)
 constexpr int MM_STAGES = 5;
 constexpr int TMEM_STAGES = 4;       // 4 x 128 columns = all 512 columns of tensor memory
 constexpr int SLAB = TILE * 32;      // bytes of codes per tile and k-block
@@ -46,7 +46,6 @@ struct MatmulArgs {
     int32_t *sums;
     int *status;
     int m, n, kb;
-    long long *dbg;  // tuning aid: cycle counts of block 0's MMA thread; null in normal use
     int probe;       // tuning aid: 1 = no arithmetic, 2 = no tensor-memory reads, 3 = neither; 0 in normal use
 };
 
@@ -244,7 +243,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
             mbar_init(empty0 + 8 * s, 1 + EPI_WARPS);      // the MMA thread's commit and the epilogue warps
         }
         for (int s = 0; s < TMEM_STAGES; s++) {
-            mbar_init(tfull0 + 8 * s, 1);
+            mbar_init(tfull0 + 8 * s, 1);            // only the first two of each are used: one a pair of accumulators
             mbar_init(tempty0 + 8 * s, EPI_WARPS);
         }
         *abort_flag = 0;
@@ -286,13 +285,13 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
             }
         }
     } else if (warp == 1) {
-        // ---- MMA issue: one thread, one instruction a k-block, each into the next of four accumulators
+        // ---- MMA issue: one thread.  The four accumulators form two pairs; a pair of k-blocks is issued into a pair of
+        // accumulators and committed to one barrier, so the barrier traffic is per two k-blocks on both sides.
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_s8(TILE, TILE);
             // descriptors differ from k-block to k-block only in the start address (16-byte units)
             const uint64_t desc_hi = smem_desc(0, SLAB / 2, 128);
-            int ts = 0, i = 0;
-            uint32_t tphase = 0;                   // parity of "the previous use of this accumulator has been read"
+            int np = 0;                            // pairs issued so far
             bool alive = true;
             for (int it = 0; it < stages_total && alive; it++) {
                 const int s = it % MM_STAGES;
@@ -300,27 +299,25 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                 tc_fence_after();
                 const uint32_t a_smem = smem_u32(ring + (size_t)s * STAGE_BYTES), b_smem = a_smem + KS * SLAB;
                 const int nkb = min(KS, p.kb - it * KS);
-                for (int kk = 0; kk < nkb; kk++, i++) {
-                    if (i >= TMEM_STAGES) {
-                        if (!mbar_wait(tempty0 + 8 * ts, tphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
+                for (int kk = 0; kk < nkb; kk += 2, np++) {
+                    const int pair = np & 1, use = np >> 1;
+                    if (use > 0) {
+                        if (!mbar_wait(tempty0 + 8 * pair, (uint32_t)(use - 1) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
                         tc_fence_after();
                     }
-                    mma_s8(tmem + (uint32_t)ts * TILE, desc_hi | (uint64_t)(((a_smem + kk * SLAB) & 0x3FFFFu) >> 4),
+                    mma_s8(tmem + (uint32_t)(2 * pair) * TILE, desc_hi | (uint64_t)(((a_smem + kk * SLAB) & 0x3FFFFu) >> 4),
                            desc_hi | (uint64_t)(((b_smem + kk * SLAB) & 0x3FFFFu) >> 4), idesc);
-                    mma_commit(tfull0 + 8 * ts);
-                    if (p.dbg && i == 0 && blockIdx.x == 0 && blockIdx.y == 0) {        // tuning aid: issue -> completion seen, in cycles
-                        long long t0 = clock64();
-                        while (!mbar_try_wait(tfull0, 0u) && clock64() - t0 < 1000000) { }
-                        p.dbg[3] = clock64() - t0;
-                    }
-                    if (++ts == TMEM_STAGES) { ts = 0; if (i >= TMEM_STAGES) tphase ^= 1u; }
+                    if (kk + 1 < nkb)
+                        mma_s8(tmem + (uint32_t)(2 * pair + 1) * TILE, desc_hi | (uint64_t)(((a_smem + (kk + 1) * SLAB) & 0x3FFFFu) >> 4),
+                               desc_hi | (uint64_t)(((b_smem + (kk + 1) * SLAB) & 0x3FFFFu) >> 4), idesc);
+                    mma_commit(tfull0 + 8 * pair);
                 }
                 mma_commit(empty0 + 8 * s);      // the stage's codes are free once these products have run
             }
         }
     } else {
         // ---- epilogue: a warp owns 32 rows (tensor-memory lanes 32*(warp%4) ..) x 32 columns of every accumulator;
-        // four warps a scheduler cover each other's tensor-memory reads.
+        // four warps a scheduler cover each other's tensor-memory reads.  Two k-blocks a barrier round.
         const int q = warp & 3, cg = (warp - 2) >> 2;
         const int row = tm * TILE + q * 32 + lane, col0 = tn * TILE + cg * 32;
         const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cg * 32);
@@ -328,31 +325,45 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
 #pragma unroll
         for (int c = 0; c < 16; c++) acc[c] = 0ull;
         bool alive = true;
-        int s = 0, kk = 0, ts = 0;
-        uint32_t sphase = 0, tphase = 0;
-        for (int i = 0; i < p.kb; i++) {
-            if (!QB_MM_WAIT(tfull0 + 8 * ts, tphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
+        int s = 0, kk = 0, np = 0;
+        uint32_t sphase = 0;
+        for (int i = 0; i < p.kb; i += 2, np++) {
+            const int pair = np & 1, cnt = min(2, p.kb - i);
+            if (!QB_MM_WAIT(tfull0 + 8 * pair, (uint32_t)(np >> 1) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
             tc_fence_after();
             int32_t v[32];
-            if (!(p.probe & 2)) tmem_ld32(tlane + (uint32_t)ts * TILE, v);
+            if (!(p.probe & 2)) tmem_ld32(tlane + (uint32_t)(2 * pair) * TILE, v);
             if (kk == 0 && !QB_MM_WAIT(full0 + 8 * s, sphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
             const float *sa_s = (const float *)(ring + (size_t)s * STAGE_BYTES + 2 * KS * SLAB) + kk * TILE;
-            const float sa = sa_s[q * 32 + lane];
+            const float *sb_s = sa_s + KS * TILE + cg * 32;
+            const float sa0 = sa_s[q * 32 + lane], sa1 = sa_s[TILE + q * 32 + lane];
             tmem_ld_wait();
-            tc_fence_before();
-            if (lane == 0) mbar_arrive(tempty0 + 8 * ts);        // this accumulator may be overwritten (the read was warp-wide)
-            if (!(p.probe & 1)) scale_add(v, sa, sa_s + KS * TILE + cg * 32, acc);
+            if (!(p.probe & 1)) scale_add(v, sa0, sb_s, acc);
             if (SUMS && row < p.m) {
 #pragma unroll
                 for (int c = 0; c < 32; c++)
                     if (col0 + c < p.n) p.sums[((size_t)row * p.n + col0 + c) * p.kb + i] = v[c];
             }
-            if (kk == KS - 1 || i == p.kb - 1) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty0 + 8 * s);      // this warp has read the stage's scales
+            if (cnt == 2) {
+                if (!(p.probe & 2)) tmem_ld32(tlane + (uint32_t)(2 * pair + 1) * TILE, v);
+                tmem_ld_wait();
             }
-            if (++ts == TMEM_STAGES) { ts = 0; tphase ^= 1u; }
-            if (++kk == KS) { kk = 0; if (++s == MM_STAGES) { s = 0; sphase ^= 1u; } }
+            tc_fence_before();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * pair);      // both accumulators have been read (warp-wide reads)
+            if (cnt == 2) {
+                if (!(p.probe & 1)) scale_add(v, sa1, sb_s + TILE, acc);
+                if (SUMS && row < p.m) {
+#pragma unroll
+                    for (int c = 0; c < 32; c++)
+                        if (col0 + c < p.n) p.sums[((size_t)row * p.n + col0 + c) * p.kb + i + 1] = v[c];
+                }
+            }
+            kk += 2;
+            if (kk >= KS || i + cnt >= p.kb) {
+                if (lane == 0) mbar_arrive(empty0 + 8 * s);      // this warp has read the stage's scales
+                kk = 0;
+                if (++s == MM_STAGES) { s = 0; sphase ^= 1u; }
+            }
         }
         if (alive && row < p.m) {
             float *out = p.c + (size_t)row * p.n + col0;
@@ -377,8 +388,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
 
 static int *g_mm_status = nullptr;
 static int g_mm_probe = 0;
-static long long *g_mm_dbg = nullptr;
-void matmul_set_dbg(long long *p) { g_mm_dbg = p; }
+
 void matmul_set_probe(int mode) { g_mm_probe = mode; }
 
 cudaError_t matmul_init(int, int max_smem, int *status)
@@ -425,7 +435,7 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, float *c, 
     args.a.codes = a_codes; args.a.scales = a_scales;
     args.b.codes = b_codes; args.b.scales = b_scales;
     args.c = c; args.sums = sums; args.status = g_mm_status;
-    args.m = m; args.n = n; args.kb = k / 32; args.probe = g_mm_probe; args.dbg = g_mm_dbg;
+    args.m = m; args.n = n; args.kb = k / 32; args.probe = g_mm_probe;
     const dim3 grid((n + TILE - 1) / TILE, (m + TILE - 1) / TILE);
     if (sums) matmul_kernel<true><<<grid, MM_THREADS, MM_SMEM, stream>>>(args);
     else matmul_kernel<false><<<grid, MM_THREADS, MM_SMEM, stream>>>(args);

@@ -48,14 +48,24 @@ class ShardPlan:
         return weights[lo:hi]
 
 
-def all_gather_rows(plan, rank, y_slice, group=None):
+def all_gather_rows(plan, rank, y_slice, group=None, out=None):
     """The full output vector from every rank's slice of it (gemv): f32[rows].
 
-    Slices are padded to ceil(N/g) so that one equal-count all-gather serves an uneven last shard.
+    When the rows divide evenly the slices are gathered in place into `out` (allocated here when not given): one
+    collective, no copy.  Otherwise slices are padded to ceil(N/g) so that one equal-count all-gather serves the uneven
+    last shard.
     """
     import torch
     import torch.distributed as dist
     per = plan.per_rank
+    if per * plan.world == plan.rows and y_slice.numel() == per:
+        if out is None:
+            out = torch.empty(plan.rows, dtype=y_slice.dtype, device=y_slice.device)
+        if plan.world == 1:
+            out.copy_(y_slice)
+        else:
+            dist.all_gather_into_tensor(out, y_slice, group=group)
+        return out
     mine = torch.zeros(per, dtype=y_slice.dtype, device=y_slice.device)
     mine[:plan.count(rank)] = y_slice[:plan.count(rank)]
     out = torch.empty(per * plan.world, dtype=y_slice.dtype, device=y_slice.device)
@@ -94,10 +104,10 @@ class ShardedGemv:
         """This rank's slice of y (no communication)."""
         return self.ops.GemvBlocks(self.fmt, self.w, x, y_slice, self.rows, self.cols, fmt_x=fmt_x, stream=stream)
 
-    def full(self, x, y_slice, fmt_x=None, group=None):
+    def full(self, x, y_slice, fmt_x=None, group=None, out=None):
         """The whole y on every rank: the local slice, then the all-gather over NVLink."""
         self.local(x, y_slice, fmt_x=fmt_x)
-        return all_gather_rows(self.plan, self.rank, y_slice, group=group)
+        return all_gather_rows(self.plan, self.rank, y_slice, group=group, out=out)
 
 
 class ShardedMatMul:
