@@ -52,8 +52,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 {
     if (mbar_try_wait(bar, parity)) return true;
     long long start = clock64();
-    for (;;) {
+    for (int spins = 0;; spins++) {
         if (mbar_try_wait(bar, parity)) return true;
+#ifdef QB_WAIT_SLEEP_NS
+        __nanosleep(QB_WAIT_SLEEP_NS);          // a waiting warp should not take issue slots from the working ones
+#endif
+        if ((spins & 15) != 15) continue;       // the give-up conditions are looked at every 16th poll
         if (*abort) return false;
         if (clock64() - start > WAIT_CYCLES) {
             *abort = 1;

@@ -71,6 +71,21 @@ __device__ __forceinline__ float warp_sum(float v)
     return v;
 }
 
+// Four row sums at once: halves of the warp trade two values, quarters one, then three plain steps.  Afterwards every
+// lane of the eight-lane group g (lanes 8g .. 8g+7) holds the whole sum of row g.  6 shuffles instead of 20.
+__device__ __forceinline__ float warp_sum4(const float (&a)[4], int lane)
+{
+    const bool up = lane & 16;
+    const float b0 = (up ? a[2] : a[0]) + __shfl_xor_sync(0xffffffffu, up ? a[0] : a[2], 16);
+    const float b1 = (up ? a[3] : a[1]) + __shfl_xor_sync(0xffffffffu, up ? a[1] : a[3], 16);
+    const bool odd = lane & 8;
+    float c = (odd ? b1 : b0) + __shfl_xor_sync(0xffffffffu, odd ? b0 : b1, 8);
+    c += __shfl_xor_sync(0xffffffffu, c, 4);
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    return c;
+}
+
 // ---------------------------------------------------------------------------------- x -> int8 + scales in shared memory
 
 // One block of 32 activations as the reference's Q8_0 encoder stores them (src/Blocks.cs:37-45, device twin
@@ -370,52 +385,69 @@ __device__ __forceinline__ void load_x(XPair &x, const GemvArgs &p, const uint8_
     x.s0 = (int)meta.z; x.s1 = (int)meta.w;
 }
 
-// Q4_K rows: eight lanes a super-block, four super-blocks a run; a lane holds 16 values of sub-block 2p and 16 of 2p+1.
+// Q4_K rows: four lanes a super-block, eight super-blocks a run; a lane holds sub-blocks 2p and 2p+1 of x (its pair's 32
+// bytes of nibbles carry the first in the low halves and the second in the high halves).
 struct XK4 {
-    uint32_t lo[4], hi[4];
+    uint32_t lo[8], hi[8];
     float da, db;
-    int sa, sb;              // whole sub-block sums of x (the min term), used by the even lane of a pair
+    int sa, sb;              // sums of the two sub-blocks' x values (the min term)
     int xb;                  // x block of sub-block 2p
     bool valid;
 };
 
 __device__ __forceinline__ void load_x(XK4 &x, const GemvArgs &p, const uint8_t *xp, int run, int lane)
 {
-    const int sb = run * 4 + (lane >> 3), part = lane & 7;
+    const int sb = run * 8 + (lane >> 2), pr = lane & 3;
     x.valid = sb < p.cols / 256;
-    x.xb = sb * 8 + (part >> 1) * 2;
+    x.xb = sb * 8 + pr * 2;
+    x.da = x.db = 0.f;
+    x.sa = x.sb = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) x.lo[i] = x.hi[i] = 0;
     if (!x.valid) return;
-    const uint8_t *xq = xp + (size_t)x.xb * 32 + (part & 1) * 16;
-    const uint4 l = *(const uint4 *)xq, h = *(const uint4 *)(xq + 32);
+    const uint4 *xq = (const uint4 *)(xp + (size_t)x.xb * 32);
+    const uint4 l0 = xq[0], l1 = xq[1], h0 = xq[2], h1 = xq[3];
     const uint2 *meta = (const uint2 *)(xp + xprep_codes_bytes(p.cols));
     const uint2 ma = meta[x.xb], mb = meta[x.xb + 1];
-    x.lo[0] = l.x; x.lo[1] = l.y; x.lo[2] = l.z; x.lo[3] = l.w;
-    x.hi[0] = h.x; x.hi[1] = h.y; x.hi[2] = h.z; x.hi[3] = h.w;
+    x.lo[0] = l0.x; x.lo[1] = l0.y; x.lo[2] = l0.z; x.lo[3] = l0.w; x.lo[4] = l1.x; x.lo[5] = l1.y; x.lo[6] = l1.z; x.lo[7] = l1.w;
+    x.hi[0] = h0.x; x.hi[1] = h0.y; x.hi[2] = h0.z; x.hi[3] = h0.w; x.hi[4] = h1.x; x.hi[5] = h1.y; x.hi[6] = h1.z; x.hi[7] = h1.w;
     x.da = __uint_as_float(ma.x); x.db = __uint_as_float(mb.x);
     x.sa = (int)ma.y; x.sb = (int)mb.y;
 }
 
-// Q6_K rows: sixteen lanes a super-block, two super-blocks a run; a lane holds four values of each of four runs of 32.
+// Q6_K rows: eight lanes a super-block, four super-blocks a run.  Runs pair up over eight super-blocks, the even run
+// taking the even ones and the odd run the odd ones: blocks are 210 bytes, so whether a lane's block starts on 4 bytes
+// is then the same for the whole warp.  A lane (h, ab, lr) holds bytes 16lr.. of x blocks 4h+ab and 4h+ab+2.
 struct XK6 {
-    uint32_t w[4];
-    float d[4];
-    int ones[4];             // sums of the four values (the -32 offset)
+    uint32_t lo[4], hi[4];
+    float dlo, dhi;
+    int olo, ohi;            // sums of those 16 values (the -32 offset)
     int sb;
     bool valid;
 };
 
+__device__ __forceinline__ int k6_run_block(int run, int lane) { return 8 * (run >> 1) + 2 * (lane >> 3) + (run & 1); }
+
 __device__ __forceinline__ void load_x(XK6 &x, const GemvArgs &p, const uint8_t *xp, int run, int lane)
 {
-    x.sb = run * 2 + (lane >> 4);
+    x.sb = k6_run_block(run, lane);
     x.valid = x.sb < p.cols / 256;
-    if (!x.valid) return;
-    const int half = (lane >> 3) & 1, t = lane & 7;
-    const uint2 *meta = (const uint2 *)(xp + xprep_codes_bytes(p.cols));
+    x.dlo = x.dhi = 0.f;
+    x.olo = x.ohi = 0;
 #pragma unroll
-    for (int g = 0; g < 4; g++) {
-        x.w[g] = *(const uint32_t *)(xp + (size_t)x.sb * 256 + half * 128 + g * 32 + t * 4);
-        x.d[g] = __uint_as_float(meta[x.sb * 8 + half * 4 + g].x);
-        x.ones[g] = dp4a_s8s8(x.w[g], 0x01010101u, 0);
+    for (int i = 0; i < 4; i++) x.lo[i] = x.hi[i] = 0;
+    if (!x.valid) return;
+    const int xb = x.sb * 8 + ((lane >> 2) & 1) * 4 + ((lane >> 1) & 1), lr = lane & 1;
+    const uint4 a = *(const uint4 *)(xp + (size_t)xb * 32 + lr * 16), b = *(const uint4 *)(xp + (size_t)(xb + 2) * 32 + lr * 16);
+    const uint2 *meta = (const uint2 *)(xp + xprep_codes_bytes(p.cols));
+    x.lo[0] = a.x; x.lo[1] = a.y; x.lo[2] = a.z; x.lo[3] = a.w;
+    x.hi[0] = b.x; x.hi[1] = b.y; x.hi[2] = b.z; x.hi[3] = b.w;
+    x.dlo = __uint_as_float(meta[xb].x);
+    x.dhi = __uint_as_float(meta[xb + 2].x);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        x.olo = dp4a_s8s8(x.lo[i], 0x01010101u, x.olo);
+        x.ohi = dp4a_s8s8(x.hi[i], 0x01010101u, x.ohi);
     }
 }
 
@@ -520,22 +552,22 @@ __device__ __forceinline__ void rows_fast(const XPair (&xr)[RUNS], const uint8_t
 
 // Q4_K: value = (d*sc)*q - dmin*m (src/Blocks.cs:79-96), so against x = dx*qx a sub-block gives
 // (d*sc)*dx*sum(q*qx) - (dmin*m)*dx*sum(qx).  The 6-bit fields are unpacked as ScaleMin does (src/Blocks.cs:73-77), four at a time.
-template <int FMT, bool SUMS>
-__device__ __forceinline__ float row_dot(const XK4 &x, const uint8_t *row, int lane, int32_t *sums_row, float acc)
+// A16 = the super-blocks start on 16 bytes (then three 16-byte loads fetch header and nibbles).
+template <bool SUMS, bool A16>
+__device__ __forceinline__ float row_dot_k4(const XK4 &x, const uint8_t *row, int lane, int32_t *sums_row, float acc)
 {
-    if (!x.valid) return acc;
-    const int part = lane & 7, pr = part >> 1, hsel = part & 1;
+    const int pr = lane & 3;
     const uint8_t *blk = row + (size_t)(x.xb >> 3) * 144;
-    uint32_t h0, s0, s1, s2, n[4];
-    if (((uint32_t)(uintptr_t)blk & 15u) == 0) {
+    uint32_t h0, s0, s1, s2, n[8];
+    if (A16) {
         const uint4 hdr = *(const uint4 *)blk;
-        const uint4 nb = *(const uint4 *)(blk + 16 + pr * 32 + hsel * 16);
+        const uint4 na = *(const uint4 *)(blk + 16 + pr * 32), nb = *(const uint4 *)(blk + 32 + pr * 32);
         h0 = hdr.x; s0 = hdr.y; s1 = hdr.z; s2 = hdr.w;
-        n[0] = nb.x; n[1] = nb.y; n[2] = nb.z; n[3] = nb.w;
+        n[0] = na.x; n[1] = na.y; n[2] = na.z; n[3] = na.w; n[4] = nb.x; n[5] = nb.y; n[6] = nb.z; n[7] = nb.w;
     } else {
         h0 = ld32_a2(blk); s0 = ld32_a2(blk + 4); s1 = ld32_a2(blk + 8); s2 = ld32_a2(blk + 12);
 #pragma unroll
-        for (int i = 0; i < 4; i++) n[i] = ld32_a2(blk + 16 + pr * 32 + hsel * 16 + 4 * i);
+        for (int i = 0; i < 8; i++) n[i] = ld32_a2(blk + 16 + pr * 32 + 4 * i);
     }
     const float d = half_bits_to_float(h0 & 0xFFFFu), dmin = half_bits_to_float(h0 >> 16);
     // scales of sub-blocks 0..3 | 4..7 and their mins, a byte each
@@ -543,59 +575,127 @@ __device__ __forceinline__ float row_dot(const XK4 &x, const uint8_t *row, int l
     const uint32_t mn_lo = s1 & 0x3F3F3F3Fu, mn_hi = ((s2 >> 4) & 0x0F0F0F0Fu) | (((s1 >> 6) & 0x03030303u) << 4);
     const uint32_t scw = (pr < 2 ? sc_lo : sc_hi) >> ((pr & 1) * 16), mnw = (pr < 2 ? mn_lo : mn_hi) >> ((pr & 1) * 16);
     const int sca = scw & 255, scb = (scw >> 8) & 255, mna = mnw & 255, mnb = (mnw >> 8) & 255;
-    int lo = 0, hi = 0;
+    int lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        lo = dp4a_u8s8(n[i] & 0x0F0F0F0Fu, x.lo[i], lo);
-        hi = dp4a_u8s8(n[i] & 0xF0F0F0F0u, x.hi[i], hi);
+    for (int i = 0; i < 8; i += 2) {
+        lo0 = dp4a_u8s8(n[i] & 0x0F0F0F0Fu, x.lo[i], lo0);
+        hi0 = dp4a_u8s8(n[i] & 0xF0F0F0F0u, x.hi[i], hi0);
+        lo1 = dp4a_u8s8(n[i + 1] & 0x0F0F0F0Fu, x.lo[i + 1], lo1);
+        hi1 = dp4a_u8s8(n[i + 1] & 0xF0F0F0F0u, x.hi[i + 1], hi1);
     }
-    hi >>= 4;
+    const int lo = lo0 + lo1, hi = (hi0 + hi1) >> 4;
     acc = __fmaf_rn(__fmul_rn(__fmul_rn(d, (float)sca), x.da), (float)lo, acc);
     acc = __fmaf_rn(__fmul_rn(__fmul_rn(d, (float)scb), x.db), (float)hi, acc);
-    if (hsel == 0) {
-        acc = __fmaf_rn(-__fmul_rn(__fmul_rn(dmin, (float)mna), x.da), (float)x.sa, acc);
-        acc = __fmaf_rn(-__fmul_rn(__fmul_rn(dmin, (float)mnb), x.db), (float)x.sb, acc);
-    }
+    acc = __fmaf_rn(-__fmul_rn(__fmul_rn(dmin, (float)mna), x.da), (float)x.sa, acc);
+    acc = __fmaf_rn(-__fmul_rn(__fmul_rn(dmin, (float)mnb), x.db), (float)x.sb, acc);
     if (SUMS) {
-        lo += __shfl_xor_sync(__activemask(), lo, 1);
-        hi += __shfl_xor_sync(__activemask(), hi, 1);
-        if (hsel == 0) {
-            sums_row[x.xb] = lo;
-            sums_row[x.xb + 1] = hi;
+        sums_row[x.xb] = lo;
+        sums_row[x.xb + 1] = hi;
+    }
+    return acc;
+}
+
+template <int FMT, bool SUMS>
+__device__ __forceinline__ float row_dot(const XK4 &x, const uint8_t *row, int lane, int32_t *sums_row, float acc)
+{
+    if (!x.valid) return acc;
+    if (((uint32_t)(uintptr_t)row & 15u) == 0) return row_dot_k4<SUMS, true>(x, row, lane, sums_row, acc);
+    return row_dot_k4<SUMS, false>(x, row, lane, sums_row, acc);
+}
+
+// RW whole rows on 16 bytes against this warp's runs: one test a run (a row can end inside the last one).
+template <int RW, int RUNS>
+__device__ __forceinline__ void rows_fast(const XK4 (&xr)[RUNS], const uint8_t *rows, uint32_t row_bytes, int lane, float (&acc)[RW])
+{
+#pragma unroll
+    for (int j = 0; j < RUNS; j++) {
+        if (!xr[j].valid) continue;
+#pragma unroll
+        for (int r = 0; r < RW; r++) acc[r] = row_dot_k4<false, true>(xr[j], rows + (size_t)r * row_bytes, lane, nullptr, acc[r]);
+    }
+}
+
+// Q6_K (src/Blocks.cs:157-171): value = d*sc*(q-32) with q = a nibble of ql and two bits of qh.  A lane takes 16 bytes
+// of ql[64h + 32ab ..] and of qh[32h ..]: the low nibbles are 16 values of run 4h+ab, the high nibbles of run 4h+ab+2,
+// each one 16-value sub-block, whose integer sum is sc * (sum q*qx - 32*sum qx).  A4 = the block starts on 4 bytes.
+template <bool A4>
+__device__ __forceinline__ void load_words4(const uint8_t *q, uint32_t (&w)[4])
+{
+    if (A4) {
+        const uint32_t *t = (const uint32_t *)q;
+#pragma unroll
+        for (int i = 0; i < 4; i++) w[i] = t[i];
+    } else {
+        const uint32_t *t = (const uint32_t *)(q - 2);
+        uint32_t prev = t[0];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t next = t[i + 1];
+            w[i] = __funnelshift_r(prev, next, 16);
+            prev = next;
+        }
+    }
+}
+
+template <bool SUMS, bool A4>
+__device__ __forceinline__ float row_dot_k6(const XK6 &x, const uint8_t *blk, int lane, int32_t *sums_row, float acc)
+{
+    const int h = (lane >> 2) & 1, ab = (lane >> 1) & 1, lr = lane & 1;
+    uint32_t W[4], H[4];
+    load_words4<A4>(blk + h * 64 + ab * 32 + lr * 16, W);
+    load_words4<A4>(blk + 128 + h * 32 + lr * 16, H);
+    const float d = half_bits_to_float(*(const uint16_t *)(blk + 208));
+    const int8_t *sc = (const int8_t *)(blk + 192 + h * 8 + ab * 2 + lr);
+    const int sc_lo = sc[0], sc_hi = sc[4];
+    const int up = 4 - 2 * ab, down = 2 * ab;
+    int dlo = 0, dhi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t qlo = (W[i] & 0x0F0F0F0Fu) | ((H[i] << up) & 0x30303030u);
+        const uint32_t qhi = ((W[i] >> 4) & 0x0F0F0F0Fu) | ((H[i] >> down) & 0x30303030u);
+        dlo = dp4a_u8s8(qlo, x.lo[i], dlo);
+        dhi = dp4a_u8s8(qhi, x.hi[i], dhi);
+    }
+    int ilo = sc_lo * (dlo - 32 * x.olo), ihi = sc_hi * (dhi - 32 * x.ohi);
+    acc = __fmaf_rn(__fmul_rn(d, x.dlo), (float)ilo, acc);
+    acc = __fmaf_rn(__fmul_rn(d, x.dhi), (float)ihi, acc);
+    if (SUMS) {             // an entry of the check output is a whole x block: this lane's half and its neighbour's
+        ilo += __shfl_xor_sync(__activemask(), ilo, 1);
+        ihi += __shfl_xor_sync(__activemask(), ihi, 1);
+        if (lr == 0) {
+            const int xb = x.sb * 8 + h * 4 + ab;
+            sums_row[xb] = ilo;
+            sums_row[xb + 2] = ihi;
         }
     }
     return acc;
 }
 
-// Q6_K: a lane takes one word of each of ql[64h..], ql[64h+32..] and qh[32h..] (src/Blocks.cs:157-171).
-// value = d*sc*(q-32); per 16-value sub-block the integer sum is sc * (sum q*qx - 32*sum qx).
 template <int FMT, bool SUMS>
 __device__ __forceinline__ float row_dot(const XK6 &x, const uint8_t *row, int lane, int32_t *sums_row, float acc)
 {
     if (!x.valid) return acc;
-    const int half = (lane >> 3) & 1, t = lane & 7;
     const uint8_t *blk = row + (size_t)x.sb * 210;
-    const uint32_t A = ld32_a2(blk + half * 64 + t * 4), B = ld32_a2(blk + half * 64 + 32 + t * 4);
-    const uint32_t H = ld32_a2(blk + 128 + half * 32 + t * 4);
-    const float d = half_bits_to_float(*(const uint16_t *)(blk + 208));
-    const int8_t *sc = (const int8_t *)(blk + 192 + half * 8 + (t >> 2));
-    uint32_t q[4];
-    q[0] = (A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u);
-    q[1] = (B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u);
-    q[2] = ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u);
-    q[3] = ((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u);
+    if (((uint32_t)(uintptr_t)blk & 2u) == 0) return row_dot_k6<SUMS, true>(x, blk, lane, sums_row, acc);
+    return row_dot_k6<SUMS, false>(x, blk, lane, sums_row, acc);
+}
+
+// RW whole rows against this warp's runs: one test a run (a row can end inside the last one).  The alignment branch is
+// uniform over the lanes that have a block.
+template <int RW, int RUNS>
+__device__ __forceinline__ void rows_fast(const XK6 (&xr)[RUNS], const uint8_t *rows, uint32_t row_bytes, int lane, float (&acc)[RW])
+{
 #pragma unroll
-    for (int g = 0; g < 4; g++) {
-        int isum = (int)sc[2 * g] * (dp4a_u8s8(q[g], x.w[g], 0) - 32 * x.ones[g]);
-        acc = __fmaf_rn(__fmul_rn(d, x.d[g]), (float)isum, acc);
-        if (SUMS) {
-            isum += __shfl_xor_sync(__activemask(), isum, 1);
-            isum += __shfl_xor_sync(__activemask(), isum, 2);
-            isum += __shfl_xor_sync(__activemask(), isum, 4);
-            if (t == 0) sums_row[x.sb * 8 + half * 4 + g] = isum;
+    for (int j = 0; j < RUNS; j++) {
+        if (!xr[j].valid) continue;
+        const uint8_t *blk0 = rows + (size_t)xr[j].sb * 210;
+#pragma unroll
+        for (int r = 0; r < RW; r++) {
+            const uint8_t *blk = blk0 + (size_t)r * row_bytes;
+            if (((uint32_t)(uintptr_t)blk & 2u) == 0) acc[r] = row_dot_k6<false, true>(xr[j], blk, lane, nullptr, acc[r]);
+            else acc[r] = row_dot_k6<false, false>(xr[j], blk, lane, nullptr, acc[r]);
         }
     }
-    return acc;
 }
 
 // ---------------------------------------------------------------------------------- the kernel
@@ -758,6 +858,18 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
                     done = true;
                 }
             }
+            if constexpr (FMT == QB200_Q6_K && !SUMS) {
+                if (!done && nvalid == RW) {
+                    rows_fast<RW, RUNS>(xr, rows, p.row_bytes, lane, acc);
+                    done = true;
+                }
+            }
+            if constexpr (FMT == QB200_Q4_K && !SUMS) {
+                if (!done && nvalid == RW && (((uint32_t)(uintptr_t)rows | p.row_bytes) & 15u) == 0) {
+                    rows_fast<RW, RUNS>(xr, rows, p.row_bytes, lane, acc);
+                    done = true;
+                }
+            }
             if (!done) {
 #pragma unroll
                 for (int j = 0; j < RUNS; j++) {
@@ -771,17 +883,29 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
             }
             long long tq2 = p.timeline ? clock64() : 0;
             c_dot += tq2 - tq1;
+            // the row sums (every lane has read its last byte of the slot once these shuffles are done)
+            if constexpr (RW == 4) {
+                const float total = warp_sum4(acc, lane);           // lanes 8r .. 8r+7 hold row r
+                if (p.timeline) c_sum += clock64() - tq2;
+                if (lane == 0) mbar_arrive(empty0 + 8 * s);
+                const int r = lane >> 3;
+                if ((lane & 7) == 0) {
+                    if (p.cs == 1) { if (r < nvalid) p.y[row0 + r] = total; }
+                    else part[((size_t)flush_i * p.stage_rows + rgi * RW + r) * p.cs + seg] = total;
+                }
+            } else {
 #pragma unroll
-            for (int r = 0; r < RW; r++) acc[r] = warp_sum(acc[r]);     // every lane has read its last byte of the slot
-            if (p.timeline) c_sum += clock64() - tq2;
-            if (lane == 0) mbar_arrive(empty0 + 8 * s);
-            if (p.cs == 1) {
+                for (int r = 0; r < RW; r++) acc[r] = warp_sum(acc[r]);
+                if (p.timeline) c_sum += clock64() - tq2;
+                if (lane == 0) mbar_arrive(empty0 + 8 * s);
+                if (p.cs == 1) {
 #pragma unroll
-                for (int r = 0; r < RW; r++) if (lane == r && r < nvalid) p.y[row0 + r] = acc[r];
-            } else if (lane == 0) {
-                float *mine = part + ((size_t)flush_i * p.stage_rows + rgi * RW) * p.cs + seg;
+                    for (int r = 0; r < RW; r++) if (lane == r && r < nvalid) p.y[row0 + r] = acc[r];
+                } else if (lane == 0) {
+                    float *mine = part + ((size_t)flush_i * p.stage_rows + rgi * RW) * p.cs + seg;
 #pragma unroll
-                for (int r = 0; r < RW; r++) mine[r * p.cs] = acc[r];
+                    for (int r = 0; r < RW; r++) mine[r * p.cs] = acc[r];
+                }
             }
         }
         if (++sl == spg) { sl = 0; phase ^= 1u; }
@@ -850,15 +974,21 @@ static void read_tuning()
     g_tune.ctas = env_int("QB200_GEMV_CTAS", 1);
 }
 
-static int cols_per_run(int fmt) { return fmt == QB200_Q4_K ? 1024 : fmt == QB200_Q6_K ? 512 : 2048; }
-static int max_runs_per_warp(int fmt) { return fmt == QB200_Q8_0 || fmt == QB200_Q4_0 ? 2 : 4; }
+// Runs of x that cover a row: 2048 columns each, but Q6_K runs are four super-blocks of one parity out of eight.
+static int runs_of(int fmt, int cols)
+{
+    if (fmt != QB200_Q6_K) return (cols + 2047) / 2048;
+    const int sb = cols / 256, rem = sb % 8;
+    return sb / 8 * 2 + (rem == 0 ? 0 : rem == 1 ? 1 : 2);
+}
+static int max_runs_per_warp(int fmt) { return fmt == QB200_Q6_K ? 4 : 2; }
 static constexpr uint32_t PART_BYTES = 16384;
 
 // Splits the consumer warps into column segments x row groups and sizes the ring.
 static int plan_gemv(int fmt_a, int rows, int cols, GemvPlan &pl)
 {
     const uint32_t row_bytes = (uint32_t)(cols / block_values(fmt_a) * block_bytes(fmt_a));
-    const int runs = (cols + cols_per_run(fmt_a) - 1) / cols_per_run(fmt_a);
+    const int runs = runs_of(fmt_a, cols);
     int nw = g_tune.warps;
     if (nw != 4 && nw != 8 && nw != 16) nw = 16;
     const int ctas = g_tune.ctas == 2 ? 2 : 1;                   // blocks meant to share an SM
@@ -879,7 +1009,7 @@ static int plan_gemv(int fmt_a, int rows, int cols, GemvPlan &pl)
     int rw = 4;
     while (rw > 1 && (uint64_t)rw * row_bytes > (uint64_t)g_tune.stage_bytes) rw /= 2;
     if (g_tune.rw == 1 || g_tune.rw == 2 || g_tune.rw == 4) rw = g_tune.rw;
-    pl.rw = rw; pl.runs_per_warp = per <= 1 ? 1 : per <= 2 ? 2 : 4; pl.nw = nw; pl.cs = cs; pl.rg = rg;
+    pl.rw = rw; pl.runs_per_warp = per; pl.nw = nw; pl.cs = cs; pl.rg = rg;
     const int stage_rows = rg * rw;
     pl.stage_stride = ((uint32_t)rw * row_bytes + 48u + 127u) / 128u * 128u;       // one chunk
     GemvArgs &a = pl.args;
@@ -936,8 +1066,9 @@ template <int FMT, int RW, bool SUMS>
 static cudaError_t launch_runs(const GemvPlan &pl, cudaStream_t stream)
 {
     if (pl.runs_per_warp == 1) return launch_one<FMT, RW, 1, SUMS>(pl, stream);
-    if (pl.runs_per_warp == 2 || FMT == QB200_Q8_0 || FMT == QB200_Q4_0) return launch_one<FMT, RW, 2, SUMS>(pl, stream);
-    return launch_one<FMT, RW, (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) ? 2 : 4, SUMS>(pl, stream);
+    if (pl.runs_per_warp == 2 || FMT != QB200_Q6_K) return launch_one<FMT, RW, 2, SUMS>(pl, stream);
+    if (pl.runs_per_warp == 3) return launch_one<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS>(pl, stream);
+    return launch_one<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS>(pl, stream);
 }
 
 template <int FMT>
@@ -957,8 +1088,10 @@ static cudaError_t set_attr_runs(int bytes)
     cudaError_t e;
     if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 1, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
     if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 2, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
-    if (FMT == QB200_Q4_K || FMT == QB200_Q6_K)
-        e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) ? 2 : 4, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (FMT == QB200_Q6_K) {
+        if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+        e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    }
     return e;
 }
 
