@@ -40,6 +40,7 @@ struct GemvArgs {
     int units;           // ceil(rows / stage_rows)
     int chunks;          // ceil(rows / RW)
     int slots;           // ring depth in chunks (a chunk = the RW rows of one row group): a multiple of rg, slots/rg a row group
+    int trigger;         // percent of a block's units after which it lets the next launch's blocks be scheduled (0: once x is in registers)
     int independent;     // 1: nothing this call reads or writes is touched by the launch before it, so no wait on that launch
     int prefetch;        // chunks a block requests before x has been asked for (the rest wait, so x's reads meet idle queues)
     int flush_units;     // units whose partial sums fit the partials area before they are added up
@@ -206,20 +207,25 @@ __global__ void __launch_bounds__(128) prepare_x_kernel(const void *x, int fmt_x
 // The same preparation inside the gemv kernel, by all its consumer threads, into shared memory.  f32 x: four threads a
 // block of 32 values (eight values each, coalesced 32-byte reads); the block's max and sum meet by two shuffles.
 // The arithmetic is quantize32's, value for value.
+#ifndef QB_GEMV_XU
+#define QB_GEMV_XU 4
+#endif
 template <bool PAIRED>
 __device__ __forceinline__ void prepare_x_in_block(const void *x, int fmt_x, int cols, uint8_t *out, int tid, int threads, uint32_t xbar)
 {
     const int blocks = cols / 32;
     uint8_t *meta = out + xprep_codes_bytes(cols);
+    constexpr int XU = QB_GEMV_XU;
     bool told = false;
     if (fmt_x == QB200_F32 && ((uintptr_t)x & 15) == 0) {
         const int items = blocks * 4;
-        // two items a thread and pass: both reads are issued before either is used
-        for (int base = 0; base < items; base += 2 * threads) {
-            float v[2][8];
-            bool valid[2];
+        // up to XU items a thread and pass: all reads are issued before any is used (a read takes about a
+        // microsecond while the matrix streams, a second pass would wait that long again)
+        for (int base = 0; base < items; base += XU * threads) {
+            float v[XU][8];
+            bool valid[XU];
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
+            for (int u = 0; u < XU; u++) {
                 const int it = base + u * threads + tid;
                 valid[u] = it < items;
                 float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
@@ -234,7 +240,8 @@ __device__ __forceinline__ void prepare_x_in_block(const void *x, int fmt_x, int
                 if ((tid & 31) == 0) mbar_arrive(xbar);
             }
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
+            for (int u = 0; u < XU; u++) {
+                if (!__any_sync(0xffffffffu, valid[u])) continue;
                 const int it = base + u * threads + tid, b = it >> 2, part = it & 3;
                 float amax = 0.f;
 #pragma unroll
@@ -704,8 +711,10 @@ __device__ __forceinline__ void rows_fast(const XK6 (&xr)[RUNS], const uint8_t *
 // and consumed by the cs warps of one row group.  Block b takes the contiguous chunks [b*C/grid, (b+1)*C/grid) of the
 // C chunks of the matrix (so blocks differ by at most one chunk); its j-th chunk goes to row group j % rg, and the rg
 // chunks dealt in one round are a unit.  RUNS = runs of x a warp holds (its column segment: runs seg, seg + cs, ...).
-template <int FMT, int RW, int RUNS, bool SUMS>
-__global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
+// NW = the most consumer warps a block of this variant has: 16 (one block an SM) or 4 (four blocks an SM, normally of
+// four successive launches: while one block prepares x or drains, the others keep the memory system busy).
+template <int FMT, int RW, int RUNS, bool SUMS, int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const GemvArgs p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = (uint64_t *)smem;
@@ -732,6 +741,7 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
         }
     };
     stamp(0);
+    if (p.trigger < 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint8_t *ring = smem + p.off_ring;
     const int chunk0 = (int)((long long)p.chunks * blockIdx.x / gridDim.x), chunk1 = (int)((long long)p.chunks * (blockIdx.x + 1) / gridDim.x);
     const int my_units = (chunk1 - chunk0 + p.rg - 1) / p.rg;
@@ -742,7 +752,8 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
         // Every lane issues its own chunk's copy (a lone thread needs some hundreds of cycles a copy for the address
         // arithmetic and the barrier calls, which would pace the whole kernel): a pass of the warp issues `step`
         // consecutive chunks, never more than there are slots, so no lane of a pass waits on another lane of it.
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        // (with x in a buffer shared between calls the consumers decide when the next call may be scheduled)
+        if (p.trigger == 0 && p.x) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         // A slot belongs to one row group for the whole kernel (spg slots a group): the warps that wait on a slot's
         // barrier are then always the ones that released its previous use, so a phase parity can never be mistaken for the
         // parity two phases back.
@@ -813,9 +824,15 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
     }
 #pragma unroll
     for (int j = 0; j < RUNS; j++) load_x(xr[j], p, xp, seg + j * p.cs, lane);
-    if (!p.x && lane == 0) mbar_arrive(xbar);
+    if (!p.x) {
+        // x came from a buffer that the next call's preparing kernel rewrites: every warp of the block has its part in
+        // registers before any of them lets that kernel be scheduled
+        if (lane == 0) mbar_arrive(xbar);
+        named_bar_sync(1, threads);
+    }
     // x is in registers: the next call's kernels may be scheduled as this grid's blocks retire
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (p.trigger == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int trigger_unit = p.trigger > 0 ? (int)((long long)my_units * p.trigger / 100) : -1;
     // whether every lane of this warp has both blocks of every run (then whole chunks take the branch-free path)
     bool whole_runs = false;
     if (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) whole_runs = (seg + (RUNS - 1) * p.cs + 1) * 64 <= p.cols / 32;
@@ -832,6 +849,7 @@ __global__ void __launch_bounds__(544, 1) gemv_kernel(const GemvArgs p)
     for (int i = 0; i < my_units; i++) {
         const int chunk = chunk0 + i * p.rg + rgi, s = rgi * spg + sl;
         const int row0 = chunk * RW;
+        if (i == trigger_unit) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         const int nvalid = chunk < chunk1 ? max(0, min(RW, p.rows - row0)) : 0;
         long long tq0 = p.timeline ? clock64() : 0;
         if (alive) alive = mbar_wait_warp(full0 + 8 * s, phase, abort_flag, p.status, STATUS_GEMV_WAIT);
@@ -947,7 +965,8 @@ static long long *g_timeline = nullptr;
 static int g_probe = 0;
 
 struct GemvPlan {
-    int rw, runs_per_warp, nw, cs, rg, stages, grid;
+    int rw, runs_per_warp, nw, nwmax, cs, rg, stages, grid;
+    bool deep;
     uint32_t stage_stride, smem_bytes;
     GemvArgs args;
 };
@@ -959,11 +978,11 @@ static int env_int(const char *name, int fallback)
 }
 
 // tuning overrides, read once when the library binds a device
-static struct { int warps, stage_bytes, rw, cs, stages, prekernel, prefetch, always_wait, ctas; } g_tune = { 16, 24576, 0, 0, 0, 0, 0, 0, 1 };
+static struct { int warps, stage_bytes, rw, cs, stages, prekernel, prefetch, always_wait, ctas, grid_ctas, trigger; } g_tune = { 0, 24576, 0, 0, 0, 0, 0, 0, 1, 0, 0 };
 
 static void read_tuning()
 {
-    g_tune.warps = env_int("QB200_GEMV_WARPS", 16);
+    g_tune.warps = env_int("QB200_GEMV_WARPS", 0);      // 4 or 16 forces a variant
     g_tune.stage_bytes = env_int("QB200_GEMV_STAGE_BYTES", 24576);
     g_tune.rw = env_int("QB200_GEMV_RW", 0);
     g_tune.cs = env_int("QB200_GEMV_CS", 0);
@@ -972,6 +991,8 @@ static void read_tuning()
     g_tune.prefetch = env_int("QB200_GEMV_PREFETCH", 0);
     g_tune.always_wait = env_int("QB200_GEMV_ALWAYS_WAIT", 0);
     g_tune.ctas = env_int("QB200_GEMV_CTAS", 1);
+    g_tune.grid_ctas = env_int("QB200_GEMV_GRID_CTAS", 0);
+    g_tune.trigger = env_int("QB200_GEMV_TRIGGER", 0);
 }
 
 // Runs of x that cover a row: 2048 columns each, but Q6_K runs are four super-blocks of one parity out of eight.
@@ -984,32 +1005,33 @@ static int runs_of(int fmt, int cols)
 static int max_runs_per_warp(int fmt) { return fmt == QB200_Q6_K ? 4 : 2; }
 static constexpr uint32_t PART_BYTES = 16384;
 
-// Splits the consumer warps into column segments x row groups and sizes the ring.
-static int plan_gemv(int fmt_a, int rows, int cols, GemvPlan &pl)
+// Splits the consumer warps of a block of at most `nwmax` warps (16 / nwmax such blocks share an SM) into column
+// segments x row groups and sizes the ring.  `rw_first` = the most rows a warp takes at once.
+static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, GemvPlan &pl)
 {
     const uint32_t row_bytes = (uint32_t)(cols / block_values(fmt_a) * block_bytes(fmt_a));
     const int runs = runs_of(fmt_a, cols);
-    int nw = g_tune.warps;
-    if (nw != 4 && nw != 8 && nw != 16) nw = 16;
-    const int ctas = g_tune.ctas == 2 ? 2 : 1;                   // blocks meant to share an SM
-    const uint32_t budget = ctas == 2 ? (uint32_t)(g_max_smem + 1024) / 2 - 2048 : (uint32_t)g_max_smem - 1024;
-    // column segments: no idle warps first, then as many segments as possible (small units, few registers of x)
+    int nw = nwmax;
+    const int ctas = 16 / nwmax;                                 // blocks meant to share an SM
+    const uint32_t budget = ctas > 1 ? (uint32_t)(g_max_smem + 1024) / ctas - 2048 : (uint32_t)g_max_smem - 1024;
+    // column segments: c segments leave nw / c row groups, each taking a chunk in ceil(runs / c) run times; the most
+    // rows per run time wins (warps that do not fill a row group stay out), then the most segments (few registers of x)
     int cs = 0;
-    double best = 1e30;
-    for (int c = 1; c <= nw; c *= 2) {
+    double best = 0.0;
+    for (int c = 1; c <= nw; c++) {
         const int per = (runs + c - 1) / c;
         if (per > max_runs_per_warp(fmt_a)) continue;
-        const double waste = (double)(per * c) / runs;
-        if (waste < best - 1e-9 || (waste < best + 1e-9 && c > cs)) { best = waste; cs = c; }
+        const double rate = (double)(nw / c) / per;
+        if (rate > best * (1.0 + 1e-9) || (rate > best * (1.0 - 1e-9) && c > cs)) { best = rate; cs = c; }
     }
-    if (g_tune.cs >= 1 && g_tune.cs <= nw && nw % g_tune.cs == 0 && (runs + g_tune.cs - 1) / g_tune.cs <= max_runs_per_warp(fmt_a)) cs = g_tune.cs;
+    if (g_tune.cs >= 1 && g_tune.cs <= nw && (runs + g_tune.cs - 1) / g_tune.cs <= max_runs_per_warp(fmt_a)) cs = g_tune.cs;
     if (cs == 0) return QB200_E_LIMIT;
     const int per = (runs + cs - 1) / cs, rg = nw / cs;
-    // rows a warp takes at once: the unit (rg * rw rows) near the target size, at least one row
-    int rw = 4;
+    nw = rg * cs;
+    // rows a warp takes at once: a chunk near the target size, at least one row
+    int rw = rw_first;
     while (rw > 1 && (uint64_t)rw * row_bytes > (uint64_t)g_tune.stage_bytes) rw /= 2;
-    if (g_tune.rw == 1 || g_tune.rw == 2 || g_tune.rw == 4) rw = g_tune.rw;
-    pl.rw = rw; pl.runs_per_warp = per; pl.nw = nw; pl.cs = cs; pl.rg = rg;
+    pl.rw = rw; pl.runs_per_warp = per; pl.nw = nw; pl.nwmax = nwmax; pl.cs = cs; pl.rg = rg;
     const int stage_rows = rg * rw;
     pl.stage_stride = ((uint32_t)rw * row_bytes + 48u + 127u) / 128u * 128u;       // one chunk
     GemvArgs &a = pl.args;
@@ -1022,14 +1044,17 @@ static int plan_gemv(int fmt_a, int rows, int cols, GemvPlan &pl)
     a.off_part = a.off_x + xprep_bytes(cols);
     // partial sums: room for every round of a block when that is small, else PART_BYTES with flushes in between
     const uint32_t round_bytes = (uint32_t)stage_rows * cs * 4u;
-    const int grid_guess = g_sm_count < 1 ? 1 : g_sm_count * ctas;
+    // blocks of one grid an SM: one, so that the blocks sharing an SM belong to successive launches
+    const int gctas = g_tune.grid_ctas >= 1 && g_tune.grid_ctas <= ctas ? g_tune.grid_ctas : 1;
+    const int grid_guess = g_sm_count < 1 ? 1 : g_sm_count * gctas;
     const uint32_t rounds = (uint32_t)(((a.chunks + grid_guess - 1) / grid_guess + rg - 1) / rg) + 1u;
-    const uint32_t part_bytes = rounds * round_bytes < PART_BYTES ? (rounds * round_bytes + 127u) / 128u * 128u : PART_BYTES;
+    const uint32_t part_cap = ctas > 1 ? PART_BYTES / 4 : PART_BYTES;
+    const uint32_t part_bytes = rounds * round_bytes < part_cap ? (rounds * round_bytes + 127u) / 128u * 128u : part_cap;
     a.off_ring = (a.off_part + part_bytes + 127u) / 128u * 128u;
     a.flush_units = (int)(part_bytes / round_bytes);
     if (a.flush_units < 1) return QB200_E_LIMIT;
     if (a.off_ring + (uint64_t)rg * pl.stage_stride > budget) return QB200_E_LIMIT;
-    pl.grid = a.units < g_sm_count * ctas ? a.units : g_sm_count * ctas;
+    pl.grid = a.chunks < g_sm_count * gctas ? a.chunks : g_sm_count * gctas;
     int slots = (int)((budget - a.off_ring) / pl.stage_stride);
     if (slots > MAX_SLOTS) slots = MAX_SLOTS;
     const int per_block = ((a.chunks + pl.grid - 1) / pl.grid + rg - 1) / rg;      // rounds of rg chunks a block takes at most
@@ -1038,14 +1063,32 @@ static int plan_gemv(int fmt_a, int rows, int cols, GemvPlan &pl)
     slots = slots / rg * rg;                     // every row group owns the same number of slots
     if (slots < rg) return QB200_E_LIMIT;
     pl.stages = slots;
+    pl.deep = slots >= 2 * rg || slots >= per_block * rg;        // a row group can compute on one chunk while the next arrives
     a.slots = slots;
+    a.trigger = g_tune.trigger > 99 ? 0 : g_tune.trigger;
     a.prefetch = g_tune.prefetch > 0 ? g_tune.prefetch : (slots + 1) / 2;
     a.slot_stride = pl.stage_stride;
     pl.smem_bytes = a.off_ring + (uint32_t)slots * pl.stage_stride;
     return 0;
 }
 
-template <int FMT, int RW, int RUNS, bool SUMS>
+// The plan of a call.  `overlapped` = the call is expected to run beside its neighbours in the stream (it shares no
+// buffer with the launch before it): then blocks of 4 consumer warps, one an SM, so that four successive launches are
+// resident together and one's start and end hide behind the others' streaming; the chunk shrinks until a row group has
+// two slots.  A call that has to wait for the one before it gets the whole SM instead: blocks of 16 warps.  The
+// checking variant (per-block sums) always takes the latter, a row at a time.
+static int plan_gemv(int fmt_a, int rows, int cols, bool sums, bool overlapped, GemvPlan &pl)
+{
+    const int forced = g_tune.warps;
+    const int rw_first = sums ? 1 : (g_tune.rw == 1 || g_tune.rw == 2 || g_tune.rw == 4) ? g_tune.rw : 4;
+    if (!sums && forced != 16 && (overlapped || forced == 4)) {
+        for (int rw = rw_first; rw >= 1; rw /= 2)
+            if (plan_blocks(fmt_a, rows, cols, 4, rw, pl) == 0 && pl.deep) return 0;
+    }
+    return plan_blocks(fmt_a, rows, cols, 16, rw_first, pl);
+}
+
+template <int FMT, int RW, int RUNS, bool SUMS, int NW>
 static cudaError_t launch_one(const GemvPlan &pl, cudaStream_t stream)
 {
     cudaLaunchConfig_t cfg;
@@ -1059,38 +1102,44 @@ static cudaError_t launch_one(const GemvPlan &pl, cudaStream_t stream)
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, RW, RUNS, SUMS>, pl.args);
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, RW, RUNS, SUMS, NW>, pl.args);
 }
 
-template <int FMT, int RW, bool SUMS>
+template <int FMT, int RW, bool SUMS, int NW>
 static cudaError_t launch_runs(const GemvPlan &pl, cudaStream_t stream)
 {
-    if (pl.runs_per_warp == 1) return launch_one<FMT, RW, 1, SUMS>(pl, stream);
-    if (pl.runs_per_warp == 2 || FMT != QB200_Q6_K) return launch_one<FMT, RW, 2, SUMS>(pl, stream);
-    if (pl.runs_per_warp == 3) return launch_one<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS>(pl, stream);
-    return launch_one<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS>(pl, stream);
+    if (pl.runs_per_warp == 1) return launch_one<FMT, RW, 1, SUMS, NW>(pl, stream);
+    if (pl.runs_per_warp == 2 || FMT != QB200_Q6_K) return launch_one<FMT, RW, 2, SUMS, NW>(pl, stream);
+    if (pl.runs_per_warp == 3) return launch_one<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS, NW>(pl, stream);
+    return launch_one<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS, NW>(pl, stream);
+}
+
+template <int FMT, int NW>
+static cudaError_t launch_rows(const GemvPlan &pl, cudaStream_t stream)
+{
+    switch (pl.rw) {
+    case 4: return launch_runs<FMT, 4, false, NW>(pl, stream);
+    case 2: return launch_runs<FMT, 2, false, NW>(pl, stream);
+    default: return launch_runs<FMT, 1, false, NW>(pl, stream);
+    }
 }
 
 template <int FMT>
 static cudaError_t launch_fmt(const GemvPlan &pl, bool sums, cudaStream_t stream)
 {
-    if (sums) return launch_runs<FMT, 1, true>(pl, stream);      // the checking variant: a row at a time
-    switch (pl.rw) {
-    case 4: return launch_runs<FMT, 4, false>(pl, stream);
-    case 2: return launch_runs<FMT, 2, false>(pl, stream);
-    default: return launch_runs<FMT, 1, false>(pl, stream);
-    }
+    if (sums) return launch_runs<FMT, 1, true, 16>(pl, stream);      // the checking variant: a row at a time
+    return pl.nwmax == 4 ? launch_rows<FMT, 4>(pl, stream) : launch_rows<FMT, 16>(pl, stream);
 }
 
-template <int FMT, int RW, bool SUMS>
+template <int FMT, int RW, bool SUMS, int NW>
 static cudaError_t set_attr_runs(int bytes)
 {
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 1, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
-    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 2, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 1, SUMS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 2, SUMS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
     if (FMT == QB200_Q6_K) {
-        if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
-        e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+        e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     }
     return e;
 }
@@ -1099,10 +1148,14 @@ template <int FMT>
 static cudaError_t set_attr(int bytes)
 {
     cudaError_t e;
-    if ((e = set_attr_runs<FMT, 1, true>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 1, false>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 2, false>(bytes))) return e;
-    return set_attr_runs<FMT, 4, false>(bytes);
+    const int small = (bytes + 1024) / 4 - 2048;                 // what a block of the four-an-SM variant may ask for
+    if ((e = set_attr_runs<FMT, 1, true, 16>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 1, false, 16>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 2, false, 16>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 4, false, 16>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 1, false, 4>(small))) return e;
+    if ((e = set_attr_runs<FMT, 2, false, 4>(small))) return e;
+    return set_attr_runs<FMT, 4, false, 4>(small);
 }
 
 cudaError_t gemv_init(int sm_count, int max_smem, int *status)
@@ -1137,21 +1190,27 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
                 cudaStream_t stream)
 {
     if (rows == 0) return 0;
+    // does this call touch anything the launch before it reads or writes?  (see t_prev)
+    const size_t row_bytes = (size_t)(cols / block_values(fmt_a)) * block_bytes(fmt_a);
+    const Touched ta = { (const uint8_t *)a, (size_t)rows * row_bytes };
+    const Touched tx = { (const uint8_t *)x, fmt_x == QB200_F32 ? (size_t)cols * 4 : (size_t)(cols / 32) * block_bytes(fmt_x) };
+    const Touched ty = { (const uint8_t *)y, (size_t)rows * 4 };
+    bool independent = !sums && t_prev.valid && t_prev.stream == stream && !g_tune.always_wait;
+    if (independent) independent = !overlap(tx, t_prev.y) && !overlap(ta, t_prev.y) && !overlap(ty, t_prev.y) && !overlap(ty, t_prev.x) && !overlap(ty, t_prev.a);
+    t_prev.stream = stream; t_prev.valid = !sums; t_prev.a = ta; t_prev.x = tx; t_prev.y = ty;
     // the last few shapes' plans are kept: a decode loop calls the same shapes over and over
-    static thread_local struct { int fmt, rows, cols, rw; GemvPlan plan; } cache[8];
+    static thread_local struct { int fmt, rows, cols, kind; GemvPlan plan; } cache[8];
     static thread_local int cached = 0, next = 0;
     GemvPlan pl;
     bool hit = false;
-    const int want_rw = sums ? 1 : 0;
+    const bool overlapped = independent && !g_tune.prekernel;
+    const int kind = sums ? 2 : overlapped ? 1 : 0;
     for (int i = 0; i < cached && !hit; i++)
-        if (cache[i].fmt == fmt_a && cache[i].rows == rows && cache[i].cols == cols && cache[i].rw == want_rw) { pl = cache[i].plan; hit = true; }
+        if (cache[i].fmt == fmt_a && cache[i].rows == rows && cache[i].cols == cols && cache[i].kind == kind) { pl = cache[i].plan; hit = true; }
     if (!hit) {
-        const int keep_rw = g_tune.rw;
-        if (sums) g_tune.rw = 1;
-        int rc = plan_gemv(fmt_a, rows, cols, pl);
-        g_tune.rw = keep_rw;
+        int rc = plan_gemv(fmt_a, rows, cols, sums != nullptr, overlapped, pl);
         if (rc) return rc;
-        cache[next].fmt = fmt_a; cache[next].rows = rows; cache[next].cols = cols; cache[next].rw = want_rw; cache[next].plan = pl;
+        cache[next].fmt = fmt_a; cache[next].rows = rows; cache[next].cols = cols; cache[next].kind = kind; cache[next].plan = pl;
         next = (next + 1) % 8;
         if (cached < 8) cached++;
     }
@@ -1159,15 +1218,7 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     pl.args.xprep = (const uint8_t *)scratch;
     pl.args.x = g_tune.prekernel ? nullptr : x;
     pl.args.fmt_x = fmt_x;
-    {
-        const Touched ta = { (const uint8_t *)a, (size_t)rows * pl.args.row_bytes };
-        const Touched tx = { (const uint8_t *)x, fmt_x == QB200_F32 ? (size_t)cols * 4 : (size_t)(cols / 32) * block_bytes(fmt_x) };
-        const Touched ty = { (const uint8_t *)y, (size_t)rows * 4 };
-        bool independent = !sums && t_prev.valid && t_prev.stream == stream;
-        if (independent) independent = !overlap(tx, t_prev.y) && !overlap(ta, t_prev.y) && !overlap(ty, t_prev.y) && !overlap(ty, t_prev.x) && !overlap(ty, t_prev.a);
-        pl.args.independent = independent && !g_tune.always_wait ? 1 : 0;
-        t_prev.stream = stream; t_prev.valid = !sums; t_prev.a = ta; t_prev.x = tx; t_prev.y = ty;
-    }
+    pl.args.independent = independent ? 1 : 0;
     pl.args.y = y;
     pl.args.sums = sums;
     pl.args.status = g_status;
@@ -1258,7 +1309,7 @@ int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, floa
     int rc = noalloc_setup(device, &dev);
     if (rc) return rc;
     GemvPlan pl;
-    if ((rc = plan_gemv(fmt_a, rows, cols, pl))) return rc;
+    if ((rc = plan_gemv(fmt_a, rows, cols, false, false, pl))) return rc;
     pl.args.a = (const uint8_t *)a;
     pl.args.xprep = (const uint8_t *)dev->scratch;
     pl.args.x = nullptr;
@@ -1298,11 +1349,13 @@ int gemv_noalloc_status(int *value)
 }
 
 // The plan for a shape: {rc, warps, column segments, rows a warp, ring depth, grid, slot bytes, shared bytes, runs a warp}.
+static int g_describe_overlapped = 0;
+void gemv_describe_mode(int overlapped) { g_describe_overlapped = overlapped; }
 void gemv_describe(int fmt_a, int rows, int cols, int *out9)
 {
     GemvPlan pl;
     memset(&pl, 0, sizeof pl);
-    int rc = plan_gemv(fmt_a, rows, cols, pl);
+    int rc = plan_gemv(fmt_a, rows, cols, false, g_describe_overlapped != 0, pl);
     out9[0] = rc; out9[1] = pl.nw; out9[2] = pl.cs; out9[3] = pl.rw; out9[4] = pl.stages; out9[5] = pl.grid;
     out9[6] = (int)pl.stage_stride; out9[7] = (int)pl.smem_bytes; out9[8] = pl.runs_per_warp;
 }

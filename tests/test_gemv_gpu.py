@@ -92,6 +92,40 @@ def test_many_chunks_per_block_back_to_back(oracle):
     assert np.all(np.abs(y.cpu().numpy().astype(np.float64) - ref) <= REL * mag)
 
 
+@pytest.mark.parametrize("fmt_a,rows,cols", [
+    (B.Q8_0, 4096, 4096), (B.Q8_0, 1021, 4064), (B.Q4_0, 8192, 8192), (B.Q4_0, 2049, 8160), (B.Q4_0, 300, 16384),
+    (B.Q4_0, 64, 32768), (B.Q4_K, 4096, 4096), (B.Q4_K, 1030, 11008), (B.Q6_K, 4096, 4096), (B.Q6_K, 1030, 11008),
+    (B.Q6_K, 515, 2304), (B.Q4_0, 28672, 8192)])
+def test_independent_calls_in_a_row(oracle, fmt_a, rows, cols):
+    # six calls that share no output: from the second on each is independent of the launch before it and takes the
+    # variant of four small blocks an SM, whose blocks run beside those of the neighbouring launches; then three calls
+    # into one y, which go back to the whole-SM variant.  Every output is checked.
+    import torch
+    n = 6
+    ws = [B.make_weights(fmt_a, rows, cols, 900 + i) for i in range(2)]
+    xf = B.make_activations(cols, 910)
+    o = H.ops()
+    dws, dx = [H.dev(w) for w in ws], H.dev(xf)
+    ys = [H.empty(rows, torch.float32) for _ in range(n)]
+    for i in range(n):
+        o.GemvBlocks(fmt_a, dws[i % 2], dx, ys[i], rows, cols, fmt_x=B.F32)
+    for i in range(3):
+        o.GemvBlocks(fmt_a, dws[i % 2], dx, ys[0], rows, cols, fmt_x=B.F32)
+    assert o.gpu.status() == 0
+    if fmt_a in (B.Q8_0, B.Q4_0):
+        refs = [oracle.gemv_blocks(fmt_a, B.F32, w, xf, rows, cols, order=1, want_abs=True) for w in ws]
+    else:                      # K-quant rows: float64 on the stored values of the matrix and of x as Q8_0
+        xv = H.x_values(B.F32, oracle, xf, cols)
+        refs = []
+        for w in ws:
+            y64 = oracle.gemv_f64(fmt_a, w, xv, rows, cols)
+            refs.append((y64, np.max(np.abs(y64))))
+    for i in range(n):
+        ref, mag = refs[i % 2]
+        assert np.all(np.abs(ys[i].cpu().numpy().astype(np.float64) - ref) <= REL * mag), i
+    assert np.array_equal(ys[2].cpu().numpy(), ys[4].cpu().numpy())
+
+
 def test_reference_signature_same_format(oracle):
     # GemvBlocks<TN>(a, x, y, rows, cols): x in a's format (src/BlockProducts.cs:178)
     for fmt in (B.Q8_0, B.Q4_0):
