@@ -299,9 +299,18 @@ def main():
         if world > 1:
             dist.all_reduce(et, op=dist.ReduceOp.MAX)
         e_s = float(et.item())
+        # the bound of this leg: a plain copy of one matrix from the same pinned buffer, timed the same way
+        dst = torch.empty(WEIGHT_BYTES, dtype=torch.uint8, device=dev)
+        dst.copy_(pinned_w[0], non_blocking=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(4):
+            dst.copy_(pinned_w[i % 2], non_blocking=True)
+        torch.cuda.synchronize()
+        h2d_gbs = 4 * WEIGHT_BYTES / (time.perf_counter() - t0) / 1e9
         e2e = {"value": world * e_steps * LAYERS * ALGO_BYTES / e_s / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": LAYERS * (WEIGHT_BYTES + COLS * 4), "d2h_bytes_per_step": LAYERS * ROWS * 4,
-               "steps": e_steps, "ms_per_step": e_s * 1e3 / e_steps}
+               "steps": e_steps, "ms_per_step": e_s * 1e3 / e_steps, "pinned_h2d_copy_GBs": h2d_gbs}
 
     sharded = None if args.no_extra else sharded_gemv_leg(ops, torch, dist, rank, world, dev)
     abt = abt_leg(ops, torch, dev) if (world == 1 and not args.no_extra) else None

@@ -46,28 +46,42 @@ struct MatmulArgs {
     int32_t *sums;
     int *status;
     int m, n, kb;
-    int probe;       // tuning aid: 1 = no arithmetic, 2 = no tensor-memory reads, 3 = neither; 0 in normal use
+    int probe;       // tuning aid: 1 = no arithmetic, 2 = no tensor-memory reads; 0 in normal use
 };
 
 // ---------------------------------------------------------------------------------- step 1: operands for the tensor cores
 
 // A block of 256 threads re-lays 32 rows x 8 k-blocks.  The rows' bytes (8 consecutive blocks of a row are contiguous
-// in the raw operand, 2-byte aligned) are first copied to shared memory with coalesced 2-byte loads; then a thread a
+// in the raw operand, 2-byte aligned) are first copied to shared memory with coalesced loads (16 bytes wide when the
+// rows lie on 16-byte boundaries, else 2); then a thread a
 // block assembles its 32 int8 values and its scale.  Row r of tile t lands at byte
 // (t*kb + b)*4096 + j*2048 + (r/8)*128 + (r%8)*16 for its bytes 16j..16j+15, and its scale at ((t*kb + b)*128 + r).
 // Rows past `rows` (the padding of the last tile) are written as zeros.
 template <int FMT>
 __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int rows, int kb, uint8_t *codes, float *scales)
 {
-    constexpr int BB = block_bytes(FMT), HALVES = 8 * BB / 2, PITCH = HALVES + 1;      // halfwords a row segment; odd pitch
-    __shared__ uint16_t seg[32 * PITCH];
+    // halfwords a row segment; the pitch is an odd number of 32-bit words, so the 32 rows start in 32 different banks
+    constexpr int BB = block_bytes(FMT), HALVES = 8 * BB / 2, PITCH = HALVES + 2, VECS = 8 * BB / 16;
+    __shared__ __align__(16) uint16_t seg[32 * PITCH];
     const int r0 = blockIdx.x * 32, b0 = blockIdx.y * 8;
     const int nb = min(8, kb - b0), halves = nb * BB / 2;
-    for (int idx = threadIdx.x; idx < 32 * HALVES; idx += 256) {
-        const int rr = idx / HALVES, h = idx - rr * HALVES;
-        uint16_t v = 0;
-        if (r0 + rr < rows && h < halves) v = __ldg((const uint16_t *)(raw + ((size_t)(r0 + rr) * kb + b0) * BB) + h);
-        seg[rr * PITCH + h] = v;
+    const size_t row_bytes = (size_t)kb * BB;
+    if (nb == 8 && (((uintptr_t)raw | row_bytes) & 15) == 0) {
+        // whole segments on 16-byte boundaries (8 blocks are 272 or 144 bytes): 16-byte loads
+        for (int idx = threadIdx.x; idx < 32 * VECS; idx += 256) {
+            const int rr = idx / VECS, c = idx - rr * VECS;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r0 + rr < rows) v = __ldg((const uint4 *)(raw + (size_t)(r0 + rr) * row_bytes + (size_t)b0 * BB) + c);
+            uint32_t *dst = (uint32_t *)(seg + rr * PITCH) + c * 4;
+            dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < 32 * HALVES; idx += 256) {
+            const int rr = idx / HALVES, h = idx - rr * HALVES;
+            uint16_t v = 0;
+            if (r0 + rr < rows && h < halves) v = __ldg((const uint16_t *)(raw + ((size_t)(r0 + rr) * kb + b0) * BB) + h);
+            seg[rr * PITCH + h] = v;
+        }
     }
     __syncthreads();
     const int rl = threadIdx.x & 31, bl = threadIdx.x >> 5, r = r0 + rl, b = b0 + bl;
@@ -429,8 +443,11 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, float *c, 
     uint8_t *b_codes = (w += align256(packed_scales_bytes(m, k)));
     float *b_scales = (float *)(w += align256(packed_codes_bytes(n, k)));
     cudaError_t e;
-    if ((e = pack(fmt_a, a, m, k, a_codes, a_scales, stream))) return (int)e;
-    if ((e = pack(fmt_b, b, n, k, b_codes, b_scales, stream))) return (int)e;
+    if (!(g_mm_probe & 8)) {                // (tuning aid: 8 = operands as packed by an earlier call, 4 = no product)
+        if ((e = pack(fmt_a, a, m, k, a_codes, a_scales, stream))) return (int)e;
+        if ((e = pack(fmt_b, b, n, k, b_codes, b_scales, stream))) return (int)e;
+    }
+    if (g_mm_probe & 4) return 0;
     MatmulArgs args;
     args.a.codes = a_codes; args.a.scales = a_scales;
     args.b.codes = b_codes; args.b.scales = b_scales;
