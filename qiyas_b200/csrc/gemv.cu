@@ -506,14 +506,18 @@ __device__ __forceinline__ float row_dot(const XPair &x, const uint8_t *row, int
 
 // The same for a lane whose two blocks both exist, with the first block's alignment known at compile time (the second
 // block, 34 or 18 bytes on, has the other alignment): no branches, so the loads of several rows can be in flight at once.
-template <int FMT, bool Q4>
+// MASK: the row may end inside this lane's pair or before it.  A lane without blocks does nothing; a lane with one reads
+// its missing partner all the same (the bytes after the row: the next row or the slot's padding) and takes its scale as 0.
+template <int FMT, bool Q4, bool MASK>
 __device__ __forceinline__ float row_dot_fast(const XPair &x, const uint8_t *row, float acc)
 {
     constexpr int BB = block_bytes(FMT), NWORDS = FMT == QB200_Q8_0 ? 8 : 4;
+    if (MASK && x.count == 0) return acc;
     const uint8_t *q = row + (size_t)x.first * BB;
     uint32_t w0[NWORDS], w1[NWORDS], h0, h1;
     load_block_at<NWORDS, Q4>(q, w0, h0);
     load_block_at<NWORDS, !Q4>(q + BB, w1, h1);
+    if (MASK && x.count < 2) h1 = 0;
     int dot0, dot1;
     if (FMT == QB200_Q8_0) {
         int e0 = 0, o0 = 0, e1 = 0, o1 = 0;
@@ -544,16 +548,30 @@ __device__ __forceinline__ float row_dot_fast(const XPair &x, const uint8_t *row
 }
 
 // RW whole rows of a unit against this warp's runs of x; row r's first block has alignment Q4E (even r) or Q4O (odd r).
-template <int FMT, int RW, int RUNS, bool Q4E, bool Q4O>
+template <int FMT, int RW, int RUNS, bool Q4E, bool Q4O, bool MASK>
 __device__ __forceinline__ void rows_fast(const XPair (&xr)[RUNS], const uint8_t *rows, uint32_t row_bytes, float (&acc)[RW])
 {
 #pragma unroll
     for (int j = 0; j < RUNS; j++) {
 #pragma unroll
         for (int r = 0; r < RW; r++) {
-            if (r & 1) acc[r] = row_dot_fast<FMT, Q4O>(xr[j], rows + (size_t)r * row_bytes, acc[r]);
-            else acc[r] = row_dot_fast<FMT, Q4E>(xr[j], rows + (size_t)r * row_bytes, acc[r]);
+            if (r & 1) acc[r] = row_dot_fast<FMT, Q4O, MASK>(xr[j], rows + (size_t)r * row_bytes, acc[r]);
+            else acc[r] = row_dot_fast<FMT, Q4E, MASK>(xr[j], rows + (size_t)r * row_bytes, acc[r]);
         }
+    }
+}
+
+// The four alignment cases of a chunk: whether its first row's first block of this lane starts on 4 bytes, and whether
+// the next row has the other alignment (rows of an odd number of halfwords).
+template <int FMT, int RW, int RUNS, bool MASK>
+__device__ __forceinline__ void rows_fast_any(const XPair (&xr)[RUNS], const uint8_t *rows, uint32_t row_bytes, bool q4, bool flip, float (&acc)[RW])
+{
+    if (!flip) {
+        if (q4) rows_fast<FMT, RW, RUNS, true, true, MASK>(xr, rows, row_bytes, acc);
+        else rows_fast<FMT, RW, RUNS, false, false, MASK>(xr, rows, row_bytes, acc);
+    } else {
+        if (q4) rows_fast<FMT, RW, RUNS, true, false, MASK>(xr, rows, row_bytes, acc);
+        else rows_fast<FMT, RW, RUNS, false, true, MASK>(xr, rows, row_bytes, acc);
     }
 }
 
@@ -784,9 +802,24 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
                         head_end = b0;
                         tail_begin = b1;
                     }
-                    // at most 15 halfwords on either side (none when the chunk starts and ends on 16 bytes)
-                    for (const uint8_t *src = g0; src < head_end; src += 2) *(uint16_t *)(slot + (src - g0)) = __ldg((const uint16_t *)src);
-                    for (const uint8_t *src = tail_begin; src < g1; src += 2) *(uint16_t *)(slot + (src - g0)) = __ldg((const uint16_t *)src);
+                    // at most 7 halfwords on either side (none when the chunk starts and ends on 16 bytes); all reads
+                    // are issued before the first is stored.  (A chunk shorter than 16 bytes has no middle: slow loop.)
+                    if (head_end - g0 <= 14 && g1 - tail_begin <= 14) {
+                        uint16_t hv[7], tv[7];
+#pragma unroll
+                        for (int i = 0; i < 7; i++) {
+                            hv[i] = g0 + 2 * i < head_end ? __ldg((const uint16_t *)(g0 + 2 * i)) : (uint16_t)0;
+                            tv[i] = tail_begin + 2 * i < g1 ? __ldg((const uint16_t *)(tail_begin + 2 * i)) : (uint16_t)0;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 7; i++) {
+                            if (g0 + 2 * i < head_end) *(uint16_t *)(slot + 2 * i) = hv[i];
+                            if (tail_begin + 2 * i < g1) *(uint16_t *)(slot + (tail_begin - g0) + 2 * i) = tv[i];
+                        }
+                    } else {
+                        for (const uint8_t *src = g0; src < head_end; src += 2) *(uint16_t *)(slot + (src - g0)) = __ldg((const uint16_t *)src);
+                        for (const uint8_t *src = tail_begin; src < g1; src += 2) *(uint16_t *)(slot + (src - g0)) = __ldg((const uint16_t *)src);
+                    }
                     mbar_arrive(full0 + 8 * s);
                 }
             }
@@ -864,15 +897,10 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
             for (int r = 0; r < RW; r++) acc[r] = 0.f;
             bool done = (p.probe & 1) != 0;
             if constexpr ((FMT == QB200_Q8_0 || FMT == QB200_Q4_0) && !SUMS) {
-                if (!done && whole_runs && nvalid == RW) {
+                if (!done && nvalid == RW) {
                     const bool q4 = (((uint32_t)(uintptr_t)rows + first_off) & 2u) == 0;
-                    if (!p.row_flip) {
-                        if (q4) rows_fast<FMT, RW, RUNS, true, true>(xr, rows, p.row_bytes, acc);
-                        else rows_fast<FMT, RW, RUNS, false, false>(xr, rows, p.row_bytes, acc);
-                    } else {
-                        if (q4) rows_fast<FMT, RW, RUNS, true, false>(xr, rows, p.row_bytes, acc);
-                        else rows_fast<FMT, RW, RUNS, false, true>(xr, rows, p.row_bytes, acc);
-                    }
+                    if (whole_runs) rows_fast_any<FMT, RW, RUNS, false>(xr, rows, p.row_bytes, q4, p.row_flip != 0, acc);
+                    else rows_fast_any<FMT, RW, RUNS, true>(xr, rows, p.row_bytes, q4, p.row_flip != 0, acc);
                     done = true;
                 }
             }
@@ -1033,7 +1061,7 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, G
     while (rw > 1 && (uint64_t)rw * row_bytes > (uint64_t)g_tune.stage_bytes) rw /= 2;
     pl.rw = rw; pl.runs_per_warp = per; pl.nw = nw; pl.nwmax = nwmax; pl.cs = cs; pl.rg = rg;
     const int stage_rows = rg * rw;
-    pl.stage_stride = ((uint32_t)rw * row_bytes + 48u + 127u) / 128u * 128u;       // one chunk
+    pl.stage_stride = ((uint32_t)rw * row_bytes + 64u + 127u) / 128u * 128u;       // one chunk, up to 15 bytes of misalignment before it and a block's length of slack after it
     GemvArgs &a = pl.args;
     a.row_bytes = row_bytes;
     a.nw = nw; a.cs = cs; a.rg = rg; a.stage_rows = stage_rows;
