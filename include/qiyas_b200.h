@@ -91,6 +91,15 @@ int qb200_device_status(int *status);
  *   cols must be whole blocks of a's format, and at most 65536.  rows >= 0. */
 int qb200_gemv_blocks(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, void *stream);
 
+/* The block branch of the public gemv, GpuOps.Gemv<TN> (src/GpuOps.cs:277-285: rent f32 lanes,
+ * GemvBlocks, then Back, src/GpuOps.cs:964-975 -> Ptx.LanesToBlock, src/Ptx.Blocks.cs:11-96), in one
+ * launch: y_lanes[rows] as qb200_gemv_blocks writes it, and y_blocks = those lanes as
+ * ceil(rows/32) blocks of fmt_y (Q8_0 or Q4_0; values past `rows` count as zero), byte for byte
+ * what qb200_encode gives on y_lanes.  y_lanes is the f32 scratch the reference rents; it must be
+ * given.  Other arguments as qb200_gemv_blocks. */
+int qb200_gemv_blocks_back(int fmt_a, int fmt_x, const void *a, const void *x, float *y_lanes, int fmt_y, void *y_blocks, int rows,
+                           int cols, void *stream);
+
 /* As qb200_gemv_blocks, and also writes the exact s32 sum of every 32-value block,
  * sums[r * (cols/32) + b] (Q8_0 / Q4_0: sum qA*qX with Q4_0's q-8; Q4_K: sum q*qX per sub-block;
  * Q6_K: scA*sum16 + scB*sum16 with q-32).  For parity checks of the integer part. */

@@ -25,6 +25,7 @@ SIGNATURES = {
     "qb200_lane_name": (C.c_char_p, [_I, _I]),
     "qb200_device_status": (_I, [C.POINTER(_I)]),
     "qb200_gemv_blocks": (_I, [_I, _I, _P, _P, _P, _I, _I, _P]),
+    "qb200_gemv_blocks_back": (_I, [_I, _I, _P, _P, _P, _I, _P, _I, _I, _P]),
     "qb200_gemv_block_sums": (_I, [_I, _I, _P, _P, _P, _P, _I, _I, _P]),
     "qb200_gemv_blocks_host": (_I, [_I, _I, _P, _P, _P, _I, _I]),
     "qb200_gemv_blocks_noalloc": (_I, [_I, _I, _P, _P, _P, _I, _I, _P]),

@@ -171,7 +171,20 @@ int qb200_gemv_blocks(int fmt_a, int fmt_x, const void *a, const void *x, float 
 {
     int rc = check_gemv(fmt_a, fmt_x, a, x, y, rows, cols);
     if (rc) return rc;
-    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, nullptr, rows, cols, g_xprep.ptr, (cudaStream_t)stream), "gemv_blocks");
+    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, nullptr, 0, nullptr, rows, cols, g_xprep.ptr, (cudaStream_t)stream), "gemv_blocks");
+}
+
+// The block branch of the public gemv (reference src/GpuOps.cs:277-285) in one launch: f32 lanes and their `Back`.
+int qb200_gemv_blocks_back(int fmt_a, int fmt_x, const void *a, const void *x, float *y_lanes, int fmt_y, void *y_blocks, int rows,
+                           int cols, void *stream)
+{
+    int rc = check_gemv(fmt_a, fmt_x, a, x, y_lanes, rows, cols);
+    if (rc) return rc;
+    if (fmt_y != QB200_Q8_0 && fmt_y != QB200_Q4_0)
+        return fail(QB200_E_FORMAT, "%s: the gemv encodes its output as Q8_0 or Q4_0; use qb200_encode for the others", fmt_name(fmt_y));
+    if (rows > 0 && (!y_blocks || ((uintptr_t)y_blocks & 1))) return fail(QB200_E_POINTER, "null or misaligned y_blocks");
+    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y_lanes, nullptr, fmt_y, y_blocks, rows, cols, g_xprep.ptr, (cudaStream_t)stream),
+                  "gemv_blocks_back");
 }
 
 int qb200_gemv_block_sums(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols, void *stream)
@@ -179,7 +192,7 @@ int qb200_gemv_block_sums(int fmt_a, int fmt_x, const void *a, const void *x, fl
     int rc = check_gemv(fmt_a, fmt_x, a, x, y, rows, cols);
     if (rc) return rc;
     if (rows > 0 && (!sums || ((uintptr_t)sums & 3))) return fail(QB200_E_POINTER, "null or misaligned sums");
-    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, sums, rows, cols, g_xprep.ptr, (cudaStream_t)stream), "gemv_block_sums");
+    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, sums, 0, nullptr, rows, cols, g_xprep.ptr, (cudaStream_t)stream), "gemv_block_sums");
 }
 
 int qb200_gemv_blocks_host(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols)

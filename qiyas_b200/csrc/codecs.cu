@@ -4,16 +4,12 @@
 // (src/Blocks.cs:31-215) operation for operation, in IEEE round-to-nearest f32 with no contraction, so the bytes and
 // values equal the CPU's; Q4_0's rounding is the reference device's fma + floor (src/Ptx.Blocks.cs:80-85).
 #include "common.cuh"
+#include "encode_blocks.cuh"
 #include "launch.h"
 
 namespace qb {
 
-__device__ __forceinline__ uint16_t f2h_bits(float v) { return __half_as_ushort(__float2half_rn(v)); }
-__device__ __forceinline__ float h2f_bits(uint16_t h) { return __half2float(__ushort_as_half(h)); }
-// blocks are 2-byte aligned and every f16 field sits at an even offset: one 16-bit store
-__device__ __forceinline__ void put16(uint8_t *p, uint16_t v) { *reinterpret_cast<volatile uint16_t *>(p) = v; }
 __device__ __forceinline__ uint16_t get16(const uint8_t *p) { return (uint16_t)(p[0] | p[1] << 8); }
-__device__ __forceinline__ int round_clamp(float x, int lo, int hi) { return max(lo, min(hi, __float2int_rn(x))); }
 
 // values [first, first + count) of the lane array, zero past n (src/Ptx.Blocks.cs:36-44)
 template <int COUNT>
@@ -23,47 +19,23 @@ __device__ __forceinline__ void load_lanes(const float *lanes, int64_t first, in
     for (int i = 0; i < COUNT; i++) v[i] = first + i < n ? lanes[first + i] : 0.f;
 }
 
-// EncodeQ8_0 (src/Blocks.cs:37-45; device src/Ptx.Blocks.cs:54-73)
+// EncodeQ8_0 / EncodeQ4_0, a thread a block (the block arithmetic is in encode_blocks.cuh)
 __global__ void encode_q8_0_kernel(const float *lanes, uint8_t *out, int64_t n, int64_t blocks)
 {
     int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= blocks) return;
     float v[32];
     load_lanes<32>(lanes, b * 32, n, v);
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(v[i]));
-    uint16_t h = f2h_bits(__fdiv_rn(amax, 127.f));
-    float d = h2f_bits(h), id = d == 0.f ? 0.f : __fdiv_rn(1.f, d);
-    uint8_t *o = out + b * 34;
-    put16(o, h);
-#pragma unroll
-    for (int i = 0; i < 32; i++) o[2 + i] = (uint8_t)(int8_t)round_clamp(__fmul_rn(v[i], id), -127, 127);
+    encode_q8_0_block(v, out + b * 34);
 }
 
-// EncodeQ4_0 (src/Blocks.cs:58-70) with the device's rounding: fma(v, id, 8.5) then floor (src/Ptx.Blocks.cs:80-85)
 __global__ void encode_q4_0_kernel(const float *lanes, uint8_t *out, int64_t n, int64_t blocks)
 {
     int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= blocks) return;
     float v[32];
     load_lanes<32>(lanes, b * 32, n, v);
-    float amax = 0.f, mx = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; i++) {
-        float a = fabsf(v[i]);
-        if (a > amax) { amax = a; mx = v[i]; }
-    }
-    uint16_t h = f2h_bits(__fdiv_rn(mx, -8.f));
-    float d = h2f_bits(h), id = d == 0.f ? 0.f : __fdiv_rn(1.f, d);
-    uint8_t *o = out + b * 18;
-    put16(o, h);
-#pragma unroll
-    for (int i = 0; i < 16; i++) {
-        int lo = max(0, min(15, __float2int_rd(__fmaf_rn(v[i], id, 8.5f))));
-        int hi = max(0, min(15, __float2int_rd(__fmaf_rn(v[i + 16], id, 8.5f))));
-        o[2 + i] = (uint8_t)(lo | hi << 4);
-    }
+    encode_q4_0_block(v, out + b * 18);
 }
 
 // EncodeQ4_K (src/Blocks.cs:98-148), a thread a super-block

@@ -18,6 +18,7 @@
 // (src/BlockProducts.cs:158-161).  The order in which a row's blocks are added differs (lanes, then a shuffle tree,
 // then column segments in ascending order); it is fixed for a given shape, so results are reproducible run to run.
 #include "common.cuh"
+#include "encode_blocks.cuh"
 #include "launch.h"
 
 namespace qb {
@@ -28,6 +29,9 @@ struct GemvArgs {
     const void *x;        // x as the caller gave it: prepared inside the kernel, in shared memory at off_x
     int fmt_x;
     float *y;
+    uint8_t *yb;         // optional: y again as Q8_0 / Q4_0 blocks (fmt_y), encoded by the block that computed the rows
+    int fmt_y;
+    int chunk_align;     // block boundaries fall on multiples of this many chunks (32 rows when yb is set, else 1 chunk)
     int32_t *sums;
     int *status;         // device word for STATUS_* bits
     long long *timeline; // optional: 8 timestamps (ns) a block, for tuning; null in normal use
@@ -761,7 +765,10 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
     stamp(0);
     if (p.trigger < 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint8_t *ring = smem + p.off_ring;
-    const int chunk0 = (int)((long long)p.chunks * blockIdx.x / gridDim.x), chunk1 = (int)((long long)p.chunks * (blockIdx.x + 1) / gridDim.x);
+    // block b takes the chunk groups [G*b/grid, G*(b+1)/grid) of the G groups of chunk_align chunks
+    const int groups = (p.chunks + p.chunk_align - 1) / p.chunk_align;
+    const int chunk0 = min(p.chunks, (int)((long long)groups * blockIdx.x / gridDim.x) * p.chunk_align);
+    const int chunk1 = min(p.chunks, (int)((long long)groups * (blockIdx.x + 1) / gridDim.x) * p.chunk_align);
     const int my_units = (chunk1 - chunk0 + p.rg - 1) / p.rg;
 
     if (warp == p.nw) {
@@ -978,6 +985,21 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
             if (i + 1 < my_units) named_bar_sync(1, threads);
         }
     }
+    // ---- the reference's `Back` step for this block's rows (src/GpuOps.cs:964-975): the f32 results, which this block
+    // alone wrote and whose first row is a multiple of 32, again as Q8_0 / Q4_0 blocks; values past the last row are zero
+    if (p.yb) {
+        named_bar_sync(1, threads);
+        const int row_lo = chunk0 * RW, row_hi = min(p.rows, chunk1 * RW);
+        const int count = *abort_flag ? 0 : (row_hi - row_lo + 31) / 32;
+        for (int b = threadIdx.x; b < count; b += threads) {
+            const int r0 = row_lo + b * 32;
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = r0 + i < p.rows ? __ldcg(p.y + r0 + i) : 0.f;
+            if (p.fmt_y == QB200_Q8_0) encode_q8_0_block(v, p.yb + (size_t)(r0 >> 5) * 34);
+            else encode_q4_0_block(v, p.yb + (size_t)(r0 >> 5) * 18);
+        }
+    }
     stamp(5);
     if (p.timeline && warp == 0 && lane == 0) {
         p.timeline[(size_t)blockIdx.x * 32 + 6] = c_wait;
@@ -1035,7 +1057,7 @@ static constexpr uint32_t PART_BYTES = 16384;
 
 // Splits the consumer warps of a block of at most `nwmax` warps (16 / nwmax such blocks share an SM) into column
 // segments x row groups and sizes the ring.  `rw_first` = the most rows a warp takes at once.
-static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, GemvPlan &pl)
+static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, bool back, GemvPlan &pl)
 {
     const uint32_t row_bytes = (uint32_t)(cols / block_values(fmt_a) * block_bytes(fmt_a));
     const int runs = runs_of(fmt_a, cols);
@@ -1067,6 +1089,7 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, G
     a.nw = nw; a.cs = cs; a.rg = rg; a.stage_rows = stage_rows;
     a.units = (rows + stage_rows - 1) / stage_rows;
     a.chunks = (rows + rw - 1) / rw;
+    a.chunk_align = back ? 32 / rw : 1;
     a.row_flip = (row_bytes & 2u) ? 1u : 0u;
     a.off_x = SMEM_HEADER;
     a.off_part = a.off_x + xprep_bytes(cols);
@@ -1085,7 +1108,7 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, G
     pl.grid = a.chunks < g_sm_count * gctas ? a.chunks : g_sm_count * gctas;
     int slots = (int)((budget - a.off_ring) / pl.stage_stride);
     if (slots > MAX_SLOTS) slots = MAX_SLOTS;
-    const int per_block = ((a.chunks + pl.grid - 1) / pl.grid + rg - 1) / rg;      // rounds of rg chunks a block takes at most
+    const int per_block = ((a.chunks + pl.grid - 1) / pl.grid + a.chunk_align - 1 + rg - 1) / rg;      // rounds of rg chunks a block takes at most
     if (slots > per_block * rg) slots = per_block * rg;
     if (g_tune.stages >= 1 && g_tune.stages * rg < slots) slots = g_tune.stages * rg;
     slots = slots / rg * rg;                     // every row group owns the same number of slots
@@ -1105,15 +1128,15 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, G
 // resident together and one's start and end hide behind the others' streaming; the chunk shrinks until a row group has
 // two slots.  A call that has to wait for the one before it gets the whole SM instead: blocks of 16 warps.  The
 // checking variant (per-block sums) always takes the latter, a row at a time.
-static int plan_gemv(int fmt_a, int rows, int cols, bool sums, bool overlapped, GemvPlan &pl)
+static int plan_gemv(int fmt_a, int rows, int cols, bool sums, bool overlapped, bool back, GemvPlan &pl)
 {
     const int forced = g_tune.warps;
     const int rw_first = sums ? 1 : (g_tune.rw == 1 || g_tune.rw == 2 || g_tune.rw == 4) ? g_tune.rw : 4;
     if (!sums && forced != 16 && (overlapped || forced == 4)) {
         for (int rw = rw_first; rw >= 1; rw /= 2)
-            if (plan_blocks(fmt_a, rows, cols, 4, rw, pl) == 0 && pl.deep) return 0;
+            if (plan_blocks(fmt_a, rows, cols, 4, rw, back, pl) == 0 && pl.deep) return 0;
     }
-    return plan_blocks(fmt_a, rows, cols, 16, rw_first, pl);
+    return plan_blocks(fmt_a, rows, cols, 16, rw_first, back, pl);
 }
 
 template <int FMT, int RW, int RUNS, bool SUMS, int NW>
@@ -1207,15 +1230,15 @@ size_t gemv_scratch_bytes(int cols) { return xprep_bytes(cols); }
 // kernels (any other kernel, copy or memset completes first).  When this call's x and y are disjoint from everything
 // that launch touched, its kernels need not wait for it.
 struct Touched { const uint8_t *p; size_t n; };
-static thread_local struct { cudaStream_t stream; bool valid; Touched a, x, y; } t_prev = { nullptr, false, {}, {}, {} };
+static thread_local struct { cudaStream_t stream; bool valid; Touched a, x, y, yb; } t_prev = { nullptr, false, {}, {}, {}, {} };
 
 static bool overlap(const Touched &u, const Touched &v)
 {
     return u.n && v.n && u.p < v.p + v.n && v.p < u.p + u.n;
 }
 
-int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols, void *scratch,
-                cudaStream_t stream)
+int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int fmt_y, void *y_blocks, int rows,
+                int cols, void *scratch, cudaStream_t stream)
 {
     if (rows == 0) return 0;
     // does this call touch anything the launch before it reads or writes?  (see t_prev)
@@ -1223,20 +1246,28 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     const Touched ta = { (const uint8_t *)a, (size_t)rows * row_bytes };
     const Touched tx = { (const uint8_t *)x, fmt_x == QB200_F32 ? (size_t)cols * 4 : (size_t)(cols / 32) * block_bytes(fmt_x) };
     const Touched ty = { (const uint8_t *)y, (size_t)rows * 4 };
+    const Touched tb = { (const uint8_t *)y_blocks, y_blocks ? (size_t)((rows + 31) / 32) * block_bytes(fmt_y) : 0 };
     bool independent = !sums && t_prev.valid && t_prev.stream == stream && !g_tune.always_wait;
-    if (independent) independent = !overlap(tx, t_prev.y) && !overlap(ta, t_prev.y) && !overlap(ty, t_prev.y) && !overlap(ty, t_prev.x) && !overlap(ty, t_prev.a);
-    t_prev.stream = stream; t_prev.valid = !sums; t_prev.a = ta; t_prev.x = tx; t_prev.y = ty;
+    if (independent) {
+        const Touched *outs[2] = { &ty, &tb }, *prev_outs[2] = { &t_prev.y, &t_prev.yb };
+        for (int i = 0; i < 2; i++) {
+            independent = independent && !overlap(tx, *prev_outs[i]) && !overlap(ta, *prev_outs[i]);       // reads of what it wrote
+            independent = independent && !overlap(*outs[i], t_prev.x) && !overlap(*outs[i], t_prev.a);     // writes of what it reads
+            for (int j = 0; j < 2; j++) independent = independent && !overlap(*outs[i], *prev_outs[j]);
+        }
+    }
+    t_prev.stream = stream; t_prev.valid = !sums; t_prev.a = ta; t_prev.x = tx; t_prev.y = ty; t_prev.yb = tb;
     // the last few shapes' plans are kept: a decode loop calls the same shapes over and over
     static thread_local struct { int fmt, rows, cols, kind; GemvPlan plan; } cache[8];
     static thread_local int cached = 0, next = 0;
     GemvPlan pl;
     bool hit = false;
     const bool overlapped = independent && !g_tune.prekernel;
-    const int kind = sums ? 2 : overlapped ? 1 : 0;
+    const int kind = (sums ? 2 : overlapped ? 1 : 0) | (y_blocks ? 4 : 0);
     for (int i = 0; i < cached && !hit; i++)
         if (cache[i].fmt == fmt_a && cache[i].rows == rows && cache[i].cols == cols && cache[i].kind == kind) { pl = cache[i].plan; hit = true; }
     if (!hit) {
-        int rc = plan_gemv(fmt_a, rows, cols, sums != nullptr, overlapped, pl);
+        int rc = plan_gemv(fmt_a, rows, cols, sums != nullptr, overlapped, y_blocks != nullptr, pl);
         if (rc) return rc;
         cache[next].fmt = fmt_a; cache[next].rows = rows; cache[next].cols = cols; cache[next].kind = kind; cache[next].plan = pl;
         next = (next + 1) % 8;
@@ -1248,6 +1279,8 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     pl.args.fmt_x = fmt_x;
     pl.args.independent = independent ? 1 : 0;
     pl.args.y = y;
+    pl.args.yb = (uint8_t *)y_blocks;
+    pl.args.fmt_y = fmt_y;
     pl.args.sums = sums;
     pl.args.status = g_status;
     pl.args.timeline = g_timeline;
@@ -1337,7 +1370,7 @@ int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, floa
     int rc = noalloc_setup(device, &dev);
     if (rc) return rc;
     GemvPlan pl;
-    if ((rc = plan_gemv(fmt_a, rows, cols, false, false, pl))) return rc;
+    if ((rc = plan_gemv(fmt_a, rows, cols, false, false, false, pl))) return rc;
     pl.args.a = (const uint8_t *)a;
     pl.args.xprep = (const uint8_t *)dev->scratch;
     pl.args.x = nullptr;
@@ -1345,6 +1378,8 @@ int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, floa
     pl.args.independent = 0;
     t_prev.valid = false;
     pl.args.y = y;
+    pl.args.yb = nullptr;
+    pl.args.fmt_y = 0;
     pl.args.sums = nullptr;
     pl.args.status = dev->status;
     pl.args.timeline = nullptr;
@@ -1383,7 +1418,7 @@ void gemv_describe(int fmt_a, int rows, int cols, int *out9)
 {
     GemvPlan pl;
     memset(&pl, 0, sizeof pl);
-    int rc = plan_gemv(fmt_a, rows, cols, false, g_describe_overlapped != 0, pl);
+    int rc = plan_gemv(fmt_a, rows, cols, false, g_describe_overlapped != 0, false, pl);
     out9[0] = rc; out9[1] = pl.nw; out9[2] = pl.cs; out9[3] = pl.rw; out9[4] = pl.stages; out9[5] = pl.grid;
     out9[6] = (int)pl.stage_stride; out9[7] = (int)pl.smem_bytes; out9[8] = pl.runs_per_warp;
 }

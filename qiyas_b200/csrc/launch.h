@@ -13,8 +13,9 @@ namespace qb {
 cudaError_t gemv_init(int sm_count, int max_smem, int *status);
 void gemv_set_device_limits(int sm_count, int max_smem);
 size_t gemv_scratch_bytes(int cols);
-int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int rows, int cols, void *scratch,
-                cudaStream_t stream);
+// y_blocks (optional) = y again as fmt_y blocks (Q8_0 / Q4_0), encoded in the same launch
+int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int fmt_y, void *y_blocks, int rows,
+                int cols, void *scratch, cudaStream_t stream);
 int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, cudaStream_t stream);
 int gemv_noalloc_status(int *value);
 void gemv_describe(int fmt_a, int rows, int cols, int *out9);

@@ -125,9 +125,16 @@ class GpuOps:
         if fa not in (Q8_0, Q4_0) or transposed or cols % 32:
             raise NotImplementedError(f"{NAMES.get(fa, fa)}: only the block-scaled branch of Gemv is built here")
         lanes = self._rent(rows * 4)
-        lane = self.GemvBlocks(fa, a, x, lanes, rows, cols, stream=stream)
-        self.Back(fa, lanes, y, rows, stream=stream)
-        return lane
+        return self.GemvBlocksBack(fa, a, x, lanes, fa, y, rows, cols, stream=stream)
+
+    def GemvBlocksBack(self, fmt, a, x, y_lanes, fmt_y, y_blocks, rows, cols, fmt_x=None, stream=None):
+        """GemvBlocks and the `Back` of its result (src/GpuOps.cs:283-284) in one launch: f32 lanes and Q8_0 / Q4_0 blocks."""
+        fa = fmt_id(fmt)
+        fx = fa if fmt_x is None else fmt_id(fmt_x)
+        rc = self.lib.qb200_gemv_blocks_back(fa, fx, _ptr(a), _ptr(x), _ptr(y_lanes), fmt_id(fmt_y), _ptr(y_blocks), int(rows),
+                                             int(cols), _stream(stream))
+        self.gpu.check(rc, "GemvBlocksBack")
+        return self.lane_name(OP_GEMV, fa)
 
     # -- A.B^T ---------------------------------------------------------------------------------
     def MatMulBlocks(self, fmt, a, b, c_lanes, m, n, k, fmt_b=None, workspace=None, workspace_bytes=0, stream=None):

@@ -190,3 +190,36 @@ def test_k_quants_layer_shapes(oracle, fmt_a, rows, cols):
 def test_k_quants_take_q8_0_x(oracle):
     check_k(oracle, B.Q4_K, 65, 1024, 77, fmt_x=B.Q8_0)
     check_k(oracle, B.Q6_K, 65, 1024, 78, fmt_x=B.Q8_0)
+
+
+@pytest.mark.parametrize("fmt_y", [B.Q8_0, B.Q4_0])
+@pytest.mark.parametrize("fmt_a,rows,cols", [
+    (B.Q8_0, 37, 64), (B.Q4_0, 32, 96), (B.Q8_0, 1000, 4096), (B.Q4_0, 8192, 8192), (B.Q4_0, 4099, 8160),
+    (B.Q4_K, 4096, 4096), (B.Q6_K, 1030, 11008), (B.Q4_0, 28669, 8160)])
+def test_back_in_the_same_launch(oracle, fmt_a, rows, cols, fmt_y):
+    # Gemv<TN>'s block branch (src/GpuOps.cs:277-285): the blocks written by the gemv's own blocks must be, byte for
+    # byte, the encoder's output on the f32 lanes of the same call (gate BlockFormats, src/Checks.cs:241-254), and
+    # the lanes must be the plain call's, for a call that waits for its predecessor and for calls that do not
+    import torch
+    a = B.make_weights(fmt_a, rows, cols, 70)
+    xf = B.make_activations(cols, 71)
+    o = H.ops()
+    da, dx = H.dev(a), H.dev(xf)
+    plain = H.empty(rows, torch.float32)
+    o.GemvBlocks(fmt_a, da, dx, plain, rows, cols, fmt_x=B.F32)
+    nbytes = B.nbytes(fmt_y, (rows + 31) // 32 * 32)
+    outs = []
+    for i in range(4):                       # four calls that share no output: independent of one another
+        lanes = H.empty(rows, torch.float32)
+        blocks = H.empty(nbytes, torch.uint8)
+        blocks.fill_(0xAB)
+        o.GemvBlocksBack(fmt_a, da, dx, lanes, fmt_y, blocks, rows, cols, fmt_x=B.F32)
+        outs.append((lanes, blocks))
+    lanes2 = outs[0][0]
+    o.GemvBlocksBack(fmt_a, da, dx, lanes2, fmt_y, outs[0][1], rows, cols, fmt_x=B.F32)      # same outputs again: a dependent call
+    assert o.gpu.status() == 0
+    want_lanes = plain.cpu().numpy()
+    for lanes, blocks in outs:
+        got = lanes.cpu().numpy()
+        assert np.allclose(got, want_lanes, rtol=0, atol=REL * np.max(np.abs(want_lanes)))
+        assert np.array_equal(blocks.cpu().numpy(), oracle.encode(fmt_y, got, device_rounding=True))
