@@ -133,7 +133,11 @@ int qb200_gemv_noalloc_status(int *status);
  * replaces: Ptx.MatMulBlocks, :178-386):  C[i,j] = sum over k-blocks of
  * fma(float(D_kb[i,j]), sA[i,kb]*sB[j,kb], acc), kb ascending, D_kb the exact s32 of 32 products.
  *   fmt_a, fmt_b: Q8_0 or Q4_0 each (the reference takes one format for both).
- *   k whole blocks of 32; m, n >= 1.
+ *   fmt_b may also be Q4_K (no block product in the reference: its Q4_K products decode both
+ *   operands to f32 first, src/GpuOps.Products.cs:28-42).  Every 32-value sub-block is then a
+ *   k-block with scale d*sc and min dmin*m as DecodeQ4_K rounds them (src/Blocks.cs:88-93):
+ *   acc = fma(float(D), sA*(d*sc), acc); acc = fma(dmin*m, -(sA*float(sum of qA)), acc).
+ *   k whole blocks of both operands (32; 256 with Q4_K); m, n >= 1.
  *   workspace: device scratch of qb200_matmul_workspace_bytes(...) bytes, 256-byte aligned,
  *   private to the call until it completes on `stream` (the operands are re-laid there for
  *   the tensor cores).  Pass NULL/0 to use a scratch buffer the library keeps and grows. */

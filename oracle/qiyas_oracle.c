@@ -659,6 +659,111 @@ QO_API int qo_matmul_blocks(int fmt_a, int fmt_b, const uint8_t *a, const uint8_
     return 0;
 }
 
+/* The block product against Q4_K rows.  The reference has no such kernel (its Q4_K products decode to f32 first,
+ * src/GpuOps.Products.cs:28-42); this restates the arithmetic this repo's device kernel defines for it, built from the
+ * reference's pieces: DecodeQ4_K's value (d*sc)*q - dmin*m with both products rounded to f32 (src/Blocks.cs:88-93) and
+ * the device tile's per-block fma (src/MatMulBlocks.cs:339-347).  Per 32-value sub-block, ascending:
+ *     acc = fma(float(sum qA*q), sA * (d*sc), acc);   acc = fma(dmin*m, -(sA * float(sum qA)), acc).
+ * sums (optional): the m*n*(k/32) exact sums of qA*q. */
+struct mmk_job { int m, n, k; const int8_t *qa; const float *sa; const uint8_t *b; float *c; int32_t *sums; };
+
+static void mmk_body(void *p, int first, int last)
+{
+    struct mmk_job *j = (struct mmk_job *)p;
+    int blocks = j->k / 32, supers = j->k / 256;
+    for (int i = first; i < last; i++)
+        for (int c = 0; c < j->n; c++) {
+            const int8_t *a = j->qa + (int64_t)i * j->k;
+            const float *sa = j->sa + (int64_t)i * blocks;
+            float acc = 0;
+            for (int sb = 0; sb < supers; sb++) {
+                const uint8_t *blk = j->b + ((int64_t)c * supers + sb) * 144;
+                float d = half_at(blk), dmin = half_at(blk + 2);
+                for (int sub = 0; sub < 8; sub++) {
+                    int sc, mn, kb = sb * 8 + sub, dot = 0, sum = 0;
+                    scale_min(blk + 4, sub, &sc, &mn);
+                    const uint8_t *qs = blk + 16 + (sub / 2) * 32;
+                    for (int t = 0; t < 32; t++) {
+                        int q = (sub & 1) ? qs[t] >> 4 : qs[t] & 15;
+                        dot += a[kb * 32 + t] * q;
+                        sum += a[kb * 32 + t];
+                    }
+                    if (j->sums) j->sums[((int64_t)i * j->n + c) * blocks + kb] = dot;
+                    float scale = d * (float)sc, min = dmin * (float)mn;
+                    float s = sa[kb] * scale;
+                    acc = fmaf((float)dot, s, acc);
+                    float u = sa[kb] * (float)sum;
+                    acc = fmaf(min, -u, acc);
+                }
+            }
+            j->c[(int64_t)i * j->n + c] = acc;
+        }
+}
+
+QO_API int qo_matmul_q4_k(int fmt_a, const uint8_t *a, const uint8_t *b, float *c, int m, int n, int k, int32_t *sums)
+{
+    if ((fmt_a != QO_Q8_0 && fmt_a != QO_Q4_0) || k % 256 != 0 || k <= 0) return -1;
+    int blocks = k / 32;
+    int8_t *qa = (int8_t *)malloc((size_t)m * k);
+    float *sa = (float *)malloc((size_t)m * blocks * 4);
+    unpack_rows(fmt_a, a, m, k, qa, sa);
+    struct mmk_job job = { m, n, k, qa, sa, b, c, sums };
+    team_for(m, 1, (int64_t)m * n * k, mmk_body, &job);
+    free(qa); free(sa);
+    return 0;
+}
+
+/* The block product against Q6_K rows (again no counterpart kernel in the reference).  DecodeQ6_K's value is
+ * d * sc * q evaluated left to right (src/Blocks.cs:167-170), i.e. (d*sc) rounded, then times the code q - 32; a scale
+ * covers 16 values.  Per 16-value sub-block s, ascending (A's block s / 2 supplies sA):
+ *     acc = fma(float(sum of qA*(q-32) over the 16), sA * (d*sc[s]), acc).
+ * sums (optional): the m*n*(k/16) exact sums. */
+static void mm6_body(void *p, int first, int last)
+{
+    struct mmk_job *j = (struct mmk_job *)p;
+    int blocks = j->k / 32, subs = j->k / 16, supers = j->k / 256;
+    for (int i = first; i < last; i++)
+        for (int c = 0; c < j->n; c++) {
+            const int8_t *a = j->qa + (int64_t)i * j->k;
+            const float *sa = j->sa + (int64_t)i * blocks;
+            float acc = 0;
+            for (int sb = 0; sb < supers; sb++) {
+                const uint8_t *blk = j->b + ((int64_t)c * supers + sb) * 210;
+                const uint8_t *ql = blk, *qh = blk + 128;
+                const int8_t *sc = (const int8_t *)(blk + 192);
+                float d = half_at(blk + 208);
+                for (int s = 0; s < 16; s++) {
+                    int half = s >> 3, g = (s >> 1) & 3, l0 = (s & 1) * 16, dot = 0, at = sb * 256 + half * 128 + g * 32 + l0;
+                    for (int t = 0; t < 16; t++) {
+                        int l = l0 + t;
+                        int byte = ql[64 * half + 32 * (g & 1) + l];
+                        int nib = g >= 2 ? byte >> 4 : byte & 15;
+                        int q = (nib | (((qh[32 * half + l] >> (2 * g)) & 3) << 4)) - 32;
+                        dot += a[at + t] * q;
+                    }
+                    if (j->sums) j->sums[((int64_t)i * j->n + c) * subs + sb * 16 + s] = dot;
+                    float scale = d * (float)sc[s];
+                    float w = sa[at / 32] * scale;
+                    acc = fmaf((float)dot, w, acc);
+                }
+            }
+            j->c[(int64_t)i * j->n + c] = acc;
+        }
+}
+
+QO_API int qo_matmul_q6_k(int fmt_a, const uint8_t *a, const uint8_t *b, float *c, int m, int n, int k, int32_t *sums)
+{
+    if ((fmt_a != QO_Q8_0 && fmt_a != QO_Q4_0) || k % 256 != 0 || k <= 0) return -1;
+    int blocks = k / 32;
+    int8_t *qa = (int8_t *)malloc((size_t)m * k);
+    float *sa = (float *)malloc((size_t)m * blocks * 4);
+    unpack_rows(fmt_a, a, m, k, qa, sa);
+    struct mmk_job job = { m, n, k, qa, sa, b, c, sums };
+    team_for(m, 1, (int64_t)m * n * k, mm6_body, &job);
+    free(qa); free(sa);
+    return 0;
+}
+
 /* References.MatMul through ProductView.Reference for B^T (Program.cs:995-1019, src/Products.cs:32-47): float64
  * products made exact by fma, accumulated as a double-double. */
 struct ref_job { int fmt_a, fmt_b, n, k; const float *va, *vb; double *c; };

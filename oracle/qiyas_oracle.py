@@ -42,6 +42,8 @@ def lib():
         _lib.qo_matmul_blocks.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                           C.c_int, C.c_void_p]
         _lib.qo_matmul_f64.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+        _lib.qo_matmul_q4_k.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        _lib.qo_matmul_q6_k.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     return _lib
 
 
@@ -136,6 +138,26 @@ def matmul_blocks(fmt_a, fmt_b, a, b, m, n, k, order=1, want_sums=False):
     sums = np.empty((m, n, k // 32), np.int32) if want_sums else None
     if lib().qo_matmul_blocks(fmt_a, fmt_b, _ptr(a), _ptr(b), _ptr(c), m, n, k, order, _ptr(sums)):
         raise ValueError("matmul_blocks: the block product takes Q8_0 or Q4_0 with k in whole blocks")
+    return (c, sums) if want_sums else c
+
+
+def matmul_q4_k(fmt_a, a, b, m, n, k, want_sums=False):
+    """C (f32) = A.B^T for A in Q8_0 / Q4_0 and B in Q4_K, in the order this repo's device kernel defines (see the C file)."""
+    a, b = _bytes(a), _bytes(b)
+    c = np.empty((m, n), np.float32)
+    sums = np.empty((m, n, k // 32), np.int32) if want_sums else None
+    if lib().qo_matmul_q4_k(fmt_a, _ptr(a), _ptr(b), _ptr(c), m, n, k, _ptr(sums)):
+        raise ValueError("matmul_q4_k: A in Q8_0 or Q4_0, k in whole super-blocks of 256")
+    return (c, sums) if want_sums else c
+
+
+def matmul_q6_k(fmt_a, a, b, m, n, k, want_sums=False):
+    """C (f32) = A.B^T for A in Q8_0 / Q4_0 and B in Q6_K, in the order this repo's device kernel defines (see the C file)."""
+    a, b = _bytes(a), _bytes(b)
+    c = np.empty((m, n), np.float32)
+    sums = np.empty((m, n, k // 16), np.int32) if want_sums else None
+    if lib().qo_matmul_q6_k(fmt_a, _ptr(a), _ptr(b), _ptr(c), m, n, k, _ptr(sums)):
+        raise ValueError("matmul_q6_k: A in Q8_0 or Q4_0, k in whole super-blocks of 256")
     return (c, sums) if want_sums else c
 
 

@@ -89,10 +89,10 @@ int check_gemv(int fmt_a, int fmt_x, const void *a, const void *x, const float *
 int check_matmul(int fmt_a, int fmt_b, const void *a, const void *b, const float *c, int m, int n, int k)
 {
     if (!g_ready) return fail(QB200_E_DEVICE, "qb200_init has not succeeded");
-    if ((fmt_a != QB200_Q8_0 && fmt_a != QB200_Q4_0) || (fmt_b != QB200_Q8_0 && fmt_b != QB200_Q4_0))
-        return fail(QB200_E_FORMAT, "%s x %s: the block product takes Q8_0 or Q4_0 with k in whole blocks", fmt_name(fmt_a), fmt_name(fmt_b));
-    if (m <= 0 || n <= 0 || k <= 0 || k % 32 != 0)
-        return fail(QB200_E_SHAPE, "the block product takes Q8_0 or Q4_0 with k in whole blocks (m %d, n %d, k %d)", m, n, k);
+    if ((fmt_a != QB200_Q8_0 && fmt_a != QB200_Q4_0) || (fmt_b != QB200_Q8_0 && fmt_b != QB200_Q4_0 && fmt_b != QB200_Q4_K && fmt_b != QB200_Q6_K))
+        return fail(QB200_E_FORMAT, "%s x %s: the block product takes Q8_0 or Q4_0 (B also Q4_K, Q6_K) with k in whole blocks", fmt_name(fmt_a), fmt_name(fmt_b));
+    if (m <= 0 || n <= 0 || k <= 0 || k % qb::block_values(fmt_b) != 0)
+        return fail(QB200_E_SHAPE, "the block product takes k in whole blocks of both operands (m %d, n %d, k %d)", m, n, k);
     if (!g_caps.tcgen05) return fail(QB200_E_DEVICE, "the block product needs the s8 tensor instruction (tcgen05, sm_100)");
     if (!a || !b || !c) return fail(QB200_E_POINTER, "null operand");
     if (((uintptr_t)a & 1) || ((uintptr_t)b & 1) || ((uintptr_t)c & 3)) return fail(QB200_E_POINTER, "misaligned operand");
@@ -269,7 +269,7 @@ int qb200_matmul_block_sums(int fmt_a, int fmt_b, const void *a, const void *b, 
     int rc = check_matmul(fmt_a, fmt_b, a, b, c, m, n, k);
     if (rc) return rc;
     if (!sums || ((uintptr_t)sums & 3)) return fail(QB200_E_POINTER, "null or misaligned sums");
-    if ((int64_t)m * n * (k / 32) > (1 << 24)) return fail(QB200_E_LIMIT, "block sums are for small shapes: m*n*(k/32) at most 2^24");
+    if ((int64_t)m * n * (k / 16) > (1 << 24)) return fail(QB200_E_LIMIT, "block sums are for small shapes: m*n*(k/16) at most 2^24");
     if ((rc = keep(g_scratch, qb::matmul_workspace_bytes(fmt_a, fmt_b, m, n, k)))) return rc;
     return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, c, sums, m, n, k, g_scratch.ptr, (cudaStream_t)stream), "matmul_block_sums");
 }

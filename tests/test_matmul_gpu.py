@@ -133,4 +133,66 @@ def test_view_surface(oracle):
     with pytest.raises(NotImplementedError):
         o.MatMulBlocks("q8_0", H.dev(a), H.dev(b), out, m, n, 33)
     with pytest.raises(NotImplementedError):
-        o.MatMulBlocks("q4_k", H.dev(a), H.dev(b), out, m, n, 256)
+        o.MatMulBlocks("q4_k", H.dev(a), H.dev(b), out, m, n, 256)                    # A is never a K-quant
+    with pytest.raises(NotImplementedError):
+        o.MatMulBlocks("q8_0", H.dev(a), H.dev(b), out, m, n, 320, fmt_b="q4_k")      # k in whole super-blocks of B
+    with pytest.raises(NotImplementedError):
+        o.MatMulBlocks("q8_0", H.dev(a), H.dev(b), out, m, n, 288, fmt_b="q6_k")
+
+
+# ---- B in Q4_K / Q6_K (no counterpart kernel in the reference, whose K-quant products decode to f32 first:
+# src/GpuOps.Products.cs:28-42).  Gates: every sub-block's s32 sum exact (32 values for Q4_K, 16 for Q6_K), C bit for
+# bit the oracle's restatement of the kernel's order, and within 1e-5 (relative to max|C|) of float64 on the stored values.
+
+def matmul_gpu_k(fmt_a, fmt_b, a, b, m, n, k, want_sums=False):
+    import torch
+    o = H.ops()
+    da, db = H.dev(a), H.dev(b)
+    c = H.empty(m * n, torch.float32)
+    c.fill_(float("nan"))
+    per = 32 if fmt_b == B.Q4_K else 16
+    if want_sums:
+        sums = H.empty(m * n * (k // per), torch.int32)
+        o.MatMulBlockSums(fmt_a, da, db, c, sums, m, n, k, fmt_b=fmt_b)
+    else:
+        o.MatMulBlocks(fmt_a, da, db, c, m, n, k, fmt_b=fmt_b)
+    assert o.gpu.status() == 0
+    out = c.cpu().numpy().reshape(m, n)
+    return (out, sums.cpu().numpy().reshape(m, n, k // per)) if want_sums else out
+
+
+def oracle_k(oracle, fmt_b):
+    return oracle.matmul_q4_k if fmt_b == B.Q4_K else oracle.matmul_q6_k
+
+
+def check_k(oracle, fmt_a, fmt_b, m, n, k, seed):
+    a, b = operands(oracle, fmt_a, fmt_b, m, n, k, seed)
+    ref, ref_sums = oracle_k(oracle, fmt_b)(fmt_a, a, b, m, n, k, want_sums=True)
+    c, got_sums = matmul_gpu_k(fmt_a, fmt_b, a, b, m, n, k, want_sums=True)
+    assert np.array_equal(got_sums, ref_sums)
+    assert np.array_equal(c.view(np.uint32), ref.view(np.uint32))
+    plain = matmul_gpu_k(fmt_a, fmt_b, a, b, m, n, k)
+    assert np.array_equal(plain.view(np.uint32), ref.view(np.uint32))
+    if m * n * k < 1 << 24:
+        c64 = oracle.matmul_f64(fmt_a, fmt_b, a, b, m, n, k)
+        assert np.max(np.abs(plain - c64)) <= 1e-5 * np.max(np.abs(c64))
+
+
+@pytest.mark.parametrize("fmt_b", [B.Q4_K, B.Q6_K])
+@pytest.mark.parametrize("fmt_a", [B.Q8_0, B.Q4_0])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 256), (37, 29, 512), (129, 127, 1280), (16, 257, 4096)])
+def test_k_quant_weights(oracle, fmt_a, fmt_b, m, n, k):
+    check_k(oracle, fmt_a, fmt_b, m, n, k, 500 + m)
+
+
+@pytest.mark.parametrize("fmt_b", [B.Q4_K, B.Q6_K])
+def test_k_quant_weights_prefill_shape(oracle, fmt_b):
+    # M 512 against an 11008 x 4096 K-quant matrix: a sample of A's rows through the oracle
+    m, n, k = 512, 11008, 4096
+    a, b = operands(oracle, B.Q8_0, fmt_b, m, n, k, 611)
+    c = matmul_gpu_k(B.Q8_0, fmt_b, a, b, m, n, k)
+    pick = np.array([0, 127, 128, 300, 511])
+    a_rows = a.reshape(m, B.row_bytes(B.Q8_0, k))[pick].reshape(-1)
+    ref = oracle_k(oracle, fmt_b)(B.Q8_0, a_rows, b, len(pick), n, k)
+    assert np.array_equal(c[pick].view(np.uint32), ref.view(np.uint32))
+    assert np.isfinite(c).all()

@@ -158,3 +158,22 @@ def test_q4_0_encoder_by_formula_and_device_rounding(oracle):
         assert np.array_equal(cpu[b, 2:], q[:16] | (q[16:] << 4))
     # the fused device rounding differs from the CPU's at most where v/d + 8.5 sits on an integer boundary
     assert np.mean(cpu != dev) < 1e-3
+
+
+@pytest.mark.parametrize("fmt_b", [B.Q4_K, B.Q6_K])
+@pytest.mark.parametrize("fmt_a", [B.Q8_0, B.Q4_0])
+def test_k_quant_block_product_restatement(oracle, fmt_a, fmt_b):
+    # The block product against K-quant rows has no kernel in the reference; its restatement here is tied to the
+    # reference through the decoders (pinned above by the reference's known answers): the product of the decoded
+    # operands in float64 (Program.cs:995-1019), and the integer sums recomputed from the decoded values.
+    m, n, k = 9, 11, 768
+    a = B.make_weights(fmt_a, m, k, 21)
+    b = B.make_weights(fmt_b, n, k, 22)
+    f = oracle.matmul_q4_k if fmt_b == B.Q4_K else oracle.matmul_q6_k
+    c, sums = f(fmt_a, a, b, m, n, k, want_sums=True)
+    c64 = oracle.matmul_f64(fmt_a, fmt_b, a, b, m, n, k)
+    assert np.max(np.abs(c - c64)) <= 1e-5 * np.max(np.abs(c64))
+    per = 32 if fmt_b == B.Q4_K else 16
+    assert sums.shape == (m, n, k // per) and np.abs(sums).max() <= per * 127 * 63
+    with pytest.raises(ValueError):
+        f(fmt_a, a, b, m, n, 288)
