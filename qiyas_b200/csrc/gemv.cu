@@ -44,7 +44,6 @@ struct GemvArgs {
     int units;           // ceil(rows / stage_rows)
     int chunks;          // ceil(rows / RW)
     int slots;           // ring depth in chunks (a chunk = the RW rows of one row group): a multiple of rg, slots/rg a row group
-    int trigger;         // percent of a block's units after which it lets the next launch's blocks be scheduled (0: once x is in registers)
     int independent;     // 1: nothing this call reads or writes is touched by the launch before it, so no wait on that launch
     int prefetch;        // chunks a block requests before x has been asked for (the rest wait, so x's reads meet idle queues)
     int flush_units;     // units whose partial sums fit the partials area before they are added up
@@ -727,6 +726,22 @@ __device__ __forceinline__ void rows_fast(const XK6 (&xr)[RUNS], const uint8_t *
     }
 }
 
+// The reference's `Back` step (src/GpuOps.cs:964-975) for the rows [row_lo, row_hi) that one block of the gemv wrote
+// (row_lo a multiple of 32): the f32 results again as Q8_0 / Q4_0 blocks, a thread a block of 32; values past the
+// last row are zero.
+__device__ __forceinline__ void back_rows(const float *y, uint8_t *yb, int fmt_y, int rows, int row_lo, int row_hi, int tid, int threads)
+{
+    const int count = (row_hi - row_lo + 31) / 32;
+    for (int b = tid; b < count; b += threads) {
+        const int r0 = row_lo + b * 32;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = r0 + i < rows ? __ldcg(y + r0 + i) : 0.f;
+        if (fmt_y == QB200_Q8_0) encode_q8_0_block(v, yb + (size_t)(r0 >> 5) * 34);
+        else encode_q4_0_block(v, yb + (size_t)(r0 >> 5) * 18);
+    }
+}
+
 // ---------------------------------------------------------------------------------- the kernel
 
 // The ring holds `slots` chunks; a chunk is RW consecutive rows, fetched by one bulk copy with its own pair of barriers
@@ -735,7 +750,8 @@ __device__ __forceinline__ void rows_fast(const XK6 (&xr)[RUNS], const uint8_t *
 // chunks dealt in one round are a unit.  RUNS = runs of x a warp holds (its column segment: runs seg, seg + cs, ...).
 // NW = the most consumer warps a block of this variant has: 16 (one block an SM) or 4 (four blocks an SM, normally of
 // four successive launches: while one block prepares x or drains, the others keep the memory system busy).
-template <int FMT, int RW, int RUNS, bool SUMS, int NW>
+// BACK = the block also encodes the rows it wrote (a variant of its own, so that the plain gemv carries none of it).
+template <int FMT, int RW, int RUNS, bool SUMS, int NW, bool BACK = false>
 __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const GemvArgs p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -763,12 +779,17 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         }
     };
     stamp(0);
-    if (p.trigger < 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint8_t *ring = smem + p.off_ring;
-    // block b takes the chunk groups [G*b/grid, G*(b+1)/grid) of the G groups of chunk_align chunks
-    const int groups = (p.chunks + p.chunk_align - 1) / p.chunk_align;
-    const int chunk0 = min(p.chunks, (int)((long long)groups * blockIdx.x / gridDim.x) * p.chunk_align);
-    const int chunk1 = min(p.chunks, (int)((long long)groups * (blockIdx.x + 1) / gridDim.x) * p.chunk_align);
+    // block b takes the chunks [C*b/grid, C*(b+1)/grid); with BACK, whole groups of chunk_align chunks (32 rows)
+    int chunk0, chunk1;
+    if constexpr (!BACK) {
+        chunk0 = (int)((long long)p.chunks * blockIdx.x / gridDim.x);
+        chunk1 = (int)((long long)p.chunks * (blockIdx.x + 1) / gridDim.x);
+    } else {
+        const int groups = (p.chunks + p.chunk_align - 1) / p.chunk_align;
+        chunk0 = min(p.chunks, (int)((long long)groups * blockIdx.x / gridDim.x) * p.chunk_align);
+        chunk1 = min(p.chunks, (int)((long long)groups * (blockIdx.x + 1) / gridDim.x) * p.chunk_align);
+    }
     const int my_units = (chunk1 - chunk0 + p.rg - 1) / p.rg;
 
     if (warp == p.nw) {
@@ -778,7 +799,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         // arithmetic and the barrier calls, which would pace the whole kernel): a pass of the warp issues `step`
         // consecutive chunks, never more than there are slots, so no lane of a pass waits on another lane of it.
         // (with x in a buffer shared between calls the consumers decide when the next call may be scheduled)
-        if (p.trigger == 0 && p.x) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        if (p.x) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         // A slot belongs to one row group for the whole kernel (spg slots a group): the warps that wait on a slot's
         // barrier are then always the ones that released its previous use, so a phase parity can never be mistaken for the
         // parity two phases back.
@@ -871,8 +892,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         named_bar_sync(1, threads);
     }
     // x is in registers: the next call's kernels may be scheduled as this grid's blocks retire
-    if (p.trigger == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int trigger_unit = p.trigger > 0 ? (int)((long long)my_units * p.trigger / 100) : -1;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // whether every lane of this warp has both blocks of every run (then whole chunks take the branch-free path)
     bool whole_runs = false;
     if (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) whole_runs = (seg + (RUNS - 1) * p.cs + 1) * 64 <= p.cols / 32;
@@ -889,7 +909,6 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
     for (int i = 0; i < my_units; i++) {
         const int chunk = chunk0 + i * p.rg + rgi, s = rgi * spg + sl;
         const int row0 = chunk * RW;
-        if (i == trigger_unit) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         const int nvalid = chunk < chunk1 ? max(0, min(RW, p.rows - row0)) : 0;
         long long tq0 = p.timeline ? clock64() : 0;
         if (alive) alive = mbar_wait_warp(full0 + 8 * s, phase, abort_flag, p.status, STATUS_GEMV_WAIT);
@@ -985,20 +1004,9 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
             if (i + 1 < my_units) named_bar_sync(1, threads);
         }
     }
-    // ---- the reference's `Back` step for this block's rows (src/GpuOps.cs:964-975): the f32 results, which this block
-    // alone wrote and whose first row is a multiple of 32, again as Q8_0 / Q4_0 blocks; values past the last row are zero
-    if (p.yb) {
+    if constexpr (BACK) {
         named_bar_sync(1, threads);
-        const int row_lo = chunk0 * RW, row_hi = min(p.rows, chunk1 * RW);
-        const int count = *abort_flag ? 0 : (row_hi - row_lo + 31) / 32;
-        for (int b = threadIdx.x; b < count; b += threads) {
-            const int r0 = row_lo + b * 32;
-            float v[32];
-#pragma unroll
-            for (int i = 0; i < 32; i++) v[i] = r0 + i < p.rows ? __ldcg(p.y + r0 + i) : 0.f;
-            if (p.fmt_y == QB200_Q8_0) encode_q8_0_block(v, p.yb + (size_t)(r0 >> 5) * 34);
-            else encode_q4_0_block(v, p.yb + (size_t)(r0 >> 5) * 18);
-        }
+        if (!*abort_flag) back_rows(p.y, p.yb, p.fmt_y, p.rows, chunk0 * RW, min(p.rows, chunk1 * RW), threadIdx.x, threads);
     }
     stamp(5);
     if (p.timeline && warp == 0 && lane == 0) {
@@ -1028,7 +1036,7 @@ static int env_int(const char *name, int fallback)
 }
 
 // tuning overrides, read once when the library binds a device
-static struct { int warps, stage_bytes, rw, cs, stages, prekernel, prefetch, always_wait, ctas, grid_ctas, trigger; } g_tune = { 0, 24576, 0, 0, 0, 0, 0, 0, 1, 0, 0 };
+static struct { int warps, stage_bytes, rw, cs, stages, prekernel, prefetch, always_wait, grid_ctas; } g_tune = { 0, 24576, 0, 0, 0, 0, 0, 0, 0 };
 
 static void read_tuning()
 {
@@ -1040,9 +1048,7 @@ static void read_tuning()
     g_tune.prekernel = env_int("QB200_GEMV_PREKERNEL", 0);
     g_tune.prefetch = env_int("QB200_GEMV_PREFETCH", 0);
     g_tune.always_wait = env_int("QB200_GEMV_ALWAYS_WAIT", 0);
-    g_tune.ctas = env_int("QB200_GEMV_CTAS", 1);
     g_tune.grid_ctas = env_int("QB200_GEMV_GRID_CTAS", 0);
-    g_tune.trigger = env_int("QB200_GEMV_TRIGGER", 0);
 }
 
 // Runs of x that cover a row: 2048 columns each, but Q6_K runs are four super-blocks of one parity out of eight.
@@ -1116,7 +1122,6 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, b
     pl.stages = slots;
     pl.deep = slots >= 2 * rg || slots >= per_block * rg;        // a row group can compute on one chunk while the next arrives
     a.slots = slots;
-    a.trigger = g_tune.trigger > 99 ? 0 : g_tune.trigger;
     a.prefetch = g_tune.prefetch > 0 ? g_tune.prefetch : (slots + 1) / 2;
     a.slot_stride = pl.stage_stride;
     pl.smem_bytes = a.off_ring + (uint32_t)slots * pl.stage_stride;
@@ -1127,19 +1132,20 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, b
 // buffer with the launch before it): then blocks of 4 consumer warps, one an SM, so that four successive launches are
 // resident together and one's start and end hide behind the others' streaming; the chunk shrinks until a row group has
 // two slots.  A call that has to wait for the one before it gets the whole SM instead: blocks of 16 warps.  The
-// checking variant (per-block sums) always takes the latter, a row at a time.
+// checking variant (per-block sums) always takes the latter, a row at a time, and so does a call that also encodes
+// its output (that variant exists for the whole-SM blocks only).
 static int plan_gemv(int fmt_a, int rows, int cols, bool sums, bool overlapped, bool back, GemvPlan &pl)
 {
     const int forced = g_tune.warps;
     const int rw_first = sums ? 1 : (g_tune.rw == 1 || g_tune.rw == 2 || g_tune.rw == 4) ? g_tune.rw : 4;
-    if (!sums && forced != 16 && (overlapped || forced == 4)) {
+    if (!sums && !back && forced != 16 && (overlapped || forced == 4)) {
         for (int rw = rw_first; rw >= 1; rw /= 2)
             if (plan_blocks(fmt_a, rows, cols, 4, rw, back, pl) == 0 && pl.deep) return 0;
     }
     return plan_blocks(fmt_a, rows, cols, 16, rw_first, back, pl);
 }
 
-template <int FMT, int RW, int RUNS, bool SUMS, int NW>
+template <int FMT, int RW, int RUNS, bool SUMS, int NW, bool BACK>
 static cudaError_t launch_one(const GemvPlan &pl, cudaStream_t stream)
 {
     cudaLaunchConfig_t cfg;
@@ -1153,44 +1159,45 @@ static cudaError_t launch_one(const GemvPlan &pl, cudaStream_t stream)
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, RW, RUNS, SUMS, NW>, pl.args);
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, RW, RUNS, SUMS, NW, BACK>, pl.args);
 }
 
-template <int FMT, int RW, bool SUMS, int NW>
+template <int FMT, int RW, bool SUMS, int NW, bool BACK>
 static cudaError_t launch_runs(const GemvPlan &pl, cudaStream_t stream)
 {
-    if (pl.runs_per_warp == 1) return launch_one<FMT, RW, 1, SUMS, NW>(pl, stream);
-    if (pl.runs_per_warp == 2 || FMT != QB200_Q6_K) return launch_one<FMT, RW, 2, SUMS, NW>(pl, stream);
-    if (pl.runs_per_warp == 3) return launch_one<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS, NW>(pl, stream);
-    return launch_one<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS, NW>(pl, stream);
+    if (pl.runs_per_warp == 1) return launch_one<FMT, RW, 1, SUMS, NW, BACK>(pl, stream);
+    if (pl.runs_per_warp == 2 || FMT != QB200_Q6_K) return launch_one<FMT, RW, 2, SUMS, NW, BACK>(pl, stream);
+    if (pl.runs_per_warp == 3) return launch_one<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS, NW, BACK>(pl, stream);
+    return launch_one<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS, NW, BACK>(pl, stream);
 }
 
-template <int FMT, int NW>
+template <int FMT, int NW, bool BACK>
 static cudaError_t launch_rows(const GemvPlan &pl, cudaStream_t stream)
 {
     switch (pl.rw) {
-    case 4: return launch_runs<FMT, 4, false, NW>(pl, stream);
-    case 2: return launch_runs<FMT, 2, false, NW>(pl, stream);
-    default: return launch_runs<FMT, 1, false, NW>(pl, stream);
+    case 4: return launch_runs<FMT, 4, false, NW, BACK>(pl, stream);
+    case 2: return launch_runs<FMT, 2, false, NW, BACK>(pl, stream);
+    default: return launch_runs<FMT, 1, false, NW, BACK>(pl, stream);
     }
 }
 
 template <int FMT>
 static cudaError_t launch_fmt(const GemvPlan &pl, bool sums, cudaStream_t stream)
 {
-    if (sums) return launch_runs<FMT, 1, true, 16>(pl, stream);      // the checking variant: a row at a time
-    return pl.nwmax == 4 ? launch_rows<FMT, 4>(pl, stream) : launch_rows<FMT, 16>(pl, stream);
+    if (sums) return launch_runs<FMT, 1, true, 16, false>(pl, stream);      // the checking variant: a row at a time
+    if (pl.args.yb) return launch_rows<FMT, 16, true>(pl, stream);          // with `Back`: always whole-SM blocks
+    return pl.nwmax == 4 ? launch_rows<FMT, 4, false>(pl, stream) : launch_rows<FMT, 16, false>(pl, stream);
 }
 
-template <int FMT, int RW, bool SUMS, int NW>
+template <int FMT, int RW, bool SUMS, int NW, bool BACK>
 static cudaError_t set_attr_runs(int bytes)
 {
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 1, SUMS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
-    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 2, SUMS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 1, SUMS, NW, BACK>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 2, SUMS, NW, BACK>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
     if (FMT == QB200_Q6_K) {
-        if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
-        e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS, NW, BACK>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+        e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS, NW, BACK>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     }
     return e;
 }
@@ -1200,13 +1207,16 @@ static cudaError_t set_attr(int bytes)
 {
     cudaError_t e;
     const int small = (bytes + 1024) / 4 - 2048;                 // what a block of the four-an-SM variant may ask for
-    if ((e = set_attr_runs<FMT, 1, true, 16>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 1, false, 16>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 2, false, 16>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 4, false, 16>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 1, false, 4>(small))) return e;
-    if ((e = set_attr_runs<FMT, 2, false, 4>(small))) return e;
-    return set_attr_runs<FMT, 4, false, 4>(small);
+    if ((e = set_attr_runs<FMT, 1, true, 16, false>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 1, false, 16, false>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 2, false, 16, false>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 4, false, 16, false>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 1, false, 16, true>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 2, false, 16, true>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 4, false, 16, true>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 1, false, 4, false>(small))) return e;
+    if ((e = set_attr_runs<FMT, 2, false, 4, false>(small))) return e;
+    return set_attr_runs<FMT, 4, false, 4, false>(small);
 }
 
 cudaError_t gemv_init(int sm_count, int max_smem, int *status)
