@@ -52,6 +52,16 @@ struct GemvArgs {
     uint32_t off_x, off_part, off_ring;   // shared-memory offsets
 };
 
+// The timeline and the probes are tuning aids: compiled in only with -DQB_GEMV_TUNING (the plain kernel is sensitive
+// to every instruction and register they cost).
+#ifdef QB_GEMV_TUNING
+#define TUNE_TIMELINE(p) ((p).timeline)
+#define TUNE_PROBE(p) ((p).probe)
+#else
+#define TUNE_TIMELINE(p) ((long long *)nullptr)
+#define TUNE_PROBE(p) 0
+#endif
+
 constexpr int MAX_SLOTS = 60;
 constexpr uint32_t SMEM_HEADER = 1024;  // full[60] and empty[60] barriers, the x barrier and the abort word
 
@@ -772,7 +782,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
     __syncthreads();
 
     auto stamp = [&](int slot) {
-        if (p.timeline && lane == 0 && warp == 0) {
+        if (TUNE_TIMELINE(p) && lane == 0 && warp == 0) {
             long long t;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
             p.timeline[(size_t)blockIdx.x * 32 + slot] = t;
@@ -824,7 +834,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
                     const uint8_t *b1 = (const uint8_t *)((uintptr_t)g1 & ~(uintptr_t)15);
                     uint8_t *slot = ring + (size_t)s * p.slot_stride + mis;      // g0's byte lands here
                     const uint8_t *head_end = g1, *tail_begin = g1;
-                    if (b1 > b0 && !(p.probe & 2)) {
+                    if (b1 > b0 && !(TUNE_PROBE(p) & 2)) {
                         mbar_expect_tx(full0 + 8 * s, (uint32_t)(b1 - b0));
                         bulk_g2s(smem_u32(slot + (b0 - g0)), b0, (uint32_t)(b1 - b0), full0 + 8 * s);
                         head_end = b0;
@@ -910,9 +920,9 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         const int chunk = chunk0 + i * p.rg + rgi, s = rgi * spg + sl;
         const int row0 = chunk * RW;
         const int nvalid = chunk < chunk1 ? max(0, min(RW, p.rows - row0)) : 0;
-        long long tq0 = p.timeline ? clock64() : 0;
+        long long tq0 = TUNE_TIMELINE(p) ? clock64() : 0;
         if (alive) alive = mbar_wait_warp(full0 + 8 * s, phase, abort_flag, p.status, STATUS_GEMV_WAIT);
-        long long tq1 = p.timeline ? clock64() : 0;
+        long long tq1 = TUNE_TIMELINE(p) ? clock64() : 0;
         c_wait += tq1 - tq0;
         if (i == 0) stamp(4);
         if (alive) {
@@ -921,7 +931,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
             float acc[RW];
 #pragma unroll
             for (int r = 0; r < RW; r++) acc[r] = 0.f;
-            bool done = (p.probe & 1) != 0;
+            bool done = (TUNE_PROBE(p) & 1) != 0;
             if constexpr ((FMT == QB200_Q8_0 || FMT == QB200_Q4_0) && !SUMS) {
                 if (!done && nvalid == RW) {
                     const bool q4 = (((uint32_t)(uintptr_t)rows + first_off) & 2u) == 0;
@@ -953,12 +963,12 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
                     }
                 }
             }
-            long long tq2 = p.timeline ? clock64() : 0;
+            long long tq2 = TUNE_TIMELINE(p) ? clock64() : 0;
             c_dot += tq2 - tq1;
             // the row sums (every lane has read its last byte of the slot once these shuffles are done)
             if constexpr (RW == 4) {
                 const float total = warp_sum4(acc, lane);           // lanes 8r .. 8r+7 hold row r
-                if (p.timeline) c_sum += clock64() - tq2;
+                if (TUNE_TIMELINE(p)) c_sum += clock64() - tq2;
                 if (lane == 0) mbar_arrive(empty0 + 8 * s);
                 const int r = lane >> 3;
                 if ((lane & 7) == 0) {
@@ -968,7 +978,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
             } else {
 #pragma unroll
                 for (int r = 0; r < RW; r++) acc[r] = warp_sum(acc[r]);
-                if (p.timeline) c_sum += clock64() - tq2;
+                if (TUNE_TIMELINE(p)) c_sum += clock64() - tq2;
                 if (lane == 0) mbar_arrive(empty0 + 8 * s);
                 if (p.cs == 1) {
 #pragma unroll
@@ -983,7 +993,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         if (++sl == spg) { sl = 0; phase ^= 1u; }
         // the partial sums of the last flush_units units: segments added in ascending order
         if (p.cs > 1 && (++flush_i == p.flush_units || i + 1 == my_units)) {
-            if (p.timeline && lane == 0 && i + 1 == my_units) {
+            if (TUNE_TIMELINE(p) && lane == 0 && i + 1 == my_units) {
                 long long t;
                 asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
                 p.timeline[(size_t)blockIdx.x * 32 + 8 + warp] = t;
@@ -1009,7 +1019,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         if (!*abort_flag) back_rows(p.y, p.yb, p.fmt_y, p.rows, chunk0 * RW, min(p.rows, chunk1 * RW), threadIdx.x, threads);
     }
     stamp(5);
-    if (p.timeline && warp == 0 && lane == 0) {
+    if (TUNE_TIMELINE(p) && warp == 0 && lane == 0) {
         p.timeline[(size_t)blockIdx.x * 32 + 6] = c_wait;
         p.timeline[(size_t)blockIdx.x * 32 + 7] = (c_dot << 24) | (c_sum & 0xFFFFFF);
     }
