@@ -24,6 +24,13 @@ namespace qb {
 #define QB_MM_WAIT mbar_wait_lanes
 #endif
 
+// The probes inside the kernel are tuning aids: compiled in only with -DQB_MM_TUNING.
+#ifdef QB_MM_TUNING
+#define MM_PROBE(p) ((p).probe)
+#else
+#define MM_PROBE(p) 0
+#endif
+
 constexpr int TILE = 128;            // rows of A and of B per block tile
 constexpr int KS = 4;                // k-blocks per shared-memory stage (even: pairs of k-blocks never straddle stages)
 constexpr int MM_STAGES = 5;
@@ -480,7 +487,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
             if (!QB_MM_WAIT(tfull0 + 8 * pair, (uint32_t)(np >> 1) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
             tc_fence_after();
             int32_t v[32];
-            if (!(p.probe & 2)) tmem_ld32(tlane + (uint32_t)(2 * pair) * TILE, v);
+            if (!(MM_PROBE(p) & 2)) tmem_ld32(tlane + (uint32_t)(2 * pair) * TILE, v);
             if (kk == 0 && !QB_MM_WAIT(full0 + 8 * s, sphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
             const float *sa_s = (const float *)(ring + (size_t)s * STAGE_BYTES + 2 * KS * SLAB) + kk * TILE;
             const float *sb_s = sa_s + KS * TILE + cg * 32;
@@ -491,7 +498,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                 nu1 = -sa_s[2 * KS * TILE + TILE + q * 32 + lane];
             }
             tmem_ld_wait();
-            if (!(p.probe & 1)) {
+            if (!(MM_PROBE(p) & 1)) {
                 scale_add(v, sa0, sb_s, acc);
                 if (MINS) min_add(nu0, sb_s + 2 * KS * TILE, acc);
             }
@@ -501,13 +508,13 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                     if (col0 + c < p.n) p.sums[((size_t)row * p.n + col0 + c) * p.kb + i] = v[c];
             }
             if (cnt == 2) {
-                if (!(p.probe & 2)) tmem_ld32(tlane + (uint32_t)(2 * pair + 1) * TILE, v);
+                if (!(MM_PROBE(p) & 2)) tmem_ld32(tlane + (uint32_t)(2 * pair + 1) * TILE, v);
                 tmem_ld_wait();
             }
             tc_fence_before();
             if (lane == 0) mbar_arrive(tempty0 + 8 * pair);      // both accumulators have been read (warp-wide reads)
             if (cnt == 2) {
-                if (!(p.probe & 1)) {
+                if (!(MM_PROBE(p) & 1)) {
                     scale_add(v, sa1, sb_s + TILE, acc);
                     if (MINS) min_add(nu1, sb_s + 2 * KS * TILE + TILE, acc);
                 }
