@@ -33,7 +33,7 @@ LAYERS = 8
 WEIGHT_BYTES = ROWS * (COLS // 32) * 18
 ALGO_BYTES = WEIGHT_BYTES + COLS * 4 + ROWS * 4          # per launch: weights once, x, y
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload's kernel (ncu; profiles/), or None
-TRAFFIC_BYTES = 37847040 + 256    # profiles/gemv_q4_0_8192x8192.md
+TRAFFIC_BYTES = 37852160              # dram__bytes_read + write of one launch, from the ncu capture in profiles/
 
 
 def measured_peak():
