@@ -339,6 +339,7 @@ int qb200_memset(void *dst, int value, size_t bytes, void *stream)
 int qb200_synchronize(void)
 {
     cudaError_t e = cudaDeviceSynchronize();
+    qb::gemv_forget_history();          // nothing launched before can still be running
     return e ? cuda_fail(e, "cudaDeviceSynchronize") : 0;
 }
 

@@ -1035,6 +1035,7 @@ static int g_probe = 0;
 struct GemvPlan {
     int rw, runs_per_warp, nw, nwmax, cs, rg, stages, grid;
     bool deep;
+    bool serial;            // launch without the programmatic attribute: after everything earlier in the stream
     uint32_t stage_stride, smem_bytes;
     GemvArgs args;
 };
@@ -1139,9 +1140,10 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, b
 }
 
 // The plan of a call.  `overlapped` = the call is expected to run beside its neighbours in the stream (it shares no
-// buffer with the launch before it): then blocks of 4 consumer warps, one an SM, so that four successive launches are
+// buffer with the launches that may still be running, or the launch before it was such a call): then blocks of 4
+// consumer warps, one an SM, so that four successive launches are
 // resident together and one's start and end hide behind the others' streaming; the chunk shrinks until a row group has
-// two slots.  A call that has to wait for the one before it gets the whole SM instead: blocks of 16 warps.  The
+// two slots.  A call in a chain of calls that wait for one another gets the whole SM instead: blocks of 16 warps.  The
 // checking variant (per-block sums) always takes the latter, a row at a time, and so does a call that also encodes
 // its output (that variant exists for the whole-SM blocks only).
 static int plan_gemv(int fmt_a, int rows, int cols, bool sums, bool overlapped, bool back, GemvPlan &pl)
@@ -1168,7 +1170,7 @@ static cudaError_t launch_one(const GemvPlan &pl, cudaStream_t stream)
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pl.serial ? 0 : 1;
     return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, RW, RUNS, SUMS, NW, BACK>, pl.args);
 }
 
@@ -1245,44 +1247,84 @@ cudaError_t gemv_init(int sm_count, int max_smem, int *status)
 // Returns 0, a negative QB200_E_* or a positive cudaError_t.  Arguments are already validated.
 size_t gemv_scratch_bytes(int cols) { return xprep_bytes(cols); }
 
-// The buffers of this thread's previous gemv launch.  A gemv is launched as a programmatic dependent, so only the launch
-// directly before it in the stream can still be running when it starts, and only if that launch was one of these
-// kernels (any other kernel, copy or memset completes first).  When this call's x and y are disjoint from everything
-// that launch touched, its kernels need not wait for it.
+// Ordering against earlier gemv launches of this thread.  A gemv is normally launched as a programmatic dependent of
+// whatever precedes it in the stream, and may skip griddepcontrol.wait; a launch that skips it can run beside its
+// predecessor, and so can its own successor, so any launch since the last point of full order may still be running
+// when a new one starts.  The history holds what those launches read and wrote.  A new call that touches none of it
+// (its inputs are not their outputs, its outputs are not their inputs or outputs) is "independent": no wait.  A call
+// that conflicts waits: by griddepcontrol.wait when the only launch that can still be running is the one directly
+// before it (a chain of calls that each waited), else by being launched without the programmatic attribute, which
+// orders it after everything earlier in the stream.  Either way the history restarts with it.  Other work in the
+// stream (kernels, copies) is launched without the attribute and only adds order.
 struct Touched { const uint8_t *p; size_t n; };
-static thread_local struct { cudaStream_t stream; bool valid; Touched a, x, y, yb; } t_prev = { nullptr, false, {}, {}, {}, {} };
+struct Launched { Touched a, x, y, yb; };
+constexpr int HISTORY = 64;
+static thread_local struct {
+    cudaStream_t stream;
+    int count;              // 0: nothing known about the stream (first call, another stream, a call outside this record)
+    bool settled;           // the newest entry waited for everything before it: only it can still be running
+    Launched at[HISTORY];
+} t_hist = { nullptr, 0, false, {} };
+
+void gemv_forget_history() { t_hist.count = 0; }
 
 static bool overlap(const Touched &u, const Touched &v)
 {
     return u.n && v.n && u.p < v.p + v.n && v.p < u.p + u.n;
 }
 
+// does the new call read what `old` wrote, or write what `old` read or wrote?
+static bool conflicts(const Launched &now, const Launched &old)
+{
+    const Touched *outs[2] = { &now.y, &now.yb }, *old_outs[2] = { &old.y, &old.yb };
+    for (int i = 0; i < 2; i++) {
+        if (overlap(now.x, *old_outs[i]) || overlap(now.a, *old_outs[i])) return true;
+        if (overlap(*outs[i], old.x) || overlap(*outs[i], old.a)) return true;
+        for (int j = 0; j < 2; j++) if (overlap(*outs[i], *old_outs[j])) return true;
+    }
+    return false;
+}
+
 int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int fmt_y, void *y_blocks, int rows,
                 int cols, void *scratch, cudaStream_t stream)
 {
     if (rows == 0) return 0;
-    // does this call touch anything the launch before it reads or writes?  (see t_prev)
     const size_t row_bytes = (size_t)(cols / block_values(fmt_a)) * block_bytes(fmt_a);
-    const Touched ta = { (const uint8_t *)a, (size_t)rows * row_bytes };
-    const Touched tx = { (const uint8_t *)x, fmt_x == QB200_F32 ? (size_t)cols * 4 : (size_t)(cols / 32) * block_bytes(fmt_x) };
-    const Touched ty = { (const uint8_t *)y, (size_t)rows * 4 };
-    const Touched tb = { (const uint8_t *)y_blocks, y_blocks ? (size_t)((rows + 31) / 32) * block_bytes(fmt_y) : 0 };
-    bool independent = !sums && t_prev.valid && t_prev.stream == stream && !g_tune.always_wait;
-    if (independent) {
-        const Touched *outs[2] = { &ty, &tb }, *prev_outs[2] = { &t_prev.y, &t_prev.yb };
-        for (int i = 0; i < 2; i++) {
-            independent = independent && !overlap(tx, *prev_outs[i]) && !overlap(ta, *prev_outs[i]);       // reads of what it wrote
-            independent = independent && !overlap(*outs[i], t_prev.x) && !overlap(*outs[i], t_prev.a);     // writes of what it reads
-            for (int j = 0; j < 2; j++) independent = independent && !overlap(*outs[i], *prev_outs[j]);
+    Launched now;
+    now.a = { (const uint8_t *)a, (size_t)rows * row_bytes };
+    now.x = { (const uint8_t *)x, fmt_x == QB200_F32 ? (size_t)cols * 4 : (size_t)(cols / 32) * block_bytes(fmt_x) };
+    now.y = { (const uint8_t *)y, (size_t)rows * 4 };
+    now.yb = { (const uint8_t *)y_blocks, y_blocks ? (size_t)((rows + 31) / 32) * block_bytes(fmt_y) : 0 };
+    const bool known = t_hist.count > 0 && t_hist.stream == stream;
+    bool conflict = !known || sums || g_tune.always_wait || g_tune.prekernel || t_hist.count == HISTORY;
+    bool weights_written = false;           // the producer reads A before any wait: nothing in flight may write it
+    if (known) {
+        for (int i = 0; i < t_hist.count; i++) {
+            conflict = conflict || conflicts(now, t_hist.at[i]);
+            weights_written = weights_written || overlap(now.a, t_hist.at[i].y) || overlap(now.a, t_hist.at[i].yb);
         }
     }
-    t_prev.stream = stream; t_prev.valid = !sums; t_prev.a = ta; t_prev.x = tx; t_prev.y = ty; t_prev.yb = tb;
+    const bool independent = !conflict;
+    // the launch before this one ran beside its neighbours: expect the same of this one and of the next, whether or
+    // not this one has to wait first (the choice of block variant below)
+    const bool in_a_burst = known && !t_hist.settled;
+    // full order by the launch itself: nothing known, or more than the direct predecessor may still be running
+    const bool serial = conflict && (!known || weights_written || !(t_hist.count == 1 || t_hist.settled));
+    if (independent) {
+        t_hist.at[t_hist.count++] = now;
+        t_hist.settled = false;
+    } else {
+        t_hist.stream = stream;
+        t_hist.at[0] = now;
+        t_hist.count = 1;
+        t_hist.settled = true;
+    }
     // the last few shapes' plans are kept: a decode loop calls the same shapes over and over
     static thread_local struct { int fmt, rows, cols, kind; GemvPlan plan; } cache[8];
     static thread_local int cached = 0, next = 0;
     GemvPlan pl;
     bool hit = false;
-    const bool overlapped = independent && !g_tune.prekernel;
+    const bool overlapped = (independent || in_a_burst) && !sums && !g_tune.prekernel;
     const int kind = (sums ? 2 : overlapped ? 1 : 0) | (y_blocks ? 4 : 0);
     for (int i = 0; i < cached && !hit; i++)
         if (cache[i].fmt == fmt_a && cache[i].rows == rows && cache[i].cols == cols && cache[i].kind == kind) { pl = cache[i].plan; hit = true; }
@@ -1298,6 +1340,7 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     pl.args.x = g_tune.prekernel ? nullptr : x;
     pl.args.fmt_x = fmt_x;
     pl.args.independent = independent ? 1 : 0;
+    pl.serial = serial;
     pl.args.y = y;
     pl.args.yb = (uint8_t *)y_blocks;
     pl.args.fmt_y = fmt_y;
@@ -1396,7 +1439,8 @@ int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, floa
     pl.args.x = nullptr;
     pl.args.fmt_x = fmt_x;
     pl.args.independent = 0;
-    t_prev.valid = false;
+    t_hist.count = 0;
+    pl.serial = false;
     pl.args.y = y;
     pl.args.yb = nullptr;
     pl.args.fmt_y = 0;

@@ -16,6 +16,8 @@ size_t gemv_scratch_bytes(int cols);
 // y_blocks (optional) = y again as fmt_y blocks (Q8_0 / Q4_0), encoded in the same launch
 int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int fmt_y, void *y_blocks, int rows,
                 int cols, void *scratch, cudaStream_t stream);
+// forgets what earlier launches touched: the next call orders itself after everything in its stream
+void gemv_forget_history();
 int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, cudaStream_t stream);
 int gemv_noalloc_status(int *value);
 void gemv_describe(int fmt_a, int rows, int cols, int *out9);

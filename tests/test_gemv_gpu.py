@@ -223,3 +223,36 @@ def test_back_in_the_same_launch(oracle, fmt_a, rows, cols, fmt_y):
         got = lanes.cpu().numpy()
         assert np.allclose(got, want_lanes, rtol=0, atol=REL * np.max(np.abs(want_lanes)))
         assert np.array_equal(blocks.cpu().numpy(), oracle.encode(fmt_y, got, device_rounding=True))
+
+
+@pytest.mark.parametrize("rounds", [1, 6])
+def test_order_against_a_launch_two_back(oracle, rounds):
+    # A writes v; B shares nothing with A (so it does not wait for A and runs beside it); C reads v as its x.  C is
+    # independent of its direct predecessor B, but not of A, which may still be running: C must order itself after A.
+    # v is poisoned before every round, so a C that starts early reads NaN.
+    import torch
+    n = 8192
+    wa = B.make_weights(B.Q4_0, n, n, 31)
+    wb = B.make_weights(B.Q8_0, 512, 2048, 32)
+    wc = B.make_weights(B.Q4_0, 1024, n, 33)
+    xa = B.make_activations(n, 34)
+    xb = B.make_activations(2048, 35)
+    o = H.ops()
+    dwa, dwb, dwc, dxa, dxb = H.dev(wa), H.dev(wb), H.dev(wc), H.dev(xa), H.dev(xb)
+    v = H.empty(n, torch.float32)
+    yb = H.empty(512, torch.float32)
+    yc = H.empty(1024, torch.float32)
+    warm = H.empty(n, torch.float32)
+    for _ in range(rounds):
+        v.fill_(float("nan"))
+        o.GemvBlocks(B.Q4_0, dwa, dxa, warm, n, n, fmt_x=B.F32)            # something to run beside
+        o.GemvBlocks(B.Q4_0, dwa, dxa, v, n, n, fmt_x=B.F32)               # A
+        o.GemvBlocks(B.Q8_0, dwb, dxb, yb, 512, 2048, fmt_x=B.F32)         # B
+        o.GemvBlocks(B.Q4_0, dwc, v, yc, 1024, n, fmt_x=B.F32)             # C
+        assert o.gpu.status() == 0
+        got_v = v.cpu().numpy()
+        assert np.isfinite(got_v).all()
+        ref, mag = oracle.gemv_blocks(B.Q4_0, B.F32, wc, got_v, 1024, n, order=1, want_abs=True)
+        got = yc.cpu().numpy().astype(np.float64)
+        assert np.isfinite(got).all()
+        assert np.all(np.abs(got - ref) <= REL * mag)
