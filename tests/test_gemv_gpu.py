@@ -256,3 +256,25 @@ def test_order_against_a_launch_two_back(oracle, rounds):
         got = yc.cpu().numpy().astype(np.float64)
         assert np.isfinite(got).all()
         assert np.all(np.abs(got - ref) <= REL * mag)
+
+
+def test_long_run_of_independent_calls(oracle):
+    # more independent calls in a row than the library remembers (64): the run is cut by a call that orders itself after
+    # everything before it, and every output is still right; the same again after the library's own synchronize
+    import torch
+    rows, cols, n = 515, 2304, 70
+    w = B.make_weights(B.Q8_0, rows, cols, 61)
+    xf = B.make_activations(cols, 62)
+    o = H.ops()
+    dw, dx = H.dev(w), H.dev(xf)
+    ref, mag = oracle.gemv_blocks(B.Q8_0, B.F32, w, xf, rows, cols, order=1, want_abs=True)
+    for _ in range(2):
+        ys = [H.empty(rows, torch.float32) for _ in range(n)]
+        for y in ys:
+            y.fill_(float("nan"))
+        for y in ys:
+            o.GemvBlocks(B.Q8_0, dw, dx, y, rows, cols, fmt_x=B.F32)
+        o.gpu.Synchronize()
+        assert o.gpu.status() == 0
+        for y in ys:
+            assert np.all(np.abs(y.cpu().numpy().astype(np.float64) - ref) <= REL * mag)
