@@ -1133,7 +1133,9 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, b
     pl.stages = slots;
     pl.deep = slots >= 2 * rg || slots >= per_block * rg;        // a row group can compute on one chunk while the next arrives
     a.slots = slots;
-    a.prefetch = g_tune.prefetch > 0 ? g_tune.prefetch : (slots + 1) / 2;
+    // the whole-SM variant holds half its ring back until x has been asked for (x's reads then meet idle queues); the
+    // small blocks, with two to four slots, ask for all of them at once (no measurable difference either way)
+    a.prefetch = g_tune.prefetch > 0 ? g_tune.prefetch : nwmax == 4 ? slots : (slots + 1) / 2;
     a.slot_stride = pl.stage_stride;
     pl.smem_bytes = a.off_ring + (uint32_t)slots * pl.stage_stride;
     return 0;
