@@ -278,3 +278,24 @@ def test_long_run_of_independent_calls(oracle):
         assert o.gpu.status() == 0
         for y in ys:
             assert np.all(np.abs(y.cpu().numpy().astype(np.float64) - ref) <= REL * mag)
+
+
+@pytest.mark.parametrize("fmt_a", [B.Q8_0, B.Q4_K])
+def test_x_encoded_in_the_kernel_at_extreme_magnitudes(oracle, fmt_a):
+    # blocks of x whose scale lands among the f16 subnormals (there amax / d can pass 127.5 and the encoder's clamp to
+    # +-127 acts), zero blocks, and large ones: f32 x encoded inside the kernel must give what the encoder's blocks give
+    rows, cols = 67, 4096
+    rng = np.random.default_rng(5)
+    xf = rng.standard_normal(cols).astype(np.float32)
+    mags = [0.0, 1e-8, 6e-8, 9e-8, 3e-7, 2e-6, 1e-5, 7e-5, 1e-3, 1.0, 3e4]
+    for b in range(cols // 32):
+        xf[b * 32:(b + 1) * 32] *= np.float32(mags[b % len(mags)])
+    a = B.make_weights(fmt_a, rows, cols, 17)
+    xq = oracle.encode(B.Q8_0, xf, device_rounding=True)
+    y_f, sums_f, _ = H.gemv_gpu(fmt_a, B.F32, a, xf, rows, cols, want_sums=True)
+    y_q, sums_q, _ = H.gemv_gpu(fmt_a, B.Q8_0, a, xq, rows, cols, want_sums=True)
+    assert np.array_equal(sums_f, sums_q)
+    assert np.array_equal(y_f.view(np.uint32), y_q.view(np.uint32))
+    plain_f, _ = H.gemv_gpu(fmt_a, B.F32, a, xf, rows, cols)
+    plain_q, _ = H.gemv_gpu(fmt_a, B.Q8_0, a, xq, rows, cols)
+    assert np.array_equal(plain_f.view(np.uint32), plain_q.view(np.uint32))
