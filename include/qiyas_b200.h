@@ -13,7 +13,18 @@
  *    f32 arrays need 4-byte alignment.
  *  - `stream` is a cudaStream_t / CUstream passed as void*; NULL is the legacy default stream,
  *    which is where the reference launches (src/Gpu.cs:300).  Calls are asynchronous and never
- *    synchronize; the caller orders them as it orders the reference's launches.
+ *    synchronize; the caller orders them as it orders the reference's launches: by stream order.
+ *  - Stream order, precisely.  The gemv kernels are launched as programmatic dependents of the work
+ *    before them in the stream, and a gemv call none of whose buffers is read or written by a gemv
+ *    launch of this library that may still be running starts beside those launches instead of after
+ *    them (every other call waits for all earlier work, as plain stream order would have it).  Two
+ *    assumptions come with that.  (1) Kernels of other origin in the same stream are launched the
+ *    plain way, as the reference launches everything (cuLaunchKernel, src/Gpu.cs:290-301): a foreign
+ *    kernel that itself releases its dependents early (griddepcontrol.launch_dependents before its
+ *    last store) and writes a gemv operand must be separated from the gemv by an event or by a
+ *    plainly launched kernel.  (2) The record of launches in flight is kept per host thread: all
+ *    calls on one stream come from one host thread (the reference is single-threaded by
+ *    construction, src/Gpu.cs:85-89), or the caller synchronizes when the stream changes hands.
  *  - Return value: 0 success; < 0 an argument error (the reference throws NotSupportedException
  *    or ArgumentException there); > 0 a cudaError_t (the reference throws
  *    InvalidOperationException, src/Gpu.cs:74-79).  qb200_last_error() gives the text.
@@ -88,7 +99,7 @@ int qb200_device_status(int *status);
  *          encoded to Q8_0 inside the kernel exactly as lanes_to_q8_0 encodes it
  *          (src/Ptx.Blocks.cs:52-73), and the product is taken on those blocks.
  *          With fmt_a Q4_K / Q6_K, fmt_x is Q8_0 or F32.
- *   cols must be whole blocks of a's format, and at most 65536.  rows >= 0. */
+ *   cols must be whole blocks of a's format, and at most 65536 (32768 with fmt_a Q6_K).  rows >= 0. */
 int qb200_gemv_blocks(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, void *stream);
 
 /* The block branch of the public gemv, GpuOps.Gemv<TN> (src/GpuOps.cs:277-285: rent f32 lanes,
@@ -115,17 +126,20 @@ int qb200_gemv_blocks_host(int fmt_a, int fmt_x, const void *a, const void *x, f
 /* No counterpart in the reference.  The same gemv for callers that must not allocate device memory: a host
  * application that owns all of it through its own pool (the reference's Gpu.Rent / Arena, src/Gpu.cs:227-249, would be
  * one: an allocation behind its back escapes its accounting and makes the driver synchronize the device), or a
- * latency-critical loop in which a cudaMalloc stall is not acceptable.  Where qb200_gemv_blocks prepares x in a buffer
- * the library allocated, this entry point prepares it in a fixed array compiled into the library (20 736 bytes of
- * every GPU that loads the library, held until the process exits), so it takes at most QB200_NOALLOC_MAX_COLS
- * columns and returns QB200_E_LIMIT beyond that.  It calls no cudaMalloc / cudaFree and needs no qb200_init.
+ * latency-critical loop in which a cudaMalloc stall is not acceptable.  The other entry points lean on qb200_init, which
+ * allocates the library's status word (and, for the host-buffer and workspace-less calls, staging that grows on demand);
+ * this one needs no qb200_init and calls no cudaMalloc / cudaFree.  Its scratch - x re-laid for the kernel by a small
+ * kernel of its own, where qb200_gemv_blocks re-lays x inside the gemv kernel - is a fixed array compiled into the
+ * library (20 736 bytes of every GPU that loads the library, held until the process exits), so it takes at most
+ * QB200_NOALLOC_MAX_COLS columns and returns QB200_E_LIMIT beyond that.
  * The first call on each device looks up the array's device address and sets the kernels' attributes on that device:
  * make that first call outside any stream capture.  All calls on a device share the one array and the one status
  * word: two calls whose kernels could overlap on the GPU (different streams, no ordering between them) race, and the
  * caller must order them.  Same arguments, arithmetic and results as qb200_gemv_blocks. */
 #define QB200_NOALLOC_MAX_COLS 16384
 int qb200_gemv_blocks_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, void *stream);
-/* The status word of the no-allocation path on the current device (as qb200_device_status; synchronizes). */
+/* Reads and clears the status word of the no-allocation path on the current device: non-zero when a bounded wait inside
+ * one of its kernels gave up in any call since the last reading (as qb200_device_status; synchronizes the device). */
 int qb200_gemv_noalloc_status(int *status);
 
 /* ---- A.B^T ------------------------------------------------------------------------------
@@ -137,16 +151,48 @@ int qb200_gemv_noalloc_status(int *status);
  *   operands to f32 first, src/GpuOps.Products.cs:28-42).  Every 32-value sub-block is then a
  *   k-block with scale d*sc and min dmin*m as DecodeQ4_K rounds them (src/Blocks.cs:88-93):
  *   acc = fma(float(D), sA*(d*sc), acc); acc = fma(dmin*m, -(sA*float(sum of qA)), acc).
- *   k whole blocks of both operands (32; 256 with Q4_K); m, n >= 1.
+ *   With fmt_b Q6_K every 16-value sub-block is a k-block with scale d*sc (src/Blocks.cs:167-170).
+ *   k whole blocks of both operands (32; 256 with Q4_K / Q6_K); m, n >= 1.
  *   workspace: device scratch of qb200_matmul_workspace_bytes(...) bytes, 256-byte aligned,
  *   private to the call until it completes on `stream` (the operands are re-laid there for
- *   the tensor cores).  Pass NULL/0 to use a scratch buffer the library keeps and grows. */
+ *   the tensor cores).  Pass NULL/0 to use one scratch buffer the library keeps and grows: calls
+ *   that use it must all be on one stream and come from one host thread, since a second call
+ *   re-lays its operands over the first's. */
 size_t qb200_matmul_workspace_bytes(int fmt_a, int fmt_b, int m, int n, int k);
 int qb200_matmul_blocks(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int m, int n, int k, void *workspace,
                         size_t workspace_bytes, void *stream);
 
+/* GpuOps.MatMulViewBlocks<TN> (src/MatMulBlocks.cs:414-424: rent f32 lanes, MatMulBlocks, then Back,
+ * src/GpuOps.cs:964-975 -> Ptx.LanesToBlock): c_lanes as qb200_matmul_blocks writes it and c_blocks = those
+ * m*n lanes as blocks of fmt_c (Q8_0 or Q4_0), byte for byte what qb200_encode gives on c_lanes.  When n is
+ * whole blocks of 32 and c_lanes is 16-byte aligned the blocks are encoded by the product kernel itself;
+ * otherwise by a second launch, as in the reference.  c_lanes is the scratch the reference rents; it must be given. */
+int qb200_matmul_blocks_back(int fmt_a, int fmt_b, const void *a, const void *b, float *c_lanes, int fmt_c, void *c_blocks, int m, int n,
+                             int k, void *workspace, size_t workspace_bytes, void *stream);
+
+/* No counterpart in the reference, whose kernel reads raw blocks on every call (src/MatMulBlocks.cs:234-254).
+ * The weights' half of the re-laying, done once: qb200_matmul_prepack writes B (n x k, fmt_b) into `packed`
+ * (qb200_matmul_prepacked_bytes bytes, 256-byte aligned) in the tensor cores' layout, which does not depend on m;
+ * qb200_matmul_blocks_prepacked then multiplies any A against it and gives the same bits as qb200_matmul_blocks
+ * on the raw B.  Its workspace holds the re-laid A only (qb200_matmul_prepacked_workspace_bytes; NULL/0 as above).
+ * The packed form belongs to this build of the library: do not store it in files. */
+size_t qb200_matmul_prepacked_bytes(int fmt_b, int n, int k);
+int qb200_matmul_prepack(int fmt_b, const void *b, int n, int k, void *packed, size_t packed_bytes, void *stream);
+size_t qb200_matmul_prepacked_workspace_bytes(int fmt_a, int fmt_b, int m, int k);
+int qb200_matmul_blocks_prepacked(int fmt_a, int fmt_b, const void *a, const void *b_packed, float *c, int m, int n, int k,
+                                  void *workspace, size_t workspace_bytes, void *stream);
+
+/* ProductView with Batch > 1 (src/Products.cs:15-22: `Batch` products at strides StrideA, StrideB, StrideC in
+ * values, 0 broadcasting an operand across the batch) on the block product, all products in one launch.  The
+ * reference's BlockView (src/MatMulBlocks.cs:410-411) sends batches to its decoded route; here product i reads
+ * A at a + i*stride_a values, B at b + i*stride_b values and writes c + i*stride_c f32 lanes.  Strides are
+ * whole blocks of their operand; stride_c >= m*n. */
+size_t qb200_matmul_batched_workspace_bytes(int fmt_a, int fmt_b, int m, int n, int k, int batch, int64_t stride_a, int64_t stride_b);
+int qb200_matmul_blocks_batched(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int m, int n, int k, int batch,
+                                int64_t stride_a, int64_t stride_b, int64_t stride_c, void *workspace, size_t workspace_bytes, void *stream);
+
 /* As qb200_matmul_blocks for a tiny shape, also writing every exact block sum
- * sums[(i*n + j)*(k/32) + kb]; m*n*(k/32) must be at most 2^24. */
+ * sums[(i*n + j)*kbs + kb], kbs = k/32 k-blocks a row (k/16 with fmt_b Q6_K); m*n*kbs must be at most 2^24. */
 int qb200_matmul_block_sums(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int32_t *sums, int m, int n, int k,
                             void *stream);
 

@@ -32,6 +32,13 @@ SIGNATURES = {
     "qb200_gemv_noalloc_status": (_I, [C.POINTER(_I)]),
     "qb200_matmul_workspace_bytes": (_Z, [_I, _I, _I, _I, _I]),
     "qb200_matmul_blocks": (_I, [_I, _I, _P, _P, _P, _I, _I, _I, _P, _Z, _P]),
+    "qb200_matmul_blocks_back": (_I, [_I, _I, _P, _P, _P, _I, _P, _I, _I, _I, _P, _Z, _P]),
+    "qb200_matmul_prepacked_bytes": (_Z, [_I, _I, _I]),
+    "qb200_matmul_prepack": (_I, [_I, _P, _I, _I, _P, _Z, _P]),
+    "qb200_matmul_prepacked_workspace_bytes": (_Z, [_I, _I, _I, _I]),
+    "qb200_matmul_blocks_prepacked": (_I, [_I, _I, _P, _P, _P, _I, _I, _I, _P, _Z, _P]),
+    "qb200_matmul_batched_workspace_bytes": (_Z, [_I, _I, _I, _I, _I, _I, _L, _L]),
+    "qb200_matmul_blocks_batched": (_I, [_I, _I, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _Z, _P]),
     "qb200_matmul_block_sums": (_I, [_I, _I, _P, _P, _P, _P, _I, _I, _I, _P]),
     "qb200_encode": (_I, [_I, _P, _P, _L, _P]),
     "qb200_decode": (_I, [_I, _P, _P, _L, _P]),

@@ -18,8 +18,9 @@ struct Kept {
     void *ptr = nullptr;
     size_t bytes = 0;
 };
-Kept g_stage_a, g_stage_x, g_stage_y, g_scratch, g_xprep;
+Kept g_stage_a, g_stage_x, g_stage_y, g_scratch;
 int *g_status = nullptr;      // device word the kernels OR their STATUS_* bits into
+int g_bound = -1;             // the device the kept buffers and the status word live on
 
 int fail(int code, const char *fmt, ...)
 {
@@ -69,6 +70,17 @@ int keep(Kept &k, size_t bytes)
     return 0;
 }
 
+void release_kept()
+{
+    Kept *all[] = { &g_stage_a, &g_stage_x, &g_stage_y, &g_scratch };
+    for (Kept *k : all) {
+        if (k->ptr) cudaFree(k->ptr);
+        *k = Kept();
+    }
+    if (g_status) cudaFree(g_status);
+    g_status = nullptr;
+}
+
 int check_gemv(int fmt_a, int fmt_x, const void *a, const void *x, const float *y, int rows, int cols)
 {
     if (!g_ready) return fail(QB200_E_DEVICE, "qb200_init has not succeeded");
@@ -79,7 +91,8 @@ int check_gemv(int fmt_a, int fmt_x, const void *a, const void *x, const float *
         return fail(QB200_E_FORMAT, "%s x %s: x comes in Q8_0 or f32 (or Q4_0 against Q8_0 / Q4_0 rows)", fmt_name(fmt_a), fmt_name(fmt_x));
     if (rows < 0 || cols <= 0 || cols % bv != 0)
         return fail(QB200_E_SHAPE, "%s: the block product takes columns in whole blocks of %d (rows %d, cols %d)", fmt_name(fmt_a), bv, rows, cols);
-    if (cols > 65536) return fail(QB200_E_LIMIT, "cols %d: at most 65536 columns", cols);
+    const int widest = fmt_a == QB200_Q6_K ? 32768 : 65536;
+    if (cols > widest) return fail(QB200_E_LIMIT, "cols %d: at most %d columns in %s rows", cols, widest, fmt_name(fmt_a));
     if (rows == 0) return 0;
     if (!a || !x || !y) return fail(QB200_E_POINTER, "null operand");
     if (((uintptr_t)a & 1) || ((uintptr_t)x & (fmt_x == QB200_F32 ? 3 : 1)) || ((uintptr_t)y & 3)) return fail(QB200_E_POINTER, "misaligned operand");
@@ -123,15 +136,20 @@ int qb200_init(int device)
     g_caps.l2_bytes = prop.l2CacheSize;
     g_caps.global_bytes = (int64_t)prop.totalGlobalMem;
     if (prop.major != 10) return fail(QB200_E_DEVICE, "device %d is sm_%d%d: the kernels are built for sm_100a only", device, prop.major, prop.minor);
+    // What an earlier binding kept lives on its device: released there before this one takes over (a second qb200_init of
+    // the same device keeps it all).
+    if (g_bound >= 0 && g_bound != device) {
+        cudaSetDevice(g_bound);
+        release_kept();
+        if ((e = cudaSetDevice(device))) return cuda_fail(e, "cudaSetDevice");
+    }
     if (!g_status) {
         if ((e = cudaMalloc((void **)&g_status, 256))) return cuda_fail(e, "cudaMalloc status");
+        if ((e = cudaMemset(g_status, 0, 256))) return cuda_fail(e, "cudaMemset status");
     }
-    if ((e = cudaMemset(g_status, 0, 256))) return cuda_fail(e, "cudaMemset status");
+    g_bound = device;
     if ((e = qb::gemv_init(g_caps.sm_count, g_caps.max_shared_bytes, g_status))) return cuda_fail(e, "gemv attributes");
     if ((e = qb::matmul_init(g_caps.sm_count, g_caps.max_shared_bytes, g_status))) return cuda_fail(e, "matmul attributes");
-    g_stage_a = g_stage_x = g_stage_y = g_scratch = g_xprep = Kept();
-    // x in the gemv's own layout: sized once for the widest x the kernels take, so no gemv call allocates
-    { int rc = keep(g_xprep, qb::gemv_scratch_bytes(65536)); if (rc) return rc; }
     g_ready = true;
     t_error[0] = 0;
     return 0;
@@ -171,7 +189,7 @@ int qb200_gemv_blocks(int fmt_a, int fmt_x, const void *a, const void *x, float 
 {
     int rc = check_gemv(fmt_a, fmt_x, a, x, y, rows, cols);
     if (rc) return rc;
-    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, nullptr, 0, nullptr, rows, cols, g_xprep.ptr, (cudaStream_t)stream), "gemv_blocks");
+    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, nullptr, 0, nullptr, rows, cols, (cudaStream_t)stream), "gemv_blocks");
 }
 
 // The block branch of the public gemv (reference src/GpuOps.cs:277-285) in one launch: f32 lanes and their `Back`.
@@ -183,7 +201,7 @@ int qb200_gemv_blocks_back(int fmt_a, int fmt_x, const void *a, const void *x, f
     if (fmt_y != QB200_Q8_0 && fmt_y != QB200_Q4_0)
         return fail(QB200_E_FORMAT, "%s: the gemv encodes its output as Q8_0 or Q4_0; use qb200_encode for the others", fmt_name(fmt_y));
     if (rows > 0 && (!y_blocks || ((uintptr_t)y_blocks & 1))) return fail(QB200_E_POINTER, "null or misaligned y_blocks");
-    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y_lanes, nullptr, fmt_y, y_blocks, rows, cols, g_xprep.ptr, (cudaStream_t)stream),
+    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y_lanes, nullptr, fmt_y, y_blocks, rows, cols, (cudaStream_t)stream),
                   "gemv_blocks_back");
 }
 
@@ -192,7 +210,7 @@ int qb200_gemv_block_sums(int fmt_a, int fmt_x, const void *a, const void *x, fl
     int rc = check_gemv(fmt_a, fmt_x, a, x, y, rows, cols);
     if (rc) return rc;
     if (rows > 0 && (!sums || ((uintptr_t)sums & 3))) return fail(QB200_E_POINTER, "null or misaligned sums");
-    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, sums, 0, nullptr, rows, cols, g_xprep.ptr, (cudaStream_t)stream), "gemv_block_sums");
+    return finish(qb::gemv_launch(fmt_a, fmt_x, a, x, y, sums, 0, nullptr, rows, cols, (cudaStream_t)stream), "gemv_block_sums");
 }
 
 int qb200_gemv_blocks_host(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols)
@@ -242,10 +260,27 @@ int qb200_gemv_noalloc_status(int *status)
     return finish(qb::gemv_noalloc_status(status), "gemv_noalloc_status");
 }
 
+// The scratch a product call needs, and where it comes from: the caller's workspace, or the buffer the library keeps.
+static int take_workspace(void *&workspace, size_t workspace_bytes, size_t need)
+{
+    if (workspace) {
+        if (workspace_bytes < need) return fail(QB200_E_WORKSPACE, "workspace of %zu bytes, %zu needed", workspace_bytes, need);
+        if ((uintptr_t)workspace & 255) return fail(QB200_E_WORKSPACE, "workspace not 256-byte aligned");
+        return 0;
+    }
+    int rc = keep(g_scratch, need);
+    if (rc) return rc;
+    workspace = g_scratch.ptr;
+    return 0;
+}
+
+static const qb::MatmulBatch ONE = { 1, 0, 0, 0 };
+
 size_t qb200_matmul_workspace_bytes(int fmt_a, int fmt_b, int m, int n, int k)
 {
-    if (m <= 0 || n <= 0 || k <= 0 || k % 32) return 0;
-    return qb::matmul_workspace_bytes(fmt_a, fmt_b, m, n, k);
+    (void)fmt_a;
+    if (m <= 0 || n <= 0 || k <= 0 || !qb::block_values(fmt_b) || k % qb::block_values(fmt_b)) return 0;
+    return qb::matmul_workspace_bytes(fmt_b, m, n, k, ONE, false);
 }
 
 int qb200_matmul_blocks(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int m, int n, int k, void *workspace,
@@ -253,15 +288,94 @@ int qb200_matmul_blocks(int fmt_a, int fmt_b, const void *a, const void *b, floa
 {
     int rc = check_matmul(fmt_a, fmt_b, a, b, c, m, n, k);
     if (rc) return rc;
-    const size_t need = qb::matmul_workspace_bytes(fmt_a, fmt_b, m, n, k);
-    if (workspace) {
-        if (workspace_bytes < need) return fail(QB200_E_WORKSPACE, "workspace of %zu bytes, %zu needed", workspace_bytes, need);
-        if ((uintptr_t)workspace & 255) return fail(QB200_E_WORKSPACE, "workspace not 256-byte aligned");
-    } else {
-        if ((rc = keep(g_scratch, need))) return rc;
-        workspace = g_scratch.ptr;
-    }
-    return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, c, nullptr, m, n, k, workspace, (cudaStream_t)stream), "matmul_blocks");
+    if ((rc = take_workspace(workspace, workspace_bytes, qb::matmul_workspace_bytes(fmt_b, m, n, k, ONE, false)))) return rc;
+    return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c, nullptr, 0, nullptr, m, n, k, ONE, workspace, (cudaStream_t)stream), "matmul_blocks");
+}
+
+// GpuOps.MatMulViewBlocks<TN> (reference src/MatMulBlocks.cs:414-424) in one product launch: the f32 lanes and their `Back`.
+int qb200_matmul_blocks_back(int fmt_a, int fmt_b, const void *a, const void *b, float *c_lanes, int fmt_c, void *c_blocks, int m, int n,
+                             int k, void *workspace, size_t workspace_bytes, void *stream)
+{
+    int rc = check_matmul(fmt_a, fmt_b, a, b, c_lanes, m, n, k);
+    if (rc) return rc;
+    if (fmt_c != QB200_Q8_0 && fmt_c != QB200_Q4_0)
+        return fail(QB200_E_FORMAT, "%s: the product encodes its output as Q8_0 or Q4_0; use qb200_encode for the others", fmt_name(fmt_c));
+    if (!c_blocks || ((uintptr_t)c_blocks & 1)) return fail(QB200_E_POINTER, "null or misaligned c_blocks");
+    if ((rc = take_workspace(workspace, workspace_bytes, qb::matmul_workspace_bytes(fmt_b, m, n, k, ONE, false)))) return rc;
+    // a block of C (32 consecutive values of the row-major m x n array) lies inside one row only when n is whole blocks,
+    // and the encoding threads read the lanes 16 bytes at a time; otherwise `Back` is the launch of its own it is in the reference
+    const bool fused = n % 32 == 0 && ((uintptr_t)c_lanes & 15) == 0;
+    rc = qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c_lanes, nullptr, fmt_c, fused ? c_blocks : nullptr, m, n, k, ONE, workspace, (cudaStream_t)stream);
+    if (rc == 0 && !fused) rc = qb::encode_launch(fmt_c, c_lanes, c_blocks, (int64_t)m * n, (cudaStream_t)stream);
+    return finish(rc, "matmul_blocks_back");
+}
+
+size_t qb200_matmul_prepacked_bytes(int fmt_b, int n, int k)
+{
+    if (n <= 0 || k <= 0 || !qb::block_values(fmt_b) || k % qb::block_values(fmt_b)) return 0;
+    return qb::matmul_prepacked_bytes(fmt_b, n, k);
+}
+
+int qb200_matmul_prepack(int fmt_b, const void *b, int n, int k, void *packed, size_t packed_bytes, void *stream)
+{
+    if (!g_ready) return fail(QB200_E_DEVICE, "qb200_init has not succeeded");
+    if (!qb::block_values(fmt_b)) return fail(QB200_E_FORMAT, "%s: not a block format", fmt_name(fmt_b));
+    if (n <= 0 || k <= 0 || k % qb::block_values(fmt_b)) return fail(QB200_E_SHAPE, "k in whole blocks of B (n %d, k %d)", n, k);
+    if (!b || ((uintptr_t)b & 1)) return fail(QB200_E_POINTER, "null or misaligned operand");
+    if (!packed || ((uintptr_t)packed & 255)) return fail(QB200_E_WORKSPACE, "the packed operand needs a 256-byte aligned buffer");
+    const size_t need = qb::matmul_prepacked_bytes(fmt_b, n, k);
+    if (packed_bytes < need) return fail(QB200_E_WORKSPACE, "packed buffer of %zu bytes, %zu needed", packed_bytes, need);
+    return finish(qb::matmul_prepack_b(fmt_b, b, n, k, packed, (cudaStream_t)stream), "matmul_prepack");
+}
+
+size_t qb200_matmul_prepacked_workspace_bytes(int fmt_a, int fmt_b, int m, int k)
+{
+    (void)fmt_a;
+    if (m <= 0 || k <= 0 || !qb::block_values(fmt_b) || k % qb::block_values(fmt_b)) return 0;
+    return qb::matmul_workspace_bytes(fmt_b, m, 1, k, ONE, true);
+}
+
+int qb200_matmul_blocks_prepacked(int fmt_a, int fmt_b, const void *a, const void *b_packed, float *c, int m, int n, int k,
+                                  void *workspace, size_t workspace_bytes, void *stream)
+{
+    int rc = check_matmul(fmt_a, fmt_b, a, b_packed, c, m, n, k);
+    if (rc) return rc;
+    if ((uintptr_t)b_packed & 255) return fail(QB200_E_WORKSPACE, "the packed operand is 256-byte aligned");
+    if ((rc = take_workspace(workspace, workspace_bytes, qb::matmul_workspace_bytes(fmt_b, m, n, k, ONE, true)))) return rc;
+    return finish(qb::matmul_launch(fmt_a, fmt_b, a, nullptr, b_packed, c, nullptr, 0, nullptr, m, n, k, ONE, workspace, (cudaStream_t)stream),
+                  "matmul_blocks_prepacked");
+}
+
+static int check_batch(int fmt_a, int fmt_b, int m, int n, int k, int batch, int64_t stride_a, int64_t stride_b, int64_t stride_c)
+{
+    if (batch < 1) return fail(QB200_E_SHAPE, "batch %d", batch);
+    if (stride_a < 0 || stride_b < 0 || stride_c < 0) return fail(QB200_E_SHAPE, "negative batch stride");
+    if (stride_a % qb::block_values(fmt_a) || stride_b % qb::block_values(fmt_b))
+        return fail(QB200_E_SHAPE, "a batch's operands start on whole blocks (strides %lld, %lld values)", (long long)stride_a, (long long)stride_b);
+    if (batch > 1 && stride_c < (int64_t)m * n) return fail(QB200_E_SHAPE, "the batch's results overlap (stride %lld values, %lld a product)", (long long)stride_c, (long long)m * n);
+    (void)k;
+    return 0;
+}
+
+size_t qb200_matmul_batched_workspace_bytes(int fmt_a, int fmt_b, int m, int n, int k, int batch, int64_t stride_a, int64_t stride_b)
+{
+    (void)fmt_a;
+    if (m <= 0 || n <= 0 || k <= 0 || batch < 1 || !qb::block_values(fmt_b) || k % qb::block_values(fmt_b)) return 0;
+    const qb::MatmulBatch bt = { batch, batch > 1 ? stride_a : 0, batch > 1 ? stride_b : 0, 0 };
+    return qb::matmul_workspace_bytes(fmt_b, m, n, k, bt, false);
+}
+
+// ProductView with Batch > 1 (reference src/Products.cs:15-22) on the block product: every product of the batch in one launch.
+int qb200_matmul_blocks_batched(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int m, int n, int k, int batch,
+                                int64_t stride_a, int64_t stride_b, int64_t stride_c, void *workspace, size_t workspace_bytes, void *stream)
+{
+    int rc = check_matmul(fmt_a, fmt_b, a, b, c, m, n, k);
+    if (rc) return rc;
+    if ((rc = check_batch(fmt_a, fmt_b, m, n, k, batch, stride_a, stride_b, stride_c))) return rc;
+    const qb::MatmulBatch bt = { batch, batch > 1 ? stride_a : 0, batch > 1 ? stride_b : 0, batch > 1 ? stride_c : 0 };
+    if ((rc = take_workspace(workspace, workspace_bytes, qb::matmul_workspace_bytes(fmt_b, m, n, k, bt, false)))) return rc;
+    return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c, nullptr, 0, nullptr, m, n, k, bt, workspace, (cudaStream_t)stream),
+                  "matmul_blocks_batched");
 }
 
 int qb200_matmul_block_sums(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int32_t *sums, int m, int n, int k, void *stream)
@@ -269,9 +383,10 @@ int qb200_matmul_block_sums(int fmt_a, int fmt_b, const void *a, const void *b, 
     int rc = check_matmul(fmt_a, fmt_b, a, b, c, m, n, k);
     if (rc) return rc;
     if (!sums || ((uintptr_t)sums & 3)) return fail(QB200_E_POINTER, "null or misaligned sums");
-    if ((int64_t)m * n * (k / 16) > (1 << 24)) return fail(QB200_E_LIMIT, "block sums are for small shapes: m*n*(k/16) at most 2^24");
-    if ((rc = keep(g_scratch, qb::matmul_workspace_bytes(fmt_a, fmt_b, m, n, k)))) return rc;
-    return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, c, sums, m, n, k, g_scratch.ptr, (cudaStream_t)stream), "matmul_block_sums");
+    const int per = fmt_b == QB200_Q6_K ? 16 : 32;
+    if ((int64_t)m * n * (k / per) > (1 << 24)) return fail(QB200_E_LIMIT, "block sums are for small shapes: m*n*(k/%d) at most 2^24", per);
+    if ((rc = keep(g_scratch, qb::matmul_workspace_bytes(fmt_b, m, n, k, ONE, false)))) return rc;
+    return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c, sums, 0, nullptr, m, n, k, ONE, g_scratch.ptr, (cudaStream_t)stream), "matmul_block_sums");
 }
 
 int qb200_encode(int fmt, const float *lanes, void *blocks, int64_t n, void *stream)

@@ -1,25 +1,33 @@
 // Block-scaled gemv for sm_100a: y = A.x with A in Q8_0 / Q4_0 / Q4_K / Q6_K rows and x in blocks or f32.
 //
 // Replaces Ptx.GemvBlocks (reference src/BlockProducts.cs:78-172), which walks one row per thread with 2-byte loads.
-// Here the matrix is one flat byte stream: a producer warp moves whole groups of rows ("units") into a ring of
+// Here the matrix is one flat byte stream: a producer warp moves whole groups of rows ("chunks") into a ring of
 // shared-memory slots with untiled TMA bulk copies (16-byte aligned middle part; the ragged head and tail bytes by
 // plain 2-byte loads), and consumer warps unpack the raw block bytes in registers, take each block's integer dot with
-// dp4a in s32, apply the f16 block scales in f32 and reduce each row with warp shuffles.  x is first turned, by a small
-// kernel of its own, into int8 values + f32 scales + per-block sums in a scratch buffer (in the reference's Q8_0
-// encoding when it arrives as f32, src/Ptx.Blocks.cs:52-73), laid out so that every lane of the gemv fetches the blocks
-// it meets in every row with a few coalesced 16-byte loads and keeps them in registers.  The gemv is launched as a
-// programmatic dependent of that kernel: its weight copies start at once and only the read of x waits for it.
+// dp4a in s32, apply the f16 block scales in f32 and reduce each row with warp shuffles.
 //
-// A consumer warp owns a fixed column segment of every row (runs of 64 blocks), so its share of x stays in registers
-// for the whole kernel; the warps of a row group split a row between them, write one partial sum per row and segment
-// to shared memory, and the block adds the segments in ascending order once at the end (no barrier per unit).
+// x is prepared inside the same kernel: the consumer threads of every block turn it into int8 values + f32 scales +
+// per-block sums in shared memory (f32 x is encoded to Q8_0 operation for operation as the reference's lanes_to_q8_0
+// does, src/Ptx.Blocks.cs:52-73; Q8_0 / Q4_0 x is unpacked), laid out so that every lane fetches the blocks it meets in
+// every row with a few 16-byte loads and keeps them in registers for the whole kernel.  (The entry point that must not
+// allocate prepares x with a small kernel of its own into a static device array instead: see the end of the file.)
+//
+// A consumer warp owns a fixed column segment of every row (runs of 64 blocks); the warps of a row group split a row
+// between them, write one partial sum per row and segment to shared memory, and the block adds the segments in
+// ascending order (no barrier per chunk).
 //
 // Per block the arithmetic is the reference kernel's: scale = dA*dX (rounded), acc = fma(scale, float(dot), acc)
 // (src/BlockProducts.cs:158-161).  The order in which a row's blocks are added differs (lanes, then a shuffle tree,
 // then column segments in ascending order); it is fixed for a given shape, so results are reproducible run to run.
+//
+// Launch order: calls are launched as programmatic dependents (PDL) of whatever precedes them in the stream.  A call
+// whose buffers none of the gemv launches still in flight touches skips griddepcontrol.wait and runs beside them; every
+// other call waits (gemv_launch).
 #include "common.cuh"
 #include "encode_blocks.cuh"
 #include "launch.h"
+
+#include <mutex>
 
 namespace qb {
 
@@ -34,8 +42,6 @@ struct GemvArgs {
     int chunk_align;     // block boundaries fall on multiples of this many chunks (32 rows when yb is set, else 1 chunk)
     int32_t *sums;
     int *status;         // device word for STATUS_* bits
-    long long *timeline; // optional: 8 timestamps (ns) a block, for tuning; null in normal use
-    int probe;           // tuning aid: 1 = consumers skip the arithmetic, 2 = the producer skips the copies; 0 in normal use
     int rows, cols;
     uint32_t row_bytes;
     int nw;              // consumer warps; the producer is warp nw
@@ -51,16 +57,6 @@ struct GemvArgs {
     uint32_t row_flip;   // 1 when a row is 2 (mod 4) bytes long: rows alternate between the two 4-byte alignments
     uint32_t off_x, off_part, off_ring;   // shared-memory offsets
 };
-
-// The timeline and the probes are tuning aids: compiled in only with -DQB_GEMV_TUNING (the plain kernel is sensitive
-// to every instruction and register they cost).
-#ifdef QB_GEMV_TUNING
-#define TUNE_TIMELINE(p) ((p).timeline)
-#define TUNE_PROBE(p) ((p).probe)
-#else
-#define TUNE_TIMELINE(p) ((long long *)nullptr)
-#define TUNE_PROBE(p) 0
-#endif
 
 constexpr int MAX_SLOTS = 60;
 constexpr uint32_t SMEM_HEADER = 1024;  // full[60] and empty[60] barriers, the x barrier and the abort word
@@ -220,15 +216,12 @@ __global__ void __launch_bounds__(128) prepare_x_kernel(const void *x, int fmt_x
 // The same preparation inside the gemv kernel, by all its consumer threads, into shared memory.  f32 x: four threads a
 // block of 32 values (eight values each, coalesced 32-byte reads); the block's max and sum meet by two shuffles.
 // The arithmetic is quantize32's, value for value.
-#ifndef QB_GEMV_XU
-#define QB_GEMV_XU 4
-#endif
 template <bool PAIRED>
 __device__ __forceinline__ void prepare_x_in_block(const void *x, int fmt_x, int cols, uint8_t *out, int tid, int threads, uint32_t xbar)
 {
     const int blocks = cols / 32;
     uint8_t *meta = out + xprep_codes_bytes(cols);
-    constexpr int XU = QB_GEMV_XU;
+    constexpr int XU = 4;
     bool told = false;
     if (fmt_x == QB200_F32 && ((uintptr_t)x & 15) == 0) {
         const int items = blocks * 4;
@@ -781,14 +774,6 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
     }
     __syncthreads();
 
-    auto stamp = [&](int slot) {
-        if (TUNE_TIMELINE(p) && lane == 0 && warp == 0) {
-            long long t;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-            p.timeline[(size_t)blockIdx.x * 32 + slot] = t;
-        }
-    };
-    stamp(0);
     uint8_t *ring = smem + p.off_ring;
     // block b takes the chunks [C*b/grid, C*(b+1)/grid); with BACK, whole groups of chunk_align chunks (32 rows)
     int chunk0, chunk1;
@@ -809,7 +794,11 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         // arithmetic and the barrier calls, which would pace the whole kernel): a pass of the warp issues `step`
         // consecutive chunks, never more than there are slots, so no lane of a pass waits on another lane of it.
         // (with x in a buffer shared between calls the consumers decide when the next call may be scheduled)
-        if (p.x) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        // Only a call that does not wait lets its dependents be scheduled from here.  A call that waits for its
+        // predecessor must not: its successor could then start while that predecessor is still writing, and the host's
+        // record of who can still be running (gemv_launch) holds only this call once it has waited.  Its blocks trigger
+        // from the consumers instead, after griddepcontrol.wait, i.e. when everything earlier has completed.
+        if (p.x && p.independent) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         // A slot belongs to one row group for the whole kernel (spg slots a group): the warps that wait on a slot's
         // barrier are then always the ones that released its previous use, so a phase parity can never be mistaken for the
         // parity two phases back.
@@ -834,7 +823,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
                     const uint8_t *b1 = (const uint8_t *)((uintptr_t)g1 & ~(uintptr_t)15);
                     uint8_t *slot = ring + (size_t)s * p.slot_stride + mis;      // g0's byte lands here
                     const uint8_t *head_end = g1, *tail_begin = g1;
-                    if (b1 > b0 && !(TUNE_PROBE(p) & 2)) {
+                    if (b1 > b0) {
                         mbar_expect_tx(full0 + 8 * s, (uint32_t)(b1 - b0));
                         bulk_g2s(smem_u32(slot + (b0 - g0)), b0, (uint32_t)(b1 - b0), full0 + 8 * s);
                         head_end = b0;
@@ -885,12 +874,10 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
     // the launch before this one (the only one that can still be running) shares no buffer with this call
     if (!p.independent || !p.x) asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint8_t *xp = p.xprep;
-    stamp(1);
     if (p.x) {
         if (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) prepare_x_in_block<true>(p.x, p.fmt_x, p.cols, smem + p.off_x, threadIdx.x, threads, xbar);
         else prepare_x_in_block<false>(p.x, p.fmt_x, p.cols, smem + p.off_x, threadIdx.x, threads, xbar);
-        stamp(2);
-        named_bar_sync(1, threads);
+            named_bar_sync(1, threads);
         xp = smem + p.off_x;
     }
 #pragma unroll
@@ -906,13 +893,11 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
     // whether every lane of this warp has both blocks of every run (then whole chunks take the branch-free path)
     bool whole_runs = false;
     if (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) whole_runs = (seg + (RUNS - 1) * p.cs + 1) * 64 <= p.cols / 32;
-    stamp(3);
 
     float *part = (float *)(smem + p.off_part);
     const int blocks32 = p.cols / 32;
     const uint32_t first_off = (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) ? (uint32_t)(seg * 64 + lane * 2) * (uint32_t)block_bytes(FMT) : 0u;
     bool alive = true;
-    long long c_wait = 0, c_dot = 0, c_sum = 0;
     const int spg = p.slots / p.rg;                  // this row group's own slots: rgi*spg .. rgi*spg + spg - 1
     int sl = 0, flush_i = 0;
     uint32_t phase = 0;
@@ -920,18 +905,14 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         const int chunk = chunk0 + i * p.rg + rgi, s = rgi * spg + sl;
         const int row0 = chunk * RW;
         const int nvalid = chunk < chunk1 ? max(0, min(RW, p.rows - row0)) : 0;
-        long long tq0 = TUNE_TIMELINE(p) ? clock64() : 0;
         if (alive) alive = mbar_wait_warp(full0 + 8 * s, phase, abort_flag, p.status, STATUS_GEMV_WAIT);
-        long long tq1 = TUNE_TIMELINE(p) ? clock64() : 0;
-        c_wait += tq1 - tq0;
-        if (i == 0) stamp(4);
         if (alive) {
             const uint32_t mis = (uint32_t)(uintptr_t)(p.a + (size_t)row0 * p.row_bytes) & 15u;
             const uint8_t *rows = ring + (size_t)s * p.slot_stride + mis;
             float acc[RW];
 #pragma unroll
             for (int r = 0; r < RW; r++) acc[r] = 0.f;
-            bool done = (TUNE_PROBE(p) & 1) != 0;
+            bool done = false;
             if constexpr ((FMT == QB200_Q8_0 || FMT == QB200_Q4_0) && !SUMS) {
                 if (!done && nvalid == RW) {
                     const bool q4 = (((uint32_t)(uintptr_t)rows + first_off) & 2u) == 0;
@@ -963,12 +944,9 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
                     }
                 }
             }
-            long long tq2 = TUNE_TIMELINE(p) ? clock64() : 0;
-            c_dot += tq2 - tq1;
             // the row sums (every lane has read its last byte of the slot once these shuffles are done)
             if constexpr (RW == 4) {
                 const float total = warp_sum4(acc, lane);           // lanes 8r .. 8r+7 hold row r
-                if (TUNE_TIMELINE(p)) c_sum += clock64() - tq2;
                 if (lane == 0) mbar_arrive(empty0 + 8 * s);
                 const int r = lane >> 3;
                 if ((lane & 7) == 0) {
@@ -978,7 +956,6 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
             } else {
 #pragma unroll
                 for (int r = 0; r < RW; r++) acc[r] = warp_sum(acc[r]);
-                if (TUNE_TIMELINE(p)) c_sum += clock64() - tq2;
                 if (lane == 0) mbar_arrive(empty0 + 8 * s);
                 if (p.cs == 1) {
 #pragma unroll
@@ -993,11 +970,6 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         if (++sl == spg) { sl = 0; phase ^= 1u; }
         // the partial sums of the last flush_units units: segments added in ascending order
         if (p.cs > 1 && (++flush_i == p.flush_units || i + 1 == my_units)) {
-            if (TUNE_TIMELINE(p) && lane == 0 && i + 1 == my_units) {
-                long long t;
-                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-                p.timeline[(size_t)blockIdx.x * 32 + 8 + warp] = t;
-            }
             named_bar_sync(1, threads);
             const int first = i + 1 - flush_i, count = flush_i * p.stage_rows;
             for (int idx = threadIdx.x; idx < count; idx += threads) {
@@ -1018,19 +990,13 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         named_bar_sync(1, threads);
         if (!*abort_flag) back_rows(p.y, p.yb, p.fmt_y, p.rows, chunk0 * RW, min(p.rows, chunk1 * RW), threadIdx.x, threads);
     }
-    stamp(5);
-    if (TUNE_TIMELINE(p) && warp == 0 && lane == 0) {
-        p.timeline[(size_t)blockIdx.x * 32 + 6] = c_wait;
-        p.timeline[(size_t)blockIdx.x * 32 + 7] = (c_dot << 24) | (c_sum & 0xFFFFFF);
-    }
 }
 
 // ---------------------------------------------------------------------------------- host side: shape -> configuration
 
 static int g_sm_count = 0, g_max_smem = 0;
+static int g_epoch = 0;          // counts the library's bindings to a device: plans made under an earlier one are void
 static int *g_status = nullptr;
-static long long *g_timeline = nullptr;
-static int g_probe = 0;
 
 struct GemvPlan {
     int rw, runs_per_warp, nw, nwmax, cs, rg, stages, grid;
@@ -1040,27 +1006,8 @@ struct GemvPlan {
     GemvArgs args;
 };
 
-static int env_int(const char *name, int fallback)
-{
-    const char *v = getenv(name);
-    return v && *v ? atoi(v) : fallback;
-}
-
-// tuning overrides, read once when the library binds a device
-static struct { int warps, stage_bytes, rw, cs, stages, prekernel, prefetch, always_wait, grid_ctas; } g_tune = { 0, 24576, 0, 0, 0, 0, 0, 0, 0 };
-
-static void read_tuning()
-{
-    g_tune.warps = env_int("QB200_GEMV_WARPS", 0);      // 4 or 16 forces a variant
-    g_tune.stage_bytes = env_int("QB200_GEMV_STAGE_BYTES", 24576);
-    g_tune.rw = env_int("QB200_GEMV_RW", 0);
-    g_tune.cs = env_int("QB200_GEMV_CS", 0);
-    g_tune.stages = env_int("QB200_GEMV_STAGES", 0);
-    g_tune.prekernel = env_int("QB200_GEMV_PREKERNEL", 0);
-    g_tune.prefetch = env_int("QB200_GEMV_PREFETCH", 0);
-    g_tune.always_wait = env_int("QB200_GEMV_ALWAYS_WAIT", 0);
-    g_tune.grid_ctas = env_int("QB200_GEMV_GRID_CTAS", 0);
-}
+// bytes of a chunk the plan aims at: rows a warp takes at once are halved until a chunk is at most this
+constexpr uint32_t CHUNK_BYTES = 24576;
 
 // Runs of x that cover a row: 2048 columns each, but Q6_K runs are four super-blocks of one parity out of eight.
 static int runs_of(int fmt, int cols)
@@ -1091,13 +1038,12 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, b
         const double rate = (double)(nw / c) / per;
         if (rate > best * (1.0 + 1e-9) || (rate > best * (1.0 - 1e-9) && c > cs)) { best = rate; cs = c; }
     }
-    if (g_tune.cs >= 1 && g_tune.cs <= nw && (runs + g_tune.cs - 1) / g_tune.cs <= max_runs_per_warp(fmt_a)) cs = g_tune.cs;
     if (cs == 0) return QB200_E_LIMIT;
     const int per = (runs + cs - 1) / cs, rg = nw / cs;
     nw = rg * cs;
     // rows a warp takes at once: a chunk near the target size, at least one row
     int rw = rw_first;
-    while (rw > 1 && (uint64_t)rw * row_bytes > (uint64_t)g_tune.stage_bytes) rw /= 2;
+    while (rw > 1 && (uint64_t)rw * row_bytes > (uint64_t)CHUNK_BYTES) rw /= 2;
     pl.rw = rw; pl.runs_per_warp = per; pl.nw = nw; pl.nwmax = nwmax; pl.cs = cs; pl.rg = rg;
     const int stage_rows = rg * rw;
     pl.stage_stride = ((uint32_t)rw * row_bytes + 64u + 127u) / 128u * 128u;       // one chunk, up to 15 bytes of misalignment before it and a block's length of slack after it
@@ -1113,7 +1059,7 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, b
     // partial sums: room for every round of a block when that is small, else PART_BYTES with flushes in between
     const uint32_t round_bytes = (uint32_t)stage_rows * cs * 4u;
     // blocks of one grid an SM: one, so that the blocks sharing an SM belong to successive launches
-    const int gctas = g_tune.grid_ctas >= 1 && g_tune.grid_ctas <= ctas ? g_tune.grid_ctas : 1;
+    const int gctas = 1;
     const int grid_guess = g_sm_count < 1 ? 1 : g_sm_count * gctas;
     const uint32_t rounds = (uint32_t)(((a.chunks + grid_guess - 1) / grid_guess + rg - 1) / rg) + 1u;
     const uint32_t part_cap = ctas > 1 ? PART_BYTES / 4 : PART_BYTES;
@@ -1127,7 +1073,6 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, b
     if (slots > MAX_SLOTS) slots = MAX_SLOTS;
     const int per_block = ((a.chunks + pl.grid - 1) / pl.grid + a.chunk_align - 1 + rg - 1) / rg;      // rounds of rg chunks a block takes at most
     if (slots > per_block * rg) slots = per_block * rg;
-    if (g_tune.stages >= 1 && g_tune.stages * rg < slots) slots = g_tune.stages * rg;
     slots = slots / rg * rg;                     // every row group owns the same number of slots
     if (slots < rg) return QB200_E_LIMIT;
     pl.stages = slots;
@@ -1135,7 +1080,7 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, b
     a.slots = slots;
     // the whole-SM variant holds half its ring back until x has been asked for (x's reads then meet idle queues); the
     // small blocks, with two to four slots, ask for all of them at once (no measurable difference either way)
-    a.prefetch = g_tune.prefetch > 0 ? g_tune.prefetch : nwmax == 4 ? slots : (slots + 1) / 2;
+    a.prefetch = nwmax == 4 ? slots : (slots + 1) / 2;
     a.slot_stride = pl.stage_stride;
     pl.smem_bytes = a.off_ring + (uint32_t)slots * pl.stage_stride;
     return 0;
@@ -1150,9 +1095,8 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, b
 // its output (that variant exists for the whole-SM blocks only).
 static int plan_gemv(int fmt_a, int rows, int cols, bool sums, bool overlapped, bool back, GemvPlan &pl)
 {
-    const int forced = g_tune.warps;
-    const int rw_first = sums ? 1 : (g_tune.rw == 1 || g_tune.rw == 2 || g_tune.rw == 4) ? g_tune.rw : 4;
-    if (!sums && !back && forced != 16 && (overlapped || forced == 4)) {
+    const int rw_first = sums ? 1 : 4;
+    if (!sums && !back && overlapped) {
         for (int rw = rw_first; rw >= 1; rw /= 2)
             if (plan_blocks(fmt_a, rows, cols, 4, rw, back, pl) == 0 && pl.deep) return 0;
     }
@@ -1235,10 +1179,11 @@ static cudaError_t set_attr(int bytes)
 
 cudaError_t gemv_init(int sm_count, int max_smem, int *status)
 {
+    g_epoch++;                   // plans and launch histories made for the device bound before are void
+    gemv_forget_history();
     g_sm_count = sm_count;
     g_max_smem = max_smem;
     g_status = status;
-    read_tuning();
     cudaError_t e;
     if ((e = set_attr<QB200_Q8_0>(max_smem))) return e;
     if ((e = set_attr<QB200_Q4_0>(max_smem))) return e;
@@ -1247,7 +1192,6 @@ cudaError_t gemv_init(int sm_count, int max_smem, int *status)
 }
 
 // Returns 0, a negative QB200_E_* or a positive cudaError_t.  Arguments are already validated.
-size_t gemv_scratch_bytes(int cols) { return xprep_bytes(cols); }
 
 // Ordering against earlier gemv launches of this thread.  A gemv is normally launched as a programmatic dependent of
 // whatever precedes it in the stream, and may skip griddepcontrol.wait; a launch that skips it can run beside its
@@ -1270,6 +1214,9 @@ static thread_local struct {
 
 void gemv_forget_history() { t_hist.count = 0; }
 
+// The host thread's cached plans belong to the device they were made for: dropped when the library binds another one.
+static thread_local int t_plans_cached = 0, t_plans_next = 0, t_plans_epoch = 0;
+
 static bool overlap(const Touched &u, const Touched &v)
 {
     return u.n && v.n && u.p < v.p + v.n && v.p < u.p + u.n;
@@ -1288,7 +1235,7 @@ static bool conflicts(const Launched &now, const Launched &old)
 }
 
 int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int fmt_y, void *y_blocks, int rows,
-                int cols, void *scratch, cudaStream_t stream)
+                int cols, cudaStream_t stream)
 {
     if (rows == 0) return 0;
     const size_t row_bytes = (size_t)(cols / block_values(fmt_a)) * block_bytes(fmt_a);
@@ -1298,7 +1245,7 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     now.y = { (const uint8_t *)y, (size_t)rows * 4 };
     now.yb = { (const uint8_t *)y_blocks, y_blocks ? (size_t)((rows + 31) / 32) * block_bytes(fmt_y) : 0 };
     const bool known = t_hist.count > 0 && t_hist.stream == stream;
-    bool conflict = !known || sums || g_tune.always_wait || g_tune.prekernel || t_hist.count == HISTORY;
+    bool conflict = !known || sums || t_hist.count == HISTORY;
     bool weights_written = false;           // the producer reads A before any wait: nothing in flight may write it
     if (known) {
         for (int i = 0; i < t_hist.count; i++) {
@@ -1323,10 +1270,11 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     }
     // the last few shapes' plans are kept: a decode loop calls the same shapes over and over
     static thread_local struct { int fmt, rows, cols, kind; GemvPlan plan; } cache[8];
-    static thread_local int cached = 0, next = 0;
+    int &cached = t_plans_cached, &next = t_plans_next;
+    if (t_plans_epoch != g_epoch) { cached = next = 0; t_plans_epoch = g_epoch; }
     GemvPlan pl;
     bool hit = false;
-    const bool overlapped = (independent || in_a_burst) && !sums && !g_tune.prekernel;
+    const bool overlapped = (independent || in_a_burst) && !sums;
     const int kind = (sums ? 2 : overlapped ? 1 : 0) | (y_blocks ? 4 : 0);
     for (int i = 0; i < cached && !hit; i++)
         if (cache[i].fmt == fmt_a && cache[i].rows == rows && cache[i].cols == cols && cache[i].kind == kind) { pl = cache[i].plan; hit = true; }
@@ -1338,8 +1286,8 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
         if (cached < 8) cached++;
     }
     pl.args.a = (const uint8_t *)a;
-    pl.args.xprep = (const uint8_t *)scratch;
-    pl.args.x = g_tune.prekernel ? nullptr : x;
+    pl.args.xprep = nullptr;
+    pl.args.x = x;
     pl.args.fmt_x = fmt_x;
     pl.args.independent = independent ? 1 : 0;
     pl.serial = serial;
@@ -1348,28 +1296,9 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     pl.args.fmt_y = fmt_y;
     pl.args.sums = sums;
     pl.args.status = g_status;
-    pl.args.timeline = g_timeline;
-    pl.args.probe = g_probe;
     pl.args.rows = rows;
     pl.args.cols = cols;
     cudaError_t e;
-    if (g_tune.prekernel) {
-        const int blocks = cols / 32, threads = 128, grid = (blocks + 1 + threads - 1) / threads;
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof cfg);
-        cfg.gridDim = dim3(grid);
-        cfg.blockDim = dim3(threads);
-        cfg.stream = stream;
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr.val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        uint8_t *out = (uint8_t *)scratch;
-        if (fmt_a == QB200_Q8_0 || fmt_a == QB200_Q4_0) e = cudaLaunchKernelEx(&cfg, prepare_x_kernel<true>, x, fmt_x, cols, out, pl.args.independent);
-        else e = cudaLaunchKernelEx(&cfg, prepare_x_kernel<false>, x, fmt_x, cols, out, pl.args.independent);
-        if (e) return (int)e;
-    }
     switch (fmt_a) {
     case QB200_Q8_0: e = launch_fmt<QB200_Q8_0>(pl, sums != nullptr, stream); break;
     case QB200_Q4_0: e = launch_fmt<QB200_Q4_0>(pl, sums != nullptr, stream); break;
@@ -1394,12 +1323,14 @@ struct NoAllocDevice {
     int *status;
 };
 static NoAllocDevice g_noalloc[64];
+static std::mutex g_noalloc_lock;           // first use on a device may come from any host thread
 
 // First use on the current device: resolves the two symbols' device addresses and gives the kernels their
 // shared-memory attribute on this device.  Allocates nothing.
 static int noalloc_setup(int device, NoAllocDevice **out)
 {
     if (device < 0 || device >= 64) return QB200_E_DEVICE;
+    std::lock_guard<std::mutex> guard(g_noalloc_lock);
     NoAllocDevice &d = g_noalloc[device];
     if (!d.scratch) {
         cudaError_t e;
@@ -1411,7 +1342,7 @@ static int noalloc_setup(int device, NoAllocDevice **out)
         void *scratch = nullptr, *status = nullptr;
         if ((e = cudaGetSymbolAddress(&scratch, g_noalloc_scratch))) return (int)e;
         if ((e = cudaGetSymbolAddress(&status, g_noalloc_status))) return (int)e;
-        if (g_sm_count == 0) { g_sm_count = sms; g_max_smem = smem; read_tuning(); }
+        if (g_sm_count == 0) { g_sm_count = sms; g_max_smem = smem; }
         if ((e = set_attr<QB200_Q8_0>(smem)) || (e = set_attr<QB200_Q4_0>(smem)) || (e = set_attr<QB200_Q4_K>(smem)) || (e = set_attr<QB200_Q6_K>(smem)))
             return (int)e;
         d.status = (int *)status;
@@ -1421,9 +1352,10 @@ static int noalloc_setup(int device, NoAllocDevice **out)
     return 0;
 }
 
-// y = A.x as gemv_launch computes it, with x prepared in the static array instead of a caller's or the library's
-// allocation.  The status word is cleared by a memset node in the stream before the kernels (it must start at zero;
-// the x scratch needs no clearing: the preparing kernel rewrites every byte the gemv reads).
+// y = A.x as gemv_launch computes it, with x prepared in the static array instead of shared memory.  Nothing in the
+// array has to start at zero: the preparing kernel rewrites every byte the gemv reads.  The status word is zero when the
+// module loads and is only ever OR-ed into by the kernels; gemv_noalloc_status reads and clears it, so a bounded wait
+// that gave up in any call since the last reading is reported, not just one in the latest call.
 int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, cudaStream_t stream)
 {
     if (cols > NOALLOC_MAX_COLS) return QB200_E_LIMIT;
@@ -1448,11 +1380,8 @@ int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, floa
     pl.args.fmt_y = 0;
     pl.args.sums = nullptr;
     pl.args.status = dev->status;
-    pl.args.timeline = nullptr;
-    pl.args.probe = 0;
     pl.args.rows = rows;
     pl.args.cols = cols;
-    if ((e = cudaMemsetAsync(dev->status, 0, sizeof(int), stream))) return (int)e;
     const int blocks = cols / 32, threads = 128, grid = (blocks + 1 + threads - 1) / threads;
     if (fmt_a == QB200_Q8_0 || fmt_a == QB200_Q4_0) prepare_x_kernel<true><<<grid, threads, 0, stream>>>(x, fmt_x, cols, (uint8_t *)dev->scratch, 0);
     else prepare_x_kernel<false><<<grid, threads, 0, stream>>>(x, fmt_x, cols, (uint8_t *)dev->scratch, 0);
@@ -1466,7 +1395,8 @@ int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, floa
     return (int)e;
 }
 
-// Reads the static status word of the current device (0 = no bounded wait gave up); synchronizes the stream's device.
+// Reads and clears the static status word of the current device (0 = no bounded wait gave up since the last reading);
+// synchronizes the device.
 int gemv_noalloc_status(int *value)
 {
     int device = -1;
@@ -1474,25 +1404,12 @@ int gemv_noalloc_status(int *value)
     if (e) return (int)e;
     if (device < 0 || device >= 64 || !g_noalloc[device].status) { *value = 0; return 0; }
     if ((e = cudaDeviceSynchronize())) return (int)e;
-    return (int)cudaMemcpy(value, g_noalloc[device].status, sizeof(int), cudaMemcpyDeviceToHost);
+    if ((e = cudaMemcpy(value, g_noalloc[device].status, sizeof(int), cudaMemcpyDeviceToHost))) return (int)e;
+    if (*value) {
+        const int zero = 0;
+        if ((e = cudaMemcpy(g_noalloc[device].status, &zero, sizeof zero, cudaMemcpyHostToDevice))) return (int)e;
+    }
+    return 0;
 }
-
-// The plan for a shape: {rc, warps, column segments, rows a warp, ring depth, grid, slot bytes, shared bytes, runs a warp}.
-static int g_describe_overlapped = 0;
-void gemv_describe_mode(int overlapped) { g_describe_overlapped = overlapped; }
-void gemv_describe(int fmt_a, int rows, int cols, int *out9)
-{
-    GemvPlan pl;
-    memset(&pl, 0, sizeof pl);
-    int rc = plan_gemv(fmt_a, rows, cols, false, g_describe_overlapped != 0, false, pl);
-    out9[0] = rc; out9[1] = pl.nw; out9[2] = pl.cs; out9[3] = pl.rw; out9[4] = pl.stages; out9[5] = pl.grid;
-    out9[6] = (int)pl.stage_stride; out9[7] = (int)pl.smem_bytes; out9[8] = pl.runs_per_warp;
-}
-
-// Tuning aid: a device buffer of 32 timestamps a block (or null to stop recording).
-void gemv_set_timeline(long long *buffer) { g_timeline = buffer; }
-void gemv_set_probe(int mode) { g_probe = mode; }
-
-void gemv_set_device_limits(int sm_count, int max_smem) { g_sm_count = sm_count; g_max_smem = max_smem; read_tuning(); }
 
 }  // namespace qb

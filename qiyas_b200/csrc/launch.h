@@ -11,23 +11,28 @@
 namespace qb {
 
 cudaError_t gemv_init(int sm_count, int max_smem, int *status);
-void gemv_set_device_limits(int sm_count, int max_smem);
-size_t gemv_scratch_bytes(int cols);
 // y_blocks (optional) = y again as fmt_y blocks (Q8_0 / Q4_0), encoded in the same launch
 int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int fmt_y, void *y_blocks, int rows,
-                int cols, void *scratch, cudaStream_t stream);
+                int cols, cudaStream_t stream);
 // forgets what earlier launches touched: the next call orders itself after everything in its stream
 void gemv_forget_history();
 int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, cudaStream_t stream);
 int gemv_noalloc_status(int *value);
-void gemv_describe(int fmt_a, int rows, int cols, int *out9);
 
 int encode_launch(int fmt, const float *lanes, void *blocks, int64_t n, cudaStream_t stream);
 int decode_launch(int fmt, const void *blocks, float *lanes, int64_t n, cudaStream_t stream);
 
 cudaError_t matmul_init(int sm_count, int max_smem, int *status);
-size_t matmul_workspace_bytes(int fmt_a, int fmt_b, int m, int n, int k);
-int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int32_t *sums, int m, int n, int k, void *workspace,
-                  cudaStream_t stream);
+// `count` products in one call: operands stride_a / stride_b values apart (0: the same operand for every product;
+// else whole blocks), results stride_c values apart.  One product: {1, 0, 0, 0}.
+struct MatmulBatch { int count; long long stride_a, stride_b, stride_c; };
+// scratch of one call: packed A of every product, then packed B of every distinct one (none when B comes prepacked)
+size_t matmul_workspace_bytes(int fmt_b, int m, int n, int k, const MatmulBatch &batch, bool b_prepacked);
+// B as matmul_prepack_b lays it (the layout does not depend on m)
+size_t matmul_prepacked_bytes(int fmt_b, int n, int k);
+int matmul_prepack_b(int fmt_b, const void *b, int n, int k, void *packed, cudaStream_t stream);
+// b_packed: null, or B as matmul_prepack_b left it (then `b` is not read); c_blocks: null, or C again as blocks of fmt_c
+int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void *b_packed, float *c, int32_t *sums, int fmt_c,
+                  void *c_blocks, int m, int n, int k, const MatmulBatch &batch, void *workspace, cudaStream_t stream);
 
 }  // namespace qb

@@ -1,84 +1,187 @@
-// Block-scaled A.B^T for sm_100a: C (m x n, f32) = A (m x k) . B (n x k)^T with A and B in Q8_0 / Q4_0 rows.
+// Block-scaled A.B^T for sm_100a: C (m x n, f32) = A (m x k) . B (n x k)^T with A in Q8_0 / Q4_0 rows and B in
+// Q8_0 / Q4_0 / Q4_K / Q6_K rows.
 //
 // Replaces Ptx.MatMulBlocks (reference src/MatMulBlocks.cs:178-386: 64 x 64 tiles, mma.sync m16n8k32, operands staged
-// by 16-bit loads).  The arithmetic is that kernel's: per k-block of 32 the exact s32 product sum D, then
+// by 16-bit loads).  The arithmetic is that kernel's: per k-block of 32 the exact product sum D, then
 //     acc = fma(float(D), sA*sB, acc)        (src/MatMulBlocks.cs:339-347), k-blocks in ascending order,
 // so the f32 result equals the reference's device result bit for bit.
 //
 // Two steps:
-//  1. pack_rows_kernel re-lays each operand in scratch memory for the tensor cores: the scales are stripped out of the
-//     34- / 18-byte blocks into an f32 plane, Q4_0 nibbles are widened to int8 (q - 8), and the int8 codes are stored
-//     tile by tile in the canonical K-major, unswizzled shared-memory layout of tcgen05 (8-row x 16-byte core matrices),
-//     so that a whole (128 rows x several k-blocks) slab is one contiguous run of bytes.
-//  2. matmul_kernel: one 128 x 128 tile of C a block.  A producer warp brings slabs of codes and scales into a ring of
-//     shared-memory stages with untiled TMA bulk copies; one thread issues a tcgen05.mma (kind::i8, M 128, N 128, K 32)
-//     per k-block into one of four 128-column accumulators in tensor memory, with accumulation off, and commits it to
-//     an mbarrier; sixteen epilogue warps read the s32 sums back with tcgen05.ld, scale them in f32 (packed f32x2
-//     instructions) and add them to register accumulators while the next k-blocks' products run.
+//  1. pack kernels re-lay an operand for the tensor cores: the scales are stripped out of the raw blocks into an f32
+//     plane, nibbles are widened, and the codes are stored as 8-row x 16-byte core matrices (the canonical K-major,
+//     unswizzled shared-memory layout of tcgen05), so that the rows a tile needs for one k-block are one contiguous run
+//     of bytes.  A (activations) is packed on every call, tile-major; B (weights) is packed k-block-major and can be
+//     packed once and kept by the caller (matmul_prepack_b): the layout does not depend on m.
+//  2. matmul_kernel: a persistent grid, one block a multiprocessor.  The output is cut into units of 16 (or 32)
+//     columns of one 128-row tile of A; block b takes a contiguous, equal share of the units and walks it in pieces of
+//     up to BNMAX columns.  A producer warp brings codes and scales into a ring of shared-memory stages with untiled
+//     TMA bulk copies; one thread issues the tcgen05.mma of every k-block (M 128, N = the piece's width, accumulation
+//     off) into one of NT accumulators in tensor memory and commits it to an mbarrier; sixteen epilogue warps read the
+//     sums back with tcgen05.ld, eight columns a chunk, scale them in f32 (packed f32x2 instructions) and add them to
+//     register accumulators while the products of the next k-blocks run.
+//
+// Where both operands carry plain f16 block scales (Q8_0 / Q4_0 against Q8_0 / Q4_0) the scale products sA*sB are taken
+// by the tensor cores as well (TCS): a second instruction a k-block, kind::f16 with K = 16, multiplies the 128 x 1 column
+// of A's scales by the 1 x N row of B's (each stored as a row [d, 0, ..., 0] of eight f16; the other eight of K come
+// from a patch of zeros) into a second accumulator.  A product of two f16 values has at most 22 significant bits, so
+// the f32 it leaves in tensor memory is exactly mul.rn.f32(sA, sB), and the epilogue is two tensor-memory reads and one
+// packed fma an element pair: no shared-memory reads, no scale product on the CUDA cores.  Q4_K / Q6_K scales are
+// products d*sc rounded to f32 (17 or more significant bits): they stay on the CUDA-core path.
+//
+// KIND selects the tensor instruction: 0 = kind::i8 (codes as int8, s32 sums, converted to f32 in the epilogue),
+// 1 = kind::f16 (codes as f16: every product and every sum of 32 products is an integer below 2^24, so the f32 sums
+// are exact and need no conversion; twice the operand bytes).
 #include "common.cuh"
+#include "encode_blocks.cuh"
 #include "launch.h"
 
 namespace qb {
 
-#ifndef QB_MM_WAIT
-#define QB_MM_WAIT mbar_wait_lanes
-#endif
+constexpr int TILE = 128;            // rows of A a tile = lanes of tensor memory
+constexpr int BNMAX = 128;           // columns of the widest piece = columns of one accumulator in tensor memory
+constexpr int EPI_WARPS = 16;
+constexpr int MM_THREADS = 32 * (2 + EPI_WARPS);     // warp 0 producer, warp 1 MMA, the rest epilogue
+constexpr uint32_t MM_HEADER = 1024;
+constexpr uint32_t MM_SMEM_MAX = 232448;           // 227 KB of shared memory a block
 
-// The probes inside the kernel are tuning aids: compiled in only with -DQB_MM_TUNING.
+// Probes for tuning runs, compiled in only with -DQB_MM_TUNING: bit 0 no epilogue arithmetic, bit 1 no tensor-memory
+// reads, bit 2 no accumulator handshake, bits 4-5 the form of the barrier wait.
 #ifdef QB_MM_TUNING
 #define MM_PROBE(p) ((p).probe)
+#define MM_TRACE(p, slot, value) do { if ((p).trace && blockIdx.x == 0) (p).trace[slot] = (value); } while (0)
+#define MM_CLOCK() clock64()
 #else
 #define MM_PROBE(p) 0
+#define MM_TRACE(p, slot, value) do { } while (0)
+#define MM_CLOCK() 0ll
 #endif
 
-constexpr int TILE = 128;            // rows of A and of B per block tile
-constexpr int KS = 4;                // k-blocks per shared-memory stage (even: pairs of k-blocks never straddle stages)
-constexpr int MM_STAGES = 5;
-constexpr int TMEM_STAGES = 4;       // 4 x 128 columns = all 512 columns of tensor memory
-constexpr int SLAB = TILE * 32;      // bytes of codes per tile and k-block
-constexpr int EPI_WARPS = 16;
-constexpr int MM_THREADS = 32 * (2 + EPI_WARPS);   // warp 0 producer, warp 1 MMA, the rest epilogue
-constexpr uint32_t STAGE_BYTES = KS * (2 * SLAB + 4 * TILE * 4);   // codes of A and B, scales of A and B, A's scaled sums, B's mins
-constexpr uint32_t MM_HEADER = 1024;
-constexpr uint32_t MM_ZEROS = MM_HEADER + MM_STAGES * STAGE_BYTES;    // 2 KB of zeros: the absent second half of a 16-value k-block
-constexpr uint32_t MM_SMEM = MM_ZEROS + SLAB / 2;
+// Sizes that follow from the tensor kind, the operand B's format (MINS: Q4_K, HALF: Q6_K with k-blocks of 16 values) and
+// where the scale products are taken (TCS: on the tensor cores).
+template <int KIND, bool MINS, bool HALF, bool TCS>
+struct Cfg {
+    static_assert(!TCS || (!MINS && !HALF), "only plain f16 block scales multiply exactly on the tensor cores");
+    static constexpr int ESZ = KIND ? 2 : 1;             // bytes a code
+    static constexpr int KV = HALF ? 16 : 32;            // values a k-block
+    static constexpr int KC = KV * ESZ / 16;             // 16-byte k-chunks a row and k-block
+    static constexpr int KS = (KIND ? 64 : 128) / KV;    // k-blocks a shared-memory stage
+    static constexpr int SW = TCS ? 16 : 4;              // bytes a scale: an f32, or a row [d, 0 x 7] of f16 for the tensor cores
+    static constexpr int TCOLS = TCS ? 2 * BNMAX : BNMAX;   // tensor-memory columns a k-block: the sums, and the scale products
+    static constexpr int NT = 512 / TCOLS;               // k-blocks in flight in tensor memory
+    static constexpr uint32_t A_KB = TILE * KC * 16, B_KB = BNMAX * KC * 16;      // bytes of codes a k-block
+    static constexpr uint32_t A_CODES = KS * A_KB, B_CODES = KS * B_KB, A_SC = KS * TILE * SW, B_SC = KS * BNMAX * SW;
+    static constexpr uint32_t O_B = A_CODES, O_SA = O_B + B_CODES, O_SB = O_SA + A_SC, O_UA = O_SB + B_SC, O_MB = O_UA + A_SC;
+    static constexpr uint32_t STAGE = A_CODES + B_CODES + (MINS ? 2 : 1) * (A_SC + B_SC);
+    static constexpr uint32_t PATCH = ((KIND == 0 && HALF) || TCS) ? 2048 : 0;    // zeros: the half of K an instruction reads but the operand does not have
+    static constexpr int S_FIT = (int)((MM_SMEM_MAX - MM_HEADER - PATCH) / STAGE);
+    static constexpr int S = S_FIT > 6 ? 6 : S_FIT;
+    static constexpr uint32_t O_PATCH = MM_HEADER + S * STAGE;
+    static constexpr uint32_t SMEM = O_PATCH + PATCH;
+    static_assert(S >= 2, "the ring needs two stages");
+    static_assert(2 * S + 2 * NT + 2 <= 64, "barriers fit the header");
+};
 
-struct PackedOperand {
-    const uint8_t *codes;    // [tile][kb][2][16][8][16]
-    const float *scales;     // [tile][kb][128]
-    const float *extra;      // [tile][kb][128]: A: scale * sum of the block's codes; B (Q4_K): dmin * m.  Null when unused.
+struct PackedA {             // tile-major: [tile][k-block][16 row groups][KC][8 rows][16 bytes], scales [tile][k-block][128]
+    const uint8_t *codes;
+    const float *scales;     // f32 each, or 16-byte rows for the tensor cores (TCS)
+    const float *extra;      // scale * sum of the block's codes (the factor of B's min); null unless B is Q4_K
+};
+struct PackedB {             // k-block-major: [k-block][rows_pad / 8 row groups][KC][8 rows][16 bytes], scales [k-block][rows_pad]
+    const uint8_t *codes;
+    const float *scales;
+    const float *extra;      // Q4_K: dmin * m
+    int rows_pad;
 };
 
 struct MatmulArgs {
-    PackedOperand a, b;
+    PackedA a;
+    PackedB b;
     float *c;
     int32_t *sums;
+    uint8_t *cb;             // optional: C again as blocks of fmt_c (the reference's `Back`), encoded by the block that wrote the lanes
+    int fmt_c;
     int *status;
-    int m, n, kb;
-    int probe;       // tuning aid: 1 = no arithmetic, 2 = no tensor-memory reads; 0 in normal use
+    int m, n, kb;            // kb = k-blocks of the product
+    int unit;                // columns a unit: 16, or 32 when cb is set (a block of C lies inside one piece)
+    int units;               // ceil(n / unit)
+    int mtiles;
+    int probe;               // tuning build only (see MM_PROBE)
+    long long *trace;        // tuning build only: clock stamps of block 0
+    int batch;               // products: operand sets a_stride / b_stride bytes apart in their packed form (0: the same for all), results c_stride values apart
+    size_t a_stride, b_stride, c_stride;
 };
 
 // ---------------------------------------------------------------------------------- step 1: operands for the tensor cores
 
-// A block of 256 threads re-lays 32 rows x 8 k-blocks.  The rows' bytes (8 consecutive blocks of a row are contiguous
-// in the raw operand, 2-byte aligned) are first copied to shared memory with coalesced loads (16 bytes wide when the
-// rows lie on 16-byte boundaries, else 2); then a thread a
-// block assembles its 32 int8 values and its scale.  Row r of tile t lands at byte
-// (t*kb + b)*4096 + j*2048 + (r/8)*128 + (r%8)*16 for its bytes 16j..16j+15, and its scale at ((t*kb + b)*128 + r).
-// Rows past `rows` (the padding of the last tile) are written as zeros.
-// SPLIT (against Q6_K rows, whose scales change every 16 values): a block becomes two k-blocks of 16 values each, 2 KB
-// of codes a tile (the other 16 values of the tensor instruction's 32 are zeros that are never stored), same scale.
+struct PackTarget {
+    uint8_t *codes;
+    float *scales;
+    float *extra;
+    int tcs;                 // scales as 16-byte rows [f16 d, 0 x 7] (operands of the tensor cores' scale product) instead of f32
+    int rows_pad;
+    int kbs;                 // k-blocks a row in the packed operand
+    int kc;                  // k-chunks a k-block
+    int tile_major;
+    int kind;
+};
+
+// Byte offset of k-chunk `kci` (counted along the whole row) of row r.
+__device__ __forceinline__ size_t chunk_offset(const PackTarget &t, int r, int kci)
+{
+    const int kblock = kci / t.kc, kc = kci - kblock * t.kc;
+    size_t group;
+    if (t.tile_major) group = ((size_t)(r / TILE) * t.kbs + kblock) * (TILE / 8) + (r % TILE) / 8;
+    else group = (size_t)kblock * (t.rows_pad / 8) + r / 8;
+    return (group * t.kc + kc) * 128 + (size_t)(r & 7) * 16;
+}
+__device__ __forceinline__ size_t scale_offset(const PackTarget &t, int r, int kblock)
+{
+    if (t.tile_major) return ((size_t)(r / TILE) * t.kbs + kblock) * TILE + r % TILE;
+    return (size_t)kblock * t.rows_pad + r;
+}
+// The scale of (row, k-block): an f32, or (tcs) the f16 bits it came from as the first of eight halves, the rest zero.
+__device__ __forceinline__ void store_scale(const PackTarget &t, int r, int kblock, float d, uint32_t d_bits)
+{
+    if (t.tcs) ((uint4 *)t.scales)[scale_offset(t, r, kblock)] = make_uint4(d_bits & 0xFFFFu, 0, 0, 0);
+    else t.scales[scale_offset(t, r, kblock)] = d;
+}
+
+// 16 int8 values (four words) as one k-chunk (int8) or two (f16), starting at k-chunk kci0 of row r.
+__device__ __forceinline__ void store_codes16(const PackTarget &t, int r, int kci0, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3)
+{
+    if (t.kind == 0) {
+        *(uint4 *)(t.codes + chunk_offset(t, r, kci0)) = make_uint4(w0, w1, w2, w3);
+        return;
+    }
+    const uint32_t w[4] = { w0, w1, w2, w3 };
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t word = w[2 * h + (i >> 1)] >> (16 * (i & 1));
+            const __half2 v = __halves2half2(__int2half_rn((int)(int8_t)(word & 255)), __int2half_rn((int)(int8_t)((word >> 8) & 255)));
+            o[i] = *(const uint32_t *)&v;
+        }
+        *(uint4 *)(t.codes + chunk_offset(t, r, kci0 + h)) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// Q8_0 / Q4_0 rows.  A block of 256 threads re-lays 32 rows x 8 blocks: the rows' bytes (8 consecutive blocks of a row
+// are contiguous in the raw operand, 2-byte aligned) go to shared memory with coalesced loads (16 bytes wide when the
+// rows lie on 16-byte boundaries, else 2); then a thread a block assembles its 32 int8 values and its scale.
+// Rows past `rows` (the padding up to rows_pad) are written as zeros.
+// SPLIT (against Q6_K rows, whose scales change every 16 values): a block becomes two k-blocks of 16 values, same scale.
 template <int FMT, bool SPLIT>
-__global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int rows, int kb, uint8_t *codes, float *scales, float *usums)
+__global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int rows, int kb32, PackTarget t, int want_usums)
 {
     // halfwords a row segment; the pitch is an odd number of 32-bit words, so the 32 rows start in 32 different banks
     constexpr int BB = block_bytes(FMT), HALVES = 8 * BB / 2, PITCH = HALVES + 2, VECS = 8 * BB / 16;
     __shared__ __align__(16) uint16_t seg[32 * PITCH];
     const int r0 = blockIdx.x * 32, b0 = blockIdx.y * 8;
-    const int nb = min(8, kb - b0), halves = nb * BB / 2;
-    const size_t row_bytes = (size_t)kb * BB;
+    const int nb = min(8, kb32 - b0), halves = nb * BB / 2;
+    const size_t row_bytes = (size_t)kb32 * BB;
     if (nb == 8 && (((uintptr_t)raw | row_bytes) & 15) == 0) {
-        // whole segments on 16-byte boundaries (8 blocks are 272 or 144 bytes): 16-byte loads
         for (int idx = threadIdx.x; idx < 32 * VECS; idx += 256) {
             const int rr = idx / VECS, c = idx - rr * VECS;
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -90,13 +193,13 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int 
         for (int idx = threadIdx.x; idx < 32 * HALVES; idx += 256) {
             const int rr = idx / HALVES, h = idx - rr * HALVES;
             uint16_t v = 0;
-            if (r0 + rr < rows && h < halves) v = __ldg((const uint16_t *)(raw + ((size_t)(r0 + rr) * kb + b0) * BB) + h);
+            if (r0 + rr < rows && h < halves) v = __ldg((const uint16_t *)(raw + ((size_t)(r0 + rr) * kb32 + b0) * BB) + h);
             seg[rr * PITCH + h] = v;
         }
     }
     __syncthreads();
     const int rl = threadIdx.x & 31, bl = threadIdx.x >> 5, r = r0 + rl, b = b0 + bl;
-    if (b >= kb) return;
+    if (b >= kb32) return;
     const uint16_t *p = seg + rl * PITCH + bl * (BB / 2);
     const float d = half_bits_to_float(p[0]);           // zero rows read as scale 0, codes 0 (Q4_0: see below)
     uint32_t w[8];
@@ -116,34 +219,33 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int 
             for (int i = 0; i < 8; i++) w[i] = 0;
         }
     }
-    const int t = r / TILE, rr = r % TILE;
-    uint8_t *slab = codes + ((size_t)t * kb + b) * SLAB + (rr >> 3) * 128 + (rr & 7) * 16;
-    *(uint4 *)slab = make_uint4(w[0], w[1], w[2], w[3]);
-    *(uint4 *)(slab + SLAB / 2) = make_uint4(w[4], w[5], w[6], w[7]);       // SPLIT: this is the next k-block's slab
+    const int per16 = t.kind ? 2 : 1;                   // k-chunks 16 values take
+    store_codes16(t, r, 2 * b * per16, w[0], w[1], w[2], w[3]);
+    store_codes16(t, r, (2 * b + 1) * per16, w[4], w[5], w[6], w[7]);
     if (SPLIT) {
-        scales[((size_t)t * kb + b) * 2 * TILE + rr] = d;
-        scales[((size_t)t * kb + b) * 2 * TILE + TILE + rr] = d;
+        t.scales[scale_offset(t, r, 2 * b)] = d;
+        t.scales[scale_offset(t, r, 2 * b + 1)] = d;
         return;
     }
-    scales[((size_t)t * kb + b) * TILE + rr] = d;
-    if (usums) {            // against a format with mins: scale * (sum of the codes), the factor of the other operand's min
+    store_scale(t, r, b, d, p[0]);
+    if (want_usums) {       // against a format with mins: scale * (sum of the codes), the factor of the other operand's min
         int sum = 0;
 #pragma unroll
         for (int i = 0; i < 8; i++) asm("dp4a.s32.s32 %0, %1, %2, %0;" : "+r"(sum) : "r"(w[i]), "r"(0x01010101));
-        usums[((size_t)t * kb + b) * TILE + rr] = __fmul_rn(d, (float)sum);
+        t.extra[scale_offset(t, r, b)] = __fmul_rn(d, (float)sum);
     }
 }
 
 // Q4_K rows as an operand: a block of 256 threads re-lays 32 rows x one super-block (144 bytes, src/Blocks.cs:79-96) into
-// eight k-blocks.  Sub-block j (32 values): codes q = the low (j even) or high nibbles of qs[32 (j/2) ..], kept as int8
+// eight k-blocks.  Sub-block j (32 values): codes q = the low (j even) or high nibbles of qs[32 (j/2) ..], kept as
 // 0..15; scale d * sc and min dmin * m, each rounded to f32 as DecodeQ4_K rounds them, with sc and m unpacked as ScaleMin
 // does (src/Blocks.cs:73-77).  value = (d*sc)*q - dmin*m, so a k-block contributes sA*(d*sc)*sum(qA*q) - (dmin*m)*sA*sum(qA).
-__global__ void __launch_bounds__(256) pack_q4_k_kernel(const uint8_t *raw, int rows, int kb, uint8_t *codes, float *scales, float *mins)
+__global__ void __launch_bounds__(256) pack_q4_k_kernel(const uint8_t *raw, int rows, int kb32, PackTarget t)
 {
     constexpr int PITCH = 37;                           // words a row of 144 bytes (36 words): odd, so rows start in different banks
     __shared__ uint32_t seg[32 * PITCH];
     const int r0 = blockIdx.x * 32, sb = blockIdx.y;
-    const size_t row_bytes = (size_t)(kb / 8) * 144;
+    const size_t row_bytes = (size_t)(kb32 / 8) * 144;
     if ((((uintptr_t)raw | row_bytes) & 15) == 0) {
         for (int idx = threadIdx.x; idx < 32 * 9; idx += 256) {
             const int rr = idx / 9, c = idx - rr * 9;
@@ -174,19 +276,18 @@ __global__ void __launch_bounds__(256) pack_q4_k_kernel(const uint8_t *raw, int 
         const uint32_t n = row[4 + (j >> 1) * 8 + i];
         w[i] = (j & 1) ? (n >> 4) & 0x0F0F0F0Fu : n & 0x0F0F0F0Fu;
     }
-    const int t = r / TILE, rr = r % TILE;
-    uint8_t *slab = codes + ((size_t)t * kb + b) * SLAB + (rr >> 3) * 128 + (rr & 7) * 16;
-    *(uint4 *)slab = make_uint4(w[0], w[1], w[2], w[3]);
-    *(uint4 *)(slab + SLAB / 2) = make_uint4(w[4], w[5], w[6], w[7]);
-    scales[((size_t)t * kb + b) * TILE + rr] = __fmul_rn(d, (float)sc);       // rows past the end read as zeros throughout
-    mins[((size_t)t * kb + b) * TILE + rr] = __fmul_rn(dmin, (float)m);
+    const int per16 = t.kind ? 2 : 1;
+    store_codes16(t, r, 2 * b * per16, w[0], w[1], w[2], w[3]);
+    store_codes16(t, r, (2 * b + 1) * per16, w[4], w[5], w[6], w[7]);
+    t.scales[scale_offset(t, r, b)] = __fmul_rn(d, (float)sc);       // rows past the end read as zeros throughout
+    t.extra[scale_offset(t, r, b)] = __fmul_rn(dmin, (float)m);
 }
 
 // Q6_K rows as an operand: a block of 256 threads re-lays 32 rows x one super-block (210 bytes, src/Blocks.cs:157-171)
-// into sixteen k-blocks of 16 values (2 KB of codes a tile each).  Sub-block s = 8 half + 2 g + (l / 16) holds the values
+// into sixteen k-blocks of 16 values.  Sub-block s = 8 half + 2 g + (l / 16) holds the values
 // 128 half + 32 g + l: code = nibble of ql[64 half + 32 (g & 1) + l] (high nibble for g >= 2) | two bits of
 // qh[32 half + l] at 2 g, minus 32; scale d * sc[s] rounded to f32, as DecodeQ6_K's d * sc * q evaluates left to right.
-__global__ void __launch_bounds__(256) pack_q6_k_kernel(const uint8_t *raw, int rows, int kb16, uint8_t *codes, float *scales)
+__global__ void __launch_bounds__(256) pack_q6_k_kernel(const uint8_t *raw, int rows, int kb16, PackTarget t)
 {
     constexpr int PITCH = 107;                          // halfwords a row of 210 bytes (105): an odd number of words + 1
     __shared__ __align__(4) uint16_t seg[32 * PITCH];
@@ -202,7 +303,7 @@ __global__ void __launch_bounds__(256) pack_q6_k_kernel(const uint8_t *raw, int 
     const int rl = threadIdx.x & 31, pairw = threadIdx.x >> 5, r = r0 + rl;
     const uint8_t *row = (const uint8_t *)(seg + rl * PITCH);
     const float d = half_bits_to_float(seg[rl * PITCH + 104]);
-    const int t = r / TILE, rr = r % TILE;
+    const int per16 = t.kind ? 2 : 1;
 #pragma unroll
     for (int e = 0; e < 2; e++) {
         const int s = pairw * 2 + e, half = s >> 3, g = (s >> 1) & 3, l0 = (s & 1) * 16;
@@ -220,9 +321,9 @@ __global__ void __launch_bounds__(256) pack_q6_k_kernel(const uint8_t *raw, int 
             }
             w[i] = word;
         }
-        const size_t kbi = (size_t)t * kb16 + (size_t)sb * 16 + s;
-        *(uint4 *)(codes + kbi * (SLAB / 2) + (rr >> 3) * 128 + (rr & 7) * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-        scales[kbi * TILE + rr] = __fmul_rn(d, (float)(int8_t)row[192 + s]);
+        const int kblock = sb * 16 + s;
+        store_codes16(t, r, kblock * per16, w[0], w[1], w[2], w[3]);
+        t.scales[scale_offset(t, r, kblock)] = __fmul_rn(d, (float)(int8_t)row[192 + s]);
     }
 }
 
@@ -241,26 +342,36 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // Shared-memory matrix descriptor: K-major, no swizzle.  Core matrices are 8 rows x 16 bytes, stored contiguously
-// (128 bytes); LBO = bytes between the two 16-byte k-chunks of a row, SBO = bytes between 8-row groups.
+// (128 bytes); LBO = bytes between the 16-byte k-chunks of a row, SBO = bytes between 8-row groups.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo)
 {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (uint64_t)(lbo >> 4) << 16 | (uint64_t)(sbo >> 4) << 32 | (uint64_t)1 << 46;
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (uint64_t)((lbo >> 4) & 0x3FFFu) << 16 | (uint64_t)((sbo >> 4) & 0x3FFFu) << 32 | (uint64_t)1 << 46;
 }
 
-// Instruction descriptor of kind::i8: D s32, A and B signed 8-bit, both K-major, dense, M x N.
-__host__ __device__ constexpr uint32_t idesc_s8(int m, int n)
+// Instruction descriptors, both operands K-major, dense, M x N.  kind::i8: D s32, A and B signed 8-bit;
+// kind::f16: D f32, A and B f16.
+__host__ __device__ constexpr uint32_t idesc_of(int kind, int m, int n)
 {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+    return (kind == 0 ? (2u << 4) | (1u << 7) | (1u << 10) : (1u << 4)) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// D[tmem] = A.B^T for one k-block (K = 32 bytes of int8), accumulation off: each k-block needs its own scale.
-__device__ __forceinline__ void mma_s8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc)
+// D[tmem] (+)= A.B^T over 32 bytes of K (32 int8 or 16 f16 values a row).
+template <int KIND>
+__device__ __forceinline__ void mma_issue(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0u)
-        : "memory");
+    if (KIND == 0) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
 }
 
 // The mbarrier gets one arrival when every tcgen05.mma this thread issued so far has completed.
@@ -269,8 +380,23 @@ __device__ __forceinline__ void mma_commit(uint32_t bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// 32 lanes x 32 columns of 32-bit accumulators: thread l of the warp gets row (lane base + l), columns c .. c+31.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, int32_t (&v)[32])
+// 32 lanes x 8 columns of 32-bit accumulators: thread l of the warp gets row (lane base + l), columns c .. c+7.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                   "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
 {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -284,8 +410,84 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int32_t (&v)[32])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The reads issued so far have landed, and nothing that uses v is scheduled above this point (the registers pass through
+// the statement, so their uses depend on it).
+__device__ __forceinline__ void tmem_ld_landed16(uint32_t (&v)[16])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
+                   "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld_landed16x2(uint32_t (&v)[16], uint32_t (&x)[16])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
+                   "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+                   "+r"(x[0]), "+r"(x[1]), "+r"(x[2]), "+r"(x[3]), "+r"(x[4]), "+r"(x[5]), "+r"(x[6]), "+r"(x[7]), "+r"(x[8]), "+r"(x[9]),
+                   "+r"(x[10]), "+r"(x[11]), "+r"(x[12]), "+r"(x[13]), "+r"(x[14]), "+r"(x[15])
+                 :
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld_landed32(uint32_t (&v)[32])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
+                   "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]),
+                   "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]),
+                   "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+                 :
+                 : "memory");
+}
 
 // ---------------------------------------------------------------------------------- step 2: the product
+
+// Barrier waits of this kernel.  WAIT_MODE 0: mbarrier.try_wait with a long suspend hint; 1: try_wait with the default
+// time limit; 2: test_wait in a plain spin.  All give up like mbar_wait (bounded, abort word, status bit).
+#ifndef MM_WAIT_MODE
+#define MM_WAIT_MODE 1
+#endif
+__device__ __forceinline__ bool mm_poll(uint32_t bar, uint32_t parity, int mode)
+{
+    uint32_t done;
+    if (mode == 0) return mbar_try_wait(bar, parity);
+    if (mode == 1)
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ bool mm_wait(uint32_t bar, uint32_t parity, volatile int *abort, int *status, int mode)
+{
+    if (mm_poll(bar, parity, mode & 3)) return true;
+    const long long start = clock64();
+    for (int spins = 0;; spins++) {
+        if (mm_poll(bar, parity, mode & 3)) return true;
+        if (mode & 16) __nanosleep(40);
+        if ((spins & 63) != 63) continue;       // the give-up conditions are looked at every 64th poll
+        if (*abort) return false;
+        if (clock64() - start > WAIT_CYCLES) {
+            *abort = 1;
+            atomicOr(status, STATUS_MATMUL_WAIT);
+            return false;
+        }
+    }
+}
+// Every lane polls; all lanes see the same barrier, so they leave together except in the give-up case, where the
+// abort word makes the stragglers follow within a few polls.
+__device__ __forceinline__ bool mm_wait_lanes(uint32_t bar, uint32_t parity, volatile int *abort, int *status, int mode)
+{
+    if (mode & 8) {             // lane 0 polls, the others get its answer
+        int ok = 1;
+        if ((threadIdx.x & 31) == 0) ok = mm_wait(bar, parity, abort, status, mode) ? 1 : 0;
+        return __shfl_sync(0xffffffffu, ok, 0) != 0;
+    }
+    const bool ok = mm_wait(bar, parity, abort, status, mode);
+    return __all_sync(0xffffffffu, ok);
+}
 
 // Packed f32 pairs (sm_100): one instruction rounds two independent products / fused multiply-adds, each exactly as
 // mul.rn.f32 / fma.rn.f32 would.
@@ -293,6 +495,12 @@ __device__ __forceinline__ uint64_t pack2(float lo, float hi)
 {
     uint64_t r;
     asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
     return r;
 }
 __device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
@@ -309,91 +517,96 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
     return r;
 }
 
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+// Two block sums as a pair of floats: converted (kind::i8) or as they are (kind::f16 leaves exact f32 sums).
+template <int KIND>
+__device__ __forceinline__ uint64_t sums2(uint32_t d0, uint32_t d1)
 {
-    uint64_t r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
+    if (KIND == 0) return pack2((float)(int32_t)d0, (float)(int32_t)d1);
+    return pack2u(d0, d1);
+}
+template <int KIND>
+__device__ __forceinline__ float sum_as_float(uint32_t d) { return KIND == 0 ? (float)(int32_t)d : __uint_as_float(d); }
+template <int KIND>
+__device__ __forceinline__ int32_t sum_as_int(uint32_t d) { return KIND == 0 ? (int32_t)d : __float2int_rn(__uint_as_float(d)); }
+
+// Eight columns of one k-block into the accumulators: acc = fma(float(D), sA*sB, acc) (src/MatMulBlocks.cs:344-346).
+template <int KIND>
+__device__ __forceinline__ void scale_add8(const uint32_t (&v)[8], uint64_t sa2, const float *sb, uint64_t (&acc)[4])
+{
+    const ulonglong2 s0 = *(const ulonglong2 *)sb, s1 = *(const ulonglong2 *)(sb + 4);
+    acc[0] = fma2(sums2<KIND>(v[0], v[1]), mul2(sa2, s0.x), acc[0]);
+    acc[1] = fma2(sums2<KIND>(v[2], v[3]), mul2(sa2, s0.y), acc[1]);
+    acc[2] = fma2(sums2<KIND>(v[4], v[5]), mul2(sa2, s1.x), acc[2]);
+    acc[3] = fma2(sums2<KIND>(v[6], v[7]), mul2(sa2, s1.y), acc[3]);
 }
 
-// Two s32 block sums as two floats, exactly, without the conversion unit: |D| <= 32*127*127 < 2^22, so the integer
-// D + 0x4B400000 is the bit pattern of the float 12582912 + D (1.5 * 2^23 has a unit in the last place of 1 and D stays
-// inside its binade), and subtracting 12582912 leaves float(D) with no rounding anywhere.
-__device__ __forceinline__ uint64_t to_float2(int32_t d0, int32_t d1)
+// The min term of one k-block for eight columns: acc = fma(dmin*m, -(sA*sum(qA)), acc); `nu2` is -(sA*sum(qA)) twice.
+__device__ __forceinline__ void min_add8(uint64_t nu2, const float *wb, uint64_t (&acc)[4])
 {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(d0 + 0x4B400000), "r"(d1 + 0x4B400000));
-    return add2(r, pack2(-12582912.f, -12582912.f));
+    const ulonglong2 w0 = *(const ulonglong2 *)wb, w1 = *(const ulonglong2 *)(wb + 4);
+    acc[0] = fma2(w0.x, nu2, acc[0]);
+    acc[1] = fma2(w0.y, nu2, acc[1]);
+    acc[2] = fma2(w1.x, nu2, acc[2]);
+    acc[3] = fma2(w1.y, nu2, acc[3]);
 }
 
-// 32 columns of one k-block into the accumulators: acc = fma(float(D), sA*sB, acc) (src/MatMulBlocks.cs:344-346).
-__device__ __forceinline__ void scale_add(const int32_t (&v)[32], float sa, const float *sb, uint64_t (&acc)[16])
-{
-#ifdef QB_MM_SCALAR
-#pragma unroll
-    for (int c4 = 0; c4 < 8; c4++) {
-        const float4 s = *(const float4 *)(sb + 4 * c4);
-        float a0, a1, a2, a3;
-        unpack2(acc[2 * c4], a0, a1);
-        unpack2(acc[2 * c4 + 1], a2, a3);
-        a0 = __fmaf_rn((float)v[4 * c4], __fmul_rn(sa, s.x), a0);
-        a1 = __fmaf_rn((float)v[4 * c4 + 1], __fmul_rn(sa, s.y), a1);
-        a2 = __fmaf_rn((float)v[4 * c4 + 2], __fmul_rn(sa, s.z), a2);
-        a3 = __fmaf_rn((float)v[4 * c4 + 3], __fmul_rn(sa, s.w), a3);
-        acc[2 * c4] = pack2(a0, a1);
-        acc[2 * c4 + 1] = pack2(a2, a3);
+// The share of block `b` of `grid`: units [lo, hi) of the batch * mtiles * units of the call, cut into pieces that stay
+// inside one tile of A (`tile` counts the tiles of all the batch's products) and are at most `wmax` units wide (as even
+// as the count allows).  Every role of the block walks the same pieces in the same order.
+struct Pieces {
+    long long at, hi;
+    int units, wmax;
+    __device__ Pieces(const MatmulArgs &p, int wmax_) : units(p.units), wmax(wmax_)
+    {
+        const long long total = (long long)p.batch * p.mtiles * p.units;
+        at = total * blockIdx.x / gridDim.x;
+        hi = total * (blockIdx.x + 1) / gridDim.x;
     }
-    return;
-#endif
-    const uint64_t sa2 = pack2(sa, sa);
-#pragma unroll
-    for (int c4 = 0; c4 < 8; c4++) {
-        const ulonglong2 s = *(const ulonglong2 *)(sb + 4 * c4);
-        acc[2 * c4] = fma2(pack2((float)v[4 * c4], (float)v[4 * c4 + 1]), mul2(sa2, s.x), acc[2 * c4]);
-        acc[2 * c4 + 1] = fma2(pack2((float)v[4 * c4 + 2], (float)v[4 * c4 + 3]), mul2(sa2, s.y), acc[2 * c4 + 1]);
+    __device__ bool next(int &tile, int &u0, int &w)
+    {
+        if (at >= hi) return false;
+        tile = (int)(at / units);
+        const long long end = min(hi, (long long)(tile + 1) * units);
+        const int len = (int)(end - at), np = (len + wmax - 1) / wmax;
+        w = (len + np - 1) / np;
+        u0 = (int)(at - (long long)tile * units);
+        at += w;
+        return true;
     }
-}
+};
 
-// The min term of one k-block for 32 columns: acc = fma(-(dmin*m), sA*sum(qA), acc); `nu` is -(sA*sum(qA)).
-__device__ __forceinline__ void min_add(float nu, const float *wb, uint64_t (&acc)[16])
-{
-    const uint64_t nu2 = pack2(nu, nu);
-#pragma unroll
-    for (int c4 = 0; c4 < 8; c4++) {
-        const ulonglong2 w = *(const ulonglong2 *)(wb + 4 * c4);
-        acc[2 * c4] = fma2(w.x, nu2, acc[2 * c4]);
-        acc[2 * c4 + 1] = fma2(w.y, nu2, acc[2 * c4 + 1]);
-    }
-}
+// VAR: how a k-block's sums are scaled.  PLAIN: f32 scales from shared memory, product and fma on the CUDA cores;
+// MINS: the same with Q4_K's min term; HALF: Q6_K's k-blocks of 16 values; TCS: scale products from the tensor cores.
+enum { VAR_PLAIN = 0, VAR_MINS = 1, VAR_HALF = 2, VAR_TCS = 3 };
 
-// MINS: B is Q4_K; every k-block also has the min term, from two more planes a stage.
-// HALF: B is Q6_K; a k-block is 16 values (2 KB of codes an operand), and the tensor instruction's other 16 are read,
-// through the descriptor's leading-dimension offset, from a patch of zeros in shared memory.
-template <bool SUMS, bool MINS, bool HALF>
+template <int KIND, bool SUMS, int VAR>
 __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs p)
 {
+    constexpr bool MINS = VAR == VAR_MINS, HALF = VAR == VAR_HALF, TCS = VAR == VAR_TCS;
+    using G = Cfg<KIND, MINS, HALF, TCS>;
+    constexpr int S = G::S, KS = G::KS, KC = G::KC, NT = G::NT, TCOLS = G::TCOLS, THREADS = MM_THREADS;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = smem_u32(smem);
-    const uint32_t full0 = base, empty0 = base + 8 * MM_STAGES, tfull0 = base + 16 * MM_STAGES, tempty0 = tfull0 + 8 * TMEM_STAGES;
-    const uint32_t holder = tempty0 + 8 * TMEM_STAGES;
-    volatile int *abort_flag = (volatile int *)(smem + 512);
+    const uint32_t full0 = base, empty0 = base + 8 * S, tfull0 = base + 16 * S, tempty0 = tfull0 + 8 * NT;
+    const uint32_t holder = tempty0 + 8 * NT;
+    volatile int *abort_flag = (volatile int *)(smem + 768);
     volatile uint32_t *holder_ptr = (volatile uint32_t *)(smem + (holder - base));
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < MM_STAGES; s++) {
+        for (int s = 0; s < S; s++) {
             mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 1 + EPI_WARPS);      // the MMA thread's commit and the epilogue warps
+            mbar_init(empty0 + 8 * s, TCS ? 1 : 1 + EPI_WARPS);      // the MMA thread's commit, and the epilogue warps where they read the scales
         }
-        for (int s = 0; s < TMEM_STAGES; s++) {
-            mbar_init(tfull0 + 8 * s, 1);            // only the first two of each are used: one a pair of accumulators
-            mbar_init(tempty0 + 8 * s, EPI_WARPS);
+        for (int t = 0; t < NT; t++) {
+            mbar_init(tfull0 + 8 * t, 1);
+            mbar_init(tempty0 + 8 * t, EPI_WARPS);
         }
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (HALF) {
-        for (int i = threadIdx.x; i < SLAB / 2 / 16; i += MM_THREADS) *(uint4 *)(smem + MM_ZEROS + i * 16) = make_uint4(0, 0, 0, 0);
+    if (G::PATCH) {
+        for (int i = threadIdx.x; i < (int)G::PATCH / 16; i += THREADS) *(uint4 *)(smem + G::O_PATCH + i * 16) = make_uint4(0, 0, 0, 0);
         fence_proxy_async();            // the tensor cores read the patch through the async proxy
     }
     if (warp == 1) tmem_alloc(holder, 512);
@@ -401,149 +614,302 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *holder_ptr;
-
-    const int tn = blockIdx.x, tm = blockIdx.y;
-    constexpr uint32_t CB = HALF ? SLAB / 2 : SLAB;       // bytes of codes a k-block and operand
-    const int stages_total = (p.kb + KS - 1) / KS;
     uint8_t *ring = smem + MM_HEADER;
+    const int wmax = BNMAX / p.unit;
+#ifdef QB_MM_TUNING
+    const int wmode = ((p.probe >> 4) & 3) | ((p.probe >> 7) & 1) << 3 | ((p.probe >> 8) & 1) << 4;
+#else
+    constexpr int wmode = MM_WAIT_MODE;
+#endif
 
     if (warp == 0) {
-        // ---- producer: four contiguous slabs a stage (A codes, B codes, A scales, B scales)
-        if (lane == 0) {
-            int issued = 0;
-            for (int it = 0; it < stages_total; it++) {
-                const int s = it % MM_STAGES;
-                const uint32_t phase = (uint32_t)(it / MM_STAGES) & 1u;
-                if (it >= MM_STAGES && !mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) break;
-                const int kb0 = it * KS, nkb = min(KS, p.kb - kb0);
-                const uint32_t dst = smem_u32(ring + (size_t)s * STAGE_BYTES), bar = full0 + 8 * s;
-                const uint32_t code_bytes = (uint32_t)nkb * CB, scale_bytes = (uint32_t)nkb * TILE * 4;
-                mbar_arrive_expect_tx(bar, 2 * code_bytes + (MINS ? 4 : 2) * scale_bytes);
-                bulk_g2s(dst, p.a.codes + ((size_t)tm * p.kb + kb0) * CB, code_bytes, bar);
-                bulk_g2s(dst + KS * SLAB, p.b.codes + ((size_t)tn * p.kb + kb0) * CB, code_bytes, bar);
-                bulk_g2s(dst + 2 * KS * SLAB, p.a.scales + ((size_t)tm * p.kb + kb0) * TILE, scale_bytes, bar);
-                bulk_g2s(dst + 2 * KS * SLAB + KS * TILE * 4, p.b.scales + ((size_t)tn * p.kb + kb0) * TILE, scale_bytes, bar);
-                if (MINS) {
-                    bulk_g2s(dst + 2 * KS * SLAB + 2 * KS * TILE * 4, p.a.extra + ((size_t)tm * p.kb + kb0) * TILE, scale_bytes, bar);
-                    bulk_g2s(dst + 2 * KS * SLAB + 3 * KS * TILE * 4, p.b.extra + ((size_t)tn * p.kb + kb0) * TILE, scale_bytes, bar);
+        // ---- producer: a stage is KS k-blocks; A's codes, scales (and scaled sums) are one copy each a stage (tile-major),
+        // B's one copy each a k-block.  Lane 0 posts the byte count, then every lane issues its own copy.
+        Pieces pieces(p, wmax);
+        int tile, u0, w, sc = 0;
+        bool alive = true;
+        long long w_empty = 0, t_begin = MM_CLOCK();
+        while (alive && pieces.next(tile, u0, w)) {
+            const int n0 = u0 * p.unit, bn = w * p.unit, bi = tile / p.mtiles, mt = tile - bi * p.mtiles;
+            const uint8_t *a_codes = p.a.codes + bi * p.a_stride, *b_codes = p.b.codes + bi * p.b_stride;
+            const uint8_t *a_scales = (const uint8_t *)p.a.scales + bi * p.a_stride, *a_extra = (const uint8_t *)p.a.extra + bi * p.a_stride;
+            const uint8_t *b_scales = (const uint8_t *)p.b.scales + bi * p.b_stride, *b_extra = (const uint8_t *)p.b.extra + bi * p.b_stride;
+            for (int kb0 = 0; kb0 < p.kb && alive; kb0 += KS, sc++) {
+                const int s = sc % S, nkb = min(KS, p.kb - kb0);
+                int ok = 1;
+                const long long w0 = MM_CLOCK();
+                if (lane == 0 && sc >= S) ok = mm_wait(empty0 + 8 * s, (uint32_t)(sc / S - 1) & 1u, abort_flag, p.status, wmode) ? 1 : 0;
+                w_empty += MM_CLOCK() - w0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { alive = false; break; }
+                const uint32_t dst = smem_u32(ring + (size_t)s * G::STAGE), bar = full0 + 8 * s;
+                const uint32_t a_code_bytes = (uint32_t)nkb * G::A_KB, a_sc_bytes = (uint32_t)nkb * TILE * G::SW;
+                uint32_t b_code_bytes = (uint32_t)bn * KC * 16, b_sc_bytes = (uint32_t)bn * G::SW;
+                if (MM_PROBE(p) & 4) b_code_bytes = 0;          // tuning: no copies of B's codes
+                if (MM_PROBE(p) & 64) b_sc_bytes = 0;           // tuning: no copies of B's scales
+                if (lane == 0)
+                    mbar_arrive_expect_tx(bar, a_code_bytes + (MINS ? 2 : 1) * a_sc_bytes + (uint32_t)nkb * (b_code_bytes + (MINS ? 2 : 1) * b_sc_bytes));
+                __syncwarp();
+                const size_t a_at = (size_t)mt * p.kb + kb0;
+                if (lane == 0) bulk_g2s(dst, a_codes + a_at * G::A_KB, a_code_bytes, bar);
+                else if (lane == 1) bulk_g2s(dst + G::O_SA, a_scales + a_at * TILE * G::SW, a_sc_bytes, bar);
+                else if (lane == 2) { if (MINS) bulk_g2s(dst + G::O_UA, a_extra + a_at * TILE * G::SW, a_sc_bytes, bar); }
+                else {
+                    constexpr int NC = MINS ? 3 : 2;
+                    const int job = lane - 3, kk = job / NC, what = job - kk * NC;
+                    if (kk < nkb) {
+                        const size_t kb = (size_t)(kb0 + kk);
+                        if ((what == 0 && b_code_bytes == 0) || (what != 0 && b_sc_bytes == 0)) { }
+                        else if (what == 0)
+                            bulk_g2s(dst + G::O_B + kk * G::B_KB, b_codes + (kb * (p.b.rows_pad / 8) + n0 / 8) * (KC * 128), b_code_bytes, bar);
+                        else if (what == 1)
+                            bulk_g2s(dst + G::O_SB + kk * BNMAX * G::SW, b_scales + (kb * p.b.rows_pad + n0) * G::SW, b_sc_bytes, bar);
+                        else
+                            bulk_g2s(dst + G::O_MB + kk * BNMAX * G::SW, b_extra + (kb * p.b.rows_pad + n0) * G::SW, b_sc_bytes, bar);
+                    }
                 }
-                issued = it + 1;
             }
-            if (*abort_flag) {          // let the copies still in flight land before the block exits
-                for (int it = max(0, issued - MM_STAGES); it < issued; it++) {
-                    long long start = clock64();
-                    while (!mbar_try_wait(full0 + 8 * (it % MM_STAGES), (uint32_t)(it / MM_STAGES) & 1u) && clock64() - start < WAIT_CYCLES) { }
-                }
+        }
+        if (lane == 0) { MM_TRACE(p, 0, w_empty); MM_TRACE(p, 1, MM_CLOCK() - t_begin); MM_TRACE(p, 2, (long long)sc); }
+        if (*abort_flag && lane == 0) {          // let the copies still in flight land before the block exits
+            for (int it = max(0, sc - S); it < sc; it++) {
+                long long start = clock64();
+                while (!mbar_try_wait(full0 + 8 * (it % S), (uint32_t)(it / S) & 1u) && clock64() - start < WAIT_CYCLES) { }
             }
         }
     } else if (warp == 1) {
-        // ---- MMA issue: one thread.  The four accumulators form two pairs; a pair of k-blocks is issued into a pair of
-        // accumulators and committed to one barrier, so the barrier traffic is per two k-blocks on both sides.
+        // ---- MMA issue: one thread, whose own instruction stream paces the kernel when it is long (a lone thread issues
+        // a dependent instruction every few cycles): descriptors are formed by one addition a k-block, the waits are a
+        // single poll when the barrier is ready.  Every k-block goes to the next accumulator and is committed to its barrier.
         if (lane == 0) {
-            constexpr uint32_t idesc = idesc_s8(TILE, TILE);
-            // descriptors differ from k-block to k-block only in the start address (16-byte units)
-            const uint64_t desc_hi = smem_desc(0, SLAB / 2, 128);
-            int np = 0;                            // pairs issued so far
+            Pieces pieces(p, wmax);
+            int tile, u0, w, sc = 0, tc = 0;
             bool alive = true;
-            for (int it = 0; it < stages_total && alive; it++) {
-                const int s = it % MM_STAGES;
-                if (!mbar_wait(full0 + 8 * s, (uint32_t)(it / MM_STAGES) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) break;
-                tc_fence_after();
-                const uint32_t a_smem = smem_u32(ring + (size_t)s * STAGE_BYTES), b_smem = a_smem + KS * SLAB;
-                const int nkb = min(KS, p.kb - it * KS);
-                for (int kk = 0; kk < nkb; kk += 2, np++) {
-                    const int pair = np & 1, use = np >> 1;
-                    if (use > 0) {
-                        if (!mbar_wait(tempty0 + 8 * pair, (uint32_t)(use - 1) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
-                        tc_fence_after();
+            long long w_full = 0, w_tempty = 0, c_mma = 0, c_commit = 0, t_begin = MM_CLOCK();
+            constexpr uint32_t SBO = KC * 128;
+            // the descriptor without its start address: LBO 128, SBO, version
+            constexpr uint64_t DESC_HI = (uint64_t)(128u >> 4) << 16 | (uint64_t)(SBO >> 4) << 32 | (uint64_t)1 << 46;
+            const uint32_t patch = base + G::O_PATCH;
+            while (alive && pieces.next(tile, u0, w)) {
+                const uint32_t idesc = idesc_of(KIND, TILE, w * p.unit), idesc_s = idesc_of(1, TILE, w * p.unit);
+                for (int kb0 = 0; kb0 < p.kb && alive; kb0 += KS, sc++) {
+                    const int s = sc % S, nkb = min(KS, p.kb - kb0);
+                    const long long w0 = MM_CLOCK();
+                    if (!mm_poll(full0 + 8 * s, (uint32_t)(sc / S) & 1u, wmode & 3) &&
+                        !mm_wait(full0 + 8 * s, (uint32_t)(sc / S) & 1u, abort_flag, p.status, wmode)) { alive = false; break; }
+                    w_full += MM_CLOCK() - w0;
+                    tc_fence_after();
+                    const uint32_t a_smem = smem_u32(ring + (size_t)s * G::STAGE);
+                    uint64_t a_desc = DESC_HI | (uint64_t)(a_smem >> 4), b_desc = DESC_HI | (uint64_t)((a_smem + G::O_B) >> 4);
+                    // scale rows: the second half of K is the patch of zeros, LBO bytes past the start; a k-block on, the start
+                    // is one slab further and the patch that much nearer
+                    uint64_t sa_desc = smem_desc(a_smem + G::O_SA, patch - (a_smem + G::O_SA), 128), sb_desc = smem_desc(a_smem + G::O_SB, patch - (a_smem + G::O_SB), 128);
+                    constexpr uint64_t SA_STEP = (uint64_t)((TILE * 16) >> 4) - ((uint64_t)((TILE * 16) >> 4) << 16);
+                    constexpr uint64_t SB_STEP = (uint64_t)((BNMAX * 16) >> 4) - ((uint64_t)((BNMAX * 16) >> 4) << 16);
+#pragma unroll
+                    for (int kk = 0; kk < KS; kk++) {
+                        if (kk < nkb) {
+                            const int t = tc % NT;
+                            if (tc >= NT) {
+                                const uint32_t par = (uint32_t)(tc / NT - 1) & 1u;
+                                const long long w1 = MM_CLOCK();
+                                if (!mm_poll(tempty0 + 8 * t, par, wmode & 3) && !mm_wait(tempty0 + 8 * t, par, abort_flag, p.status, wmode)) { alive = false; break; }
+                                w_tempty += MM_CLOCK() - w1;
+                                tc_fence_after();
+                            }
+                            const uint32_t d = tmem + (uint32_t)(t * TCOLS);
+                            const long long c0 = MM_CLOCK();
+                            if (MM_PROBE(p) & 8) { }            // tuning: no products, commits only
+                            else if (KIND == 0 && HALF) {
+                                // the second 16-byte k-chunk of every row of A is the patch of zeros; B's may then be anything
+                                const uint32_t a_at = a_smem + kk * G::A_KB, b_at = a_smem + G::O_B + kk * G::B_KB;
+                                mma_issue<KIND>(d, smem_desc(a_at, patch - a_at, 128), smem_desc(b_at, 128, 128), idesc, 0u);
+                            } else {
+                                mma_issue<KIND>(d, a_desc, b_desc, idesc, 0u);
+                                if (KC == 4) mma_issue<KIND>(d, a_desc + (256 >> 4), b_desc + (256 >> 4), idesc, 1u);
+                            }
+                            if (TCS && !(MM_PROBE(p) & 8)) {
+                                // the scale products: rows [d, 0 x 7] of A's and B's scales, the other half of K from the zeros
+                                mma_issue<1>(d + BNMAX, sa_desc, sb_desc, idesc_s, 0u);
+                                sa_desc += SA_STEP;
+                                sb_desc += SB_STEP;
+                            }
+                            const long long c1 = MM_CLOCK();
+                            mma_commit(tfull0 + 8 * t);
+                            c_commit += MM_CLOCK() - c1;
+                            c_mma += c1 - c0;
+                            a_desc += G::A_KB >> 4;
+                            b_desc += G::B_KB >> 4;
+                            tc++;
+                        }
                     }
-                    // HALF: the second 16-byte k-chunk of every row is the zero patch (for A; B's may be anything finite)
-                    auto desc = [&](uint32_t addr, bool zeros) {
-                        if (HALF) return smem_desc(addr, zeros ? base + MM_ZEROS - addr : SLAB / 2, 128);
-                        return desc_hi | (uint64_t)((addr & 0x3FFFFu) >> 4);
-                    };
-                    mma_s8(tmem + (uint32_t)(2 * pair) * TILE, desc(a_smem + kk * CB, true), desc(b_smem + kk * CB, true), idesc);
-                    if (kk + 1 < nkb)
-                        mma_s8(tmem + (uint32_t)(2 * pair + 1) * TILE, desc(a_smem + (kk + 1) * CB, true), desc(b_smem + (kk + 1) * CB, true), idesc);
-                    mma_commit(tfull0 + 8 * pair);
+                    if (alive) mma_commit(empty0 + 8 * s);      // the stage is free once these products have run
                 }
-                mma_commit(empty0 + 8 * s);      // the stage's codes are free once these products have run
             }
+            MM_TRACE(p, 8, w_full); MM_TRACE(p, 9, w_tempty); MM_TRACE(p, 10, MM_CLOCK() - t_begin); MM_TRACE(p, 11, (long long)tc); MM_TRACE(p, 12, c_mma); MM_TRACE(p, 13, c_commit);
         }
     } else {
-        // ---- epilogue: a warp owns 32 rows (tensor-memory lanes 32*(warp%4) ..) x 32 columns of every accumulator;
-        // four warps a scheduler cover each other's tensor-memory reads.  Two k-blocks a barrier round.
-        const int q = warp & 3, cg = (warp - 2) >> 2;
-        const int row = tm * TILE + q * 32 + lane, col0 = tn * TILE + cg * 32;
-        const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cg * 32);
-        uint64_t acc[16];
-#pragma unroll
-        for (int c = 0; c < 16; c++) acc[c] = 0ull;
+        // ---- epilogue: warp (q, g) owns rows 32 q .. 32 q + 31 of the tile (the tensor-memory lanes a warp may read) and
+        // columns 32 g .. 32 g + 31 of the piece (none when the piece is narrower); the four warps of a q share a scheduler.
+        // A k-block costs a warp one poll of its barrier, one or two wide tensor-memory reads, one wait for them, and
+        // the arithmetic: the instruction count of this loop is what bounds the kernel.
+        const int q = warp & 3, g = (warp - 2) >> 2;
+        const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(g * 32);
+        Pieces pieces(p, wmax);
+        int tile, u0, w, sc = 0, tc = 0;
         bool alive = true;
-        int s = 0, kk = 0, np = 0;
-        uint32_t sphase = 0;
-        for (int i = 0; i < p.kb; i += 2, np++) {
-            const int pair = np & 1, cnt = min(2, p.kb - i);
-            if (!QB_MM_WAIT(tfull0 + 8 * pair, (uint32_t)(np >> 1) & 1u, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
-            tc_fence_after();
-            int32_t v[32];
-            if (!(MM_PROBE(p) & 2)) tmem_ld32(tlane + (uint32_t)(2 * pair) * TILE, v);
-            if (kk == 0 && !QB_MM_WAIT(full0 + 8 * s, sphase, abort_flag, p.status, STATUS_MATMUL_WAIT)) { alive = false; break; }
-            const float *sa_s = (const float *)(ring + (size_t)s * STAGE_BYTES + 2 * KS * SLAB) + kk * TILE;
-            const float *sb_s = sa_s + KS * TILE + cg * 32;
-            const float sa0 = sa_s[q * 32 + lane], sa1 = sa_s[TILE + q * 32 + lane];
-            float nu0 = 0.f, nu1 = 0.f;
-            if (MINS) {
-                nu0 = -sa_s[2 * KS * TILE + q * 32 + lane];
-                nu1 = -sa_s[2 * KS * TILE + TILE + q * 32 + lane];
+        long long w_tfull = 0, t_store = 0, t_begin = MM_CLOCK();
+        while (alive && pieces.next(tile, u0, w)) {
+            const int n0 = u0 * p.unit, bi = tile / p.mtiles, mt = tile - bi * p.mtiles;
+            const bool active = g * 32 < w * p.unit;                    // this warp has columns in the piece
+            const int row = mt * TILE + q * 32 + lane;
+            float *c_out = p.c + bi * p.c_stride;
+            int32_t *sums_out = SUMS ? p.sums + (size_t)bi * p.m * p.n * p.kb : nullptr;
+            // 32 f32 accumulators: as 16 pairs for the packed instructions of the CUDA-core scale path, as 32 scalars for TCS
+            uint64_t acc[TCS ? 1 : 16];
+            float accf[TCS ? 32 : 1];
+#pragma unroll
+            for (int j = 0; j < (TCS ? 1 : 16); j++) acc[j] = 0ull;
+#pragma unroll
+            for (int j = 0; j < (TCS ? 32 : 1); j++) accf[j] = 0.f;
+            int kk = 0;
+            for (int i = 0; i < p.kb && alive; i++, tc++) {
+                const int t = tc % NT, s = sc % S;
+                {
+                    const uint32_t bar = tfull0 + 8 * t, par = (uint32_t)(tc / NT) & 1u;
+                    const long long w0 = MM_CLOCK();
+                    if (!((wmode & 8) ? false : mm_poll(bar, par, wmode & 3)) && !mm_wait_lanes(bar, par, abort_flag, p.status, wmode)) { alive = false; break; }
+                    w_tfull += MM_CLOCK() - w0;
+                }
+                tc_fence_after();
+                const uint32_t at = tlane + (uint32_t)(t * TCOLS);
+                if (TCS) {
+                    // two halves of 16 columns: sums and scale products side by side in registers
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        uint32_t v[16], x[16];
+                        if (active && !(MM_PROBE(p) & 2)) {
+                            tmem_ld16(at + 16 * h, v);
+                            tmem_ld16(at + BNMAX + 16 * h, x);
+                        }
+                        tmem_ld_landed16x2(v, x);
+                        if (h == 1) {
+                            tc_fence_before();
+                            if (lane == 0) mbar_arrive(tempty0 + 8 * t);         // the accumulator has been read (warp-wide reads)
+                        }
+                        if (active && !(MM_PROBE(p) & 1)) {
+                            // scalar fma on the registers the reads filled: forming f32x2 pairs would cost a move or two a pair
+#pragma unroll
+                            for (int c = 0; c < 16; c++) accf[16 * h + c] = __fmaf_rn(sum_as_float<KIND>(v[c]), __uint_as_float(x[c]), accf[16 * h + c]);
+                        }
+                        if (SUMS && active && row < p.m) {
+#pragma unroll
+                            for (int c = 0; c < 16; c++) {
+                                const int col = n0 + g * 32 + 16 * h + c;
+                                if (col < p.n) sums_out[((size_t)row * p.n + col) * p.kb + i] = sum_as_int<KIND>(v[c]);
+                            }
+                        }
+                    }
+                } else {
+                    uint32_t v[32];
+                    if (active && !(MM_PROBE(p) & 2)) tmem_ld32(at, v);
+                    // the stage's scales (complete long since: the product that filled the accumulator read the same stage)
+                    if (kk == 0 && !mm_poll(full0 + 8 * s, (uint32_t)(sc / S) & 1u, wmode & 3) &&
+                        !mm_wait_lanes(full0 + 8 * s, (uint32_t)(sc / S) & 1u, abort_flag, p.status, wmode)) { alive = false; }
+                    const uint8_t *stage = ring + (size_t)s * G::STAGE;
+                    const float sa = ((const float *)(stage + G::O_SA))[kk * TILE + q * 32 + lane];
+                    const uint64_t sa2 = pack2(sa, sa);
+                    uint64_t nu2 = 0ull;
+                    if (MINS) {
+                        const float nu = -((const float *)(stage + G::O_UA))[kk * TILE + q * 32 + lane];
+                        nu2 = pack2(nu, nu);
+                    }
+                    const float *sb = (const float *)(stage + G::O_SB) + kk * BNMAX + g * 32;
+                    tmem_ld_landed32(v);
+                    tc_fence_before();
+                    if (lane == 0) mbar_arrive(tempty0 + 8 * t);         // the accumulator has been read (warp-wide reads)
+                    if (!alive) break;
+                    if (active && !(MM_PROBE(p) & 1)) {
+#pragma unroll
+                        for (int c4 = 0; c4 < 8; c4++) {
+                            const ulonglong2 sc2 = *(const ulonglong2 *)(sb + 4 * c4);
+                            acc[2 * c4] = fma2(sums2<KIND>(v[4 * c4], v[4 * c4 + 1]), mul2(sa2, sc2.x), acc[2 * c4]);
+                            acc[2 * c4 + 1] = fma2(sums2<KIND>(v[4 * c4 + 2], v[4 * c4 + 3]), mul2(sa2, sc2.y), acc[2 * c4 + 1]);
+                        }
+                        if (MINS) {
+                            const float *wb = sb + (G::O_MB - G::O_SB) / 4;
+#pragma unroll
+                            for (int c4 = 0; c4 < 8; c4++) {
+                                const ulonglong2 m2 = *(const ulonglong2 *)(wb + 4 * c4);
+                                acc[2 * c4] = fma2(m2.x, nu2, acc[2 * c4]);
+                                acc[2 * c4 + 1] = fma2(m2.y, nu2, acc[2 * c4 + 1]);
+                            }
+                        }
+                    }
+                    if (SUMS && active && row < p.m) {
+#pragma unroll
+                        for (int c = 0; c < 32; c++) {
+                            const int col = n0 + g * 32 + c;
+                            if (col < p.n) sums_out[((size_t)row * p.n + col) * p.kb + i] = sum_as_int<KIND>(v[c]);
+                        }
+                    }
+                }
+                if (++kk == KS || i + 1 == p.kb) {
+                    if (!TCS) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty0 + 8 * s);      // this warp has read the stage's scales
+                    }
+                    kk = 0;
+                    sc++;
+                }
             }
             tmem_ld_wait();
-            if (!(MM_PROBE(p) & 1)) {
-                scale_add(v, sa0, sb_s, acc);
-                if (MINS) min_add(nu0, sb_s + 2 * KS * TILE, acc);
-            }
-            if (SUMS && row < p.m) {
+            const long long s0 = MM_CLOCK();
+            if (alive && active && row < p.m) {
+                const bool vec = (p.n & 3) == 0 && ((uintptr_t)c_out & 15) == 0;
+                const int col0 = n0 + g * 32;
+                float *out = c_out + (size_t)row * p.n + col0;
 #pragma unroll
-                for (int c = 0; c < 32; c++)
-                    if (col0 + c < p.n) p.sums[((size_t)row * p.n + col0 + c) * p.kb + i] = v[c];
-            }
-            if (cnt == 2) {
-                if (!(MM_PROBE(p) & 2)) tmem_ld32(tlane + (uint32_t)(2 * pair + 1) * TILE, v);
-                tmem_ld_wait();
-            }
-            tc_fence_before();
-            if (lane == 0) mbar_arrive(tempty0 + 8 * pair);      // both accumulators have been read (warp-wide reads)
-            if (cnt == 2) {
-                if (!(MM_PROBE(p) & 1)) {
-                    scale_add(v, sa1, sb_s + TILE, acc);
-                    if (MINS) min_add(nu1, sb_s + 2 * KS * TILE + TILE, acc);
-                }
-                if (SUMS && row < p.m) {
+                for (int c4 = 0; c4 < 8; c4++) {
+                    float f[4];
+                    if (TCS) {
 #pragma unroll
-                    for (int c = 0; c < 32; c++)
-                        if (col0 + c < p.n) p.sums[((size_t)row * p.n + col0 + c) * p.kb + i + 1] = v[c];
+                        for (int c = 0; c < 4; c++) f[c] = accf[(TCS ? 4 * c4 : 0) + (TCS ? c : 0)];
+                    } else {
+                        unpack2(acc[TCS ? 0 : 2 * c4], f[0], f[1]);
+                        unpack2(acc[TCS ? 0 : 2 * c4 + 1], f[2], f[3]);
+                    }
+                    if (vec && col0 + 4 * c4 + 4 <= p.n) *(float4 *)(out + 4 * c4) = make_float4(f[0], f[1], f[2], f[3]);
+                    else {
+#pragma unroll
+                        for (int c = 0; c < 4; c++) if (col0 + 4 * c4 + c < p.n) out[4 * c4 + c] = f[c];
+                    }
                 }
             }
-            kk += 2;
-            if (kk >= KS || i + cnt >= p.kb) {
-                if (lane == 0) mbar_arrive(empty0 + 8 * s);      // this warp has read the stage's scales
-                kk = 0;
-                if (++s == MM_STAGES) { s = 0; sphase ^= 1u; }
+            t_store += MM_CLOCK() - s0;
+            if (p.cb) {
+                // `Back` for the piece (src/MatMulBlocks.cs:421 -> Ptx.LanesToBlock): once every epilogue warp has stored its
+                // lanes, the epilogue threads encode the piece's blocks of 32 consecutive values (n % 32 == 0, unit 32: a block
+                // lies in one row of one piece).  All warps come here whether or not a wait gave up, then look at the flag.
+                named_bar_sync(2, EPI_WARPS * 32);
+                if (*abort_flag) { alive = false; break; }
+                const int bw = w * p.unit / 32, tid = threadIdx.x - 64;
+                const int rows_here = min(TILE, p.m - mt * TILE);
+                for (int idx = tid; idx < rows_here * bw; idx += EPI_WARPS * 32) {
+                    const int rr = idx / bw, bc = idx - rr * bw;
+                    const size_t first = bi * p.c_stride + (size_t)(mt * TILE + rr) * p.n + n0 + bc * 32;      // c_stride is whole blocks
+                    float f[32];
+#pragma unroll
+                    for (int c = 0; c < 8; c++) {
+                        const float4 x = __ldcg((const float4 *)(p.c + first) + c);
+                        f[4 * c] = x.x; f[4 * c + 1] = x.y; f[4 * c + 2] = x.z; f[4 * c + 3] = x.w;
+                    }
+                    if (p.fmt_c == QB200_Q8_0) encode_q8_0_block(f, p.cb + (first >> 5) * 34);
+                    else encode_q4_0_block(f, p.cb + (first >> 5) * 18);
+                }
             }
         }
-        if (alive && row < p.m) {
-            float *out = p.c + (size_t)row * p.n + col0;
-            float f[32];
-#pragma unroll
-            for (int c = 0; c < 16; c++) unpack2(acc[c], f[2 * c], f[2 * c + 1]);
-            if ((p.n & 3) == 0 && col0 + 32 <= p.n && ((uintptr_t)p.c & 15) == 0) {
-#pragma unroll
-                for (int c4 = 0; c4 < 8; c4++) *(float4 *)(out + 4 * c4) = make_float4(f[4 * c4], f[4 * c4 + 1], f[4 * c4 + 2], f[4 * c4 + 3]);
-            } else {
-#pragma unroll
-                for (int c = 0; c < 32; c++) if (col0 + c < p.n) out[c] = f[c];
-            }
-        }
+        if (lane == 0 && warp < 6) { MM_TRACE(p, 16 + 4 * (warp - 2), w_tfull); MM_TRACE(p, 17 + 4 * (warp - 2), MM_CLOCK() - t_begin); MM_TRACE(p, 18 + 4 * (warp - 2), t_store); }
     }
     tc_fence_before();
     __syncthreads();
@@ -553,103 +919,192 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
 // ---------------------------------------------------------------------------------- host side
 
 static int *g_mm_status = nullptr;
-static int g_mm_probe = 0;
+#ifdef QB_MM_TUNING
+static long long *g_mm_trace = nullptr;
+extern "C" void qb200_mm_set_trace(long long *buffer) { g_mm_trace = buffer; }
+#endif
+static int g_mm_sms = 0;
+static int g_mm_kind = 0;          // the tensor kind the library packs for and multiplies with
+static int g_mm_tcs = 1;           // scale products of plain f16 scales on the tensor cores
 
-void matmul_set_probe(int mode) { g_mm_probe = mode; }
-
-template <bool SUMS>
+template <int KIND, bool SUMS, int VAR>
+static cudaError_t set_mm_attr_var()
+{
+    return cudaFuncSetAttribute(matmul_kernel<KIND, SUMS, VAR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)Cfg<KIND, VAR == VAR_MINS, VAR == VAR_HALF, VAR == VAR_TCS>::SMEM);
+}
+template <int KIND, bool SUMS>
 static cudaError_t set_mm_attr()
 {
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(matmul_kernel<SUMS, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MM_SMEM))) return e;
-    if ((e = cudaFuncSetAttribute(matmul_kernel<SUMS, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MM_SMEM))) return e;
-    return cudaFuncSetAttribute(matmul_kernel<SUMS, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MM_SMEM);
+    if ((e = set_mm_attr_var<KIND, SUMS, VAR_PLAIN>()) || (e = set_mm_attr_var<KIND, SUMS, VAR_MINS>())) return e;
+    if ((e = set_mm_attr_var<KIND, SUMS, VAR_HALF>())) return e;
+    return set_mm_attr_var<KIND, SUMS, VAR_TCS>();
 }
 
-cudaError_t matmul_init(int, int max_smem, int *status)
+cudaError_t matmul_init(int sm_count, int max_smem, int *status)
 {
     g_mm_status = status;
-    if ((int)MM_SMEM > max_smem) return cudaErrorInvalidValue;
+    g_mm_sms = sm_count;
+    if ((int)MM_SMEM_MAX > max_smem) return cudaErrorInvalidValue;
+#ifdef QB_MM_TUNING
+    const char *kind = getenv("QB200_MM_KIND"), *tcs = getenv("QB200_MM_TCS");
+    g_mm_kind = kind && *kind ? atoi(kind) != 0 : 0;
+    g_mm_tcs = tcs && *tcs ? atoi(tcs) != 0 : 1;
+#endif
     cudaError_t e;
-    if ((e = set_mm_attr<false>())) return e;
-    return set_mm_attr<true>();
+    if ((e = set_mm_attr<0, false>()) || (e = set_mm_attr<0, true>())) return e;
+    if ((e = set_mm_attr<1, false>()) || (e = set_mm_attr<1, true>())) return e;
+    return cudaSuccess;
 }
 
 // k-blocks of the product: 32 values each, 16 against Q6_K rows
 static int k_blocks(int fmt_b, int k) { return fmt_b == QB200_Q6_K ? k / 16 : k / 32; }
-static size_t packed_codes_bytes(int rows, int k) { return (size_t)((rows + TILE - 1) / TILE) * (k / 32) * SLAB; }
-static size_t packed_scales_bytes(int rows, int kbs) { return (size_t)((rows + TILE - 1) / TILE) * kbs * TILE * 4; }
+static int pad_rows(int rows) { return (rows + TILE - 1) / TILE * TILE; }
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+static size_t codes_bytes(int rows, int k) { return (size_t)pad_rows(rows) * k * (g_mm_kind ? 2 : 1); }
+// a plane of per-(row, k-block) values: f32, or the 16-byte rows of the tensor cores' scale product
+static size_t plane_bytes(int rows, int kbs, bool tcs = false) { return (size_t)pad_rows(rows) * kbs * (tcs ? 16 : 4); }
+// whether the scale products of a product against fmt_b rows run on the tensor cores
+static bool use_tcs(int fmt_b) { return g_mm_tcs && (fmt_b == QB200_Q8_0 || fmt_b == QB200_Q4_0); }
 
-// Scratch for both packed operands: codes, scales and the extra plane of A, then the same of B, each on a 256-byte
-// boundary (the extra planes are only written when B is Q4_K, but always have their place).
-size_t matmul_workspace_bytes(int, int fmt_b, int m, int n, int k)
+// A packed operand in one buffer: codes, scales, extra plane, each on a 256-byte boundary (the extra plane is only
+// written when B is Q4_K, but always has its place).
+static size_t packed_bytes(int rows, int k, int kbs, bool tcs)
 {
-    const int kbs = k_blocks(fmt_b, k);
-    return align256(packed_codes_bytes(m, k)) + 2 * align256(packed_scales_bytes(m, kbs)) + align256(packed_codes_bytes(n, k)) +
-           2 * align256(packed_scales_bytes(n, kbs));
+    return align256(codes_bytes(rows, k)) + align256(plane_bytes(rows, kbs, tcs)) + align256(plane_bytes(rows, kbs));
 }
 
-static cudaError_t pack(int fmt, const void *raw, int rows, int k, uint8_t *codes, float *scales, float *extra, bool want_extra,
-                        bool split, cudaStream_t stream)
+size_t matmul_prepacked_bytes(int fmt_b, int n, int k) { return packed_bytes(n, k, k_blocks(fmt_b, k), use_tcs(fmt_b)); }
+
+// Scratch of a call: every product's packed A (one when A is the same for all), then every distinct packed B
+// (none when the caller brings B prepacked).
+size_t matmul_workspace_bytes(int fmt_b, int m, int n, int k, const MatmulBatch &batch, bool b_prepacked)
 {
-    const int kb = k / 32, padded = (rows + TILE - 1) / TILE * TILE;
-    if (fmt == QB200_Q4_K) {
-        pack_q4_k_kernel<<<dim3(padded / 32, kb / 8), 256, 0, stream>>>((const uint8_t *)raw, rows, kb, codes, scales, extra);
-        return cudaGetLastError();
-    }
-    if (fmt == QB200_Q6_K) {
-        pack_q6_k_kernel<<<dim3(padded / 32, k / 256), 256, 0, stream>>>((const uint8_t *)raw, rows, k / 16, codes, scales);
-        return cudaGetLastError();
-    }
-    const dim3 grid(padded / 32, (kb + 7) / 8);
-    float *usums = want_extra ? extra : nullptr;
+    const int kbs = k_blocks(fmt_b, k);
+    const size_t a_sets = batch.stride_a ? batch.count : 1, b_sets = b_prepacked ? 0 : (batch.stride_b ? batch.count : 1);
+    return a_sets * packed_bytes(m, k, kbs, use_tcs(fmt_b)) + b_sets * packed_bytes(n, k, kbs, use_tcs(fmt_b));
+}
+
+// bytes between two products' raw operands `stride` values apart (whole blocks)
+static size_t raw_bytes(int fmt, long long stride) { return (size_t)(stride / block_values(fmt)) * block_bytes(fmt); }
+
+static PackTarget target_in(void *buffer, int rows, int k, int kbs, bool tile_major, bool tcs)
+{
+    uint8_t *w = (uint8_t *)buffer;
+    PackTarget t;
+    t.codes = w;
+    t.scales = (float *)(w + align256(codes_bytes(rows, k)));
+    t.extra = (float *)(w + align256(codes_bytes(rows, k)) + align256(plane_bytes(rows, kbs, tcs)));
+    t.tcs = tcs ? 1 : 0;
+    t.rows_pad = pad_rows(rows);
+    t.kbs = kbs;
+    t.kc = (k / kbs) * (g_mm_kind ? 2 : 1) / 16;
+    t.tile_major = tile_major ? 1 : 0;
+    t.kind = g_mm_kind;
+    return t;
+}
+
+static cudaError_t pack(int fmt, const void *raw, int rows, int k, const PackTarget &t, bool want_usums, bool split, cudaStream_t stream)
+{
+    const int kb32 = k / 32, padded = t.rows_pad;
     const uint8_t *r = (const uint8_t *)raw;
-    if (fmt == QB200_Q8_0) {
-        if (split) pack_rows_kernel<QB200_Q8_0, true><<<grid, 256, 0, stream>>>(r, rows, kb, codes, scales, usums);
-        else pack_rows_kernel<QB200_Q8_0, false><<<grid, 256, 0, stream>>>(r, rows, kb, codes, scales, usums);
-    } else {
-        if (split) pack_rows_kernel<QB200_Q4_0, true><<<grid, 256, 0, stream>>>(r, rows, kb, codes, scales, usums);
-        else pack_rows_kernel<QB200_Q4_0, false><<<grid, 256, 0, stream>>>(r, rows, kb, codes, scales, usums);
+    if (fmt == QB200_Q4_K) pack_q4_k_kernel<<<dim3(padded / 32, kb32 / 8), 256, 0, stream>>>(r, rows, kb32, t);
+    else if (fmt == QB200_Q6_K) pack_q6_k_kernel<<<dim3(padded / 32, k / 256), 256, 0, stream>>>(r, rows, k / 16, t);
+    else {
+        const dim3 grid(padded / 32, (kb32 + 7) / 8);
+        const int us = want_usums ? 1 : 0;
+        if (fmt == QB200_Q8_0) {
+            if (split) pack_rows_kernel<QB200_Q8_0, true><<<grid, 256, 0, stream>>>(r, rows, kb32, t, us);
+            else pack_rows_kernel<QB200_Q8_0, false><<<grid, 256, 0, stream>>>(r, rows, kb32, t, us);
+        } else {
+            if (split) pack_rows_kernel<QB200_Q4_0, true><<<grid, 256, 0, stream>>>(r, rows, kb32, t, us);
+            else pack_rows_kernel<QB200_Q4_0, false><<<grid, 256, 0, stream>>>(r, rows, kb32, t, us);
+        }
     }
     return cudaGetLastError();
 }
 
-template <bool SUMS>
-static void launch_product(bool mins, bool half, dim3 grid, const MatmulArgs &args, cudaStream_t stream)
+// B (n x k, fmt_b) re-laid for the product into `packed` (matmul_prepacked_bytes): the weights' half of a call's packing,
+// done once by a caller that keeps the result.
+int matmul_prepack_b(int fmt_b, const void *b, int n, int k, void *packed, cudaStream_t stream)
 {
-    if (mins) matmul_kernel<SUMS, true, false><<<grid, MM_THREADS, MM_SMEM, stream>>>(args);
-    else if (half) matmul_kernel<SUMS, false, true><<<grid, MM_THREADS, MM_SMEM, stream>>>(args);
-    else matmul_kernel<SUMS, false, false><<<grid, MM_THREADS, MM_SMEM, stream>>>(args);
+    const PackTarget t = target_in(packed, n, k, k_blocks(fmt_b, k), false, use_tcs(fmt_b));
+    return (int)pack(fmt_b, b, n, k, t, false, false, stream);
 }
 
-// fmt_a: Q8_0 / Q4_0; fmt_b: Q8_0 / Q4_0 / Q4_K / Q6_K (k then in whole super-blocks of 256).
-int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int32_t *sums, int m, int n, int k, void *workspace,
-                  cudaStream_t stream)
+template <int KIND, bool SUMS, int VAR>
+static void launch_var(int grid, const MatmulArgs &args, cudaStream_t stream)
+{
+    matmul_kernel<KIND, SUMS, VAR><<<grid, MM_THREADS, Cfg<KIND, VAR == VAR_MINS, VAR == VAR_HALF, VAR == VAR_TCS>::SMEM, stream>>>(args);
+}
+
+template <int KIND, bool SUMS>
+static void launch_product(int var, int grid, const MatmulArgs &args, cudaStream_t stream)
+{
+    if (var == VAR_MINS) launch_var<KIND, SUMS, VAR_MINS>(grid, args, stream);
+    else if (var == VAR_HALF) launch_var<KIND, SUMS, VAR_HALF>(grid, args, stream);
+    else if (var == VAR_TCS) launch_var<KIND, SUMS, VAR_TCS>(grid, args, stream);
+    else launch_var<KIND, SUMS, VAR_PLAIN>(grid, args, stream);
+}
+
+template <int KIND>
+static void launch_kind(bool sums, int var, int grid, const MatmulArgs &args, cudaStream_t stream)
+{
+    if (sums) launch_product<KIND, true>(var, grid, args, stream);
+    else launch_product<KIND, false>(var, grid, args, stream);
+}
+
+// fmt_a: Q8_0 / Q4_0; fmt_b: Q8_0 / Q4_0 / Q4_K / Q6_K (k then in whole super-blocks of 256).  `b_packed`: B as
+// matmul_prepack_b left it, or null to pack `b` into the workspace now.  `c_blocks`: optional `Back` of C as fmt_c.
+int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void *b_packed, float *c, int32_t *sums, int fmt_c,
+                  void *c_blocks, int m, int n, int k, const MatmulBatch &batch, void *workspace, cudaStream_t stream)
 {
     const bool mins = fmt_b == QB200_Q4_K, half = fmt_b == QB200_Q6_K;
     const int kbs = k_blocks(fmt_b, k);
-    uint8_t *w = (uint8_t *)workspace;
-    uint8_t *a_codes = w;
-    float *a_scales = (float *)(w += align256(packed_codes_bytes(m, k)));
-    float *a_extra = (float *)(w += align256(packed_scales_bytes(m, kbs)));
-    uint8_t *b_codes = (w += align256(packed_scales_bytes(m, kbs)));
-    float *b_scales = (float *)(w += align256(packed_codes_bytes(n, k)));
-    float *b_extra = (float *)(w += align256(packed_scales_bytes(n, kbs)));
     cudaError_t e;
-    if (!(g_mm_probe & 8)) {                // (tuning aid: 8 = operands as packed by an earlier call, 4 = no product)
-        if ((e = pack(fmt_a, a, m, k, a_codes, a_scales, a_extra, mins, half, stream))) return (int)e;
-        if ((e = pack(fmt_b, b, n, k, b_codes, b_scales, b_extra, false, false, stream))) return (int)e;
+    // every product's A, and every distinct B, is packed into a slab of its own
+    const bool tcs = use_tcs(fmt_b);
+    const size_t a_slab = packed_bytes(m, k, kbs, tcs), b_slab = packed_bytes(n, k, kbs, tcs);
+    const int b_sets = b_packed ? 0 : (batch.stride_b ? batch.count : 1);
+    const size_t a_raw = raw_bytes(fmt_a, batch.stride_a), b_raw = raw_bytes(fmt_b, batch.stride_b);
+    const PackTarget ta = target_in(workspace, m, k, kbs, true, tcs);
+    for (int i = 0; i < batch.count; i++) {
+        PackTarget t = target_in((uint8_t *)workspace + i * a_slab, m, k, kbs, true, tcs);
+        if ((e = pack(fmt_a, (const uint8_t *)a + i * a_raw, m, k, t, mins, half, stream))) return (int)e;
+        if (!batch.stride_a) break;
     }
-    if (g_mm_probe & 4) return 0;
+    const int a_sets = batch.stride_a ? batch.count : 1;
+    uint8_t *b_area = (uint8_t *)workspace + a_sets * a_slab;
+    PackTarget tb = target_in(b_packed ? (void *)b_packed : (void *)b_area, n, k, kbs, false, tcs);
+    for (int i = 0; i < b_sets; i++) {
+        PackTarget t = target_in(b_area + i * b_slab, n, k, kbs, false, tcs);
+        if ((e = pack(fmt_b, (const uint8_t *)b + i * b_raw, n, k, t, false, false, stream))) return (int)e;
+    }
     MatmulArgs args;
-    args.a.codes = a_codes; args.a.scales = a_scales; args.a.extra = mins ? a_extra : nullptr;
-    args.b.codes = b_codes; args.b.scales = b_scales; args.b.extra = mins ? b_extra : nullptr;
+    args.a.codes = ta.codes; args.a.scales = ta.scales; args.a.extra = mins ? ta.extra : nullptr;
+    args.b.codes = tb.codes; args.b.scales = tb.scales; args.b.extra = mins ? tb.extra : nullptr; args.b.rows_pad = tb.rows_pad;
     args.c = c; args.sums = sums; args.status = g_mm_status;
-    args.m = m; args.n = n; args.kb = kbs; args.probe = g_mm_probe;
-    const dim3 grid((n + TILE - 1) / TILE, (m + TILE - 1) / TILE);
-    if (sums) launch_product<true>(mins, half, grid, args, stream);
-    else launch_product<false>(mins, half, grid, args, stream);
+    args.cb = (uint8_t *)c_blocks; args.fmt_c = fmt_c;
+    args.m = m; args.n = n; args.kb = kbs;
+    args.probe = 0;
+    args.trace = nullptr;
+#ifdef QB_MM_TUNING
+    { const char *pr = getenv("QB200_MM_PROBE"); args.probe = pr && *pr ? atoi(pr) : 0; }
+    args.trace = g_mm_trace;
+#endif
+    args.unit = 32;          // columns a warp of the epilogue owns: pieces are whole units
+    args.units = (n + args.unit - 1) / args.unit;
+    args.mtiles = (m + TILE - 1) / TILE;
+    args.batch = batch.count;
+    args.a_stride = batch.stride_a ? a_slab : 0;
+    args.b_stride = !b_packed && batch.stride_b ? b_slab : 0;
+    args.c_stride = (size_t)batch.stride_c;
+    const long long total = (long long)args.batch * args.mtiles * args.units;
+    const int grid = (int)(total < g_mm_sms ? total : g_mm_sms);
+    const int var = mins ? VAR_MINS : half ? VAR_HALF : tcs ? VAR_TCS : VAR_PLAIN;
+    if (g_mm_kind) launch_kind<1>(sums != nullptr, var, grid, args, stream);
+    else launch_kind<0>(sums != nullptr, var, grid, args, stream);
     return (int)cudaGetLastError();
 }
 

@@ -28,10 +28,14 @@ class ProductView:
     TransA: bool = False
     TransB: bool = True
     Batch: int = 1
+    StrideA: int = 0
+    StrideB: int = 0
+    StrideC: int = 0
 
     @property
     def ValuesC(self):
-        return self.M * self.N
+        """src/Products.cs:30: the values C spans over all the batch's products."""
+        return self.M * self.N + (self.Batch - 1) * (self.StrideC if self.Batch > 1 else 0)
 
 
 def _ptr(x):
@@ -67,7 +71,8 @@ class Gpu:
         return self.lib.qb200_last_error().decode()
 
     def check(self, rc, what):
-        """Maps a return code as the C# shim maps it: < 0 not supported, > 0 a CUDA failure."""
+        """Maps a return code as a C# shim would: format / shape / limit errors are the reference's NotSupportedException,
+        other negative codes an argument error, positive codes a CUDA failure (its InvalidOperationException)."""
         if rc == 0:
             return
         if rc in (-1, -2, -6):
@@ -157,24 +162,82 @@ class GpuOps:
         fa = fmt_id(fmt)
         return int(self.lib.qb200_matmul_workspace_bytes(fa, fa if fmt_b is None else fmt_id(fmt_b), int(m), int(n), int(k)))
 
+    def MatMulBlocksBack(self, fmt, a, b, c_lanes, fmt_c, c_blocks, m, n, k, fmt_b=None, workspace=None, workspace_bytes=0, stream=None):
+        """MatMulBlocks and the `Back` of its result (src/MatMulBlocks.cs:418-421) in one call: f32 lanes and Q8_0 / Q4_0 blocks."""
+        fa = fmt_id(fmt)
+        fb = fa if fmt_b is None else fmt_id(fmt_b)
+        rc = self.lib.qb200_matmul_blocks_back(fa, fb, _ptr(a), _ptr(b), _ptr(c_lanes), fmt_id(fmt_c), _ptr(c_blocks), int(m), int(n), int(k),
+                                               _ptr(workspace), int(workspace_bytes), _stream(stream))
+        self.gpu.check(rc, "MatMulBlocksBack")
+        return self.lane_name(OP_MATMUL, fa)
+
+    def Prepack(self, fmt_b, b, n, k, stream=None):
+        """The weights re-laid once for the tensor cores: a device buffer that MatMulBlocksPrepacked takes in place of b."""
+        import torch
+        fb = fmt_id(fmt_b)
+        need = int(self.lib.qb200_matmul_prepacked_bytes(fb, int(n), int(k)))
+        if need == 0:
+            raise NotImplementedError("the block product takes k in whole blocks of B")
+        packed = torch.empty(need, dtype=torch.uint8, device=f"cuda:{self.gpu.device}")       # torch allocations are 256-byte aligned
+        self.gpu.check(self.lib.qb200_matmul_prepack(fb, _ptr(b), int(n), int(k), packed.data_ptr(), need, _stream(stream)), "Prepack")
+        return packed
+
+    def MatMulBlocksPrepacked(self, fmt, a, b_packed, c_lanes, m, n, k, fmt_b=None, workspace=None, workspace_bytes=0, stream=None):
+        fa = fmt_id(fmt)
+        fb = fa if fmt_b is None else fmt_id(fmt_b)
+        rc = self.lib.qb200_matmul_blocks_prepacked(fa, fb, _ptr(a), _ptr(b_packed), _ptr(c_lanes), int(m), int(n), int(k), _ptr(workspace),
+                                                    int(workspace_bytes), _stream(stream))
+        self.gpu.check(rc, "MatMulBlocksPrepacked")
+        return self.lane_name(OP_MATMUL, fa)
+
+    def MatMulBlocksBatched(self, fmt, a, b, c_lanes, m, n, k, batch, stride_a, stride_b, stride_c, fmt_b=None, stream=None):
+        """`batch` products in one launch; strides in values as ProductView gives them (0 broadcasts an operand)."""
+        fa = fmt_id(fmt)
+        fb = fa if fmt_b is None else fmt_id(fmt_b)
+        rc = self.lib.qb200_matmul_blocks_batched(fa, fb, _ptr(a), _ptr(b), _ptr(c_lanes), int(m), int(n), int(k), int(batch), int(stride_a),
+                                                  int(stride_b), int(stride_c), None, 0, _stream(stream))
+        self.gpu.check(rc, "MatMulBlocksBatched")
+        return self.lane_name(OP_MATMUL, fa)
+
     def BlockView(self, fmt, v):
-        """src/MatMulBlocks.cs:410-411."""
-        return (fmt_id(fmt) in (Q8_0, Q4_0) and v.Batch == 1 and not v.TransA and v.TransB and v.K % 32 == 0
-                and self.BlockProductAvailable)
+        """src/MatMulBlocks.cs:410-411, widened to batches whose operands start on whole blocks (the reference sends every
+        batch to its decoded route)."""
+        if not (fmt_id(fmt) in (Q8_0, Q4_0) and not v.TransA and v.TransB and v.K % 32 == 0 and self.BlockProductAvailable):
+            return False
+        if v.Batch == 1:
+            return True
+        return v.StrideA % 32 == 0 and v.StrideB % 32 == 0 and v.StrideC % 32 == 0 and v.StrideC >= v.M * v.N
 
     def MatMulViewBlocks(self, fmt, v, a, b, c, stream=None):
         """The block product for the view, C encoded to the type by blocks (src/MatMulBlocks.cs:414-424)."""
-        lanes = self._rent(v.M * v.N * 4)
-        lane = self.MatMulBlocks(fmt, a, b, lanes, v.M, v.N, v.K, stream=stream)
-        self.Back(fmt, lanes, c, v.M * v.N, stream=stream)
+        if v.Batch == 1:
+            lanes = self._rent(v.M * v.N * 4)
+            return self.MatMulBlocksBack(fmt, a, b, lanes, fmt, c, v.M, v.N, v.K, stream=stream)
+        lanes = self._rent(v.ValuesC * 4)
+        if v.StrideC > v.M * v.N:             # values between two products' results belong to no product: they encode as zeros
+            self.gpu.check(self.lib.qb200_memset(_ptr(lanes), 0, int(v.ValuesC * 4), _stream(stream)), "memset")
+        lane = self.MatMulBlocksBatched(fmt, a, b, lanes, v.M, v.N, v.K, v.Batch, v.StrideA, v.StrideB, v.StrideC, stream=stream)
+        self.Back(fmt, lanes, c, v.ValuesC, stream=stream)
         return lane
 
     def MatMulView(self, fmt, v, a, b, c, stream=None):
         """src/GpuOps.Products.cs:15-19: the block product where the view allows it.  The decoded route is not part of
         this library, so a view outside the block path, or `BlockProducts = False`, is not supported."""
-        if self.BlockView(fmt, v) and self.BlockProducts is not False:
+        if self.BlockView(fmt, v) and self.UseBlocks(fmt, v):
             return self.MatMulViewBlocks(fmt, v, a, b, c, stream=stream)
         raise NotImplementedError("only A.B^T of two Q8_0 / Q4_0 operands with k in whole blocks is built here")
+
+    def UseBlocks(self, fmt, v):
+        """src/MatMulBlocks.cs:428-442 chooses between the block product and the decoded route by timing both once a
+        shape; with one route built the choice is the gate's override alone: False refuses, True or None take the blocks."""
+        return self.BlockProducts is not False
+
+    def MatMulBackward(self, fmt, a, b, dc, da, db, m, n, k, stream=None):
+        """src/GpuOps.Products.cs:101-106: dA = dC.B^T is the view (m, k, n, TransB) and takes the block product when n is
+        whole blocks; dB = A^T.dC is a transposed-A view, which only the decoded route serves: pass db=None."""
+        if db is not None:
+            raise NotImplementedError("dB = A^T.dC is a view of the decoded route, which is not part of this library")
+        return self.MatMulView(fmt, ProductView(m, k, n, False, True), dc, b, da, stream=stream)
 
     # -- codecs --------------------------------------------------------------------------------
     def Back(self, fmt, lanes, stored, count, stream=None):

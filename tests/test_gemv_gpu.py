@@ -258,6 +258,39 @@ def test_order_against_a_launch_two_back(oracle, rounds):
         assert np.all(np.abs(got - ref) <= REL * mag)
 
 
+@pytest.mark.parametrize("rounds", [6])
+def test_order_against_the_predecessor_of_a_call_that_waited(oracle, rounds):
+    # A (few rows: its blocks leave most multiprocessors free) writes v; B reads v, so it waits for A; C also reads v but
+    # shares nothing with B.  C is scheduled as B's dependent: were B to release its dependents before its own wait for A
+    # has passed, C would read v while A is still writing it.  v is poisoned before every round, so an early C reads NaN.
+    import torch
+    k, rows_a = 8192, 256
+    wa = B.make_weights(B.Q4_0, rows_a, k, 41)
+    wb = B.make_weights(B.Q8_0, 2048, rows_a, 42)
+    wc = B.make_weights(B.Q4_0, 1024, rows_a, 43)
+    xa = B.make_activations(k, 44)
+    o = H.ops()
+    dwa, dwb, dwc, dxa = H.dev(wa), H.dev(wb), H.dev(wc), H.dev(xa)
+    v = H.empty(rows_a, torch.float32)
+    yb = H.empty(2048, torch.float32)
+    yc = H.empty(1024, torch.float32)
+    for _ in range(rounds):
+        v.fill_(float("nan"))
+        yb.fill_(float("nan"))
+        yc.fill_(float("nan"))
+        o.GemvBlocks(B.Q4_0, dwa, dxa, v, rows_a, k, fmt_x=B.F32)          # A
+        o.GemvBlocks(B.Q8_0, dwb, v, yb, 2048, rows_a, fmt_x=B.F32)        # B = f(v)
+        o.GemvBlocks(B.Q4_0, dwc, v, yc, 1024, rows_a, fmt_x=B.F32)        # C = g(v), outputs disjoint from B's
+        assert o.gpu.status() == 0
+        got_v = v.cpu().numpy()
+        assert np.isfinite(got_v).all()
+        for fmt, w, y, rows in ((B.Q8_0, wb, yb, 2048), (B.Q4_0, wc, yc, 1024)):
+            ref, mag = oracle.gemv_blocks(fmt, B.F32, w, got_v, rows, rows_a, order=1, want_abs=True)
+            got = y.cpu().numpy().astype(np.float64)
+            assert np.isfinite(got).all()
+            assert np.all(np.abs(got - ref) <= REL * mag)
+
+
 def test_long_run_of_independent_calls(oracle):
     # more independent calls in a row than the library remembers (64): the run is cut by a call that orders itself after
     # everything before it, and every output is still right; the same again after the library's own synchronize

@@ -90,11 +90,29 @@ def test_caller_workspace(oracle):
     assert np.array_equal(c.view(np.uint32), ref.view(np.uint32))
 
 
-def sampled_rows_check(oracle, fmt_a, fmt_b, m, n, k, seed, rows=12):
+def tile_rows(m, seed, extra=4):
+    """Rows of A to check at a full-size shape: the first and last row, one row of every 128-row tile, a few at random."""
+    rng = np.random.default_rng(seed)
+    per_tile = [t * 128 + int(rng.integers(0, min(128, m - t * 128))) for t in range((m + 127) // 128)]
+    return np.unique(np.concatenate([[0, m - 1], per_tile, rng.integers(0, m, extra)])).astype(np.int64)
+
+
+def sampled_rows_check(oracle, fmt_a, fmt_b, m, n, k, seed, prepacked=False):
     """Full-size shapes: C on the GPU; a sample of A's rows through the oracle (a row of C needs that row of A only)."""
+    import torch
     a, b = operands(oracle, fmt_a, fmt_b, m, n, k, seed)
-    c = matmul_gpu(fmt_a, fmt_b, a, b, m, n, k)
-    pick = np.unique(np.concatenate([[0, m - 1], np.random.default_rng(seed).integers(0, m, rows)]))
+    if prepacked:
+        o = H.ops()
+        da, db = H.dev(a), H.dev(b)
+        c_dev = H.empty(m * n, torch.float32)
+        c_dev.fill_(float("nan"))
+        packed = o.Prepack(fmt_b, db, n, k)
+        o.MatMulBlocksPrepacked(fmt_a, da, packed, c_dev, m, n, k, fmt_b=fmt_b)
+        assert o.gpu.status() == 0
+        c = c_dev.cpu().numpy().reshape(m, n)
+    else:
+        c = matmul_gpu(fmt_a, fmt_b, a, b, m, n, k)
+    pick = tile_rows(m, seed)
     rb = B.row_bytes(fmt_a, k)
     a_rows = a.reshape(m, rb)[pick].reshape(-1)
     ref = oracle.matmul_blocks(fmt_a, fmt_b, a_rows, b, len(pick), n, k, order=1)
@@ -111,9 +129,101 @@ def test_prefill_config_odd(oracle):
     sampled_rows_check(oracle, B.Q8_0, B.Q8_0, 509, 11003, 4096, 77)
 
 
-def test_q4_0_weights_q8_0_activations(oracle):
-    sampled_rows_check(oracle, B.Q8_0, B.Q4_0, 64, 28672 // 8, 8192, 78)
-    sampled_rows_check(oracle, B.Q8_0, B.Q4_0, 33, 1021, 8160, 79)
+@pytest.mark.parametrize("m", [1, 8, 64, 512, 2048])
+def test_sharded_config_q4_0_weights_q8_0_activations(oracle, m):
+    # BASELINE configs[4] on one GPU: Q8_0 activations against the whole 28672 x 8192 Q4_0 matrix, weights prepacked
+    sampled_rows_check(oracle, B.Q8_0, B.Q4_0, m, 28672, 8192, 700 + m, prepacked=True)
+
+
+def test_sharded_config_odd(oracle):
+    sampled_rows_check(oracle, B.Q8_0, B.Q4_0, 67, 28669, 8160, 79)
+    sampled_rows_check(oracle, B.Q8_0, B.Q4_0, 33, 1021, 8160, 80)
+
+
+def test_prepacked_weights_give_the_same_bits(oracle):
+    import torch
+    o = H.ops()
+    for fmt_b, (m, n, k) in [(B.Q8_0, (70, 300, 512)), (B.Q4_0, (129, 257, 1056)), (B.Q4_K, (37, 61, 512)), (B.Q6_K, (37, 61, 512))]:
+        a, b = operands(oracle, B.Q8_0, fmt_b, m, n, k, 21)
+        want = matmul_gpu(B.Q8_0, fmt_b, a, b, m, n, k) if fmt_b in (B.Q8_0, B.Q4_0) else matmul_gpu_k(B.Q8_0, fmt_b, a, b, m, n, k)
+        da, db = H.dev(a), H.dev(b)
+        packed = o.Prepack(fmt_b, db, n, k)
+        db.fill_(0)                                          # the packed form is all the product reads
+        for _ in range(2):                                   # the packed weights serve call after call
+            c = H.empty(m * n, torch.float32)
+            c.fill_(float("nan"))
+            o.MatMulBlocksPrepacked(B.Q8_0, da, packed, c, m, n, k, fmt_b=fmt_b)
+            assert o.gpu.status() == 0
+            assert np.array_equal(c.cpu().numpy().reshape(m, n).view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("fmt", [B.Q8_0, B.Q4_0])
+@pytest.mark.parametrize("m,n,k", [(37, 64, 320), (130, 352, 96), (37, 29, 64), (512, 1024, 256)])
+def test_back_in_the_product_launch(oracle, fmt, m, n, k):
+    # MatMulViewBlocks: lanes, then Back (src/MatMulBlocks.cs:414-424); blocks byte for byte the encoder's on the same lanes
+    import torch
+    o = H.ops()
+    a, b = operands(oracle, fmt, fmt, m, n, k, 55)
+    da, db = H.dev(a), H.dev(b)
+    lanes = H.empty(m * n, torch.float32)
+    lanes.fill_(float("nan"))
+    blocks = H.empty(B.nbytes(fmt, m * n), torch.uint8)
+    blocks.fill_(0xEE)
+    o.MatMulBlocksBack(fmt, da, db, lanes, fmt, blocks, m, n, k)
+    assert o.gpu.status() == 0
+    ref = oracle.matmul_blocks(fmt, fmt, a, b, m, n, k, order=1)
+    assert np.array_equal(lanes.cpu().numpy().reshape(m, n).view(np.uint32), ref.view(np.uint32))
+    assert np.array_equal(blocks.cpu().numpy(), oracle.encode(fmt, ref.reshape(-1), device_rounding=True))
+
+
+def test_batched_products(oracle):
+    # ProductView with Batch > 1 (src/Products.cs:15-22): strides in values, 0 broadcasts an operand
+    import torch
+    from qiyas_b200.ops import ProductView
+    o = H.ops()
+    m, n, k, batch = 45, 70, 160, 3
+    sa, sb, sc = m * k + 64, n * k + 96, (m * n + 31) // 32 * 32 + 32     # gaps between the batch's operands and results, whole blocks
+    rng = np.random.default_rng(8)
+    a = oracle.encode(B.Q8_0, rng.uniform(-1, 1, sa * batch).astype(np.float32), device_rounding=True)
+    b = oracle.encode(B.Q8_0, rng.uniform(-1, 1, sb * batch).astype(np.float32), device_rounding=True)
+    da, db = H.dev(a), H.dev(b)
+    for stride_a, stride_b in [(sa, sb), (0, sb), (sa, 0)]:
+        c = H.empty(sc * batch, torch.float32)
+        c.fill_(float("nan"))
+        o.MatMulBlocksBatched(B.Q8_0, da, db, c, m, n, k, batch, stride_a, stride_b, sc)
+        assert o.gpu.status() == 0
+        got = c.cpu().numpy()
+        for i in range(batch):
+            ai = a[stride_a * i // 32 * 34:][:m * k // 32 * 34]
+            bi = b[stride_b * i // 32 * 34:][:n * k // 32 * 34]
+            ref = oracle.matmul_blocks(B.Q8_0, B.Q8_0, ai, bi, m, n, k, order=1)
+            assert np.array_equal(got[i * sc:i * sc + m * n].view(np.uint32), ref.reshape(-1).view(np.uint32)), (stride_a, stride_b, i)
+    # through the view: C encoded to blocks over the whole batch
+    v = ProductView(m, n, k, False, True, batch, sa, sb, sc)
+    assert o.BlockView("q8_0", v)
+    out = H.empty(B.nbytes(B.Q8_0, v.ValuesC), torch.uint8)
+    assert o.MatMulView("q8_0", v, da, db, out) == "s8 tcgen05 blocks"
+    full = np.zeros(v.ValuesC, np.float32)
+    for i in range(batch):
+        ref = oracle.matmul_blocks(B.Q8_0, B.Q8_0, a[sa * i // 32 * 34:][:m * k // 32 * 34], b[sb * i // 32 * 34:][:n * k // 32 * 34], m, n, k, order=1)
+        full[i * sc:i * sc + m * n] = ref.reshape(-1)
+    assert np.array_equal(out.cpu().numpy(), oracle.encode(B.Q8_0, full, device_rounding=True))
+
+
+def test_backward_da_takes_the_block_product(oracle):
+    # MatMulBackward (src/GpuOps.Products.cs:101-106): dA = dC.B^T is the view (m, k, n, TransB) on dC (m x n) and B (k x n)
+    import torch
+    o = H.ops()
+    m, n, k = 33, 96, 50                       # C = A.B with A m x k, B k x n: the product for dA contracts over n
+    rng = np.random.default_rng(12)
+    dc = oracle.encode(B.Q8_0, rng.uniform(-1, 1, m * n).astype(np.float32), device_rounding=True)
+    b = oracle.encode(B.Q8_0, rng.uniform(-1, 1, k * n).astype(np.float32), device_rounding=True)
+    da = H.empty(B.nbytes(B.Q8_0, m * k), torch.uint8)
+    assert o.MatMulBackward("q8_0", None, H.dev(b), H.dev(dc), da, None, m, n, k) == "s8 tcgen05 blocks"
+    lanes = oracle.matmul_blocks(B.Q8_0, B.Q8_0, dc, b, m, k, n, order=1).reshape(-1)
+    assert np.array_equal(da.cpu().numpy(), oracle.encode(B.Q8_0, lanes, device_rounding=True))
+    with pytest.raises(NotImplementedError):
+        o.MatMulBackward("q8_0", None, H.dev(b), H.dev(dc), da, da, m, n, k)
 
 
 def test_view_surface(oracle):
@@ -130,6 +240,10 @@ def test_view_surface(oracle):
     assert np.array_equal(out.cpu().numpy(), oracle.encode(B.Q8_0, lanes, device_rounding=True))
     with pytest.raises(NotImplementedError):
         o.MatMulView("q8_0", ProductView(m, n, k, True, True), H.dev(a), H.dev(b), out)
+    o.BlockProducts = False                  # the gate's override: never the block product
+    with pytest.raises(NotImplementedError):
+        o.MatMulView("q8_0", v, H.dev(a), H.dev(b), out)
+    o.BlockProducts = None
     with pytest.raises(NotImplementedError):
         o.MatMulBlocks("q8_0", H.dev(a), H.dev(b), out, m, n, 33)
     with pytest.raises(NotImplementedError):
