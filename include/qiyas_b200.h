@@ -86,7 +86,8 @@ int qb200_block_product_available(void);
 const char *qb200_lane_name(int op, int fmt_a);
 
 /* Reads and clears the device-side status word.  0 = every kernel so far ran to the end;
- * non-zero = a bounded wait inside a kernel gave up (bit 0: gemv ring, bit 1: A.B^T pipeline).
+ * non-zero = a bounded wait inside a kernel gave up (bit 0: gemv ring, bit 1: A.B^T pipeline,
+ * bit 2: a sharded product's wait for its peers).
  * Synchronizes the device. */
 int qb200_device_status(int *status);
 
@@ -204,6 +205,41 @@ int qb200_matmul_block_sums(int fmt_a, int fmt_b, const void *a, const void *b, 
  * array as f32, bit-for-bit Blocks.Decode* (src/Blocks.cs:31-35,48-56,79-96,151-173). */
 int qb200_encode(int fmt, const float *lanes, void *blocks, int64_t n, void *stream);
 int qb200_decode(int fmt, const void *blocks, float *lanes, int64_t n, void *stream);
+
+/* ---- N-row sharding across the GPUs of one box -------------------------------------------
+ * No counterpart in the reference, which runs on device ordinal 0 alone (src/Gpu.cs:94-96).  The output rows of a
+ * product are independent, so rank r of `world` keeps rows [first, first + count) of the weights (qb200_shard_range:
+ * ceil(rows / world) rows a rank, the last ranks fewer or none) and computes that slice of y with the single-GPU
+ * kernels; x is replicated.  Where every rank needs the whole y, the slices are exchanged by the gemv kernel itself:
+ * its blocks store the rows they computed into every other rank's copy of y through peer-mapped pointers (plain
+ * stores over NVLink: no copy engine, no collective launch), and the grid's last block then stores `epoch` into this
+ * rank's word of every rank's flag array.  qb200_shard_wait puts a small kernel in the stream that waits, for at most
+ * `limit_cycles` clock cycles (<= 0: about a second), until every rank's word of the local flag array has reached
+ * `epoch`; work queued after it on that stream sees the whole y.  A wait that runs out sets bit 2 of the status word
+ * (qb200_device_status) and returns: nothing hangs when a peer is late or gone.
+ *
+ * One process drives one GPU (qb200_init(device) in each); the ranks map one another's buffers with the CUDA IPC
+ * helpers below (or, in one process, with peer access).  peers->out[w] is rank w's y (rows_total f32, 16-byte aligned),
+ * peers->flags[w] its flag array (QB200_SHARD_MAX words, zeroed once before the first call), both as THIS process
+ * addresses them.  Successive calls pass increasing epochs (1, 2, ...).  A rank must not overwrite its x or start the
+ * next qb200_shard_gemv into the same buffers before its own qb200_shard_wait for the previous epoch is in its stream:
+ * that wait is also what tells it the peers have finished writing into its y.  All of a rank's sharded calls go to one
+ * stream.  An NCCL all-gather of the slices gives the same y and remains the choice across boxes. */
+#define QB200_SHARD_MAX 8
+typedef struct qb200_shard_peers {
+    int world, rank;
+    float *out[QB200_SHARD_MAX];
+    unsigned int *flags[QB200_SHARD_MAX];
+} qb200_shard_peers_t;
+int qb200_shard_range(int rows, int world, int rank, int *first, int *count);
+int qb200_shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const qb200_shard_peers_t *peers,
+                     unsigned int epoch, void *stream);
+int qb200_shard_wait(const qb200_shard_peers_t *peers, unsigned int epoch, long long limit_cycles, void *stream);
+/* A device allocation of this process (qb200_malloc) as a 64-byte handle another process on the same box can open
+ * (cudaIpcGetMemHandle / cudaIpcOpenMemHandle / cudaIpcCloseMemHandle); opening enables peer access to the owner's GPU. */
+int qb200_ipc_export(const void *ptr, void *handle64);
+int qb200_ipc_import(const void *handle64, void **ptr);
+int qb200_ipc_close(void *ptr);
 
 /* ---- plain device memory for hosts without a CUDA binding of their own (tests, bench) ---- */
 int qb200_malloc(void **ptr, size_t bytes);

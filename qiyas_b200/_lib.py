@@ -10,6 +10,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIBRARY = os.path.join(HERE, "libqiyas_b200.so")
 
 
+SHARD_MAX = 8
+
+
+class ShardPeers(C.Structure):
+    """qb200_shard_peers_t: every rank's output vector and flag array as this process addresses them."""
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("out", C.c_void_p * SHARD_MAX), ("flags", C.c_void_p * SHARD_MAX)]
+
+
 class Caps(C.Structure):
     _fields_ = [("device", C.c_int), ("sm_major", C.c_int), ("sm_minor", C.c_int), ("sm_count", C.c_int),
                 ("tcgen05", C.c_int), ("max_shared_bytes", C.c_int), ("l2_bytes", C.c_int64), ("global_bytes", C.c_int64)]
@@ -40,6 +48,12 @@ SIGNATURES = {
     "qb200_matmul_batched_workspace_bytes": (_Z, [_I, _I, _I, _I, _I, _I, _L, _L]),
     "qb200_matmul_blocks_batched": (_I, [_I, _I, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _Z, _P]),
     "qb200_matmul_block_sums": (_I, [_I, _I, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "qb200_shard_range": (_I, [_I, _I, _I, C.POINTER(_I), C.POINTER(_I)]),
+    "qb200_shard_gemv": (_I, [_I, _I, _P, _P, _I, _I, C.POINTER(ShardPeers), C.c_uint, _P]),
+    "qb200_shard_wait": (_I, [C.POINTER(ShardPeers), C.c_uint, C.c_longlong, _P]),
+    "qb200_ipc_export": (_I, [_P, _P]),
+    "qb200_ipc_import": (_I, [_P, C.POINTER(_P)]),
+    "qb200_ipc_close": (_I, [_P]),
     "qb200_encode": (_I, [_I, _P, _P, _L, _P]),
     "qb200_decode": (_I, [_I, _P, _P, _L, _P]),
     "qb200_malloc": (_I, [C.POINTER(_P), _Z]),

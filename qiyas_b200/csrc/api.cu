@@ -150,6 +150,7 @@ int qb200_init(int device)
     g_bound = device;
     if ((e = qb::gemv_init(g_caps.sm_count, g_caps.max_shared_bytes, g_status))) return cuda_fail(e, "gemv attributes");
     if ((e = qb::matmul_init(g_caps.sm_count, g_caps.max_shared_bytes, g_status))) return cuda_fail(e, "matmul attributes");
+    if ((e = qb::shard_init(g_status))) return cuda_fail(e, "shard set-up");
     g_ready = true;
     t_error[0] = 0;
     return 0;
@@ -405,6 +406,71 @@ int qb200_decode(int fmt, const void *blocks, float *lanes, int64_t n, void *str
     if (n < 0 || n > 2147483647LL) return fail(QB200_E_SHAPE, "count %lld", (long long)n);
     if (n && (!lanes || !blocks || ((uintptr_t)lanes & 3))) return fail(QB200_E_POINTER, "null or misaligned operand");
     return finish(qb::decode_launch(fmt, blocks, lanes, n, (cudaStream_t)stream), "decode");
+}
+
+int qb200_shard_range(int rows, int world, int rank, int *first, int *count)
+{
+    if (rows < 0 || world < 1 || rank < 0 || rank >= world) return fail(QB200_E_SHAPE, "rank %d of %d over %d rows", rank, world, rows);
+    const int per = (rows + world - 1) / world;
+    const int lo = (long long)rank * per < rows ? rank * per : rows, hi = lo + per < rows ? lo + per : rows;
+    if (first) *first = lo;
+    if (count) *count = hi - lo;
+    return 0;
+}
+
+static int check_peers(const qb200_shard_peers_t *peers)
+{
+    if (!g_ready) return fail(QB200_E_DEVICE, "qb200_init has not succeeded");
+    if (!peers) return fail(QB200_E_POINTER, "null peers");
+    if (peers->world < 1 || peers->world > QB200_SHARD_MAX || peers->rank < 0 || peers->rank >= peers->world)
+        return fail(QB200_E_SHAPE, "rank %d of %d (at most %d ranks)", peers->rank, peers->world, QB200_SHARD_MAX);
+    for (int w = 0; w < peers->world; w++) {
+        if (!peers->out[w] || !peers->flags[w]) return fail(QB200_E_POINTER, "rank %d's output or flags are not mapped", w);
+        if (((uintptr_t)peers->out[w] & 15) || ((uintptr_t)peers->flags[w] & 3)) return fail(QB200_E_POINTER, "rank %d's output or flags are misaligned", w);
+    }
+    return 0;
+}
+
+int qb200_shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const qb200_shard_peers_t *peers,
+                     unsigned int epoch, void *stream)
+{
+    int rc = check_peers(peers);
+    if (rc) return rc;
+    int first = 0, count = 0;
+    if ((rc = qb200_shard_range(rows_total, peers->world, peers->rank, &first, &count))) return rc;
+    // the slice as an ordinary gemv: formats, whole blocks, limits, alignment (a rank without rows has nothing to check but x)
+    if ((rc = check_gemv(fmt_a, fmt_x, count ? a_shard : x, x, peers->out[peers->rank] + first, count, cols))) return rc;
+    return finish(qb::shard_gemv(fmt_a, fmt_x, a_shard, x, rows_total, cols, peers, epoch, (cudaStream_t)stream), "shard_gemv");
+}
+
+int qb200_shard_wait(const qb200_shard_peers_t *peers, unsigned int epoch, long long limit_cycles, void *stream)
+{
+    int rc = check_peers(peers);
+    if (rc) return rc;
+    return finish(qb::shard_wait(peers, epoch, limit_cycles, (cudaStream_t)stream), "shard_wait");
+}
+
+int qb200_ipc_export(const void *ptr, void *handle64)
+{
+    if (!ptr || !handle64) return fail(QB200_E_POINTER, "null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is 64 bytes");
+    cudaError_t e = cudaIpcGetMemHandle((cudaIpcMemHandle_t *)handle64, (void *)ptr);
+    return e ? cuda_fail(e, "cudaIpcGetMemHandle") : 0;
+}
+
+int qb200_ipc_import(const void *handle64, void **ptr)
+{
+    if (!ptr || !handle64) return fail(QB200_E_POINTER, "null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof h);
+    cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    return e ? cuda_fail(e, "cudaIpcOpenMemHandle") : 0;
+}
+
+int qb200_ipc_close(void *ptr)
+{
+    cudaError_t e = cudaIpcCloseMemHandle(ptr);
+    return e ? cuda_fail(e, "cudaIpcCloseMemHandle") : 0;
 }
 
 int qb200_malloc(void **ptr, size_t bytes)

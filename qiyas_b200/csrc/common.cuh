@@ -18,6 +18,7 @@ __host__ __device__ constexpr int block_bytes(int fmt) { return fmt == QB200_Q8_
 // (read by qb200_device_status).
 constexpr int STATUS_GEMV_WAIT = 1;
 constexpr int STATUS_MATMUL_WAIT = 2;
+constexpr int STATUS_SHARD_WAIT = 4;
 
 // A wait gives up after this many clock cycles (about a second at 2 GHz).
 constexpr long long WAIT_CYCLES = 2000000000LL;

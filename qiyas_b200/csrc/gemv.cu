@@ -41,6 +41,7 @@ struct GemvArgs {
     int fmt_y;
     int chunk_align;     // block boundaries fall on multiples of this many chunks (32 rows when yb is set, else 1 chunk)
     int32_t *sums;
+    GemvPublish publish;          // where the rows this launch wrote go besides y (the sharded gemv's exchange); world 0: nowhere
     int *status;         // device word for STATUS_* bits
     int rows, cols;
     uint32_t row_bytes;
@@ -753,8 +754,11 @@ __device__ __forceinline__ void back_rows(const float *y, uint8_t *yb, int fmt_y
 // chunks dealt in one round are a unit.  RUNS = runs of x a warp holds (its column segment: runs seg, seg + cs, ...).
 // NW = the most consumer warps a block of this variant has: 16 (one block an SM) or 4 (four blocks an SM, normally of
 // four successive launches: while one block prepares x or drains, the others keep the memory system busy).
-// BACK = the block also encodes the rows it wrote (a variant of its own, so that the plain gemv carries none of it).
-template <int FMT, int RW, int RUNS, bool SUMS, int NW, bool BACK = false>
+// TAIL = what a block does with the rows it wrote once they are in y (variants of their own, so that the plain gemv
+// carries none of it): TAIL_BACK encodes them as blocks (the reference's `Back`); TAIL_PUBLISH stores them into the
+// other GPUs' copies of the output vector and, from the grid's last block, raises this rank's flag on every GPU.
+enum { TAIL_NONE = 0, TAIL_BACK = 1, TAIL_PUBLISH = 2 };
+template <int FMT, int RW, int RUNS, bool SUMS, int NW, int TAIL = TAIL_NONE>
 __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const GemvArgs p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -775,9 +779,9 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
     __syncthreads();
 
     uint8_t *ring = smem + p.off_ring;
-    // block b takes the chunks [C*b/grid, C*(b+1)/grid); with BACK, whole groups of chunk_align chunks (32 rows)
+    // block b takes the chunks [C*b/grid, C*(b+1)/grid); with TAIL_BACK, whole groups of chunk_align chunks (32 rows)
     int chunk0, chunk1;
-    if constexpr (!BACK) {
+    if constexpr (TAIL != TAIL_BACK) {
         chunk0 = (int)((long long)p.chunks * blockIdx.x / gridDim.x);
         chunk1 = (int)((long long)p.chunks * (blockIdx.x + 1) / gridDim.x);
     } else {
@@ -986,9 +990,40 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
             if (i + 1 < my_units) named_bar_sync(1, threads);
         }
     }
-    if constexpr (BACK) {
+    if constexpr (TAIL == TAIL_BACK) {
         named_bar_sync(1, threads);
         if (!*abort_flag) back_rows(p.y, p.yb, p.fmt_y, p.rows, chunk0 * RW, min(p.rows, chunk1 * RW), threadIdx.x, threads);
+    }
+    if constexpr (TAIL == TAIL_PUBLISH) {
+        // The block's rows are in y (this GPU's copy of the output vector): plain stores carry them into every other
+        // GPU's copy, a fence orders them before the block's count, and the block that counts last raises the flags.
+        // A block that gave up on a wait publishes nothing and does not count: the flags then never show this epoch
+        // and the readers' bounded waits report it.
+        named_bar_sync(1, threads);
+        if (!*abort_flag) {
+            const GemvPublish *pub = &p.publish;
+            const int r0 = chunk0 * RW, r1 = min(p.rows, chunk1 * RW), world = pub->world;
+            for (int idx = r0 + (int)threadIdx.x; idx < r1; idx += threads) {
+                const float v = __ldcg(p.y + idx);
+                for (int w = 0; w < world; w++) {
+                    float *dst = pub->out[w];
+                    if (dst) dst[idx] = v;
+                }
+            }
+            __threadfence_system();
+            named_bar_sync(1, threads);
+            if (threadIdx.x == 0) {
+                const unsigned int before = atomicAdd(pub->counter, 1u);
+                if (before == gridDim.x - 1) {
+                    *pub->counter = 0u;
+                    __threadfence_system();
+                    for (int w = 0; w < world; w++) {
+                        unsigned int *f = pub->flag[w];
+                        if (f) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(pub->epoch) : "memory");
+                    }
+                }
+            }
+        }
     }
 }
 
@@ -1096,14 +1131,14 @@ static int plan_blocks(int fmt_a, int rows, int cols, int nwmax, int rw_first, b
 static int plan_gemv(int fmt_a, int rows, int cols, bool sums, bool overlapped, bool back, GemvPlan &pl)
 {
     const int rw_first = sums ? 1 : 4;
-    if (!sums && !back && overlapped) {
+    if (!sums && !back && overlapped) {      // (a publishing call is never `overlapped`)
         for (int rw = rw_first; rw >= 1; rw /= 2)
             if (plan_blocks(fmt_a, rows, cols, 4, rw, back, pl) == 0 && pl.deep) return 0;
     }
     return plan_blocks(fmt_a, rows, cols, 16, rw_first, back, pl);
 }
 
-template <int FMT, int RW, int RUNS, bool SUMS, int NW, bool BACK>
+template <int FMT, int RW, int RUNS, bool SUMS, int NW, int TAIL>
 static cudaError_t launch_one(const GemvPlan &pl, cudaStream_t stream)
 {
     cudaLaunchConfig_t cfg;
@@ -1117,45 +1152,46 @@ static cudaError_t launch_one(const GemvPlan &pl, cudaStream_t stream)
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = pl.serial ? 0 : 1;
-    return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, RW, RUNS, SUMS, NW, BACK>, pl.args);
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, RW, RUNS, SUMS, NW, TAIL>, pl.args);
 }
 
-template <int FMT, int RW, bool SUMS, int NW, bool BACK>
+template <int FMT, int RW, bool SUMS, int NW, int TAIL>
 static cudaError_t launch_runs(const GemvPlan &pl, cudaStream_t stream)
 {
-    if (pl.runs_per_warp == 1) return launch_one<FMT, RW, 1, SUMS, NW, BACK>(pl, stream);
-    if (pl.runs_per_warp == 2 || FMT != QB200_Q6_K) return launch_one<FMT, RW, 2, SUMS, NW, BACK>(pl, stream);
-    if (pl.runs_per_warp == 3) return launch_one<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS, NW, BACK>(pl, stream);
-    return launch_one<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS, NW, BACK>(pl, stream);
+    if (pl.runs_per_warp == 1) return launch_one<FMT, RW, 1, SUMS, NW, TAIL>(pl, stream);
+    if (pl.runs_per_warp == 2 || FMT != QB200_Q6_K) return launch_one<FMT, RW, 2, SUMS, NW, TAIL>(pl, stream);
+    if (pl.runs_per_warp == 3) return launch_one<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS, NW, TAIL>(pl, stream);
+    return launch_one<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS, NW, TAIL>(pl, stream);
 }
 
-template <int FMT, int NW, bool BACK>
+template <int FMT, int NW, int TAIL>
 static cudaError_t launch_rows(const GemvPlan &pl, cudaStream_t stream)
 {
     switch (pl.rw) {
-    case 4: return launch_runs<FMT, 4, false, NW, BACK>(pl, stream);
-    case 2: return launch_runs<FMT, 2, false, NW, BACK>(pl, stream);
-    default: return launch_runs<FMT, 1, false, NW, BACK>(pl, stream);
+    case 4: return launch_runs<FMT, 4, false, NW, TAIL>(pl, stream);
+    case 2: return launch_runs<FMT, 2, false, NW, TAIL>(pl, stream);
+    default: return launch_runs<FMT, 1, false, NW, TAIL>(pl, stream);
     }
 }
 
 template <int FMT>
 static cudaError_t launch_fmt(const GemvPlan &pl, bool sums, cudaStream_t stream)
 {
-    if (sums) return launch_runs<FMT, 1, true, 16, false>(pl, stream);      // the checking variant: a row at a time
-    if (pl.args.yb) return launch_rows<FMT, 16, true>(pl, stream);          // with `Back`: always whole-SM blocks
-    return pl.nwmax == 4 ? launch_rows<FMT, 4, false>(pl, stream) : launch_rows<FMT, 16, false>(pl, stream);
+    if (sums) return launch_runs<FMT, 1, true, 16, TAIL_NONE>(pl, stream);      // the checking variant: a row at a time
+    if (pl.args.yb) return launch_rows<FMT, 16, TAIL_BACK>(pl, stream);         // with `Back`: always whole-SM blocks
+    if (pl.args.publish.world > 0) return launch_rows<FMT, 16, TAIL_PUBLISH>(pl, stream); // with the exchange: whole-SM blocks too
+    return pl.nwmax == 4 ? launch_rows<FMT, 4, TAIL_NONE>(pl, stream) : launch_rows<FMT, 16, TAIL_NONE>(pl, stream);
 }
 
-template <int FMT, int RW, bool SUMS, int NW, bool BACK>
+template <int FMT, int RW, bool SUMS, int NW, int TAIL>
 static cudaError_t set_attr_runs(int bytes)
 {
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 1, SUMS, NW, BACK>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
-    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 2, SUMS, NW, BACK>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 1, SUMS, NW, TAIL>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, 2, SUMS, NW, TAIL>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
     if (FMT == QB200_Q6_K) {
-        if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS, NW, BACK>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
-        e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS, NW, BACK>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if ((e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 3 : 2, SUMS, NW, TAIL>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))) return e;
+        e = cudaFuncSetAttribute(gemv_kernel<FMT, RW, FMT == QB200_Q6_K ? 4 : 2, SUMS, NW, TAIL>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     }
     return e;
 }
@@ -1165,16 +1201,19 @@ static cudaError_t set_attr(int bytes)
 {
     cudaError_t e;
     const int small = (bytes + 1024) / 4 - 2048;                 // what a block of the four-an-SM variant may ask for
-    if ((e = set_attr_runs<FMT, 1, true, 16, false>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 1, false, 16, false>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 2, false, 16, false>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 4, false, 16, false>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 1, false, 16, true>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 2, false, 16, true>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 4, false, 16, true>(bytes))) return e;
-    if ((e = set_attr_runs<FMT, 1, false, 4, false>(small))) return e;
-    if ((e = set_attr_runs<FMT, 2, false, 4, false>(small))) return e;
-    return set_attr_runs<FMT, 4, false, 4, false>(small);
+    if ((e = set_attr_runs<FMT, 1, true, 16, TAIL_NONE>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 1, false, 16, TAIL_NONE>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 2, false, 16, TAIL_NONE>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 4, false, 16, TAIL_NONE>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 1, false, 16, TAIL_BACK>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 2, false, 16, TAIL_BACK>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 4, false, 16, TAIL_BACK>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 1, false, 16, TAIL_PUBLISH>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 2, false, 16, TAIL_PUBLISH>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 4, false, 16, TAIL_PUBLISH>(bytes))) return e;
+    if ((e = set_attr_runs<FMT, 1, false, 4, TAIL_NONE>(small))) return e;
+    if ((e = set_attr_runs<FMT, 2, false, 4, TAIL_NONE>(small))) return e;
+    return set_attr_runs<FMT, 4, false, 4, TAIL_NONE>(small);
 }
 
 cudaError_t gemv_init(int sm_count, int max_smem, int *status)
@@ -1235,7 +1274,7 @@ static bool conflicts(const Launched &now, const Launched &old)
 }
 
 int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int fmt_y, void *y_blocks, int rows,
-                int cols, cudaStream_t stream)
+                int cols, cudaStream_t stream, const void *publish)
 {
     if (rows == 0) return 0;
     const size_t row_bytes = (size_t)(cols / block_values(fmt_a)) * block_bytes(fmt_a);
@@ -1245,7 +1284,8 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     now.y = { (const uint8_t *)y, (size_t)rows * 4 };
     now.yb = { (const uint8_t *)y_blocks, y_blocks ? (size_t)((rows + 31) / 32) * block_bytes(fmt_y) : 0 };
     const bool known = t_hist.count > 0 && t_hist.stream == stream;
-    bool conflict = !known || sums || t_hist.count == HISTORY;
+    // a publishing launch writes memory this record does not describe (the other GPUs' copies): it waits, and so does its successor
+    bool conflict = !known || sums || publish || t_hist.count == HISTORY;
     bool weights_written = false;           // the producer reads A before any wait: nothing in flight may write it
     if (known) {
         for (int i = 0; i < t_hist.count; i++) {
@@ -1259,7 +1299,8 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     const bool in_a_burst = known && !t_hist.settled;
     // full order by the launch itself: nothing known, or more than the direct predecessor may still be running
     const bool serial = conflict && (!known || weights_written || !(t_hist.count == 1 || t_hist.settled));
-    if (independent) {
+    if (publish) t_hist.count = 0;          // nothing is known about what runs beside the next call
+    else if (independent) {
         t_hist.at[t_hist.count++] = now;
         t_hist.settled = false;
     } else {
@@ -1274,8 +1315,8 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     if (t_plans_epoch != g_epoch) { cached = next = 0; t_plans_epoch = g_epoch; }
     GemvPlan pl;
     bool hit = false;
-    const bool overlapped = (independent || in_a_burst) && !sums;
-    const int kind = (sums ? 2 : overlapped ? 1 : 0) | (y_blocks ? 4 : 0);
+    const bool overlapped = (independent || in_a_burst) && !sums && !publish;
+    const int kind = (sums ? 2 : overlapped ? 1 : 0) | (y_blocks ? 4 : 0) | (publish ? 8 : 0);
     for (int i = 0; i < cached && !hit; i++)
         if (cache[i].fmt == fmt_a && cache[i].rows == rows && cache[i].cols == cols && cache[i].kind == kind) { pl = cache[i].plan; hit = true; }
     if (!hit) {
@@ -1295,6 +1336,8 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     pl.args.yb = (uint8_t *)y_blocks;
     pl.args.fmt_y = fmt_y;
     pl.args.sums = sums;
+    if (publish) pl.args.publish = *(const GemvPublish *)publish;
+    else memset(&pl.args.publish, 0, sizeof pl.args.publish);
     pl.args.status = g_status;
     pl.args.rows = rows;
     pl.args.cols = cols;
@@ -1379,6 +1422,7 @@ int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, floa
     pl.args.yb = nullptr;
     pl.args.fmt_y = 0;
     pl.args.sums = nullptr;
+    memset(&pl.args.publish, 0, sizeof pl.args.publish);
     pl.args.status = dev->status;
     pl.args.rows = rows;
     pl.args.cols = cols;

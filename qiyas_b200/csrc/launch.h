@@ -8,16 +8,37 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include "../../include/qiyas_b200.h"
+
 namespace qb {
+
+// The sharded gemv's output exchange (world = 0: none).  A rank's y is a slice of the whole output vector; `out[w]` is
+// where that slice starts in rank w's copy of the whole vector, as this GPU addresses it (peer-mapped memory; null for
+// this rank itself, whose copy y already is), `flag[w]` the word of rank w's flag array that belongs to this rank.  When
+// the last block of the grid has published its rows, `epoch` is stored to every flag.
+struct GemvPublish {
+    float *out[QB200_SHARD_MAX];
+    unsigned int *flag[QB200_SHARD_MAX];
+    unsigned int *counter;        // blocks of this grid that have published (device-local, returns to zero)
+    int world;
+    unsigned int epoch;
+};
 
 cudaError_t gemv_init(int sm_count, int max_smem, int *status);
 // y_blocks (optional) = y again as fmt_y blocks (Q8_0 / Q4_0), encoded in the same launch
+// publish (optional) = a GemvPublish (host memory, copied into the launch): the launch also stores y into the other GPUs' copies of it
 int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int32_t *sums, int fmt_y, void *y_blocks, int rows,
-                int cols, cudaStream_t stream);
+                int cols, cudaStream_t stream, const void *publish = nullptr);
 // forgets what earlier launches touched: the next call orders itself after everything in its stream
 void gemv_forget_history();
 int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, cudaStream_t stream);
 int gemv_noalloc_status(int *value);
+
+// The sharded gemv (shard.cu): rows [first, first + count) of a rows_total-row product on this rank, published to the peers.
+cudaError_t shard_init(int *status);
+int shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const void *peers, unsigned int epoch,
+               cudaStream_t stream);
+int shard_wait(const void *peers, unsigned int epoch, long long limit_cycles, cudaStream_t stream);
 
 int encode_launch(int fmt, const float *lanes, void *blocks, int64_t n, cudaStream_t stream);
 int decode_launch(int fmt, const void *blocks, float *lanes, int64_t n, cudaStream_t stream);

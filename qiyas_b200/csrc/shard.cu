@@ -1,0 +1,83 @@
+// N-row sharding of a product across the GPUs of one box: the shard plan, the sharded gemv with its fused output
+// exchange (the gemv kernel's publishing variant, gemv.cu), the bounded wait for the peers' flags, and the CUDA IPC
+// helpers the one-process-per-GPU model needs.  The reference is single-device (src/Gpu.cs:94-96): nothing here
+// replaces reference code; it is the parallel strategy the path's multi-GPU configuration asks for.
+#include "common.cuh"
+#include "launch.h"
+
+namespace qb {
+
+// blocks of a publishing grid that have finished (one publishing launch a device is in flight at a time)
+static __device__ unsigned int g_publish_counter;
+static unsigned int *g_publish_counter_ptr = nullptr;
+static int *g_shard_status = nullptr;
+
+cudaError_t shard_init(int *status)
+{
+    g_shard_status = status;
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_publish_counter);
+    if (e) return e;
+    g_publish_counter_ptr = (unsigned int *)ptr;
+    return cudaMemset(ptr, 0, sizeof(unsigned int));
+}
+
+// A rank without rows still owes its peers its flag.
+__global__ void shard_flag_kernel(GemvPublish pub)
+{
+    if (threadIdx.x < pub.world) {
+        unsigned int *f = pub.flag[threadIdx.x];
+        if (f) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(pub.epoch) : "memory");
+    }
+}
+
+// Thread w waits until word w of this rank's flag array has reached `epoch` (the words only grow), for at most `limit`
+// cycles; then it gives up, sets the status bit and returns.  The acquire pairs with the publisher's release: what
+// follows this kernel in the stream sees every row the peers stored.
+__global__ void shard_wait_kernel(const unsigned int *flags, int world, unsigned int epoch, long long limit, int *status)
+{
+    if (threadIdx.x >= world) return;
+    const unsigned int *f = flags + threadIdx.x;
+    const long long start = clock64();
+    for (;;) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+        if ((int)(v - epoch) >= 0) return;
+        if (clock64() - start > limit) {
+            atomicOr(status, STATUS_SHARD_WAIT);
+            return;
+        }
+        __nanosleep(100);
+    }
+}
+
+int shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const void *peers_v, unsigned int epoch,
+               cudaStream_t stream)
+{
+    const qb200_shard_peers_t *peers = (const qb200_shard_peers_t *)peers_v;
+    int first = 0, count = 0;
+    qb200_shard_range(rows_total, peers->world, peers->rank, &first, &count);
+    GemvPublish pub;
+    memset(&pub, 0, sizeof pub);
+    pub.world = peers->world;
+    pub.epoch = epoch;
+    pub.counter = g_publish_counter_ptr;
+    for (int w = 0; w < peers->world; w++) {
+        pub.out[w] = w == peers->rank ? nullptr : peers->out[w] + first;
+        pub.flag[w] = peers->flags[w] + peers->rank;
+    }
+    if (count == 0) {
+        shard_flag_kernel<<<1, 32, 0, stream>>>(pub);
+        return (int)cudaGetLastError();
+    }
+    return gemv_launch(fmt_a, fmt_x, a_shard, x, peers->out[peers->rank] + first, nullptr, 0, nullptr, count, cols, stream, &pub);
+}
+
+int shard_wait(const void *peers_v, unsigned int epoch, long long limit_cycles, cudaStream_t stream)
+{
+    const qb200_shard_peers_t *peers = (const qb200_shard_peers_t *)peers_v;
+    shard_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[peers->rank], peers->world, epoch, limit_cycles > 0 ? limit_cycles : WAIT_CYCLES, g_shard_status);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace qb

@@ -5,6 +5,11 @@ output rows are independent (gemv: one dot a row; A.B^T: column j of C needs row
 [r*ceil(N/g), ...) of the weights, computes its slice with the ordinary single-GPU kernels, and nothing crosses
 NVLink unless a full output vector is wanted, in which case the f32 slices are joined by one all-gather
 (`torch.distributed`: NCCL on GPUs, gloo in the CPU tests).  x / A are replicated (they are small).
+
+For the gemv, whose slices are a few kilobytes, the all-gather's launch latency is several times the product's own
+time.  `PeerExchange` is the alternative on one box: every rank maps every other rank's output vector (CUDA IPC) and
+the gemv kernel itself stores its rows into all of them, followed by a flag a rank; `ShardedGemv.exchange` is that call
+plus the bounded wait for the peers' flags (qb200_shard_gemv / qb200_shard_wait).
 """
 from dataclasses import dataclass
 
@@ -126,3 +131,91 @@ class ShardedMatMul:
     def full(self, fmt_a, a, c_slice, m, group=None):
         self.local(fmt_a, a, c_slice, m)
         return all_gather_columns(self.plan, self.rank, c_slice, m, group=group)
+
+
+class _DeviceArray:
+    """A raw device allocation as something torch can wrap (`torch.as_tensor(obj, device=...)`), without owning it."""
+
+    def __init__(self, ptr, count, typestr):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+class PeerExchange:
+    """Every rank's copy of the whole output vector and its flag array, as this process addresses them.
+
+    Each rank allocates its own (plain cudaMalloc through the library, so that the allocation can be exported), hands the
+    others a CUDA IPC handle over `torch.distributed` (any backend: the handles are 64 bytes of host data), and opens
+    theirs.  With world 1 nothing is exchanged.  `close()` unmaps and frees; the object must outlive every call that uses it.
+    """
+
+    def __init__(self, ops, rows_total, rank, world, group=None):
+        import ctypes as C
+
+        from . import _lib
+        if not 1 <= world <= _lib.SHARD_MAX:
+            raise ValueError(f"at most {_lib.SHARD_MAX} ranks")
+        self.ops, self.lib, self.rows_total, self.rank, self.world = ops, ops.lib, int(rows_total), rank, world
+        self._own, self._opened = [], []
+        y, flags = C.c_void_p(), C.c_void_p()
+        y_bytes = max(256, (self.rows_total * 4 + 255) // 256 * 256)
+        ops.gpu.check(self.lib.qb200_malloc(C.byref(y), y_bytes), "malloc y")
+        self._own.append(y.value)
+        ops.gpu.check(self.lib.qb200_malloc(C.byref(flags), 256), "malloc flags")
+        self._own.append(flags.value)
+        ops.gpu.check(self.lib.qb200_memset(y, 0, y_bytes, None), "memset")
+        ops.gpu.check(self.lib.qb200_memset(flags, 0, 256, None), "memset")
+        ops.gpu.Synchronize()
+        out, fl = [None] * world, [None] * world
+        out[rank], fl[rank] = y.value, flags.value
+        if world > 1:
+            import torch.distributed as dist
+            mine = (C.create_string_buffer(64), C.create_string_buffer(64))
+            ops.gpu.check(self.lib.qb200_ipc_export(y, mine[0]), "ipc export")
+            ops.gpu.check(self.lib.qb200_ipc_export(flags, mine[1]), "ipc export")
+            handles = [None] * world
+            dist.all_gather_object(handles, (mine[0].raw, mine[1].raw), group=group)
+            for w in range(world):
+                if w == rank:
+                    continue
+                for which, store in ((0, out), (1, fl)):
+                    ptr = C.c_void_p()
+                    ops.gpu.check(self.lib.qb200_ipc_import(C.create_string_buffer(handles[w][which], 64), C.byref(ptr)), "ipc import")
+                    self._opened.append(ptr.value)
+                    store[w] = ptr.value
+            dist.barrier(group=group)          # everyone has opened everything before anyone stores
+        self.peers = _lib.ShardPeers()
+        self.peers.world, self.peers.rank = world, rank
+        for w in range(world):
+            self.peers.out[w], self.peers.flags[w] = out[w], fl[w]
+        self.y_ptr = y.value
+        self.epoch = 0
+
+    def y(self):
+        """This rank's copy of the whole output vector as a torch tensor (a view of the allocation, not a copy)."""
+        import torch
+        return torch.as_tensor(_DeviceArray(self.y_ptr, self.rows_total, "<f4"), device=f"cuda:{self.ops.gpu.device}")
+
+    def close(self):
+        for ptr in self._opened:
+            self.lib.qb200_ipc_close(ptr)
+        for ptr in self._own:
+            self.lib.qb200_free(ptr)
+        self._opened, self._own = [], []
+
+
+def _exchange(self, x, exchange, fmt_x=None, stream=None, limit_cycles=0):
+    """This rank's slice into every rank's copy of y (stores from inside the gemv kernel), then the bounded wait for the
+    peers' slices: after it, work on `stream` sees the whole y in `exchange.y()`."""
+    import ctypes as C
+
+    from .ops import _ptr, _stream
+    exchange.epoch += 1
+    fx = self.fmt if fmt_x is None else fmt_id(fmt_x)
+    rc = self.ops.lib.qb200_shard_gemv(self.fmt, fx, _ptr(self.w), _ptr(x), self.plan.rows, self.cols, C.byref(exchange.peers), exchange.epoch,
+                                       _stream(stream))
+    self.ops.gpu.check(rc, "shard_gemv")
+    self.ops.gpu.check(self.ops.lib.qb200_shard_wait(C.byref(exchange.peers), exchange.epoch, int(limit_cycles), _stream(stream)), "shard_wait")
+    return exchange.y()
+
+
+ShardedGemv.exchange = _exchange

@@ -27,6 +27,22 @@ def test_plan_covers_rows_once():
             assert seen == list(range(rows))
 
 
+def test_c_abi_range_is_the_plan():
+    # qb200_shard_range needs no device: the same arithmetic as ShardPlan, uneven and empty shards included
+    import ctypes as C
+
+    from qiyas_b200 import _lib
+    lib = _lib.load()
+    for rows in (0, 1, 7, 28669, 28672, 11003):
+        for world in (1, 2, 3, 8):
+            plan = ShardPlan(rows, world)
+            for r in range(world):
+                first, count = C.c_int(-1), C.c_int(-1)
+                assert lib.qb200_shard_range(rows, world, r, C.byref(first), C.byref(count)) == 0
+                assert (first.value, first.value + count.value) == plan.range(r)
+    assert lib.qb200_shard_range(10, 0, 0, None, None) == -2 and lib.qb200_shard_range(10, 2, 2, None, None) == -2
+
+
 def test_plan_bytes_and_views():
     plan = ShardPlan(28669, 8)
     assert plan.per_rank == 3584 and plan.count(7) == 28669 - 7 * 3584

@@ -1,6 +1,10 @@
-"""N-row sharding on real GPUs: two ranks, NCCL all-gather of the slices, against the unsharded oracle result.
+"""N-row sharding on real GPUs against the unsharded oracle result.
 
-Needs two GPUs; on a one-GPU box it is skipped (the gather logic is covered by the gloo test on the CPU)."""
+Two ranks on two GPUs: the NCCL all-gather of the slices, and the exchange fused into the gemv kernel (stores into the
+peer's copy of y through CUDA IPC, flags, bounded wait).  Those need two GPUs and are skipped on a one-GPU box, where the
+exchange's kernels are still exercised: two ranks' launches run one after the other on the one GPU into two buffers
+(no kernel ever waits for one that has not been launched before it), and a wait on a flag that nothing sets runs out
+and reports it."""
 import os
 import sys
 
@@ -36,6 +40,21 @@ def _worker(rank, world, port, rows, cols, m, out):
         mm = ShardedMatMul(ops, plan, rank, B.Q4_0, cols, shard)
         c = mm.full(B.Q8_0, a, torch.empty(max(m * mm.n, 1), dtype=torch.float32, device=dev), m)
         assert ops.gpu.status() == 0
+        # the same y by the exchange inside the gemv kernel, three epochs with three different x
+        from qiyas_b200.shard import PeerExchange
+        ex = PeerExchange(ops, rows, rank, world)
+        try:
+            for epoch in range(3):
+                xe = torch.from_numpy(B.make_activations(cols, 60 + epoch)).to(dev)
+                got = gemv.exchange(xe, ex, fmt_x=B.F32)
+                torch.cuda.synchronize()
+                assert ops.gpu.status() == 0
+                np.save(f"{out}.x{epoch}.r{rank}.npy", got.cpu().numpy())
+                dist.barrier()                 # the peers have read their y before the next epoch overwrites it
+        finally:
+            torch.cuda.synchronize()
+            dist.barrier()
+            ex.close()
         if rank == 0:
             np.save(out + ".y.npy", y.cpu().numpy())
             np.save(out + ".c.npy", c.cpu().numpy())
@@ -61,3 +80,70 @@ def test_two_ranks_equal_unsharded(oracle, tmp_path, rows, cols):
     a = oracle.encode(B.Q8_0, B.make_activations(m * cols, 7))
     want_c = oracle.matmul_blocks(B.Q8_0, B.Q4_0, a, w, m, rows, cols, order=1)
     assert np.array_equal(np.load(out + ".c.npy").view(np.uint32), want_c.view(np.uint32))
+    for epoch in range(3):
+        want = oracle.gemv_blocks(B.Q4_0, B.F32, w, B.make_activations(cols, 60 + epoch), rows, cols, order=1)
+        for rank in range(world):
+            got = np.load(f"{out}.x{epoch}.r{rank}.npy")
+            assert np.max(np.abs(got - want)) <= 1e-5 * np.abs(want).max(), (epoch, rank)
+
+
+def _peers(lib, world, rank, ys, flags):
+    from qiyas_b200 import _lib
+    p = _lib.ShardPeers()
+    p.world, p.rank = world, rank
+    for w in range(world):
+        p.out[w], p.flags[w] = ys[w].data_ptr(), flags[w].data_ptr()
+    return p
+
+
+@pytest.mark.parametrize("rows,world", [(4096, 2), (4093, 4), (5, 8)])
+def test_exchange_kernels_on_one_gpu(oracle, rows, world):
+    # every rank's launches in turn on the one GPU, each with its own copy of y and its own flags; then every rank's wait
+    import ctypes as C
+    import torch
+
+    from . import helpers as H
+    from qiyas_b200.shard import ShardPlan
+    o = H.ops()
+    cols = 2048
+    w = B.make_weights(B.Q4_0, rows, cols, 15)
+    plan = ShardPlan(rows, world)
+    shards = [H.dev(plan.slice_weights(r, B.Q4_0, cols, w)) if plan.count(r) else None for r in range(world)]
+    ys = [torch.full((rows + 8,), float("nan"), dtype=torch.float32, device="cuda:0") for _ in range(world)]
+    flags = [torch.zeros(8, dtype=torch.int32, device="cuda:0") for _ in range(world)]
+    for epoch in (1, 2):
+        xf = B.make_activations(cols, 16 + epoch)
+        x = H.dev(xf)
+        for r in range(world):
+            p = _peers(o.lib, world, r, ys, flags)
+            a = shards[r].data_ptr() if shards[r] is not None else None
+            assert o.lib.qb200_shard_gemv(B.Q4_0, B.F32, a, x.data_ptr(), rows, cols, C.byref(p), epoch, None) == 0, o.gpu.error()
+        for r in range(world):
+            p = _peers(o.lib, world, r, ys, flags)
+            assert o.lib.qb200_shard_wait(C.byref(p), epoch, 0, None) == 0
+        assert o.gpu.status() == 0
+        want = oracle.gemv_blocks(B.Q4_0, B.F32, w, xf, rows, cols, order=1)
+        for r in range(world):
+            got = ys[r].cpu().numpy()
+            assert np.max(np.abs(got[:rows] - want)) <= 1e-5 * np.abs(want).max(), (epoch, r)
+            assert np.isnan(got[rows:]).all()                       # nothing stored past the vector
+            assert (flags[r].cpu().numpy()[:world] == epoch).all()
+
+
+def test_a_wait_nobody_answers_runs_out():
+    # a flag that nothing sets: the wait gives up after its limit, reports bit 2 and the context stays usable
+    import ctypes as C
+    import torch
+
+    from . import helpers as H
+    o = H.ops()
+    ys = [torch.zeros(64, dtype=torch.float32, device="cuda:0") for _ in range(2)]
+    flags = [torch.zeros(8, dtype=torch.int32, device="cuda:0") for _ in range(2)]
+    p = _peers(o.lib, 2, 0, ys, flags)
+    assert o.gpu.status() == 0
+    assert o.lib.qb200_shard_wait(C.byref(p), 1, 2_000_000, None) == 0           # about a millisecond
+    assert o.gpu.status() == 4
+    assert o.gpu.status() == 0                                                  # read and cleared
+    flags[0][:2] = 1
+    assert o.lib.qb200_shard_wait(C.byref(p), 1, 2_000_000, None) == 0
+    assert o.gpu.status() == 0
