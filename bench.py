@@ -1,19 +1,29 @@
-"""Benchmark of the block-scaled quantized gemv (the memory-bound decode path) on B200.
+"""Benchmark of the block-scaled quantized products on B200.
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
-Workload (BASELINE.json configs[1]): Q4_0 gemv, weight 8192 x 8192 in 18-byte blocks, x f32[8192] ~ N(0,1),
-y f32[8192].  One step = one pass of the gemv over LAYERS distinct seeded weight matrices (a stack of
-layers, 8 x 37.7 MB = 302 MB > 2 x L2), so every launch reads its weights from HBM, not from L2.
-The metric is algorithmic bytes per second: (weight blocks + x + y) bytes / time.
+Headline workload (BASELINE.json configs[4] at M = 1): the Q4_0 gemv of a 28672 x 8192 weight matrix (18-byte blocks)
+against x f32[8192], the matrix sharded by output rows over the N ranks (strong scaling: the work is one matrix whatever
+N is) and every rank ending up with the whole y f32[28672].  At N = 1 that is the plain gemv; at N > 1 each rank's
+kernel stores its slice into every peer's copy of y (peer-mapped memory over NVLink) and a bounded wait on the peers'
+flags follows it (qb200_shard_gemv / qb200_shard_wait).  The metric is algorithmic bytes per second of the whole
+product: (weight blocks + x + y) bytes x launches / time, max over ranks.
 
-The JSON line carries the device-timed `value`, the end-to-end `e2e` through the host-buffer C-ABI
-call (pinned host operands, H2D + kernel + D2H every launch), the `roofline` of the gemv kernel against
-the measured HBM copy bandwidth, and `cpu_baseline`: the C restatement of the reference's CPU gemv
-(thread team + integer block dots) timed on this machine's host cores.  `--impl reference` times only
-that CPU restatement (the reference itself is C#/.NET and cannot run here).
+A launch sequence = one pass over LAYERS distinct seeded weight matrices (LAYERS x shard > 2 x L2, so every launch reads
+its weights from HBM), captured once as a CUDA graph.  One STEP = REPLAYS replays of that graph, timed with its own pair
+of CUDA events on the launching stream; the timed region is exactly --steps steps and the line also carries the median,
+fastest and slowest step.
+
+Beside the headline the JSON line carries: `local` (the same sharded product without the exchange) and, at N > 1,
+`with_allgather` (slices joined by NCCL instead); `c2` (BASELINE configs[1], Q4_0 8192 x 8192, every rank its own
+matrices: calls independent of one another and calls chained through y); `configs` (the other gemv configurations, N = 1);
+`abt` (the Q8_0 x Q8_0 A.B^T of configs[2] and the Q4_0-weight product of configs[4], N = 1); `e2e` (the headline product
+through the host-buffer C-ABI call: pinned host operands, H2D + kernel + D2H every call); `roofline`; `cpu_baseline` (the C
+restatement of the reference's CPU gemv on this machine's host cores).  `--impl reference` times only that CPU
+restatement (the reference itself is C#/.NET and cannot run here).
 """
 import argparse
+import ctypes as C
 import json
 import os
 import subprocess
@@ -28,15 +38,21 @@ sys.path.insert(0, ROOT)
 
 from qiyas_b200 import blocks as B  # noqa: E402
 
-ROWS, COLS, FMT_A, FMT_X = 8192, 8192, B.Q4_0, B.F32
-LAYERS = 8
-WEIGHT_BYTES = ROWS * (COLS // 32) * 18
-ALGO_BYTES = WEIGHT_BYTES + COLS * 4 + ROWS * 4          # per launch: weights once, x, y
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload's kernel (ncu; profiles/), or None
-TRAFFIC_BYTES = 37852160              # dram__bytes_read + write of one launch, from the ncu capture in profiles/
+FMT_A, FMT_X = B.Q4_0, B.F32
+N5, K5 = 28672, 8192                                      # configs[4]: the 70B-class FFN up-projection
+WEIGHT5 = N5 * (K5 // 32) * 18
+ALGO5 = WEIGHT5 + K5 * 4 + N5 * 4                         # weights once, x, y
+REPLAYS = 100                                             # graph replays a step
+L2_BYTES = 126e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the gemv on the 8192 x 8192 Q4_0 matrix (ncu, profiles/):
+# 37 852 160 bytes against 37 814 272 algorithmic, a ratio the larger matrix shares (the kernel reads every byte once)
+TRAFFIC_RATIO = 37852160 / 37814272
+# tcgen05.mma kind::i8, M 128, N 128, K 32 from shared memory with nothing else on the SM: 64.0 cycles an instruction
+# (profiles/tcgen05_mma_i8_rate.md) = 16384 int8 operations a cycle and SM
+MMA_OPS_PER_CYCLE_SM = 2 * 128 * 128 * 32 / 64.0
 
 
-def measured_peak():
+def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         try:
@@ -129,128 +145,218 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm), "via": "nvidia-smi"}
 
 
-def cpu_baseline(seconds=12.0):
-    """The reference's CPU block gemv (src/BlockProducts.cs:17-71) as restated in oracle/, on all host threads."""
+WORKLOAD = f"Q4_0 gemv {N5}x{K5} (BASELINE configs[4], M 1), x f32 -> Q8_0, sharded by output rows over the ranks, whole y on every rank"
+
+
+def layers_for(shard_bytes):
+    """Distinct weight matrices a pass rotates over: more than twice L2 in all."""
+    return int(max(2, min(40, -(-2.2 * L2_BYTES // max(1, shard_bytes)))))
+
+
+# ---------------------------------------------------------------------------------------------------------- the CPU arm
+
+def cpu_gemv(seconds, layers):
+    """The reference's CPU block gemv (src/BlockProducts.cs:17-71) as restated in oracle/, on all host threads, over the
+    same rotation of `layers` matrices as the GPU arm; both integer-dot lanes, the faster one reported."""
     from oracle import qiyas_oracle as O
-    weights = B.make_weights(FMT_A, ROWS, COLS, 1000)
-    x = B.make_activations(COLS, 2000)
-    O.time_gemv_blocks(FMT_A, FMT_X, weights, x, ROWS, COLS, 1)               # warm the team and the pages
-    one = O.time_gemv_blocks(FMT_A, FMT_X, weights, x, ROWS, COLS, 2)
-    reps = max(3, min(2000, int(seconds / max(one, 1e-6))))
-    per_call = O.time_gemv_blocks(FMT_A, FMT_X, weights, x, ROWS, COLS, reps)
-    return {"value": ALGO_BYTES / per_call / 1e9, "unit": "GB/s", "cores": O.threads(), "kind": "port",
-            "sample": f"{reps} calls of the {ROWS}x{COLS} Q4_0 gemv (x f32 -> Q8_0), {per_call * 1e3:.3f} ms each, "
-                      f"C restatement of Kernels.GemvBlocks on the thread team"}, per_call
+    ws = [B.make_weights(FMT_A, N5, K5, 1000 + i) for i in range(layers)]
+    x = B.make_activations(K5, 2000)
+    out = {}
+    for variant, name in ((0, "plain integer loop (the reference's 's32 blocks' lane)"), (1, "AVX2 multiply-adds + F16C (standing in for its 's8dp blocks' lane)")):
+        if not O.set_dot_variant(variant):
+            continue
+        for w in ws:
+            O.time_gemv_blocks(FMT_A, FMT_X, w, x, N5, K5, 1)               # warm the team and the pages
+        one = O.time_gemv_blocks(FMT_A, FMT_X, ws[0], x, N5, K5, 1)
+        passes = max(1, min(200, int(seconds / 2 / max(one * layers, 1e-6))))
+        t0 = time.perf_counter()
+        for _ in range(passes):
+            for w in ws:
+                O.time_gemv_blocks(FMT_A, FMT_X, w, x, N5, K5, 1)
+        per_call = (time.perf_counter() - t0) / (passes * layers)
+        out[variant] = {"GBs": ALGO5 / per_call / 1e9, "ms_per_call": per_call * 1e3, "calls": passes * layers, "lane": name}
+    O.set_dot_variant(0)
+    best = max(out, key=lambda v: out[v]["GBs"])
+    base = {"value": out[best]["GBs"], "unit": "GB/s", "cores": O.threads(), "kind": "port",
+            "sample": f"{out[best]['calls']} calls of the {N5}x{K5} Q4_0 gemv (x f32 -> Q8_0) over {layers} matrices in rotation, "
+                      f"{out[best]['ms_per_call']:.3f} ms each; C restatement of Kernels.GemvBlocks on the thread team, {out[best]['lane']}",
+            "variants": {str(v): out[v] for v in out}}
+    return base, out[best]["ms_per_call"] * 1e-3
 
 
-def run_reference(args, rank, world):
+def run_reference(args, rank):
     if rank != 0:
         return
     t0 = time.time()
-    base, per_call = cpu_baseline(seconds=max(2.0, min(20.0, 1.5 * (args.steps + args.warmup))))
+    layers = layers_for(WEIGHT5)
+    base, per_call = cpu_gemv(max(4.0, min(24.0, 1.2 * (args.steps + args.warmup))), layers)
     line = {"impl": "reference", "metric": "quant gemv HBM GB/s", "value": base["value"], "unit": "GB/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_call * 1e3 * LAYERS, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "s8 dot / f32 scale", "data": "synthetic",
-            "config": {"workload": f"Q4_0 gemv {ROWS}x{COLS}, x f32, {LAYERS} weight matrices per step (CPU: one matrix repeated)"},
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_call * 1e3 * layers * REPLAYS, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "s8 dot / f32 scale", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers_per_pass": layers, "cpu": "one matrix a call on all host threads; a step is a bounded sample of the GPU arm's step"},
             "cpu_baseline": base, "gpu_launches": 0,
             "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "wall_s": time.time() - t0}
     print(json.dumps(line), flush=True)
 
 
-def sharded_gemv_leg(ops, torch, dist, rank, world, dev):
-    """BASELINE configs[4] at M = 1: Q4_0 28672 x 8192 sharded by output rows over the ranks (strong scaling of one matrix),
-    timed without and with the all-gather of the f32 slices.  Each rank rotates over copies of its shard larger than L2."""
-    from qiyas_b200.shard import ShardPlan, all_gather_rows
-    n, k = 28672, 8192
-    plan = ShardPlan(n, world)
-    rows = plan.count(rank)
-    shard = plan.slice_weights(rank, FMT_A, k, B.make_weights(FMT_A, n, k, 4000))
-    copies = max(2, min(24, int(300e6 // max(1, shard.size)) + 1))
-    ws = [torch.from_numpy(shard).to(dev).clone() for _ in range(copies)]
-    x = torch.from_numpy(B.make_activations(k, 4001)).to(dev)
-    y = torch.empty(max(rows, 1), dtype=torch.float32, device=dev)
-    y_full = torch.empty(n, dtype=torch.float32, device=dev)
-    reps = 5
+# ---------------------------------------------------------------------------------------------------------- GPU helpers
 
-    def timed(gather):
-        for w in ws[:2]:
-            ops.GemvBlocks(FMT_A, w, x, y, rows, k, fmt_x=FMT_X)
-            if gather:
-                all_gather_rows(plan, rank, y, out=y_full)
-        if world > 1:
-            dist.barrier()
+class Timer:
+    """Steps of REPLAYS graph replays on a side stream, each step between its own pair of events."""
+
+    def __init__(self, torch, dist, world, dev, stream):
+        self.torch, self.dist, self.world, self.dev, self.stream = torch, dist, world, dev, stream
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def run(self, replay, steps, warmup, replays=REPLAYS):
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            for _ in range(warmup):
+                for _ in range(replays):
+                    replay()
+        self.barrier()
+        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        self.barrier()
+        with torch.cuda.stream(self.stream):
+            for e0, e1 in events:
+                e0.record()
+                for _ in range(replays):
+                    replay()
+                e1.record()
+        self.barrier()
+        per_step = [e0.elapsed_time(e1) for e0, e1 in events]
+        total = events[0][0].elapsed_time(events[-1][1])           # exactly `steps` steps, first start to last end
+        t = torch.tensor([total] + per_step, dtype=torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        t = t.cpu().numpy()
+        return float(t[0]), [float(v) for v in t[1:]]
+
+
+def capture(torch, stream, launch):
+    with torch.cuda.stream(stream):
+        launch(stream)                                  # once outside the capture: first-use set-up must not be captured
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            launch(stream)
+    return graph
+
+
+def stats(total_ms, per_step, launches_per_step, bytes_per_launch, peak):
+    per_launch = total_ms * 1e-3 / (len(per_step) * launches_per_step)
+    med = float(np.median(per_step)) * 1e-3 / launches_per_step
+    return {"us_per_launch": per_launch * 1e6, "GBs": bytes_per_launch / per_launch / 1e9, "pct_of_measured_hbm": 100 * bytes_per_launch / per_launch / 1e9 / peak,
+            "median_step_us_per_launch": med * 1e6, "fastest_step_us_per_launch": min(per_step) * 1e3 / launches_per_step,
+            "slowest_step_us_per_launch": max(per_step) * 1e3 / launches_per_step}
+
+
+def gemv_record(ops, torch, timer, fmt, rows, cols, steps, warmup, peak, chained=False, seed=100):
+    """One gemv configuration on this rank's GPU: `layers` matrices in rotation, calls independent of one another or (square
+    matrices) chained, each call's y the next call's x."""
+    bytes_w = B.nbytes(fmt, rows * cols)
+    layers = layers_for(bytes_w)
+    ws = [torch.from_numpy(B.make_weights(fmt, rows, cols, seed + i)).to(timer.dev) for i in range(layers)]
+    x = torch.from_numpy(B.make_activations(cols, seed + 50)).to(timer.dev)
+    ys = [torch.empty(rows, dtype=torch.float32, device=timer.dev) for _ in range(layers)]
+
+    def launch(stream):
+        for i, w in enumerate(ws):
+            src = ys[i - 1] if (chained and i) else (ys[-1] if chained else x)
+            ops.GemvBlocks(fmt, w, src, ys[i], rows, cols, fmt_x=B.F32, stream=stream)
+
+    if chained:
+        ys[-1].copy_(x)                                  # the chain needs a finite start; values decay or grow, the time does not care
+    graph = capture(torch, timer.stream, launch)
+    total, per_step = timer.run(graph.replay, steps, warmup, replays=max(10, REPLAYS * 3 // layers))
+    algo = bytes_w + cols * 4 + rows * 4
+    out = stats(total, per_step, layers * max(10, REPLAYS * 3 // layers), algo, peak)
+    out.update({"shape": f"{B.NAMES[fmt]} {rows}x{cols}", "layers": layers, "calls": "chained through y" if chained else "independent"})
+    return out
+
+
+def abt_record(ops, torch, timer, fmt_b, m, n, k, sm_count, clock_mhz):
+    """A.B^T with Q8_0 activations: operands re-laid on every call, and weights prepacked once."""
+    dev = timer.dev
+    a = torch.from_numpy(B.make_weights(B.Q8_0, m, k, 5000)).to(dev)
+    b = torch.from_numpy(B.make_weights(fmt_b, n, k, 5001)).to(dev)
+    c = torch.empty(m * n, dtype=torch.float32, device=dev)
+    need = ops.workspace_bytes(B.Q8_0, m, n, k, fmt_b=fmt_b)
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    packed = ops.Prepack(fmt_b, b, n, k)
+    need_a = int(ops.lib.qb200_matmul_prepacked_workspace_bytes(B.Q8_0, fmt_b, m, k))
+    ws_a = torch.empty(need_a, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=20):
+        for _ in range(3):
+            fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(reps):
-            for w in ws:
-                ops.GemvBlocks(FMT_A, w, x, y, rows, k, fmt_x=FMT_X)
-                if gather:
-                    all_gather_rows(plan, rank, y, out=y_full)
+            fn()
         e1.record()
         torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / (reps * copies)], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) * 1e-3
+        return e0.elapsed_time(e1) * 1e-3 / reps
 
-    local_s, full_s = timed(False), timed(True)
-    algo = n * (k // 32) * 18 + k * 4 + n * 4
-    return {"workload": f"Q4_0 gemv {n}x{k} sharded by output rows over {world} GPU(s), x f32 replicated", "scaling": "strong",
-            "local_us": local_s * 1e6, "local_GBs": algo / local_s / 1e9,
-            "with_allgather_us": full_s * 1e6, "with_allgather_GBs": algo / full_s / 1e9,
-            "launch": "host-launched (not graph-replayed); max over ranks"}
+    every = timed(lambda: ops.MatMulBlocks(B.Q8_0, a, b, c, m, n, k, fmt_b=fmt_b, workspace=ws, workspace_bytes=need))
+    pre = timed(lambda: ops.MatMulBlocksPrepacked(B.Q8_0, a, packed, c, m, n, k, fmt_b=fmt_b, workspace=ws_a, workspace_bytes=need_a))
+    ops_count = 2.0 * m * n * k
+    peak_measured = MMA_OPS_PER_CYCLE_SM * sm_count * clock_mhz * 1e6 / 1e12
+    return {"shape": f"Q8_0 x {B.NAMES[fmt_b]}  M {m} N {n} K {k}", "us_packed_every_call": every * 1e6, "us_weights_prepacked": pre * 1e6,
+            "int8_TOPS": ops_count / pre / 1e12, "int8_TOPS_packed_every_call": ops_count / every / 1e12,
+            "frac_of_nominal_4500": ops_count / pre / 1e12 / 4500.0, "frac_of_measured_mma_rate": ops_count / pre / 1e12 / peak_measured,
+            "peak_measured_TOPS": peak_measured}
 
 
-def abt_leg(ops, torch, dev):
-    """BASELINE configs[2]: Q8_0 x Q8_0 A.B^T, M 512, N 11008, K 4096 through qb200_matmul_blocks (repack + tcgen05 product)."""
-    m, n, k = 512, 11008, 4096
-    a = torch.from_numpy(B.make_weights(B.Q8_0, m, k, 5000)).to(dev)
-    b = torch.from_numpy(B.make_weights(B.Q8_0, n, k, 5001)).to(dev)
-    c = torch.empty(m * n, dtype=torch.float32, device=dev)
-    need = ops.workspace_bytes(B.Q8_0, m, n, k)
-    ws = torch.empty(need, dtype=torch.uint8, device=dev)
-    for _ in range(3):
-        ops.MatMulBlocks(B.Q8_0, a, b, c, m, n, k, workspace=ws, workspace_bytes=need)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 20
-    e0.record()
-    for _ in range(reps):
-        ops.MatMulBlocks(B.Q8_0, a, b, c, m, n, k, workspace=ws, workspace_bytes=need)
-    e1.record()
-    torch.cuda.synchronize()
-    s = e0.elapsed_time(e1) * 1e-3 / reps
-    tops = 2.0 * m * n * k / s / 1e12
-    return {"workload": f"Q8_0 x Q8_0 A.B^T M {m} N {n} K {k} (BASELINE configs[2]), operands repacked every call",
-            "us_per_call": s * 1e6, "int8_TOPS": tops,
-            "roofline": {"bound": "tensor", "achieved": tops, "peak": 4500.0, "unit": "TOP/s", "frac": tops / 4500.0,
-                         "peak_kind": "nominal dense int8 (no measured int8 figure exists)"}}
+def abt_cpu_baseline(seconds=8.0):
+    """The reference's CPU tile product (src/MatMulBlocks.cs:28-36, 84-169) as restated in oracle/, on a reduced configs[2]."""
+    from oracle import qiyas_oracle as O
+    m, n, k = 512, 2048, 4096
+    a = B.make_weights(B.Q8_0, m, k, 5000)
+    b = B.make_weights(B.Q8_0, n, k, 5001)
+    O.matmul_blocks(B.Q8_0, B.Q8_0, a, b, m, n, k, order=0)
+    t0, calls = time.perf_counter(), 0
+    while time.perf_counter() - t0 < seconds and calls < 50:
+        O.matmul_blocks(B.Q8_0, B.Q8_0, a, b, m, n, k, order=0)
+        calls += 1
+    s = (time.perf_counter() - t0) / calls
+    return {"value": 2.0 * m * n * k / s / 1e12, "unit": "int8 TOP/s", "cores": O.threads(), "kind": "port",
+            "sample": f"{calls} calls of Q8_0 x Q8_0 M {m} N {n} K {k} (configs[2] with N reduced from 11008), {s * 1e3:.1f} ms each; "
+                      "C restatement of Kernels.MatMulBlocks (unpack both operands, 4 x 2 tile, scalar integer dots) on the thread team"}
 
+
+# ---------------------------------------------------------------------------------------------------------- main
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--no-extra", action="store_true", help="skip the sharded-gemv and A.B^T legs (profiling runs)")
+    ap.add_argument("--no-extra", action="store_true", help="only the headline (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.steps = max(args.steps, 1)
 
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(args, rank)
         return
 
     import torch
     import torch.distributed as dist
     from qiyas_b200.ops import GpuOps
+    from qiyas_b200.shard import PeerExchange, ShardedGemv, ShardPlan, all_gather_rows
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
@@ -258,137 +364,196 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     ops = GpuOps(device=local)
-
-    # ---- inputs resident in HBM: LAYERS weight matrices, x, y (each rank its own stack: rows shard with no exchange)
     dev = f"cuda:{local}"
-    host_w = [B.make_weights(FMT_A, ROWS, COLS, 1000 + 97 * rank + i) for i in range(LAYERS)]
-    host_x = B.make_activations(COLS, 2000 + rank)
-    weights = [torch.from_numpy(w).to(dev) for w in host_w]
-    x = torch.from_numpy(host_x).to(dev)
-    ys = [torch.empty(ROWS, dtype=torch.float32, device=dev) for _ in range(LAYERS)]
-
-    # the step's launches are captured once in a CUDA graph on a side stream and replayed: at 6 us a kernel the
-    # host's launch rate, not the GPU, would otherwise set the pace
     side = torch.cuda.Stream(device=dev)
+    timer = Timer(torch, dist, world, dev, side)
+    peak, peak_kind = measured_peaks()
 
-    def launch_all(stream):
-        for w, y in zip(weights, ys):
-            ops.GemvBlocks(FMT_A, w, x, y, ROWS, COLS, fmt_x=FMT_X, stream=stream)
+    # ---- the rank's shard of every layer's matrix, x, and its copy of y
+    plan = ShardPlan(N5, world)
+    rows = plan.count(rank)
+    shard_bytes = rows * (K5 // 32) * 18
+    layers = layers_for(shard_bytes)
+    host_shards = [B.make_weights(FMT_A, rows, K5, 1000 + 131 * rank + i) for i in range(layers)]
+    host_x = B.make_activations(K5, 2000)
+    shards = [torch.from_numpy(w).to(dev) for w in host_shards]
+    x = torch.from_numpy(host_x).to(dev)
+    exchange = PeerExchange(ops, N5, rank, world)
+    y_full = exchange.y()
+    first = plan.range(rank)[0]
+    y_slice = y_full[first:first + rows]
+    gemvs = [ShardedGemv(ops, plan, rank, FMT_A, K5, w) for w in shards]
+    # without the exchange every layer writes a slice of its own (the calls are then independent of one another, as the
+    # layers of a model are); with it all layers publish into the one whole y every rank holds
+    y_locals = [y_slice] + [torch.empty(max(rows, 1), dtype=torch.float32, device=dev)[:rows] for _ in range(layers - 1)]
 
+    def launch_local(stream):
+        for g, y in zip(gemvs, y_locals):
+            g.local(x, y, fmt_x=FMT_X, stream=stream)
+
+    def launch_exchange(stream):
+        for g in gemvs:
+            rc = ops.lib.qb200_shard_gemv(g.fmt, FMT_X, g.w.data_ptr(), x.data_ptr(), N5, K5, C.byref(exchange.peers), 0, stream.cuda_stream)
+            ops.gpu.check(rc, "shard_gemv")
+            ops.gpu.check(ops.lib.qb200_shard_wait(C.byref(exchange.peers), 0, 0, stream.cuda_stream), "shard_wait")
+
+    # ---- one pass checked before anything is timed: the rank's own rows against the oracle, and (N > 1) the whole y on
+    # every rank against the slices the ranks computed
+    from oracle import qiyas_oracle as O
     with torch.cuda.stream(side):
-        launch_all(side)
+        (launch_exchange if world > 1 else launch_local)(side)
         side.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            launch_all(side)
+    if ops.gpu.status() != 0:
+        raise SystemExit("a kernel gave up on a bounded wait during the check pass")
+    pick = np.unique(np.concatenate([[0, rows - 1], np.random.default_rng(rank).integers(0, rows, 6)])) if rows else np.array([], np.int64)
+    xq = O.decode(B.Q8_0, O.encode(B.Q8_0, host_x), K5)
+    rb = B.row_bytes(FMT_A, K5)
+    got = y_full.cpu().numpy()
+    for r in pick:
+        want = float(O.gemv_f64(FMT_A, host_shards[-1 if world > 1 else 0].reshape(rows, rb)[r], xq, 1, K5)[0])
+        if abs(float(got[first + r]) - want) > 1e-4 * max(1.0, abs(want)):
+            raise SystemExit(f"bench output check failed on rank {rank}: row {first + r} = {got[first + r]}, float64 says {want}")
+    if world > 1:
+        joined = all_gather_rows(plan, rank, y_slice.clone())
+        if not torch.equal(joined.view(torch.int32), y_full.view(torch.int32)):
+            raise SystemExit(f"bench exchange check failed on rank {rank}: y after the exchange differs from the ranks' own slices")
 
-    def step():
-        graph.replay()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    with torch.cuda.stream(side):
-        for _ in range(args.warmup):
-            step()
-    barrier()
-    # a first check that the timed thing computes the product: one row against the decoded dot (float64 on the host)
+    # ---- the headline: the sharded product with the exchange (N = 1: the plain product)
+    graph_local = capture(torch, side, launch_local)
+    graph_head = capture(torch, side, launch_exchange) if world > 1 else graph_local
+    launches_per_step = layers * REPLAYS
     sampler = ClockSampler(local)
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    with torch.cuda.stream(side):
-        start.record()
-        for _ in range(args.steps):
-            step()
-        stop.record()
-    barrier()
+    total_ms, per_step = timer.run(graph_head.replay, args.steps, args.warmup)
     clocks = sampler.stop()
-    ms = start.elapsed_time(stop)
     if ops.gpu.status() != 0:
         raise SystemExit("a kernel gave up on a bounded wait: the timing is void")
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    launches = args.steps * LAYERS
-    per_launch_s = ms * 1e-3 / launches
-    value = world * launches * ALGO_BYTES / (ms * 1e-3) / 1e9
+    head = stats(total_ms, per_step, launches_per_step, ALGO5, peak)
+    value = ALGO5 * args.steps * launches_per_step / (total_ms * 1e-3) / 1e9
+    rank_algo = shard_bytes + K5 * 4 + rows * 4                       # what one rank's launch reads and writes
+    per_launch_s = total_ms * 1e-3 / (args.steps * launches_per_step)
 
-    # ---- end to end: the host-buffer call (pinned operands up, kernel, y down) every launch
+    extra_steps = max(3, min(args.steps, 7))
+    local_rec = None
+    if world > 1 and not args.no_extra:
+        t, ps = timer.run(graph_local.replay, extra_steps, 3)
+        local_rec = stats(t, ps, launches_per_step, ALGO5, peak)
+        local_rec["note"] = "every rank its slice only, no exchange"
+
+    gather_rec = None
+    if world > 1 and not args.no_extra:
+        y_tmp = torch.empty(N5, dtype=torch.float32, device=dev)
+        reps = 40
+
+        def gather_pass():
+            for g in gemvs:
+                g.local(x, y_slice, fmt_x=FMT_X)
+                all_gather_rows(plan, rank, y_slice, out=y_tmp)
+        for _ in range(2):
+            gather_pass()
+        timer.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            gather_pass()
+        e1.record()
+        timer.barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        s = float(t.item()) * 1e-3 / (reps * layers)
+        gather_rec = {"us_per_launch": s * 1e6, "GBs": ALGO5 / s / 1e9, "note": "slices joined by ncclAllGather, host-launched (not graph-replayed)"}
+
+    # ---- end to end: the host-buffer call (pinned operands up, kernel, y down) on the rank's shard, every call
     e2e = None
-    if not args.no_e2e:
-        pinned_w = [torch.from_numpy(w).pin_memory() for w in host_w[:2]]
+    if not args.no_e2e and rows:
+        pinned_w = [torch.from_numpy(w).pin_memory() for w in host_shards[:2]]
         pinned_x = torch.from_numpy(host_x).pin_memory()
-        pinned_y = torch.empty(ROWS, dtype=torch.float32).pin_memory()
+        pinned_y = torch.empty(rows, dtype=torch.float32).pin_memory()
         wn, xn, yn = [p.numpy() for p in pinned_w], pinned_x.numpy(), pinned_y.numpy()
-        e_steps = max(2, min(args.steps, 6))
+        calls = max(4, min(4 * args.steps, 24))
         for i in range(2):
-            ops.GemvBlocksHost(FMT_A, wn[i % 2], xn, yn, ROWS, COLS, fmt_x=FMT_X)
-        barrier()
+            ops.GemvBlocksHost(FMT_A, wn[i % 2], xn, yn, rows, K5, fmt_x=FMT_X)
+        timer.barrier()
         t0 = time.perf_counter()
-        for _ in range(e_steps):
-            for i in range(LAYERS):
-                ops.GemvBlocksHost(FMT_A, wn[i % 2], xn, yn, ROWS, COLS, fmt_x=FMT_X)
+        for i in range(calls):
+            ops.GemvBlocksHost(FMT_A, wn[i % 2], xn, yn, rows, K5, fmt_x=FMT_X)
         torch.cuda.synchronize()
         e_s = time.perf_counter() - t0
         et = torch.tensor([e_s], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(et, op=dist.ReduceOp.MAX)
         e_s = float(et.item())
-        # the bound of this leg: a plain copy of one matrix from the same pinned buffer, timed the same way
-        dst = torch.empty(WEIGHT_BYTES, dtype=torch.uint8, device=dev)
+        dst = torch.empty(shard_bytes, dtype=torch.uint8, device=dev)
         dst.copy_(pinned_w[0], non_blocking=True)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for i in range(4):
             dst.copy_(pinned_w[i % 2], non_blocking=True)
         torch.cuda.synchronize()
-        h2d_gbs = 4 * WEIGHT_BYTES / (time.perf_counter() - t0) / 1e9
-        e2e = {"value": world * e_steps * LAYERS * ALGO_BYTES / e_s / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": LAYERS * (WEIGHT_BYTES + COLS * 4), "d2h_bytes_per_step": LAYERS * ROWS * 4,
-               "steps": e_steps, "ms_per_step": e_s * 1e3 / e_steps, "pinned_h2d_copy_GBs": h2d_gbs}
+        h2d_gbs = 4 * shard_bytes / (time.perf_counter() - t0) / 1e9
+        # a step of this leg = `launches_per_step` host-buffer calls; the figure is per call, the bytes per step follow
+        e2e = {"value": ALGO5 * calls / e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": launches_per_step * (shard_bytes + K5 * 4),
+               "d2h_bytes_per_step": launches_per_step * rows * 4, "calls_timed": calls, "ms_per_call": e_s * 1e3 / calls,
+               "pinned_h2d_copy_GBs": h2d_gbs, "note": "each rank uploads its shard and x, runs the gemv, downloads its slice; slices are not exchanged in this leg"}
 
-    sharded = None if args.no_extra else sharded_gemv_leg(ops, torch, dist, rank, world, dev)
-    abt = abt_leg(ops, torch, dev) if (world == 1 and not args.no_extra) else None
+    # ---- the other configurations (rank-local; N = 1 for the long lists)
+    c2 = None
+    configs = None
+    abt = None
+    if not args.no_extra:
+        c2 = {"independent": gemv_record(ops, torch, timer, B.Q4_0, 8192, 8192, extra_steps, 3, peak),
+              "chained": gemv_record(ops, torch, timer, B.Q4_0, 8192, 8192, extra_steps, 3, peak, chained=True),
+              "workload": "BASELINE configs[1]: every rank its own matrices"}
+        if world == 1:
+            configs = [gemv_record(ops, torch, timer, f, r, c, 3, 3, peak) for f, r, c in
+                       [(B.Q8_0, 4096, 4096), (B.Q8_0, 4093, 4064), (B.Q4_0, 8191, 8160), (B.Q4_K, 4096, 4096), (B.Q4_K, 11008, 4096),
+                        (B.Q4_K, 4096, 11008), (B.Q6_K, 4096, 4096), (B.Q6_K, 11008, 4096), (B.Q6_K, 4096, 11008), (B.Q4_0, 28669, 8160)]]
+            configs.append(gemv_record(ops, torch, timer, B.Q8_0, 4096, 4096, 3, 3, peak, chained=True))
+            clock = clocks.get("sm_max_mhz") or 1965.0
+            abt = {"configs2": [abt_record(ops, torch, timer, B.Q8_0, m, 11008, 4096, ops.gpu.caps.sm_count, clock) for m in (512, 2048, 128)],
+                   "configs4": [abt_record(ops, torch, timer, B.Q4_0, m, N5, K5, ops.gpu.caps.sm_count, clock) for m in (64, 512)],
+                   "roofline": {"bound": "tensor", "unit": "TOP/s", "peak_nominal": 4500.0,
+                                "peak_kind": "nominal dense int8; peak_measured_TOPS = the measured tcgen05.mma rate x SMs x the max SM clock"}}
+            if not args.no_cpu:
+                abt["cpu_baseline"] = abt_cpu_baseline()
 
     if rank != 0:
+        exchange.close()
         if world > 1:
             dist.destroy_process_group()
         return
 
-    # one output row checked on the host against float64 of the decoded stored values
-    from oracle import qiyas_oracle as O
-    r = 4321
-    row = host_w[LAYERS - 1].reshape(ROWS, -1)[r]
-    xq = O.decode(B.Q8_0, O.encode(B.Q8_0, host_x), COLS)
-    want = float(O.gemv_f64(FMT_A, row, xq, 1, COLS)[0])
-    got = float(ys[LAYERS - 1][r].item())
-    if abs(got - want) > 1e-4 * max(1.0, abs(want)):
-        raise SystemExit(f"bench output check failed: row {r} = {got}, float64 says {want}")
-
-    peak, peak_kind = measured_peak()
-    achieved = ALGO_BYTES / per_launch_s / 1e9
+    achieved = rank_algo / per_launch_s / 1e9
+    kernels_per_call = 2 if world > 1 else 1
     line = {"metric": "quant gemv HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "s8 dot / f32 scale", "data": "synthetic",
-            "config": {"workload": f"Q4_0 gemv {ROWS}x{COLS} (BASELINE configs[1]), x f32 -> Q8_0 in-kernel",
-                       "layers_per_step": LAYERS, "launch": "one CUDA graph of the step's kernels, replayed", "l2": f"inputs larger than L2: {LAYERS} distinct weight matrices, "
-                       f"{LAYERS * WEIGHT_BYTES / 1e6:.0f} MB per step", "pct_of_8TBs": 100.0 * value / world / 8000.0},
+            "config": {"workload": WORKLOAD, "layers_per_pass": layers, "graph_replays_per_step": REPLAYS, "launches_per_step": launches_per_step,
+                       "launch": "one CUDA graph of a pass's kernels, replayed", "l2": f"inputs larger than L2: {layers} distinct shards of {shard_bytes / 1e6:.1f} MB a rank",
+                       "exchange": "peer stores from the gemv kernel + flags + bounded wait" if world > 1 else "none (one rank holds all rows)",
+                       "pct_of_8TBs_per_gpu": 100.0 * value / world / 8000.0, "median_step_ms": float(np.median(per_step)),
+                       "fastest_step_ms": min(per_step), "slowest_step_ms": max(per_step)},
+            "with_exchange": head,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": TRAFFIC_BYTES, "peak_kind": f"of {peak_kind}", "kernel": "gemv_kernel<Q4_0>",
-                         "launch_us": per_launch_s * 1e6, "kernels_per_call": 1, "algorithmic_bytes_per_launch": ALGO_BYTES},
-            "clocks": clocks, "gpu_launches": launches}      # one kernel a call: x is encoded inside the gemv kernel
+                         "traffic": int(rank_algo * TRAFFIC_RATIO), "peak_kind": f"of {peak_kind}", "kernel": "gemv_kernel<Q4_0>",
+                         "launch_us": per_launch_s * 1e6, "kernels_per_call": kernels_per_call, "algorithmic_bytes_per_launch": rank_algo,
+                         "note": "per rank: its shard + x + its slice over the time of a launch, the exchange's wait included at N > 1"},
+            "clocks": clocks, "gpu_launches": args.steps * launches_per_step * kernels_per_call}
+    if local_rec is not None:
+        line["local"] = local_rec
+    if gather_rec is not None:
+        line["with_allgather"] = gather_rec
     if e2e is not None:
         line["e2e"] = e2e
-    if sharded is not None:
-        line["sharded"] = sharded
+    if c2 is not None:
+        line["c2"] = c2
+    if configs is not None:
+        line["configs"] = configs
     if abt is not None:
         line["abt"] = abt
     if world == 1 and not args.no_cpu:
-        line["cpu_baseline"], _ = cpu_baseline()
+        line["cpu_baseline"], _ = cpu_gemv(10.0, layers)
     print(json.dumps(line), flush=True)
+    exchange.close()
     if world > 1:
         dist.destroy_process_group()
 

@@ -220,8 +220,10 @@ int qb200_decode(int fmt, const void *blocks, float *lanes, int64_t n, void *str
  *
  * One process drives one GPU (qb200_init(device) in each); the ranks map one another's buffers with the CUDA IPC
  * helpers below (or, in one process, with peer access).  peers->out[w] is rank w's y (rows_total f32, 16-byte aligned),
- * peers->flags[w] its flag array (QB200_SHARD_MAX words, zeroed once before the first call), both as THIS process
- * addresses them.  Successive calls pass increasing epochs (1, 2, ...).  A rank must not overwrite its x or start the
+ * peers->flags[w] its flag array (2 * QB200_SHARD_MAX words, zeroed once before the first call: a word a rank, then the
+ * owner's own counters), both as THIS process addresses them.  Successive calls pass increasing epochs (1, 2, ...), or
+ * all pass 0: publisher and waiter then count their calls on the device, which is what a captured CUDA graph needs, since
+ * its replays repeat the captured arguments (every rank must then make the same sequence of calls).  A rank must not overwrite its x or start the
  * next qb200_shard_gemv into the same buffers before its own qb200_shard_wait for the previous epoch is in its stream:
  * that wait is also what tells it the peers have finished writing into its y.  All of a rank's sharded calls go to one
  * stream.  An NCCL all-gather of the slices gives the same y and remains the choice across boxes. */

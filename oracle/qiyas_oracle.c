@@ -18,6 +18,7 @@
  * -ffp-contract=off so that no multiply-add is fused unless written as fmaf().
  */
 #define _GNU_SOURCE
+#include <immintrin.h>
 #include <math.h>
 #include <pthread.h>
 #include <sched.h>
@@ -413,13 +414,45 @@ static void unpack_block(int fmt, const uint8_t *b, float *scale, int8_t *q)
     for (int i = 0; i < 16; i++) { q[i] = (int8_t)((b[2 + i] & 15) - 8); q[i + 16] = (int8_t)((b[2 + i] >> 4) - 8); }
 }
 
-/* Dot32's plain-integer branch (src/BlockProducts.cs:66-69); the s8 dot lane gives the same integer. */
-static int dot32(const int8_t *p, const int8_t *q)
+/* Dot32 (src/BlockProducts.cs:58-70).  Variant 0 is its plain-integer branch (:66-69, the lane the reference calls
+ * "s32 blocks"); variant 1 stands in for its vector branch (:60-64: one 256-bit S8Dot.Fma and a horizontal sum, the
+ * lane "s8dp blocks", which needs AVX-VNNI-INT8): the same exact integer from AVX2's widening multiply-adds, |p| times
+ * q with p's sign (pairs of products fit 16 bits: 2 * 127 * 128 < 2^15), then pairs of 16-bit sums into 32 bits.
+ * Variant 1 also unpacks Q4_0 nibbles 16 at a time.  Both give bit-identical results; the bench times both. */
+static int g_dot_variant = 0;
+QO_API void qo_set_dot_variant(int v) { g_dot_variant = v; }
+QO_API int qo_dot_variant_available(int v) { return v == 0 || (v == 1 && __builtin_cpu_supports("avx2") && __builtin_cpu_supports("f16c")); }
+/* the block's f16 scale by the F16C instruction (bit-identical to qo_half_to_float: the conversion is exact) */
+__attribute__((target("avx2,f16c"))) static float half_at_f16c(const uint8_t *p) { return _cvtsh_ss((unsigned short)(p[0] | p[1] << 8)); }
+
+static int dot32_scalar(const int8_t *p, const int8_t *q)
 {
     int sum = 0;
     for (int i = 0; i < 32; i++) sum += p[i] * q[i];
     return sum;
 }
+
+__attribute__((target("avx2"))) static int dot32_avx2(const int8_t *p, const int8_t *q)
+{
+    const __m256i a = _mm256_loadu_si256((const __m256i *)p), b = _mm256_loadu_si256((const __m256i *)q);
+    const __m256i pairs = _mm256_maddubs_epi16(_mm256_abs_epi8(a), _mm256_sign_epi8(b, a));
+    const __m256i quads = _mm256_madd_epi16(pairs, _mm256_set1_epi16(1));
+    __m128i s = _mm_add_epi32(_mm256_castsi256_si128(quads), _mm256_extracti128_si256(quads, 1));
+    s = _mm_add_epi32(s, _mm_shuffle_epi32(s, 0x4E));
+    s = _mm_add_epi32(s, _mm_shuffle_epi32(s, 0xB1));
+    return _mm_cvtsi128_si32(s);
+}
+
+/* UnpackBlock for Q4_0 with 128-bit operations: low nibbles are values 0..15, high nibbles values 16..31, each minus 8. */
+__attribute__((target("avx2,f16c"))) static void unpack_q4_0_avx2(const uint8_t *b, float *scale, int8_t *q)
+{
+    *scale = half_at_f16c(b);
+    const __m128i raw = _mm_loadu_si128((const __m128i *)(b + 2)), m = _mm_set1_epi8(15), eight = _mm_set1_epi8(8);
+    _mm_storeu_si128((__m128i *)q, _mm_sub_epi8(_mm_and_si128(raw, m), eight));
+    _mm_storeu_si128((__m128i *)(q + 16), _mm_sub_epi8(_mm_and_si128(_mm_srli_epi16(raw, 4), m), eight));
+}
+
+static int dot32(const int8_t *p, const int8_t *q) { return g_dot_variant == 1 ? dot32_avx2(p, q) : dot32_scalar(p, q); }
 
 struct gemv_job {
     int fmt_a, order, cols, bb;
@@ -439,17 +472,21 @@ static void gemv_body(void *p, int first, int last)
     struct gemv_job *j = (struct gemv_job *)p;
     int blocks = j->cols / 32;
     int8_t q[32];
+    const int fast = g_dot_variant == 1;
     for (int r = first; r < last; r++) {
         float acc = 0;
         double mag = 0;
         for (int b = 0; b < blocks; b++) {
             float d;
-            unpack_block(j->fmt_a, j->a + ((int64_t)r * blocks + b) * j->bb, &d, q);
-            int dot = dot32(q, j->xq + b * 32);
+            const uint8_t *blk = j->a + ((int64_t)r * blocks + b) * j->bb;
+            int dot;
+            if (fast && j->fmt_a == QO_Q8_0) { d = half_at_f16c(blk); dot = dot32_avx2((const int8_t *)blk + 2, j->xq + b * 32); }
+            else if (fast) { unpack_q4_0_avx2(blk, &d, q); dot = dot32_avx2(q, j->xq + b * 32); }
+            else { unpack_block(j->fmt_a, blk, &d, q); dot = dot32_scalar(q, j->xq + b * 32); }
             if (j->sums) j->sums[(int64_t)r * blocks + b] = dot;
             if (j->order == 0) { float s = d * j->xs[b]; float t = s * (float)dot; acc = acc + t; }
             else { float s = d * j->xs[b]; acc = fmaf(s, (float)dot, acc); }
-            mag += fabs((double)d * (double)j->xs[b] * (double)dot);
+            if (j->abs_sum) mag += fabs((double)d * (double)j->xs[b] * (double)dot);      /* test-only: not in the timed path */
         }
         j->y[r] = acc;
         if (j->abs_sum) j->abs_sum[r] = mag;

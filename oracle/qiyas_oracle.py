@@ -32,6 +32,8 @@ def lib():
         _lib.qo_now.restype = C.c_double
         _lib.qo_time_gemv_blocks.restype = C.c_double
         _lib.qo_time_gemv_blocks.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+        _lib.qo_set_dot_variant.argtypes = [C.c_int]
+        _lib.qo_dot_variant_available.argtypes = [C.c_int]
         _lib.qo_decode.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_void_p]
         _lib.qo_encode.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_int]
         _lib.qo_gemv_blocks.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
@@ -62,6 +64,15 @@ def nbytes(fmt, values):
 
 def threads():
     return int(lib().qo_team_size())
+
+
+def set_dot_variant(variant):
+    """The CPU gemv's integer dot: 0 the plain loop (the reference's "s32 blocks" lane), 1 AVX2 widening multiply-adds
+    (standing in for its "s8dp blocks" vector lane).  Same results bit for bit; returns False when the host lacks AVX2."""
+    if not lib().qo_dot_variant_available(int(variant)):
+        return False
+    lib().qo_set_dot_variant(int(variant))
+    return True
 
 
 def half_to_float(h):

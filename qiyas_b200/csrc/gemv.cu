@@ -798,11 +798,10 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         // arithmetic and the barrier calls, which would pace the whole kernel): a pass of the warp issues `step`
         // consecutive chunks, never more than there are slots, so no lane of a pass waits on another lane of it.
         // (with x in a buffer shared between calls the consumers decide when the next call may be scheduled)
-        // Only a call that does not wait lets its dependents be scheduled from here.  A call that waits for its
-        // predecessor must not: its successor could then start while that predecessor is still writing, and the host's
-        // record of who can still be running (gemv_launch) holds only this call once it has waited.  Its blocks trigger
-        // from the consumers instead, after griddepcontrol.wait, i.e. when everything earlier has completed.
-        if (p.x && p.independent) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        // The trigger comes before this call's own wait (if it has one) has passed, so the next call can start while
+        // this call's predecessors are still running: the host's record of launches in flight keeps them for that
+        // reason (gemv_launch).  (Making the trigger conditional on the call not waiting cost 1-8 % of every launch.)
+        if (p.x) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         // A slot belongs to one row group for the whole kernel (spg slots a group): the warps that wait on a slot's
         // barrier are then always the ones that released its previous use, so a phase parity can never be mistaken for the
         // parity two phases back.
@@ -1017,9 +1016,11 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
                 if (before == gridDim.x - 1) {
                     *pub->counter = 0u;
                     __threadfence_system();
+                    // epoch 0: the call's number is counted on the device (a captured graph replays the same arguments)
+                    const unsigned int epoch = pub->epoch ? pub->epoch : atomicAdd(pub->epoch_counter, 1u) + 1u;
                     for (int w = 0; w < world; w++) {
                         unsigned int *f = pub->flag[w];
-                        if (f) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(pub->epoch) : "memory");
+                        if (f) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
                     }
                 }
             }
@@ -1233,21 +1234,23 @@ cudaError_t gemv_init(int sm_count, int max_smem, int *status)
 // Returns 0, a negative QB200_E_* or a positive cudaError_t.  Arguments are already validated.
 
 // Ordering against earlier gemv launches of this thread.  A gemv is normally launched as a programmatic dependent of
-// whatever precedes it in the stream, and may skip griddepcontrol.wait; a launch that skips it can run beside its
-// predecessor, and so can its own successor, so any launch since the last point of full order may still be running
-// when a new one starts.  The history holds what those launches read and wrote.  A new call that touches none of it
-// (its inputs are not their outputs, its outputs are not their inputs or outputs) is "independent": no wait.  A call
-// that conflicts waits: by griddepcontrol.wait when the only launch that can still be running is the one directly
-// before it (a chain of calls that each waited), else by being launched without the programmatic attribute, which
-// orders it after everything earlier in the stream.  Either way the history restarts with it.  Other work in the
-// stream (kernels, copies) is launched without the attribute and only adds order.
+// whatever precedes it in the stream, and may skip griddepcontrol.wait; every launch lets its successor be scheduled
+// at its very start, before its own wait (if any) has passed, so any launch since the last point of full order may still
+// be running when a new one starts.  The history holds what those launches read and wrote.  A new call that touches
+// none of it (its inputs are not their outputs, its outputs are not their inputs or outputs) is "independent": no
+// wait.  A call that conflicts waits.  griddepcontrol.wait orders it after its direct predecessor's completion, which is
+// enough when that predecessor itself waited for everything before it (`settled`: waiting for the newest entry is then
+// waiting for all of them); the call joins the history, which stays: its own successor may start while any of them
+// still runs.  Otherwise (launches running side by side, or nothing known) the call is launched without the
+// programmatic attribute, which orders it after everything earlier in the stream, and the history restarts with it.
+// Other work in the stream (kernels, copies) is launched without the attribute and only adds order.
 struct Touched { const uint8_t *p; size_t n; };
 struct Launched { Touched a, x, y, yb; };
 constexpr int HISTORY = 64;
 static thread_local struct {
     cudaStream_t stream;
     int count;              // 0: nothing known about the stream (first call, another stream, a call outside this record)
-    bool settled;           // the newest entry waited for everything before it: only it can still be running
+    bool settled;           // the newest entry waited for everything before it: to wait for it is to wait for them all
     Launched at[HISTORY];
 } t_hist = { nullptr, 0, false, {} };
 
@@ -1297,16 +1300,22 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     // the launch before this one ran beside its neighbours: expect the same of this one and of the next, whether or
     // not this one has to wait first (the choice of block variant below)
     const bool in_a_burst = known && !t_hist.settled;
-    // full order by the launch itself: nothing known, or more than the direct predecessor may still be running
-    const bool serial = conflict && (!known || weights_written || !(t_hist.count == 1 || t_hist.settled));
+    // full order by the launch itself: nothing known, the weights themselves in flight (the producer reads them before
+    // any wait), launches side by side that a wait on the newest would not cover, or a history that has no room left
+    const bool serial = conflict && (!known || weights_written || !t_hist.settled || t_hist.count == HISTORY);
     if (publish) t_hist.count = 0;          // nothing is known about what runs beside the next call
     else if (independent) {
         t_hist.at[t_hist.count++] = now;
         t_hist.settled = false;
-    } else {
+    } else if (serial) {
         t_hist.stream = stream;
         t_hist.at[0] = now;
         t_hist.count = 1;
+        t_hist.settled = true;
+    } else {
+        // waited by griddepcontrol.wait: everything before it is covered by waiting for it, but may still be running
+        // when the next call is scheduled
+        t_hist.at[t_hist.count++] = now;
         t_hist.settled = true;
     }
     // the last few shapes' plans are kept: a decode loop calls the same shapes over and over

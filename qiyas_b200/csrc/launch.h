@@ -20,8 +20,9 @@ struct GemvPublish {
     float *out[QB200_SHARD_MAX];
     unsigned int *flag[QB200_SHARD_MAX];
     unsigned int *counter;        // blocks of this grid that have published (device-local, returns to zero)
+    unsigned int *epoch_counter;  // this rank's count of published calls (device-local), used when epoch is 0
     int world;
-    unsigned int epoch;
+    unsigned int epoch;           // the value stored to the flags; 0: the next value of epoch_counter
 };
 
 cudaError_t gemv_init(int sm_count, int max_smem, int *status);

@@ -25,17 +25,26 @@ cudaError_t shard_init(int *status)
 // A rank without rows still owes its peers its flag.
 __global__ void shard_flag_kernel(GemvPublish pub)
 {
+    __shared__ unsigned int epoch;
+    if (threadIdx.x == 0) epoch = pub.epoch ? pub.epoch : atomicAdd(pub.epoch_counter, 1u) + 1u;
+    __syncthreads();
     if (threadIdx.x < pub.world) {
         unsigned int *f = pub.flag[threadIdx.x];
-        if (f) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(pub.epoch) : "memory");
+        if (f) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
     }
 }
 
 // Thread w waits until word w of this rank's flag array has reached `epoch` (the words only grow), for at most `limit`
 // cycles; then it gives up, sets the status bit and returns.  The acquire pairs with the publisher's release: what
 // follows this kernel in the stream sees every row the peers stored.
-__global__ void shard_wait_kernel(const unsigned int *flags, int world, unsigned int epoch, long long limit, int *status)
+__global__ void shard_wait_kernel(unsigned int *flags, int world, unsigned int epoch, long long limit, int *status)
 {
+    __shared__ unsigned int counted;
+    if (epoch == 0) {           // the wait's number is counted on the device, as the publisher's is
+        if (threadIdx.x == 0) counted = atomicAdd(flags + QB200_SHARD_MAX + 1, 1u) + 1u;
+        __syncthreads();
+        epoch = counted;
+    }
     if (threadIdx.x >= world) return;
     const unsigned int *f = flags + threadIdx.x;
     const long long start = clock64();
@@ -62,6 +71,7 @@ int shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int row
     pub.world = peers->world;
     pub.epoch = epoch;
     pub.counter = g_publish_counter_ptr;
+    pub.epoch_counter = peers->flags[peers->rank] + QB200_SHARD_MAX;
     for (int w = 0; w < peers->world; w++) {
         pub.out[w] = w == peers->rank ? nullptr : peers->out[w] + first;
         pub.flag[w] = peers->flags[w] + peers->rank;

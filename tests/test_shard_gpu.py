@@ -96,8 +96,9 @@ def _peers(lib, world, rank, ys, flags):
     return p
 
 
+@pytest.mark.parametrize("counted", [False, True])
 @pytest.mark.parametrize("rows,world", [(4096, 2), (4093, 4), (5, 8)])
-def test_exchange_kernels_on_one_gpu(oracle, rows, world):
+def test_exchange_kernels_on_one_gpu(oracle, rows, world, counted):
     # every rank's launches in turn on the one GPU, each with its own copy of y and its own flags; then every rank's wait
     import ctypes as C
     import torch
@@ -110,17 +111,17 @@ def test_exchange_kernels_on_one_gpu(oracle, rows, world):
     plan = ShardPlan(rows, world)
     shards = [H.dev(plan.slice_weights(r, B.Q4_0, cols, w)) if plan.count(r) else None for r in range(world)]
     ys = [torch.full((rows + 8,), float("nan"), dtype=torch.float32, device="cuda:0") for _ in range(world)]
-    flags = [torch.zeros(8, dtype=torch.int32, device="cuda:0") for _ in range(world)]
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda:0") for _ in range(world)]
     for epoch in (1, 2):
         xf = B.make_activations(cols, 16 + epoch)
         x = H.dev(xf)
         for r in range(world):
             p = _peers(o.lib, world, r, ys, flags)
             a = shards[r].data_ptr() if shards[r] is not None else None
-            assert o.lib.qb200_shard_gemv(B.Q4_0, B.F32, a, x.data_ptr(), rows, cols, C.byref(p), epoch, None) == 0, o.gpu.error()
+            assert o.lib.qb200_shard_gemv(B.Q4_0, B.F32, a, x.data_ptr(), rows, cols, C.byref(p), 0 if counted else epoch, None) == 0, o.gpu.error()
         for r in range(world):
             p = _peers(o.lib, world, r, ys, flags)
-            assert o.lib.qb200_shard_wait(C.byref(p), epoch, 0, None) == 0
+            assert o.lib.qb200_shard_wait(C.byref(p), 0 if counted else epoch, 0, None) == 0      # 0: epochs counted on the device
         assert o.gpu.status() == 0
         want = oracle.gemv_blocks(B.Q4_0, B.F32, w, xf, rows, cols, order=1)
         for r in range(world):
@@ -138,7 +139,7 @@ def test_a_wait_nobody_answers_runs_out():
     from . import helpers as H
     o = H.ops()
     ys = [torch.zeros(64, dtype=torch.float32, device="cuda:0") for _ in range(2)]
-    flags = [torch.zeros(8, dtype=torch.int32, device="cuda:0") for _ in range(2)]
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda:0") for _ in range(2)]
     p = _peers(o.lib, 2, 0, ys, flags)
     assert o.gpu.status() == 0
     assert o.lib.qb200_shard_wait(C.byref(p), 1, 2_000_000, None) == 0           # about a millisecond
