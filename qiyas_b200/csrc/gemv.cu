@@ -1009,9 +1009,12 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
                     if (dst) dst[idx] = v;
                 }
             }
-            __threadfence_system();
+            // The block's stores are ordered before its count by one fence: the barrier makes them thread 0's to order.
+            // Device scope is enough here (the count is read on this GPU); the block that counts last adds the
+            // system-scope fence before the flags, and causality carries the other blocks' stores along with it.
             named_bar_sync(1, threads);
             if (threadIdx.x == 0) {
+                __threadfence();
                 const unsigned int before = atomicAdd(pub->counter, 1u);
                 if (before == gridDim.x - 1) {
                     *pub->counter = 0u;
@@ -1020,7 +1023,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
                     const unsigned int epoch = pub->epoch ? pub->epoch : atomicAdd(pub->epoch_counter, 1u) + 1u;
                     for (int w = 0; w < world; w++) {
                         unsigned int *f = pub->flag[w];
-                        if (f) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+                        // (the fence above is the release: the flags themselves are plain system-scope stores, one a peer)
+                        if (f) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
                     }
                 }
             }
@@ -1245,7 +1249,7 @@ cudaError_t gemv_init(int sm_count, int max_smem, int *status)
 // programmatic attribute, which orders it after everything earlier in the stream, and the history restarts with it.
 // Other work in the stream (kernels, copies) is launched without the attribute and only adds order.
 struct Touched { const uint8_t *p; size_t n; };
-struct Launched { Touched a, x, y, yb; };
+struct Launched { Touched a, x, y, yb; bool everything; };
 constexpr int HISTORY = 64;
 static thread_local struct {
     cudaStream_t stream;
@@ -1255,6 +1259,15 @@ static thread_local struct {
 } t_hist = { nullptr, 0, false, {} };
 
 void gemv_forget_history() { t_hist.count = 0; }
+
+void gemv_history_everything(cudaStream_t stream)
+{
+    memset(&t_hist.at[0], 0, sizeof t_hist.at[0]);
+    t_hist.at[0].everything = true;
+    t_hist.stream = stream;
+    t_hist.count = 1;
+    t_hist.settled = true;
+}
 
 // The host thread's cached plans belong to the device they were made for: dropped when the library binds another one.
 static thread_local int t_plans_cached = 0, t_plans_next = 0, t_plans_epoch = 0;
@@ -1267,6 +1280,7 @@ static bool overlap(const Touched &u, const Touched &v)
 // does the new call read what `old` wrote, or write what `old` read or wrote?
 static bool conflicts(const Launched &now, const Launched &old)
 {
+    if (old.everything) return true;
     const Touched *outs[2] = { &now.y, &now.yb }, *old_outs[2] = { &old.y, &old.yb };
     for (int i = 0; i < 2; i++) {
         if (overlap(now.x, *old_outs[i]) || overlap(now.a, *old_outs[i])) return true;
@@ -1286,6 +1300,7 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     now.x = { (const uint8_t *)x, fmt_x == QB200_F32 ? (size_t)cols * 4 : (size_t)(cols / 32) * block_bytes(fmt_x) };
     now.y = { (const uint8_t *)y, (size_t)rows * 4 };
     now.yb = { (const uint8_t *)y_blocks, y_blocks ? (size_t)((rows + 31) / 32) * block_bytes(fmt_y) : 0 };
+    now.everything = false;
     const bool known = t_hist.count > 0 && t_hist.stream == stream;
     // a publishing launch writes memory this record does not describe (the other GPUs' copies): it waits, and so does its successor
     bool conflict = !known || sums || publish || t_hist.count == HISTORY;

@@ -32,6 +32,9 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
                 int cols, cudaStream_t stream, const void *publish = nullptr);
 // forgets what earlier launches touched: the next call orders itself after everything in its stream
 void gemv_forget_history();
+// the stream's newest launch touches memory the history cannot describe and has itself waited for everything before it:
+// the next gemv on that stream waits for it (by griddepcontrol.wait)
+void gemv_history_everything(cudaStream_t stream);
 int gemv_launch_noalloc(int fmt_a, int fmt_x, const void *a, const void *x, float *y, int rows, int cols, cudaStream_t stream);
 int gemv_noalloc_status(int *value);
 

@@ -37,27 +37,34 @@ __global__ void shard_flag_kernel(GemvPublish pub)
 // Thread w waits until word w of this rank's flag array has reached `epoch` (the words only grow), for at most `limit`
 // cycles; then it gives up, sets the status bit and returns.  The acquire pairs with the publisher's release: what
 // follows this kernel in the stream sees every row the peers stored.
+// The kernel is launched as a programmatic dependent of the publishing gemv before it: it is resident and polling while
+// that gemv still runs (the peers' flags do not depend on it), lets the kernel after it be scheduled at once, and only at
+// its end waits for the gemv's completion, so that whatever follows it in the stream, waiting for this kernel, has
+// waited for both the peers' rows and this rank's own.
 __global__ void shard_wait_kernel(unsigned int *flags, int world, unsigned int epoch, long long limit, int *status)
 {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ unsigned int counted;
     if (epoch == 0) {           // the wait's number is counted on the device, as the publisher's is
         if (threadIdx.x == 0) counted = atomicAdd(flags + QB200_SHARD_MAX + 1, 1u) + 1u;
         __syncthreads();
         epoch = counted;
     }
-    if (threadIdx.x >= world) return;
-    const unsigned int *f = flags + threadIdx.x;
-    const long long start = clock64();
-    for (;;) {
-        unsigned int v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-        if ((int)(v - epoch) >= 0) return;
-        if (clock64() - start > limit) {
-            atomicOr(status, STATUS_SHARD_WAIT);
-            return;
+    if (threadIdx.x < world) {
+        const unsigned int *f = flags + threadIdx.x;
+        const long long start = clock64();
+        for (;;) {
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if ((int)(v - epoch) >= 0) break;
+            if (clock64() - start > limit) {
+                atomicOr(status, STATUS_SHARD_WAIT);
+                break;
+            }
+            __nanosleep(50);
         }
-        __nanosleep(100);
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 int shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const void *peers_v, unsigned int epoch,
@@ -86,8 +93,22 @@ int shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int row
 int shard_wait(const void *peers_v, unsigned int epoch, long long limit_cycles, cudaStream_t stream)
 {
     const qb200_shard_peers_t *peers = (const qb200_shard_peers_t *)peers_v;
-    shard_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[peers->rank], peers->world, epoch, limit_cycles > 0 ? limit_cycles : WAIT_CYCLES, g_shard_status);
-    return (int)cudaGetLastError();
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, shard_wait_kernel, peers->flags[peers->rank], peers->world, epoch,
+                                       limit_cycles > 0 ? limit_cycles : WAIT_CYCLES, g_shard_status);
+    // everything launched so far on this stream is complete once this kernel is: the next gemv may wait for it by
+    // griddepcontrol.wait alone
+    if (!e) gemv_history_everything(stream);
+    return (int)e;
 }
 
 }  // namespace qb
