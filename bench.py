@@ -47,9 +47,7 @@ L2_BYTES = 126e6
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the gemv on the 8192 x 8192 Q4_0 matrix (ncu, profiles/):
 # 37 852 160 bytes against 37 814 272 algorithmic, a ratio the larger matrix shares (the kernel reads every byte once)
 TRAFFIC_RATIO = 37852160 / 37814272
-# tcgen05.mma kind::i8, M 128, N 128, K 32 from shared memory with nothing else on the SM: 64.0 cycles an instruction
-# (profiles/tcgen05_mma_i8_rate.md) = 16384 int8 operations a cycle and SM
-MMA_OPS_PER_CYCLE_SM = 2 * 128 * 128 * 32 / 64.0
+MMA_OPS = 2 * 128 * 128 * 32                              # int8 operations of one tcgen05.mma of the product's shape
 
 
 def measured_peaks():
@@ -280,7 +278,16 @@ def gemv_record(ops, torch, timer, fmt, rows, cols, steps, warmup, peak, chained
     return out
 
 
-def abt_record(ops, torch, timer, fmt_b, m, n, k, sm_count, clock_mhz):
+def tensor_peak(ops, clock_mhz):
+    """Dense int8 peak from the measured rate of the product's own tensor instruction (qb200_tensor_rate), at the max SM clock."""
+    cycles = C.c_double(0.0)
+    ops.gpu.check(ops.lib.qb200_tensor_rate(C.byref(cycles)), "tensor_rate")
+    if cycles.value <= 0:
+        return None, None
+    return MMA_OPS / cycles.value * ops.gpu.caps.sm_count * clock_mhz * 1e6 / 1e12, cycles.value
+
+
+def abt_record(ops, torch, timer, fmt_b, m, n, k, peak_measured):
     """A.B^T with Q8_0 activations: operands re-laid on every call, and weights prepacked once."""
     dev = timer.dev
     a = torch.from_numpy(B.make_weights(B.Q8_0, m, k, 5000)).to(dev)
@@ -307,11 +314,10 @@ def abt_record(ops, torch, timer, fmt_b, m, n, k, sm_count, clock_mhz):
     every = timed(lambda: ops.MatMulBlocks(B.Q8_0, a, b, c, m, n, k, fmt_b=fmt_b, workspace=ws, workspace_bytes=need))
     pre = timed(lambda: ops.MatMulBlocksPrepacked(B.Q8_0, a, packed, c, m, n, k, fmt_b=fmt_b, workspace=ws_a, workspace_bytes=need_a))
     ops_count = 2.0 * m * n * k
-    peak_measured = MMA_OPS_PER_CYCLE_SM * sm_count * clock_mhz * 1e6 / 1e12
     return {"shape": f"Q8_0 x {B.NAMES[fmt_b]}  M {m} N {n} K {k}", "us_packed_every_call": every * 1e6, "us_weights_prepacked": pre * 1e6,
             "int8_TOPS": ops_count / pre / 1e12, "int8_TOPS_packed_every_call": ops_count / every / 1e12,
-            "frac_of_nominal_4500": ops_count / pre / 1e12 / 4500.0, "frac_of_measured_mma_rate": ops_count / pre / 1e12 / peak_measured,
-            "peak_measured_TOPS": peak_measured}
+            "frac_of_nominal_4500": ops_count / pre / 1e12 / 4500.0,
+            "frac_of_measured_mma_rate": ops_count / pre / 1e12 / peak_measured if peak_measured else None}
 
 
 def abt_cpu_baseline(seconds=8.0):
@@ -342,6 +348,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-extra", action="store_true", help="only the headline (profiling runs)")
+    ap.add_argument("--leg", default=None, choices=["c2-chained", "abt"],
+                    help="run one small leg alone and print its record (profiling runs): the Q4_0 8192 x 8192 gemv with calls chained "
+                         "through y, or the Q8_0 x Q8_0 A.B^T of configs[2] at M 512")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     args.steps = max(args.steps, 1)
@@ -368,6 +377,14 @@ def main():
     side = torch.cuda.Stream(device=dev)
     timer = Timer(torch, dist, world, dev, side)
     peak, peak_kind = measured_peaks()
+    if args.leg:
+        if args.leg == "c2-chained":
+            rec = gemv_record(ops, torch, timer, B.Q4_0, 8192, 8192, 3, 3, peak, chained=True)
+        else:
+            rec = abt_record(ops, torch, timer, B.Q8_0, 512, 11008, 4096, tensor_peak(ops, 1965.0)[0])
+        if rank == 0:
+            print(json.dumps({"leg": args.leg, "record": rec}), flush=True)
+        return
 
     # ---- the rank's shard of every layer's matrix, x, and its copy of y
     plan = ShardPlan(N5, world)
@@ -509,10 +526,13 @@ def main():
                         (B.Q4_K, 4096, 11008), (B.Q6_K, 4096, 4096), (B.Q6_K, 11008, 4096), (B.Q6_K, 4096, 11008), (B.Q4_0, 28669, 8160)]]
             configs.append(gemv_record(ops, torch, timer, B.Q8_0, 4096, 4096, 3, 3, peak, chained=True))
             clock = clocks.get("sm_max_mhz") or 1965.0
-            abt = {"configs2": [abt_record(ops, torch, timer, B.Q8_0, m, 11008, 4096, ops.gpu.caps.sm_count, clock) for m in (512, 2048, 128)],
-                   "configs4": [abt_record(ops, torch, timer, B.Q4_0, m, N5, K5, ops.gpu.caps.sm_count, clock) for m in (64, 512)],
-                   "roofline": {"bound": "tensor", "unit": "TOP/s", "peak_nominal": 4500.0,
-                                "peak_kind": "nominal dense int8; peak_measured_TOPS = the measured tcgen05.mma rate x SMs x the max SM clock"}}
+            peak_mma, mma_cycles = tensor_peak(ops, clock)
+            abt = {"configs2": [abt_record(ops, torch, timer, B.Q8_0, m, 11008, 4096, peak_mma) for m in (512, 2048, 128, 16)],
+                   "configs4": [abt_record(ops, torch, timer, B.Q4_0, m, N5, K5, peak_mma) for m in (8, 64, 512)],
+                   "roofline": {"bound": "tensor", "unit": "TOP/s", "peak_nominal": 4500.0, "peak_measured": peak_mma,
+                                "cycles_per_mma_128x128x32": mma_cycles,
+                                "peak_kind": "nominal dense int8; peak_measured = the rate of the product's tcgen05.mma measured in this run "
+                                             "(qb200_tensor_rate) x SMs x the max SM clock"}}
             if not args.no_cpu:
                 abt["cpu_baseline"] = abt_cpu_baseline()
 

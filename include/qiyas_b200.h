@@ -197,6 +197,12 @@ int qb200_matmul_blocks_batched(int fmt_a, int fmt_b, const void *a, const void 
 int qb200_matmul_block_sums(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int32_t *sums, int m, int n, int k,
                             void *stream);
 
+/* No counterpart in the reference.  The tensor pipe's own rate on the bound device, for rooflines: clock cycles one
+ * tcgen05.mma kind::i8 of the product's shape (M 128, N 128, K 32: 2^20 int8 operations) takes on one multiprocessor when
+ * nothing else runs (a short kernel, a few microseconds, synchronizes the default stream); 0 when the measurement did
+ * not complete.  Dense int8 peak = 2^20 / cycles x multiprocessors x SM clock. */
+int qb200_tensor_rate(double *cycles_per_mma);
+
 /* ---- codecs -----------------------------------------------------------------------------
  * qb200_encode: Ptx.LanesToBlock, the `Back` step (src/Ptx.Blocks.cs:11-331, src/GpuOps.cs:964-975):
  * n f32 lanes -> whole blocks of fmt, zeros read past n; byte-for-byte the CPU encoder

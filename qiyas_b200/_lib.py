@@ -54,6 +54,7 @@ SIGNATURES = {
     "qb200_ipc_export": (_I, [_P, _P]),
     "qb200_ipc_import": (_I, [_P, C.POINTER(_P)]),
     "qb200_ipc_close": (_I, [_P]),
+    "qb200_tensor_rate": (_I, [C.POINTER(C.c_double)]),
     "qb200_encode": (_I, [_I, _P, _P, _L, _P]),
     "qb200_decode": (_I, [_I, _P, _P, _L, _P]),
     "qb200_malloc": (_I, [C.POINTER(_P), _Z]),

@@ -916,6 +916,64 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
     if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
+// ---------------------------------------------------------------------------------- the tensor pipe's own rate
+
+// One thread of one block issues `iters` x 4 tcgen05.mma kind::i8 (M 128, N 128, K 32, the product's instruction) on
+// whatever bytes shared memory holds, into two alternating accumulators, commits once and waits for the commit with a
+// bound: clock cycles from the first issue to the completion, what the tensor pipe of one multiprocessor does with no
+// epilogue, no copies and nothing else on the chip.  out[0] = cycles, out[1] = 1 when the wait completed.
+__global__ void __launch_bounds__(128, 1) mma_rate_kernel(int iters, long long *out)
+{
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t base = smem_u32(smem), bar = base, holder = base + 64;
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        mbar_fence_init();
+    }
+    for (int i = threadIdx.x; i < 16384 / 4; i += 128) ((uint32_t *)(smem + 1024))[i] = 0x01010101u * (uint32_t)(i & 3);
+    fence_proxy_async();
+    if (threadIdx.x < 32) tmem_alloc(holder, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *(volatile uint32_t *)(smem + 64);
+    if (threadIdx.x == 0) {
+        const uint32_t idesc = idesc_of(0, TILE, 128);
+        const uint64_t a = smem_desc(base + 1024, 128, 256), b = smem_desc(base + 1024 + 8192, 128, 256);
+        const long long t0 = clock64();
+        for (int i = 0; i < iters; i++) {
+#pragma unroll
+            for (int k = 0; k < 4; k++) mma_issue<0>(tmem + (uint32_t)(k & 1) * 128, a, b, idesc, 0u);
+        }
+        mma_commit(bar);
+        bool done = false;
+        while (!(done = mbar_try_wait(bar, 0u)) && clock64() - t0 < WAIT_CYCLES) { }
+        out[0] = clock64() - t0;
+        out[1] = done ? 1 : 0;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) tmem_dealloc(tmem, 512);
+}
+
+// Cycles one tcgen05.mma kind::i8 of the product's shape takes on one multiprocessor (64.0 at the rate the data sheet's
+// dense int8 figure implies); 0 when the measurement did not complete.  Allocates 16 bytes for its result.
+int matmul_mma_rate(double *cycles_per_mma, cudaStream_t stream)
+{
+    const int iters = 512;
+    long long *out = nullptr, host[2] = { 0, 0 };
+    cudaError_t e = cudaMalloc((void **)&out, 2 * sizeof(long long));
+    if (e) return (int)e;
+    if ((e = cudaFuncSetAttribute(mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768))) { cudaFree(out); return (int)e; }
+    mma_rate_kernel<<<1, 128, 32768, stream>>>(iters, out);
+    if (!(e = cudaGetLastError())) e = cudaMemcpyAsync(host, out, sizeof host, cudaMemcpyDeviceToHost, stream);
+    if (!e) e = cudaStreamSynchronize(stream);
+    cudaFree(out);
+    if (e) return (int)e;
+    *cycles_per_mma = host[1] ? (double)host[0] / (4.0 * iters) : 0.0;
+    return 0;
+}
+
 // ---------------------------------------------------------------------------------- host side
 
 static int *g_mm_status = nullptr;

@@ -82,6 +82,19 @@ def test_edges(oracle, m, n, k):
     check(oracle, B.Q8_0, B.Q8_0, m, n, k, 9 + m, f64=m * n * k < 1 << 24)
 
 
+@pytest.mark.parametrize("fmt_a,fmt_b", [(B.Q8_0, B.Q8_0), (B.Q4_0, B.Q4_0), (B.Q8_0, B.Q4_0), (B.Q4_0, B.Q8_0)])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 32), (5, 3, 96), (16, 257, 4096), (8, 1021, 8160), (13, 130, 1056), (16, 16, 8192), (2, 4099, 64)])
+def test_few_rows_of_a(oracle, fmt_a, fmt_b, m, n, k):
+    # m <= 16 takes the CUDA-core path (the weights stream once past activations held in shared memory): the same bits
+    a, b = operands(oracle, fmt_a, fmt_b, m, n, k, 900 + m + n)
+    c = matmul_gpu(fmt_a, fmt_b, a, b, m, n, k)
+    ref = oracle.matmul_blocks(fmt_a, fmt_b, a, b, m, n, k, order=1)
+    assert np.array_equal(c.view(np.uint32), ref.view(np.uint32))
+    # and the tensor-core path gives them too (the checking entry point always takes it)
+    c2, _ = matmul_gpu(fmt_a, fmt_b, a, b, m, n, k, want_sums=True) if m * n * (k // 32) <= 1 << 24 else (c, None)
+    assert np.array_equal(c2.view(np.uint32), ref.view(np.uint32))
+
+
 def test_caller_workspace(oracle):
     m, n, k = 70, 300, 512
     a, b = operands(oracle, B.Q8_0, B.Q8_0, m, n, k, 3)
