@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIBRARY = os.path.join(HERE, "libqiyas_b200.so")
-SOURCES = ["api.cu", "gemv.cu", "codecs.cu", "matmul.cu", "shard.cu", "smallm.cu"]
+SOURCES = ["api.cu", "gemv.cu", "codecs.cu", "matmul.cu", "shard.cu"]
 HEADERS = ["common.cuh", "launch.h", "encode_blocks.cuh", os.path.join("..", "..", "include", "qiyas_b200.h")]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--compiler-options", "-fPIC",
          "-Xptxas", "-v"]

@@ -151,7 +151,6 @@ int qb200_init(int device)
     if ((e = qb::gemv_init(g_caps.sm_count, g_caps.max_shared_bytes, g_status))) return cuda_fail(e, "gemv attributes");
     if ((e = qb::matmul_init(g_caps.sm_count, g_caps.max_shared_bytes, g_status))) return cuda_fail(e, "matmul attributes");
     if ((e = qb::shard_init(g_status))) return cuda_fail(e, "shard set-up");
-    if ((e = qb::smallm_init(g_caps.sm_count, g_caps.max_shared_bytes))) return cuda_fail(e, "small-m attributes");
     g_ready = true;
     t_error[0] = 0;
     return 0;
@@ -291,8 +290,6 @@ int qb200_matmul_blocks(int fmt_a, int fmt_b, const void *a, const void *b, floa
     int rc = check_matmul(fmt_a, fmt_b, a, b, c, m, n, k);
     if (rc) return rc;
     // a few rows of A: the weights stream once past activations held on the chip, no re-laying, no tensor tile of padding
-    if (qb::smallm_takes(fmt_a, fmt_b, m, k))
-        return finish(qb::smallm_launch(fmt_a, fmt_b, a, b, c, m, n, k, (cudaStream_t)stream), "matmul_blocks");
     if ((rc = take_workspace(workspace, workspace_bytes, qb::matmul_workspace_bytes(fmt_b, m, n, k, ONE, false)))) return rc;
     return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c, nullptr, 0, nullptr, m, n, k, ONE, workspace, (cudaStream_t)stream), "matmul_blocks");
 }

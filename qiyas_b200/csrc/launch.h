@@ -63,9 +63,5 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
 // clock cycles a tcgen05.mma kind::i8 (M 128, N 128, K 32) takes on one multiprocessor, measured now
 int matmul_mma_rate(double *cycles_per_mma, cudaStream_t stream);
 
-// A.B^T for m <= 16 rows of A on the CUDA cores (smallm.cu): same results as matmul_launch, raw operands, no workspace
-cudaError_t smallm_init(int sm_count, int max_smem);
-bool smallm_takes(int fmt_a, int fmt_b, int m, int k);
-int smallm_launch(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int m, int n, int k, cudaStream_t stream);
 
 }  // namespace qb

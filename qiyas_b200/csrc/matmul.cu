@@ -40,6 +40,7 @@ namespace qb {
 constexpr int TILE = 128;            // rows of A a tile = lanes of tensor memory
 constexpr int BNMAX = 128;           // columns of the widest piece = columns of one accumulator in tensor memory
 constexpr int EPI_WARPS = 16;
+constexpr int GROUP = 8;             // k-blocks a group of B with f16 scales = f16 a 16-byte scale row
 constexpr int MM_THREADS = 32 * (2 + EPI_WARPS);     // warp 0 producer, warp 1 MMA, the rest epilogue
 constexpr uint32_t MM_HEADER = 1024;
 constexpr uint32_t MM_SMEM_MAX = 232448;           // 227 KB of shared memory a block
@@ -69,7 +70,8 @@ struct Cfg {
     static constexpr int TCOLS = TCS ? 2 * BNMAX : BNMAX;   // tensor-memory columns a k-block: the sums, and the scale products
     static constexpr int NT = 512 / TCOLS;               // k-blocks in flight in tensor memory
     static constexpr uint32_t A_KB = TILE * KC * 16, B_KB = BNMAX * KC * 16;      // bytes of codes a k-block
-    static constexpr uint32_t A_CODES = KS * A_KB, B_CODES = KS * B_KB, A_SC = KS * TILE * SW, B_SC = KS * BNMAX * SW;
+    // TCS: B's scale rows hold eight k-blocks each, one set of rows serves the whole stage
+    static constexpr uint32_t A_CODES = KS * A_KB, B_CODES = KS * B_KB, A_SC = KS * TILE * SW, B_SC = (TCS ? 1 : KS) * BNMAX * SW;
     static constexpr uint32_t O_B = A_CODES, O_SA = O_B + B_CODES, O_SB = O_SA + A_SC, O_UA = O_SB + B_SC, O_MB = O_UA + A_SC;
     static constexpr uint32_t STAGE = A_CODES + B_CODES + (MINS ? 2 : 1) * (A_SC + B_SC);
     static constexpr uint32_t PATCH = ((KIND == 0 && HALF) || TCS) ? 2048 : 0;    // zeros: the half of K an instruction reads but the operand does not have
@@ -79,18 +81,20 @@ struct Cfg {
     static constexpr uint32_t SMEM = O_PATCH + PATCH;
     static_assert(S >= 2, "the ring needs two stages");
     static_assert(2 * S + 2 * NT + 2 <= 64, "barriers fit the header");
+    static_assert(!TCS || GROUP % KS == 0, "a stage lies inside one group of k-blocks");
 };
 
 struct PackedA {             // tile-major: [tile][k-block][16 row groups][KC][8 rows][16 bytes], scales [tile][k-block][128]
     const uint8_t *codes;
-    const float *scales;     // f32 each, or 16-byte rows for the tensor cores (TCS)
+    const float *scales;     // f32 each, or 16-byte rows for the tensor cores (TCS); the few-rows kernel's A is `codes` alone (LAY_FEW)
     const float *extra;      // scale * sum of the block's codes (the factor of B's min); null unless B is Q4_K
 };
-struct PackedB {             // k-block-major: [k-block][rows_pad / 8 row groups][KC][8 rows][16 bytes], scales [k-block][rows_pad]
+struct PackedB {             // LAY_KBLOCK (codes, scales, extra) or LAY_GROUPED (codes only: the slabs hold the scale rows)
     const uint8_t *codes;
     const float *scales;
     const float *extra;      // Q4_K: dmin * m
     int rows_pad;
+    int groups;              // LAY_GROUPED: groups of eight k-blocks a tile
 };
 
 struct MatmulArgs {
@@ -113,42 +117,88 @@ struct MatmulArgs {
 
 // ---------------------------------------------------------------------------------- step 1: operands for the tensor cores
 
+// Layouts of a packed operand.
+//  LAY_TILE: A of the 128-row-tile kernel.  Codes [tile][k-block][16 row groups][kc][8 rows][16 bytes]; scales
+//            [tile][k-block][128], f32 each or (tcs) a 16-byte row of eight f16 with the scale at position k-block % 8.
+//  LAY_KBLOCK: B whose scale products are taken on the CUDA cores (Q4_K, Q6_K).  Codes [k-block][rows_pad / 8 row
+//            groups][kc][8][16]; f32 planes [k-block][rows_pad].
+//  LAY_GROUPED: B with plain f16 block scales (Q8_0, Q4_0).  One slab a 128-row tile and group of eight k-blocks: the
+//            eight k-blocks' codes (each [16 row groups][kc][8][16]) and then 128 scale rows of eight f16, the scale of
+//            k-block 8 g + j at position j (zero past the last k-block).  A row of B and a row of A whose only non-zero
+//            is at position j multiply to exactly sB * sA of that k-block.
+//  LAY_FEW: A of the few-rows kernel, bn rows.  One slab a group of eight k-blocks: the eight k-blocks' codes (each
+//            [bn / 8 row groups][kc][8][16]), then 8 x bn scale rows: row j * bn + r has row r's scale of k-block
+//            8 g + j at position j and zeros elsewhere, so that one instruction over the rows of several k-blocks
+//            leaves every k-block's scale products side by side.
+enum { LAY_TILE = 0, LAY_KBLOCK = 1, LAY_GROUPED = 2, LAY_FEW = 3 };
+
 struct PackTarget {
     uint8_t *codes;
     float *scales;
     float *extra;
-    int tcs;                 // scales as 16-byte rows [f16 d, 0 x 7] (operands of the tensor cores' scale product) instead of f32
+    int layout;
+    int tcs;                 // LAY_TILE: scales as 16-byte rows for the tensor cores' scale product instead of f32
     int rows_pad;
     int kbs;                 // k-blocks a row in the packed operand
     int kc;                  // k-chunks a k-block
-    int tile_major;
     int kind;
+    int bn;                  // LAY_FEW: rows kept
 };
+
+__host__ __device__ inline size_t grouped_slab(int kc) { return (size_t)GROUP * TILE * kc * 16 + TILE * 16; }
+__host__ __device__ inline size_t few_slab(int bn, int kc) { return (size_t)GROUP * bn * kc * 16 + (size_t)GROUP * bn * 16; }
+__host__ __device__ inline int groups_of(int kbs) { return (kbs + GROUP - 1) / GROUP; }
 
 // Byte offset of k-chunk `kci` (counted along the whole row) of row r.
 __device__ __forceinline__ size_t chunk_offset(const PackTarget &t, int r, int kci)
 {
     const int kblock = kci / t.kc, kc = kci - kblock * t.kc;
+    if (t.layout == LAY_GROUPED) {
+        const size_t slab = ((size_t)(r / TILE) * groups_of(t.kbs) + kblock / GROUP) * grouped_slab(t.kc);
+        return slab + (size_t)(kblock % GROUP) * (TILE * t.kc * 16) + (size_t)(((r % TILE) / 8) * t.kc + kc) * 128 + (size_t)(r & 7) * 16;
+    }
+    if (t.layout == LAY_FEW) {
+        const size_t slab = (size_t)(kblock / GROUP) * few_slab(t.bn, t.kc);
+        return slab + (size_t)(kblock % GROUP) * (t.bn * t.kc * 16) + (size_t)((r / 8) * t.kc + kc) * 128 + (size_t)(r & 7) * 16;
+    }
     size_t group;
-    if (t.tile_major) group = ((size_t)(r / TILE) * t.kbs + kblock) * (TILE / 8) + (r % TILE) / 8;
+    if (t.layout == LAY_TILE) group = ((size_t)(r / TILE) * t.kbs + kblock) * (TILE / 8) + (r % TILE) / 8;
     else group = (size_t)kblock * (t.rows_pad / 8) + r / 8;
     return (group * t.kc + kc) * 128 + (size_t)(r & 7) * 16;
 }
+// Index of (row, k-block) in a plane of LAY_TILE / LAY_KBLOCK.
 __device__ __forceinline__ size_t scale_offset(const PackTarget &t, int r, int kblock)
 {
-    if (t.tile_major) return ((size_t)(r / TILE) * t.kbs + kblock) * TILE + r % TILE;
+    if (t.layout == LAY_TILE) return ((size_t)(r / TILE) * t.kbs + kblock) * TILE + r % TILE;
     return (size_t)kblock * t.rows_pad + r;
 }
-// The scale of (row, k-block): an f32, or (tcs) the f16 bits it came from as the first of eight halves, the rest zero.
+// A 16-byte row of eight f16: `bits` at position j, zeros elsewhere.
+__device__ __forceinline__ uint4 scale_row(uint32_t bits, int j)
+{
+    const uint32_t w = (bits & 0xFFFFu) << (16 * (j & 1));
+    return make_uint4(j >> 1 == 0 ? w : 0u, j >> 1 == 1 ? w : 0u, j >> 1 == 2 ? w : 0u, j >> 1 == 3 ? w : 0u);
+}
+// The scale of (row, k-block): d as an f32, or its f16 bits where the layout feeds the tensor cores' scale product.
 __device__ __forceinline__ void store_scale(const PackTarget &t, int r, int kblock, float d, uint32_t d_bits)
 {
-    if (t.tcs) ((uint4 *)t.scales)[scale_offset(t, r, kblock)] = make_uint4(d_bits & 0xFFFFu, 0, 0, 0);
+    const int j = kblock % GROUP;
+    if (t.layout == LAY_GROUPED) {
+        const size_t slab = ((size_t)(r / TILE) * groups_of(t.kbs) + kblock / GROUP) * grouped_slab(t.kc);
+        uint16_t *row = (uint16_t *)(t.codes + slab + (size_t)GROUP * TILE * t.kc * 16 + (size_t)(r % TILE) * 16);
+        row[j] = (uint16_t)d_bits;
+        if (kblock == t.kbs - 1) for (int z = j + 1; z < GROUP; z++) row[z] = 0;      // positions past the last k-block multiply as zeros
+    } else if (t.layout == LAY_FEW) {
+        if (r >= t.bn) return;
+        const size_t slab = (size_t)(kblock / GROUP) * few_slab(t.bn, t.kc);
+        *(uint4 *)(t.codes + slab + (size_t)GROUP * t.bn * t.kc * 16 + (size_t)(j * t.bn + r) * 16) = scale_row(d_bits, j);
+    } else if (t.tcs) ((uint4 *)t.scales)[scale_offset(t, r, kblock)] = scale_row(d_bits, j);
     else t.scales[scale_offset(t, r, kblock)] = d;
 }
 
 // 16 int8 values (four words) as one k-chunk (int8) or two (f16), starting at k-chunk kci0 of row r.
 __device__ __forceinline__ void store_codes16(const PackTarget &t, int r, int kci0, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3)
 {
+    if (t.layout == LAY_FEW && r >= t.bn) return;
     if (t.kind == 0) {
         *(uint4 *)(t.codes + chunk_offset(t, r, kci0)) = make_uint4(w0, w1, w2, w3);
         return;
@@ -648,13 +698,29 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                 if (MM_PROBE(p) & 4) b_code_bytes = 0;          // tuning: no copies of B's codes
                 if (MM_PROBE(p) & 64) b_sc_bytes = 0;           // tuning: no copies of B's scales
                 if (lane == 0)
-                    mbar_arrive_expect_tx(bar, a_code_bytes + (MINS ? 2 : 1) * a_sc_bytes + (uint32_t)nkb * (b_code_bytes + (MINS ? 2 : 1) * b_sc_bytes));
+                    mbar_arrive_expect_tx(bar, a_code_bytes + (MINS ? 2 : 1) * a_sc_bytes + (uint32_t)nkb * b_code_bytes +
+                                                   (TCS ? 1u : (uint32_t)nkb * (MINS ? 2 : 1)) * b_sc_bytes);
                 __syncwarp();
                 const size_t a_at = (size_t)mt * p.kb + kb0;
                 if (lane == 0) bulk_g2s(dst, a_codes + a_at * G::A_KB, a_code_bytes, bar);
                 else if (lane == 1) bulk_g2s(dst + G::O_SA, a_scales + a_at * TILE * G::SW, a_sc_bytes, bar);
                 else if (lane == 2) { if (MINS) bulk_g2s(dst + G::O_UA, a_extra + a_at * TILE * G::SW, a_sc_bytes, bar); }
-                else {
+                else if (TCS) {
+                    // B's slabs (a 128-row tile and group of eight k-blocks each): a piece's rows lie in one slab, or in two
+                    // when it crosses a multiple of 128 (lanes 16.. copy the second part); codes a k-block, scale rows a stage
+                    const int part = lane >> 4, job = (lane & 15) - 3, kk = job >> 1, what = job & 1;
+                    const int first = min(bn, TILE - n0 % TILE);                 // rows in the first slab
+                    const int rows_here = part ? bn - first : first, row0 = part ? 0 : n0 % TILE, done = part ? first : 0;
+                    if (job >= 0 && kk < nkb && rows_here > 0 && !(what == 0 ? b_code_bytes == 0 : b_sc_bytes == 0)) {
+                        const size_t kb = (size_t)(kb0 + kk);
+                        const uint8_t *slab = b_codes + ((size_t)(n0 / TILE + part) * p.b.groups + kb / GROUP) * grouped_slab(KC);
+                        if (what == 0)
+                            bulk_g2s(dst + G::O_B + kk * G::B_KB + done * (KC * 16), slab + (kb % GROUP) * (size_t)(TILE * KC * 16) + (size_t)(row0 / 8) * (KC * 128),
+                                     (uint32_t)rows_here * KC * 16, bar);
+                        else if (kk == 0)
+                            bulk_g2s(dst + G::O_SB + done * 16, slab + (size_t)GROUP * TILE * KC * 16 + (size_t)row0 * 16, (uint32_t)rows_here * 16, bar);
+                    }
+                } else {
                     constexpr int NC = MINS ? 3 : 2;
                     const int job = lane - 3, kk = job / NC, what = job - kk * NC;
                     if (kk < nkb) {
@@ -705,7 +771,6 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                     // is one slab further and the patch that much nearer
                     uint64_t sa_desc = smem_desc(a_smem + G::O_SA, patch - (a_smem + G::O_SA), 128), sb_desc = smem_desc(a_smem + G::O_SB, patch - (a_smem + G::O_SB), 128);
                     constexpr uint64_t SA_STEP = (uint64_t)((TILE * 16) >> 4) - ((uint64_t)((TILE * 16) >> 4) << 16);
-                    constexpr uint64_t SB_STEP = (uint64_t)((BNMAX * 16) >> 4) - ((uint64_t)((BNMAX * 16) >> 4) << 16);
 #pragma unroll
                     for (int kk = 0; kk < KS; kk++) {
                         if (kk < nkb) {
@@ -731,8 +796,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                             if (TCS && !(MM_PROBE(p) & 8)) {
                                 // the scale products: rows [d, 0 x 7] of A's and B's scales, the other half of K from the zeros
                                 mma_issue<1>(d + BNMAX, sa_desc, sb_desc, idesc_s, 0u);
-                                sa_desc += SA_STEP;
-                                sb_desc += SB_STEP;
+                                sa_desc += SA_STEP;      // B's rows hold the group's eight scales: the same rows for every k-block
                             }
                             const long long c1 = MM_CLOCK();
                             mma_commit(tfull0 + 8 * t);
@@ -916,6 +980,260 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
     if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
+// ---------------------------------------------------------------------------------- few rows of A: the operands change sides
+
+// With few rows of A (m <= 64: a decoding batch) a 128-row tile of A is mostly padding, and the kernel above still pays
+// a full accumulator and a full handshake a k-block.  Here the operands change sides: the 128 rows of a tile of B are the
+// tensor instruction's M (the lanes of tensor memory), the rows of A its N = BN (16, 32 or 64).  The sums are the same
+// integers and the scale product commutes exactly, so acc = fma(float(D), sB*sA, acc) is the same f32 as above.
+// A k-block's sums now take BN columns of tensor memory, so BATCH = 64 / BN k-blocks form a batch of 64 + 64 columns:
+// BATCH instructions for the sums, ONE for the scale products of all of them (B's scale rows hold the group's eight
+// scales; A's rows for k-block j are zero except at position j: LAY_FEW), one commit, one barrier round trip, one wait of
+// the epilogue; NB batches are in flight.  Thread (q, lane) of the four epilogue warps owns row n0 + 32 q + lane of B,
+// i.e. column n of C, and keeps its BN accumulators in registers; a warp's stores of one row of C are 32 consecutive
+// floats.  A shared-memory stage is one group of eight k-blocks: B's slab in one copy (read once from HBM), A's in another.
+template <int BN>
+struct FewCfg {
+    static constexpr int KS = GROUP;                               // k-blocks a shared-memory stage
+    static constexpr int BATCH = 64 / BN;                          // k-blocks a batch in tensor memory
+    static constexpr int BCOLS = 128;                              // its columns: 64 of sums, 64 of scale products
+    static constexpr int NB = 512 / BCOLS;                         // batches in flight
+    static constexpr uint32_t B_KB = TILE * 32, A_KB = BN * 32;    // bytes of codes a k-block
+    static constexpr uint32_t B_SLAB = GROUP * B_KB + TILE * 16, A_SLAB = GROUP * A_KB + GROUP * BN * 16;
+    static constexpr uint32_t O_BS = GROUP * B_KB, O_A = B_SLAB, O_AS = O_A + GROUP * A_KB;
+    static constexpr uint32_t STAGE = B_SLAB + A_SLAB;
+    static constexpr uint32_t PATCH = 2048;
+    static constexpr int S_FIT = (int)((MM_SMEM_MAX - MM_HEADER - PATCH) / STAGE);
+    static constexpr int S = S_FIT > 8 ? 8 : S_FIT;
+    static constexpr uint32_t O_PATCH = MM_HEADER + S * STAGE;
+    static constexpr uint32_t SMEM = O_PATCH + PATCH;
+    static_assert(BN == 16 || BN == 32 || BN == 64, "the batch is 64 columns of sums");
+    static_assert(S >= 2 && 2 * S + 2 * NB + 2 <= 64, "barriers fit the header");
+};
+constexpr int FEW_THREADS = 32 * 6;              // warp 0 producer, warp 1 MMA, four epilogue warps
+
+// Nothing is emitted: the registers pass through the statement, so that what uses them stays below the wait before it.
+__device__ __forceinline__ void pin16(uint32_t *v)
+{
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
+                      "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]) :: "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N])
+{
+    static_assert(N % 16 == 0, "whole reads of 16 columns");
+#pragma unroll
+    for (int c = 0; c < N; c += 16) tmem_ld16(taddr + c, *(uint32_t(*)[16])(v + c));
+}
+
+template <int BN>
+__global__ void __launch_bounds__(FEW_THREADS, 1) fewrows_kernel(const MatmulArgs p)
+{
+    using G = FewCfg<BN>;
+    constexpr int S = G::S, KS = G::KS, BATCH = G::BATCH, NB = G::NB;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = smem_u32(smem);
+    const uint32_t full0 = base, empty0 = base + 8 * S, tfull0 = base + 16 * S, tempty0 = tfull0 + 8 * NB;
+    const uint32_t holder = tempty0 + 8 * NB;
+    volatile int *abort_flag = (volatile int *)(smem + 768);
+    volatile uint32_t *holder_ptr = (volatile uint32_t *)(smem + (holder - base));
+    constexpr int wmode = MM_WAIT_MODE;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int t = 0; t < NB; t++) {
+            mbar_init(tfull0 + 8 * t, 1);
+            mbar_init(tempty0 + 8 * t, 4);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    for (int i = threadIdx.x; i < (int)G::PATCH / 16; i += FEW_THREADS) *(uint4 *)(smem + G::O_PATCH + i * 16) = make_uint4(0, 0, 0, 0);
+    fence_proxy_async();
+    if (warp == 1) tmem_alloc(holder, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *holder_ptr;
+    uint8_t *ring = smem + MM_HEADER;
+    const int ntiles = p.b.rows_pad / TILE, tiles = p.batch * ntiles;       // a tile: 128 rows of B of one product
+
+    if (warp == 0) {
+        // ---- producer: a stage is a group of eight k-blocks: the slab of the tile of B (codes and scale rows, one copy)
+        // and A's slab of the group (another)
+        int sc = 0;
+        bool alive = true;
+        long long w_empty = 0;
+        const long long t_begin = MM_CLOCK();
+        for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
+            const int bi = tile / ntiles, nt = tile - bi * ntiles;
+            const uint8_t *a_slabs = p.a.codes + bi * p.a_stride;
+            const uint8_t *b_slabs = p.b.codes + bi * p.b_stride + (size_t)nt * p.b.groups * G::B_SLAB;
+            for (int g = 0; g < p.b.groups && alive; g++, sc++) {
+                const int s = sc % S;
+                int ok = 1;
+                const long long w0 = MM_CLOCK();
+                if (lane == 0 && sc >= S) ok = mm_wait(empty0 + 8 * s, (uint32_t)(sc / S - 1) & 1u, abort_flag, p.status, wmode) ? 1 : 0;
+                w_empty += MM_CLOCK() - w0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { alive = false; break; }
+                const uint32_t dst = smem_u32(ring + (size_t)s * G::STAGE), bar = full0 + 8 * s;
+                if (lane == 0) {
+                    const bool with_a = !(MM_PROBE(p) & 1);
+                    mbar_arrive_expect_tx(bar, G::B_SLAB + (with_a ? G::A_SLAB : 0u));
+                    bulk_g2s(dst, b_slabs + (size_t)g * G::B_SLAB, G::B_SLAB, bar);
+                    if (with_a) bulk_g2s(dst + G::O_A, a_slabs + (size_t)g * G::A_SLAB, G::A_SLAB, bar);
+                }
+            }
+        }
+        if (lane == 0) { MM_TRACE(p, 0, w_empty); MM_TRACE(p, 1, MM_CLOCK() - t_begin); MM_TRACE(p, 2, (long long)sc); }
+        if (*abort_flag && lane == 0) {          // let the copies still in flight land before the block exits
+            for (int it = max(0, sc - S); it < sc; it++) {
+                long long start = clock64();
+                while (!mbar_try_wait(full0 + 8 * (it % S), (uint32_t)(it / S) & 1u) && clock64() - start < WAIT_CYCLES) { }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue: per k-block the sums (kind::i8, M 128, N BN, K 32); per batch the scale products of its k-blocks
+        // (kind::f16, N 64, K 16: the 16-byte scale rows, the other half of K from the patch of zeros) and one commit
+        if (lane == 0) {
+            int sc = 0, tc = 0, slot = 0;
+            uint32_t d = tmem;
+            bool alive = true;
+            long long w_full = 0, w_tempty = 0;
+            const long long t_begin = MM_CLOCK();
+            static_assert((NB & (NB - 1)) == 0, "batches in flight: a power of two");
+            constexpr uint64_t DESC_HI = (uint64_t)(128u >> 4) << 16 | (uint64_t)(256u >> 4) << 32 | (uint64_t)1 << 46;
+            const uint32_t patch = base + G::O_PATCH;
+            constexpr uint32_t idesc = idesc_of(0, TILE, BN), idesc_s = idesc_of(1, TILE, 64);
+            for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
+                for (int kb0 = 0; kb0 < p.kb && alive; kb0 += KS, sc++) {
+                    const int s = sc % S, nkb = min(KS, p.kb - kb0);
+                    const long long w0 = MM_CLOCK();
+                    if (!mm_poll(full0 + 8 * s, (uint32_t)(sc / S) & 1u, wmode & 3) &&
+                        !mm_wait(full0 + 8 * s, (uint32_t)(sc / S) & 1u, abort_flag, p.status, wmode)) { alive = false; break; }
+                    w_full += MM_CLOCK() - w0;
+                    tc_fence_after();
+                    // this thread's own instruction stream paces the block: descriptors advance by one addition a k-block;
+                    // B's scale rows are the same for the whole group, A's move a batch of rows on (and the patch that much nearer)
+                    const uint32_t st = smem_u32(ring + (size_t)s * G::STAGE);
+                    uint64_t bc = DESC_HI | (uint64_t)(st >> 4), ac = DESC_HI | (uint64_t)((st + G::O_A) >> 4);
+                    const uint64_t bs = smem_desc(st + G::O_BS, patch - (st + G::O_BS), 128);
+                    uint64_t as = smem_desc(st + G::O_AS, patch - (st + G::O_AS), 128);
+                    constexpr uint64_t AS_STEP = (uint64_t)((64 * 16) >> 4) - ((uint64_t)((64 * 16) >> 4) << 16);
+#pragma unroll
+                    for (int kk = 0; kk < KS; kk++) {
+                        if (kk < nkb) {
+                            const int j = kk % BATCH;
+                            if (j == 0) {
+                                slot = tc & (NB - 1);
+                                if (tc >= NB) {
+                                    const uint32_t par = (uint32_t)(tc / NB - 1) & 1u;
+                                    const long long w1 = MM_CLOCK();
+                                    if (!mm_poll(tempty0 + 8 * slot, par, wmode & 3) && !mm_wait(tempty0 + 8 * slot, par, abort_flag, p.status, wmode)) { alive = false; break; }
+                                    w_tempty += MM_CLOCK() - w1;
+                                    tc_fence_after();
+                                }
+                                d = tmem + (uint32_t)(slot * G::BCOLS);
+                            }
+                            mma_issue<0>(d + j * BN, bc, ac, idesc, 0u);
+                            bc += G::B_KB >> 4; ac += G::A_KB >> 4;
+                            if (j == BATCH - 1 || kk == nkb - 1) {
+                                // the rows of a k-block the group does not have give columns nobody reads
+                                if (!(MM_PROBE(p) & 8)) mma_issue<1>(d + 64, bs, as, idesc_s, 0u);
+                                as += AS_STEP;
+                                mma_commit(tfull0 + 8 * slot);
+                                tc++;
+                            }
+                        }
+                    }
+                    if (alive) mma_commit(empty0 + 8 * s);      // the stage is free once these products have run
+                }
+            }
+            MM_TRACE(p, 8, w_full); MM_TRACE(p, 9, w_tempty); MM_TRACE(p, 10, MM_CLOCK() - t_begin); MM_TRACE(p, 11, (long long)tc);
+        }
+    } else {
+        // ---- epilogue: warp q reads lanes 32 q .. 32 q + 31 of every batch
+        const int q = warp & 3;
+        const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
+        int tc = 0;
+        bool alive = true;
+        long long w_tfull = 0, w_ld = 0;
+        const long long t_begin = MM_CLOCK();
+        for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
+            const int bi = tile / ntiles, n0 = (tile - bi * ntiles) * TILE;
+            float acc[BN];
+#pragma unroll
+            for (int c = 0; c < BN; c++) acc[c] = 0.f;
+            for (int i = 0; i < p.kb && alive; i += BATCH, tc++) {
+                const int t = tc % NB, nb = min(BATCH, p.kb - i);
+                const uint32_t bar = tfull0 + 8 * t, par = (uint32_t)(tc / NB) & 1u;
+                const long long w0 = MM_CLOCK();
+                if (!mm_poll(bar, par, wmode & 3) && !mm_wait_lanes(bar, par, abort_flag, p.status, wmode)) { alive = false; break; }
+                const long long w1 = MM_CLOCK();
+                w_tfull += w1 - w0;
+                tc_fence_after();
+                const uint32_t at = tlane + (uint32_t)(t * G::BCOLS);
+                uint32_t v[BATCH][BN], x[BATCH][BN];
+#pragma unroll
+                for (int j = 0; j < BATCH; j++) {
+                    tmem_ld_cols<BN>(at + j * BN, v[j]);
+                    tmem_ld_cols<BN>(at + 64 + j * BN, x[j]);
+                }
+                tmem_ld_wait();
+                w_ld += MM_CLOCK() - w1;
+#pragma unroll
+                for (int j = 0; j < BATCH; j++) {
+#pragma unroll
+                    for (int c = 0; c < BN; c += 16) { pin16(v[j] + c); pin16(x[j] + c); }
+                }
+                tc_fence_before();
+                if (lane == 0) mbar_arrive(tempty0 + 8 * t);             // the batch has been read (warp-wide reads)
+#pragma unroll
+                for (int j = 0; j < BATCH; j++) {
+                    if (j < nb && !(MM_PROBE(p) & 4)) {
+#pragma unroll
+                        for (int c = 0; c < BN; c++) acc[c] = __fmaf_rn((float)(int32_t)v[j][c], __uint_as_float(x[j][c]), acc[c]);
+                    }
+                }
+            }
+            const int col = n0 + q * 32 + lane;
+            float *c_out = p.c + bi * p.c_stride;
+            if (alive && col < p.n) {
+#pragma unroll
+                for (int r = 0; r < BN; r++) if (r < p.m) c_out[(size_t)r * p.n + col] = acc[r];
+            }
+            if (p.cb) {
+                // `Back` for the tile: once the four warps have stored their lanes, the 128 threads encode the tile's blocks of
+                // 32 consecutive values of a row of C (n % 32 == 0: a block lies inside one warp's columns)
+                named_bar_sync(2, 128);
+                if (*abort_flag) { alive = false; break; }
+                const int bw = min(TILE, p.n - n0) / 32, tid = threadIdx.x - 64;
+                for (int idx = tid; idx < p.m * bw; idx += 128) {
+                    const int rr = idx / bw, bc = idx - rr * bw;
+                    const size_t first = bi * p.c_stride + (size_t)rr * p.n + n0 + bc * 32;
+                    float f[32];
+#pragma unroll
+                    for (int c = 0; c < 8; c++) {
+                        const float4 x4 = __ldcg((const float4 *)(p.c + first) + c);
+                        f[4 * c] = x4.x; f[4 * c + 1] = x4.y; f[4 * c + 2] = x4.z; f[4 * c + 3] = x4.w;
+                    }
+                    if (p.fmt_c == QB200_Q8_0) encode_q8_0_block(f, p.cb + (first >> 5) * 34);
+                    else encode_q4_0_block(f, p.cb + (first >> 5) * 18);
+                }
+            }
+        }
+        if (lane == 0) { MM_TRACE(p, 16 + 4 * (warp - 2), w_tfull); MM_TRACE(p, 17 + 4 * (warp - 2), MM_CLOCK() - t_begin); MM_TRACE(p, 18 + 4 * (warp - 2), w_ld); }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
 // ---------------------------------------------------------------------------------- the tensor pipe's own rate
 
 // One thread of one block issues `iters` x 4 tcgen05.mma kind::i8 (M 128, N 128, K 32, the product's instruction) on
@@ -984,6 +1302,7 @@ extern "C" void qb200_mm_set_trace(long long *buffer) { g_mm_trace = buffer; }
 static int g_mm_sms = 0;
 static int g_mm_kind = 0;          // the tensor kind the library packs for and multiplies with
 static int g_mm_tcs = 1;           // scale products of plain f16 scales on the tensor cores
+static int g_mm_few = 64;          // most rows of A the kernel with the operands' sides exchanged takes
 
 template <int KIND, bool SUMS, int VAR>
 static cudaError_t set_mm_attr_var()
@@ -1009,8 +1328,13 @@ cudaError_t matmul_init(int sm_count, int max_smem, int *status)
     const char *kind = getenv("QB200_MM_KIND"), *tcs = getenv("QB200_MM_TCS");
     g_mm_kind = kind && *kind ? atoi(kind) != 0 : 0;
     g_mm_tcs = tcs && *tcs ? atoi(tcs) != 0 : 1;
+    const char *few = getenv("QB200_MM_FEW");
+    g_mm_few = few && *few ? atoi(few) : 64;
 #endif
     cudaError_t e;
+    if ((e = cudaFuncSetAttribute(fewrows_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewCfg<16>::SMEM))) return e;
+    if ((e = cudaFuncSetAttribute(fewrows_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewCfg<32>::SMEM))) return e;
+    if ((e = cudaFuncSetAttribute(fewrows_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewCfg<64>::SMEM))) return e;
     if ((e = set_mm_attr<0, false>()) || (e = set_mm_attr<0, true>())) return e;
     if ((e = set_mm_attr<1, false>()) || (e = set_mm_attr<1, true>())) return e;
     return cudaSuccess;
@@ -1026,14 +1350,26 @@ static size_t plane_bytes(int rows, int kbs, bool tcs = false) { return (size_t)
 // whether the scale products of a product against fmt_b rows run on the tensor cores
 static bool use_tcs(int fmt_b) { return g_mm_tcs && (fmt_b == QB200_Q8_0 || fmt_b == QB200_Q4_0); }
 
-// A packed operand in one buffer: codes, scales, extra plane, each on a 256-byte boundary (the extra plane is only
-// written when B is Q4_K, but always has its place).
-static size_t packed_bytes(int rows, int k, int kbs, bool tcs)
+// A packed operand in one buffer.  LAY_GROUPED: the slabs alone.  LAY_TILE / LAY_KBLOCK: codes, scales, extra plane, each
+// on a 256-byte boundary (the extra plane is only written when B is Q4_K, but always has its place).
+static int kc_of(int k, int kbs) { return (k / kbs) * (g_mm_kind ? 2 : 1) / 16; }
+static size_t packed_bytes(int layout, int rows, int k, int kbs, bool tcs)
 {
+    if (layout == LAY_GROUPED) return align256((size_t)(pad_rows(rows) / TILE) * groups_of(kbs) * grouped_slab(kc_of(k, kbs)));
     return align256(codes_bytes(rows, k)) + align256(plane_bytes(rows, kbs, tcs)) + align256(plane_bytes(rows, kbs));
 }
+// A's slab of the workspace: its LAY_TILE form, or its LAY_FEW form where that is larger (whole groups of k-blocks)
+static int few_bn(int m) { return m <= 16 ? 16 : m <= 32 ? 32 : 64; }
+static size_t a_packed_bytes(int m, int k, int kbs, bool tcs)
+{
+    const size_t tile = packed_bytes(LAY_TILE, m, k, kbs, tcs);
+    const size_t few = tcs && m <= 64 ? align256((size_t)groups_of(kbs) * few_slab(few_bn(m), kc_of(k, kbs))) : 0;
+    return tile > few ? tile : few;
+}
+// B with plain f16 scales is grouped for the tensor cores' scale product, any other B is k-block-major with f32 planes
+static int b_layout(int fmt_b) { return use_tcs(fmt_b) ? LAY_GROUPED : LAY_KBLOCK; }
 
-size_t matmul_prepacked_bytes(int fmt_b, int n, int k) { return packed_bytes(n, k, k_blocks(fmt_b, k), use_tcs(fmt_b)); }
+size_t matmul_prepacked_bytes(int fmt_b, int n, int k) { return packed_bytes(b_layout(fmt_b), n, k, k_blocks(fmt_b, k), false); }
 
 // Scratch of a call: every product's packed A (one when A is the same for all), then every distinct packed B
 // (none when the caller brings B prepacked).
@@ -1041,25 +1377,27 @@ size_t matmul_workspace_bytes(int fmt_b, int m, int n, int k, const MatmulBatch 
 {
     const int kbs = k_blocks(fmt_b, k);
     const size_t a_sets = batch.stride_a ? batch.count : 1, b_sets = b_prepacked ? 0 : (batch.stride_b ? batch.count : 1);
-    return a_sets * packed_bytes(m, k, kbs, use_tcs(fmt_b)) + b_sets * packed_bytes(n, k, kbs, use_tcs(fmt_b));
+    return a_sets * a_packed_bytes(m, k, kbs, use_tcs(fmt_b)) + b_sets * packed_bytes(b_layout(fmt_b), n, k, kbs, false);
 }
 
 // bytes between two products' raw operands `stride` values apart (whole blocks)
 static size_t raw_bytes(int fmt, long long stride) { return (size_t)(stride / block_values(fmt)) * block_bytes(fmt); }
 
-static PackTarget target_in(void *buffer, int rows, int k, int kbs, bool tile_major, bool tcs)
+// `bn`: rows kept in LAY_FEW
+static PackTarget target_in(void *buffer, int rows, int k, int kbs, int layout, bool tcs, int bn = 0)
 {
     uint8_t *w = (uint8_t *)buffer;
     PackTarget t;
     t.codes = w;
     t.scales = (float *)(w + align256(codes_bytes(rows, k)));
     t.extra = (float *)(w + align256(codes_bytes(rows, k)) + align256(plane_bytes(rows, kbs, tcs)));
+    t.layout = layout;
     t.tcs = tcs ? 1 : 0;
-    t.rows_pad = pad_rows(rows);
+    t.rows_pad = layout == LAY_FEW ? (bn < 32 ? 32 : bn) : pad_rows(rows);      // the pack kernels take 32 rows a block
     t.kbs = kbs;
-    t.kc = (k / kbs) * (g_mm_kind ? 2 : 1) / 16;
-    t.tile_major = tile_major ? 1 : 0;
+    t.kc = kc_of(k, kbs);
     t.kind = g_mm_kind;
+    t.bn = bn;
     return t;
 }
 
@@ -1087,7 +1425,7 @@ static cudaError_t pack(int fmt, const void *raw, int rows, int k, const PackTar
 // done once by a caller that keeps the result.
 int matmul_prepack_b(int fmt_b, const void *b, int n, int k, void *packed, cudaStream_t stream)
 {
-    const PackTarget t = target_in(packed, n, k, k_blocks(fmt_b, k), false, use_tcs(fmt_b));
+    const PackTarget t = target_in(packed, n, k, k_blocks(fmt_b, k), b_layout(fmt_b), false);
     return (int)pack(fmt_b, b, n, k, t, false, false, stream);
 }
 
@@ -1123,25 +1461,28 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     cudaError_t e;
     // every product's A, and every distinct B, is packed into a slab of its own
     const bool tcs = use_tcs(fmt_b);
-    const size_t a_slab = packed_bytes(m, k, kbs, tcs), b_slab = packed_bytes(n, k, kbs, tcs);
+    // few rows of A: B's rows become the lanes of tensor memory (fewrows_kernel), A is packed for that
+    const bool few = tcs && !sums && g_mm_kind == 0 && m <= g_mm_few;
+    const int bn = few_bn(m), a_layout = few ? LAY_FEW : LAY_TILE, lay_b = b_layout(fmt_b);
+    const size_t a_slab = a_packed_bytes(m, k, kbs, tcs), b_slab = packed_bytes(lay_b, n, k, kbs, false);
     const int b_sets = b_packed ? 0 : (batch.stride_b ? batch.count : 1);
     const size_t a_raw = raw_bytes(fmt_a, batch.stride_a), b_raw = raw_bytes(fmt_b, batch.stride_b);
-    const PackTarget ta = target_in(workspace, m, k, kbs, true, tcs);
+    const PackTarget ta = target_in(workspace, m, k, kbs, a_layout, tcs, bn);
     for (int i = 0; i < batch.count; i++) {
-        PackTarget t = target_in((uint8_t *)workspace + i * a_slab, m, k, kbs, true, tcs);
+        PackTarget t = target_in((uint8_t *)workspace + i * a_slab, m, k, kbs, a_layout, tcs, bn);
         if ((e = pack(fmt_a, (const uint8_t *)a + i * a_raw, m, k, t, mins, half, stream))) return (int)e;
         if (!batch.stride_a) break;
     }
     const int a_sets = batch.stride_a ? batch.count : 1;
     uint8_t *b_area = (uint8_t *)workspace + a_sets * a_slab;
-    PackTarget tb = target_in(b_packed ? (void *)b_packed : (void *)b_area, n, k, kbs, false, tcs);
+    PackTarget tb = target_in(b_packed ? (void *)b_packed : (void *)b_area, n, k, kbs, lay_b, false);
     for (int i = 0; i < b_sets; i++) {
-        PackTarget t = target_in(b_area + i * b_slab, n, k, kbs, false, tcs);
+        PackTarget t = target_in(b_area + i * b_slab, n, k, kbs, lay_b, false);
         if ((e = pack(fmt_b, (const uint8_t *)b + i * b_raw, n, k, t, false, false, stream))) return (int)e;
     }
     MatmulArgs args;
     args.a.codes = ta.codes; args.a.scales = ta.scales; args.a.extra = mins ? ta.extra : nullptr;
-    args.b.codes = tb.codes; args.b.scales = tb.scales; args.b.extra = mins ? tb.extra : nullptr; args.b.rows_pad = tb.rows_pad;
+    args.b.codes = tb.codes; args.b.scales = tb.scales; args.b.extra = mins ? tb.extra : nullptr; args.b.rows_pad = tb.rows_pad; args.b.groups = groups_of(kbs);
     args.c = c; args.sums = sums; args.status = g_mm_status;
     args.cb = (uint8_t *)c_blocks; args.fmt_c = fmt_c;
     args.m = m; args.n = n; args.kb = kbs;
@@ -1158,6 +1499,13 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     args.a_stride = batch.stride_a ? a_slab : 0;
     args.b_stride = !b_packed && batch.stride_b ? b_slab : 0;
     args.c_stride = (size_t)batch.stride_c;
+    if (few) {
+        const int tiles = batch.count * (tb.rows_pad / TILE), grid = tiles < g_mm_sms ? tiles : g_mm_sms;
+        if (bn == 16) fewrows_kernel<16><<<grid, FEW_THREADS, FewCfg<16>::SMEM, stream>>>(args);
+        else if (bn == 32) fewrows_kernel<32><<<grid, FEW_THREADS, FewCfg<32>::SMEM, stream>>>(args);
+        else fewrows_kernel<64><<<grid, FEW_THREADS, FewCfg<64>::SMEM, stream>>>(args);
+        return (int)cudaGetLastError();
+    }
     const long long total = (long long)args.batch * args.mtiles * args.units;
     const int grid = (int)(total < g_mm_sms ? total : g_mm_sms);
     const int var = mins ? VAR_MINS : half ? VAR_HALF : tcs ? VAR_TCS : VAR_PLAIN;

@@ -83,14 +83,16 @@ def test_edges(oracle, m, n, k):
 
 
 @pytest.mark.parametrize("fmt_a,fmt_b", [(B.Q8_0, B.Q8_0), (B.Q4_0, B.Q4_0), (B.Q8_0, B.Q4_0), (B.Q4_0, B.Q8_0)])
-@pytest.mark.parametrize("m,n,k", [(1, 1, 32), (5, 3, 96), (16, 257, 4096), (8, 1021, 8160), (13, 130, 1056), (16, 16, 8192), (2, 4099, 64)])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 32), (5, 3, 96), (16, 257, 4096), (8, 1021, 8160), (13, 130, 1056), (16, 16, 8192), (2, 4099, 64),
+                                   (17, 300, 160), (32, 129, 2080), (33, 260, 1024), (64, 515, 4096), (48, 128, 7 * 32), (65, 140, 320)])
 def test_few_rows_of_a(oracle, fmt_a, fmt_b, m, n, k):
-    # m <= 16 takes the CUDA-core path (the weights stream once past activations held in shared memory): the same bits
+    # m <= 64 takes the kernel with the operands' sides exchanged (B's rows on the lanes of tensor memory, 16 / 32 / 64
+    # columns for A's rows, several k-blocks a commit): the same bits; k-block counts that leave a ragged last batch and stage
     a, b = operands(oracle, fmt_a, fmt_b, m, n, k, 900 + m + n)
     c = matmul_gpu(fmt_a, fmt_b, a, b, m, n, k)
     ref = oracle.matmul_blocks(fmt_a, fmt_b, a, b, m, n, k, order=1)
     assert np.array_equal(c.view(np.uint32), ref.view(np.uint32))
-    # and the tensor-core path gives them too (the checking entry point always takes it)
+    # and the 128-row-tile kernel gives them too (the checking entry point always takes it)
     c2, _ = matmul_gpu(fmt_a, fmt_b, a, b, m, n, k, want_sums=True) if m * n * (k // 32) <= 1 << 24 else (c, None)
     assert np.array_equal(c2.view(np.uint32), ref.view(np.uint32))
 
