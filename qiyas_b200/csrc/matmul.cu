@@ -228,6 +228,8 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int 
     // halfwords a row segment; the pitch is an odd number of 32-bit words, so the 32 rows start in 32 different banks
     constexpr int BB = block_bytes(FMT), HALVES = 8 * BB / 2, PITCH = HALVES + 2, VECS = 8 * BB / 16;
     __shared__ __align__(16) uint16_t seg[32 * PITCH];
+    // a product launched as a programmatic dependent may start its prologue now (it waits for this grid before it reads A)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int r0 = blockIdx.x * 32, b0 = blockIdx.y * 8;
     const int nb = min(8, kb32 - b0), halves = nb * BB / 2;
     const size_t row_bytes = (size_t)kb32 * BB;
@@ -1010,7 +1012,10 @@ struct FewCfg {
     static_assert(BN == 16 || BN == 32 || BN == 64, "the batch is 64 columns of sums");
     static_assert(S >= 2 && 2 * S + 2 * NB + 2 <= 64, "barriers fit the header");
 };
-constexpr int FEW_THREADS = 32 * 6;              // warp 0 producer, warp 1 MMA, four epilogue warps
+// Warps of the few-rows kernel: 0 producer, 1 and 2 issue the tensor instructions of the even and the odd batches (one
+// thread each: an instruction costs its issuer about 60 cycles, whatever its shape, and this kernel's are small), 3 idle,
+// 4 .. the epilogue: four warps (one a quarter of the lanes) for every 32 columns of sums.
+template <int BN> __host__ __device__ constexpr int few_threads() { return 32 * (4 + 4 * (BN > 32 ? BN / 32 : 1)); }
 
 // Nothing is emitted: the registers pass through the statement, so that what uses them stays below the wait before it.
 __device__ __forceinline__ void pin16(uint32_t *v)
@@ -1027,10 +1032,11 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N])
 }
 
 template <int BN>
-__global__ void __launch_bounds__(FEW_THREADS, 1) fewrows_kernel(const MatmulArgs p)
+__global__ void __launch_bounds__(few_threads<BN>(), 1) fewrows_kernel(const MatmulArgs p)
 {
     using G = FewCfg<BN>;
-    constexpr int S = G::S, KS = G::KS, BATCH = G::BATCH, NB = G::NB;
+    constexpr int S = G::S, KS = G::KS, BATCH = G::BATCH, NB = G::NB, BPS = KS / BATCH;
+    constexpr int CG = BN > 32 ? BN / 32 : 1, CW = BN / CG;         // column groups of the epilogue, columns a warp
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = smem_u32(smem);
@@ -1039,20 +1045,21 @@ __global__ void __launch_bounds__(FEW_THREADS, 1) fewrows_kernel(const MatmulArg
     volatile int *abort_flag = (volatile int *)(smem + 768);
     volatile uint32_t *holder_ptr = (volatile uint32_t *)(smem + (holder - base));
     constexpr int wmode = MM_WAIT_MODE;
+    static_assert((NB & (NB - 1)) == 0, "batches in flight: a power of two");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
             mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 2);                // both issuers' commits
         }
         for (int t = 0; t < NB; t++) {
             mbar_init(tfull0 + 8 * t, 1);
-            mbar_init(tempty0 + 8 * t, 4);
+            mbar_init(tempty0 + 8 * t, 4 * CG);
         }
         *abort_flag = 0;
         mbar_fence_init();
     }
-    for (int i = threadIdx.x; i < (int)G::PATCH / 16; i += FEW_THREADS) *(uint4 *)(smem + G::O_PATCH + i * 16) = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < (int)G::PATCH / 16; i += few_threads<BN>()) *(uint4 *)(smem + G::O_PATCH + i * 16) = make_uint4(0, 0, 0, 0);
     fence_proxy_async();
     if (warp == 1) tmem_alloc(holder, 512);
     tc_fence_before();
@@ -1060,117 +1067,123 @@ __global__ void __launch_bounds__(FEW_THREADS, 1) fewrows_kernel(const MatmulArg
     tc_fence_after();
     const uint32_t tmem = *holder_ptr;
     uint8_t *ring = smem + MM_HEADER;
-    const int ntiles = p.b.rows_pad / TILE, tiles = p.batch * ntiles;       // a tile: 128 rows of B of one product
+    // a tile: 128 rows of B of one product; this block takes tiles blockIdx.x, + gridDim.x, ...; a stage: one group of a tile
+    const int ntiles = p.b.rows_pad / TILE, tiles = p.batch * ntiles, groups = p.b.groups;
+    const int my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0, stages = my_tiles * groups;
+    const int bpt = (p.kb + BATCH - 1) / BATCH;                        // batches a tile
 
     if (warp == 0) {
-        // ---- producer: a stage is a group of eight k-blocks: the slab of the tile of B (codes and scale rows, one copy)
-        // and A's slab of the group (another)
-        int sc = 0;
-        bool alive = true;
-        long long w_empty = 0;
-        const long long t_begin = MM_CLOCK();
-        for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
-            const int bi = tile / ntiles, nt = tile - bi * ntiles;
-            const uint8_t *a_slabs = p.a.codes + bi * p.a_stride;
-            const uint8_t *b_slabs = p.b.codes + bi * p.b_stride + (size_t)nt * p.b.groups * G::B_SLAB;
-            for (int g = 0; g < p.b.groups && alive; g++, sc++) {
+        // ---- producer (one thread): per stage the slab of the tile of B (codes and scale rows, one copy) and A's slab of
+        // the group (another).  B does not depend on the kernel before this one (A's packing), so the first stages' copies
+        // of B are issued before griddepcontrol.wait lets A's follow.
+        if (lane == 0) {
+            long long w_empty = 0;
+            const long long t_begin = MM_CLOCK();
+            const bool with_a = !(MM_PROBE(p) & 1);
+            auto b_src = [&](int sc) {
+                const int tile = blockIdx.x + (sc / groups) * gridDim.x, bi = tile / ntiles, nt = tile - bi * ntiles;
+                return p.b.codes + bi * p.b_stride + ((size_t)nt * groups + sc % groups) * G::B_SLAB;
+            };
+            auto a_src = [&](int sc) {
+                const int tile = blockIdx.x + (sc / groups) * gridDim.x, bi = tile / ntiles;
+                return p.a.codes + bi * p.a_stride + (size_t)(sc % groups) * G::A_SLAB;
+            };
+            const int pre = min(S, stages);
+            for (int sc = 0; sc < pre; sc++) {
+                mbar_arrive_expect_tx(full0 + 8 * sc, G::B_SLAB + (with_a ? G::A_SLAB : 0u));
+                bulk_g2s(smem_u32(ring + (size_t)sc * G::STAGE), b_src(sc), G::B_SLAB, full0 + 8 * sc);
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int sc = 0; sc < pre && with_a; sc++) bulk_g2s(smem_u32(ring + (size_t)sc * G::STAGE) + G::O_A, a_src(sc), G::A_SLAB, full0 + 8 * sc);
+            int sc = pre;
+            for (; sc < stages; sc++) {
                 const int s = sc % S;
-                int ok = 1;
                 const long long w0 = MM_CLOCK();
-                if (lane == 0 && sc >= S) ok = mm_wait(empty0 + 8 * s, (uint32_t)(sc / S - 1) & 1u, abort_flag, p.status, wmode) ? 1 : 0;
+                if (!mm_wait(empty0 + 8 * s, (uint32_t)(sc / S - 1) & 1u, abort_flag, p.status, wmode)) break;
                 w_empty += MM_CLOCK() - w0;
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) { alive = false; break; }
                 const uint32_t dst = smem_u32(ring + (size_t)s * G::STAGE), bar = full0 + 8 * s;
-                if (lane == 0) {
-                    const bool with_a = !(MM_PROBE(p) & 1);
-                    mbar_arrive_expect_tx(bar, G::B_SLAB + (with_a ? G::A_SLAB : 0u));
-                    bulk_g2s(dst, b_slabs + (size_t)g * G::B_SLAB, G::B_SLAB, bar);
-                    if (with_a) bulk_g2s(dst + G::O_A, a_slabs + (size_t)g * G::A_SLAB, G::A_SLAB, bar);
+                mbar_arrive_expect_tx(bar, G::B_SLAB + (with_a ? G::A_SLAB : 0u));
+                bulk_g2s(dst, b_src(sc), G::B_SLAB, bar);
+                if (with_a) bulk_g2s(dst + G::O_A, a_src(sc), G::A_SLAB, bar);
+            }
+            MM_TRACE(p, 0, w_empty); MM_TRACE(p, 1, MM_CLOCK() - t_begin); MM_TRACE(p, 2, (long long)sc);
+            if (*abort_flag) {          // let the copies still in flight land before the block exits
+                for (int it = max(0, sc - S); it < sc; it++) {
+                    long long start = clock64();
+                    while (!mbar_try_wait(full0 + 8 * (it % S), (uint32_t)(it / S) & 1u) && clock64() - start < WAIT_CYCLES) { }
                 }
             }
         }
-        if (lane == 0) { MM_TRACE(p, 0, w_empty); MM_TRACE(p, 1, MM_CLOCK() - t_begin); MM_TRACE(p, 2, (long long)sc); }
-        if (*abort_flag && lane == 0) {          // let the copies still in flight land before the block exits
-            for (int it = max(0, sc - S); it < sc; it++) {
-                long long start = clock64();
-                while (!mbar_try_wait(full0 + 8 * (it % S), (uint32_t)(it / S) & 1u) && clock64() - start < WAIT_CYCLES) { }
-            }
-        }
-    } else if (warp == 1) {
-        // ---- MMA issue: per k-block the sums (kind::i8, M 128, N BN, K 32); per batch the scale products of its k-blocks
-        // (kind::f16, N 64, K 16: the 16-byte scale rows, the other half of K from the patch of zeros) and one commit
+    } else if (warp == 1 || warp == 2) {
+        // ---- MMA issue, the batches of this warp's parity (the epilogue takes batches in order, so neither issuer gets a
+        // whole round of the NB accumulators ahead of the other): per k-block the sums (kind::i8, M 128, N BN, K 32); per
+        // batch the scale products of its k-blocks (kind::f16, N 64, K 16: the 16-byte scale rows, the other half of K
+        // from the patch of zeros) and one commit.  Batch b of stage sc is batch (sc / groups) * bpt + (sc % groups) * BPS + b
+        // of the block.  Both issuers commit a stage's release.
         if (lane == 0) {
-            int sc = 0, tc = 0, slot = 0;
-            uint32_t d = tmem;
             bool alive = true;
             long long w_full = 0, w_tempty = 0;
             const long long t_begin = MM_CLOCK();
-            static_assert((NB & (NB - 1)) == 0, "batches in flight: a power of two");
+            const int role = warp - 1;
             constexpr uint64_t DESC_HI = (uint64_t)(128u >> 4) << 16 | (uint64_t)(256u >> 4) << 32 | (uint64_t)1 << 46;
             const uint32_t patch = base + G::O_PATCH;
             constexpr uint32_t idesc = idesc_of(0, TILE, BN), idesc_s = idesc_of(1, TILE, 64);
-            for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
-                for (int kb0 = 0; kb0 < p.kb && alive; kb0 += KS, sc++) {
-                    const int s = sc % S, nkb = min(KS, p.kb - kb0);
-                    const long long w0 = MM_CLOCK();
-                    if (!mm_poll(full0 + 8 * s, (uint32_t)(sc / S) & 1u, wmode & 3) &&
-                        !mm_wait(full0 + 8 * s, (uint32_t)(sc / S) & 1u, abort_flag, p.status, wmode)) { alive = false; break; }
-                    w_full += MM_CLOCK() - w0;
-                    tc_fence_after();
-                    // this thread's own instruction stream paces the block: descriptors advance by one addition a k-block;
-                    // B's scale rows are the same for the whole group, A's move a batch of rows on (and the patch that much nearer)
-                    const uint32_t st = smem_u32(ring + (size_t)s * G::STAGE);
-                    uint64_t bc = DESC_HI | (uint64_t)(st >> 4), ac = DESC_HI | (uint64_t)((st + G::O_A) >> 4);
-                    const uint64_t bs = smem_desc(st + G::O_BS, patch - (st + G::O_BS), 128);
-                    uint64_t as = smem_desc(st + G::O_AS, patch - (st + G::O_AS), 128);
-                    constexpr uint64_t AS_STEP = (uint64_t)((64 * 16) >> 4) - ((uint64_t)((64 * 16) >> 4) << 16);
+            for (int sc = 0; sc < stages && alive; sc++) {
+                const int s = sc % S, g = sc % groups, nkb = min(KS, p.kb - g * KS);
+                const int tc0 = (sc / groups) * bpt + g * BPS;
+                const long long w0 = MM_CLOCK();
+                if (!mm_poll(full0 + 8 * s, (uint32_t)(sc / S) & 1u, wmode & 3) &&
+                    !mm_wait(full0 + 8 * s, (uint32_t)(sc / S) & 1u, abort_flag, p.status, wmode)) { alive = false; break; }
+                w_full += MM_CLOCK() - w0;
+                tc_fence_after();
+                // B's scale rows are the same for the whole group, A's move a batch of rows on (and the patch that much nearer)
+                const uint32_t st = smem_u32(ring + (size_t)s * G::STAGE);
+                const uint64_t bc = DESC_HI | (uint64_t)(st >> 4), ac = DESC_HI | (uint64_t)((st + G::O_A) >> 4);
+                const uint64_t bs = smem_desc(st + G::O_BS, patch - (st + G::O_BS), 128);
+                const uint64_t as = smem_desc(st + G::O_AS, patch - (st + G::O_AS), 128);
+                constexpr uint64_t AS_STEP = (uint64_t)((64 * 16) >> 4) - ((uint64_t)((64 * 16) >> 4) << 16);
 #pragma unroll
-                    for (int kk = 0; kk < KS; kk++) {
-                        if (kk < nkb) {
-                            const int j = kk % BATCH;
-                            if (j == 0) {
-                                slot = tc & (NB - 1);
-                                if (tc >= NB) {
-                                    const uint32_t par = (uint32_t)(tc / NB - 1) & 1u;
-                                    const long long w1 = MM_CLOCK();
-                                    if (!mm_poll(tempty0 + 8 * slot, par, wmode & 3) && !mm_wait(tempty0 + 8 * slot, par, abort_flag, p.status, wmode)) { alive = false; break; }
-                                    w_tempty += MM_CLOCK() - w1;
-                                    tc_fence_after();
-                                }
-                                d = tmem + (uint32_t)(slot * G::BCOLS);
-                            }
-                            mma_issue<0>(d + j * BN, bc, ac, idesc, 0u);
-                            bc += G::B_KB >> 4; ac += G::A_KB >> 4;
-                            if (j == BATCH - 1 || kk == nkb - 1) {
-                                // the rows of a k-block the group does not have give columns nobody reads
-                                if (!(MM_PROBE(p) & 8)) mma_issue<1>(d + 64, bs, as, idesc_s, 0u);
-                                as += AS_STEP;
-                                mma_commit(tfull0 + 8 * slot);
-                                tc++;
-                            }
+                for (int b = 0; b < BPS; b++) {
+                    const int tc = tc0 + b;
+                    if (b * BATCH < nkb && (tc & 1) == role) {
+                        const int slot = tc & (NB - 1);
+                        if (tc >= NB) {
+                            const uint32_t par = (uint32_t)(tc / NB - 1) & 1u;
+                            const long long w1 = MM_CLOCK();
+                            if (!mm_poll(tempty0 + 8 * slot, par, wmode & 3) && !mm_wait(tempty0 + 8 * slot, par, abort_flag, p.status, wmode)) { alive = false; break; }
+                            w_tempty += MM_CLOCK() - w1;
+                            tc_fence_after();
                         }
+                        const uint32_t d = tmem + (uint32_t)(slot * G::BCOLS);
+#pragma unroll
+                        for (int j = 0; j < BATCH; j++) {
+                            const int kk = b * BATCH + j;
+                            if (kk < nkb) mma_issue<0>(d + j * BN, bc + (uint64_t)kk * (G::B_KB >> 4), ac + (uint64_t)kk * (G::A_KB >> 4), idesc, 0u);
+                        }
+                        // the rows of a k-block the group does not have give columns nobody reads
+                        if (!(MM_PROBE(p) & 8)) mma_issue<1>(d + 64, bs, as + (uint64_t)b * AS_STEP, idesc_s, 0u);
+                        mma_commit(tfull0 + 8 * slot);
                     }
-                    if (alive) mma_commit(empty0 + 8 * s);      // the stage is free once these products have run
                 }
+                if (alive) mma_commit(empty0 + 8 * s);      // the stage is free once both issuers' products have run
             }
-            MM_TRACE(p, 8, w_full); MM_TRACE(p, 9, w_tempty); MM_TRACE(p, 10, MM_CLOCK() - t_begin); MM_TRACE(p, 11, (long long)tc);
+            MM_TRACE(p, 8 + 4 * (warp - 1), w_full); MM_TRACE(p, 9 + 4 * (warp - 1), w_tempty); MM_TRACE(p, 10 + 4 * (warp - 1), MM_CLOCK() - t_begin);
         }
-    } else {
-        // ---- epilogue: warp q reads lanes 32 q .. 32 q + 31 of every batch
-        const int q = warp & 3;
-        const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
+    } else if (warp >= 4) {
+        // ---- epilogue: warp (q, cg) reads lanes 32 q .. 32 q + 31 and columns cg * CW .. of every k-block's sums
+        const int q = warp & 3, cg = (warp - 4) >> 2;
+        const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cg * CW);
         int tc = 0;
         bool alive = true;
         long long w_tfull = 0, w_ld = 0;
         const long long t_begin = MM_CLOCK();
         for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
             const int bi = tile / ntiles, n0 = (tile - bi * ntiles) * TILE;
-            float acc[BN];
+            float acc[CW];
 #pragma unroll
-            for (int c = 0; c < BN; c++) acc[c] = 0.f;
+            for (int c = 0; c < CW; c++) acc[c] = 0.f;
             for (int i = 0; i < p.kb && alive; i += BATCH, tc++) {
-                const int t = tc % NB, nb = min(BATCH, p.kb - i);
+                const int t = tc & (NB - 1), nb = min(BATCH, p.kb - i);
                 const uint32_t bar = tfull0 + 8 * t, par = (uint32_t)(tc / NB) & 1u;
                 const long long w0 = MM_CLOCK();
                 if (!mm_poll(bar, par, wmode & 3) && !mm_wait_lanes(bar, par, abort_flag, p.status, wmode)) { alive = false; break; }
@@ -1178,18 +1191,18 @@ __global__ void __launch_bounds__(FEW_THREADS, 1) fewrows_kernel(const MatmulArg
                 w_tfull += w1 - w0;
                 tc_fence_after();
                 const uint32_t at = tlane + (uint32_t)(t * G::BCOLS);
-                uint32_t v[BATCH][BN], x[BATCH][BN];
+                uint32_t v[BATCH][CW], x[BATCH][CW];
 #pragma unroll
                 for (int j = 0; j < BATCH; j++) {
-                    tmem_ld_cols<BN>(at + j * BN, v[j]);
-                    tmem_ld_cols<BN>(at + 64 + j * BN, x[j]);
+                    tmem_ld_cols<CW>(at + j * BN, v[j]);
+                    tmem_ld_cols<CW>(at + 64 + j * BN, x[j]);
                 }
                 tmem_ld_wait();
                 w_ld += MM_CLOCK() - w1;
 #pragma unroll
                 for (int j = 0; j < BATCH; j++) {
 #pragma unroll
-                    for (int c = 0; c < BN; c += 16) { pin16(v[j] + c); pin16(x[j] + c); }
+                    for (int c = 0; c < CW; c += 16) { pin16(v[j] + c); pin16(x[j] + c); }
                 }
                 tc_fence_before();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * t);             // the batch has been read (warp-wide reads)
@@ -1197,7 +1210,7 @@ __global__ void __launch_bounds__(FEW_THREADS, 1) fewrows_kernel(const MatmulArg
                 for (int j = 0; j < BATCH; j++) {
                     if (j < nb && !(MM_PROBE(p) & 4)) {
 #pragma unroll
-                        for (int c = 0; c < BN; c++) acc[c] = __fmaf_rn((float)(int32_t)v[j][c], __uint_as_float(x[j][c]), acc[c]);
+                        for (int c = 0; c < CW; c++) acc[c] = __fmaf_rn((float)(int32_t)v[j][c], __uint_as_float(x[j][c]), acc[c]);
                     }
                 }
             }
@@ -1205,15 +1218,15 @@ __global__ void __launch_bounds__(FEW_THREADS, 1) fewrows_kernel(const MatmulArg
             float *c_out = p.c + bi * p.c_stride;
             if (alive && col < p.n) {
 #pragma unroll
-                for (int r = 0; r < BN; r++) if (r < p.m) c_out[(size_t)r * p.n + col] = acc[r];
+                for (int r = 0; r < CW; r++) if (cg * CW + r < p.m) c_out[(size_t)(cg * CW + r) * p.n + col] = acc[r];
             }
             if (p.cb) {
-                // `Back` for the tile: once the four warps have stored their lanes, the 128 threads encode the tile's blocks of
+                // `Back` for the tile: once the epilogue warps have stored their lanes, their threads encode the tile's blocks of
                 // 32 consecutive values of a row of C (n % 32 == 0: a block lies inside one warp's columns)
-                named_bar_sync(2, 128);
+                named_bar_sync(2, 128 * CG);
                 if (*abort_flag) { alive = false; break; }
-                const int bw = min(TILE, p.n - n0) / 32, tid = threadIdx.x - 64;
-                for (int idx = tid; idx < p.m * bw; idx += 128) {
+                const int bw = min(TILE, p.n - n0) / 32, tid = threadIdx.x - 128;
+                for (int idx = tid; idx < p.m * bw; idx += 128 * CG) {
                     const int rr = idx / bw, bc = idx - rr * bw;
                     const size_t first = bi * p.c_stride + (size_t)rr * p.n + n0 + bc * 32;
                     float f[32];
@@ -1227,7 +1240,7 @@ __global__ void __launch_bounds__(FEW_THREADS, 1) fewrows_kernel(const MatmulArg
                 }
             }
         }
-        if (lane == 0) { MM_TRACE(p, 16 + 4 * (warp - 2), w_tfull); MM_TRACE(p, 17 + 4 * (warp - 2), MM_CLOCK() - t_begin); MM_TRACE(p, 18 + 4 * (warp - 2), w_ld); }
+        if (lane == 0 && warp < 8) { MM_TRACE(p, 16 + 4 * (warp - 4), w_tfull); MM_TRACE(p, 17 + 4 * (warp - 4), MM_CLOCK() - t_begin); MM_TRACE(p, 18 + 4 * (warp - 4), w_ld); }
     }
     tc_fence_before();
     __syncthreads();
@@ -1467,18 +1480,19 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     const size_t a_slab = a_packed_bytes(m, k, kbs, tcs), b_slab = packed_bytes(lay_b, n, k, kbs, false);
     const int b_sets = b_packed ? 0 : (batch.stride_b ? batch.count : 1);
     const size_t a_raw = raw_bytes(fmt_a, batch.stride_a), b_raw = raw_bytes(fmt_b, batch.stride_b);
-    const PackTarget ta = target_in(workspace, m, k, kbs, a_layout, tcs, bn);
-    for (int i = 0; i < batch.count; i++) {
-        PackTarget t = target_in((uint8_t *)workspace + i * a_slab, m, k, kbs, a_layout, tcs, bn);
-        if ((e = pack(fmt_a, (const uint8_t *)a + i * a_raw, m, k, t, mins, half, stream))) return (int)e;
-        if (!batch.stride_a) break;
-    }
+    // B first: A's packing is then the launch right before the product, whose start the few-rows kernel overlaps
     const int a_sets = batch.stride_a ? batch.count : 1;
     uint8_t *b_area = (uint8_t *)workspace + a_sets * a_slab;
     PackTarget tb = target_in(b_packed ? (void *)b_packed : (void *)b_area, n, k, kbs, lay_b, false);
     for (int i = 0; i < b_sets; i++) {
         PackTarget t = target_in(b_area + i * b_slab, n, k, kbs, lay_b, false);
         if ((e = pack(fmt_b, (const uint8_t *)b + i * b_raw, n, k, t, false, false, stream))) return (int)e;
+    }
+    const PackTarget ta = target_in(workspace, m, k, kbs, a_layout, tcs, bn);
+    for (int i = 0; i < batch.count; i++) {
+        PackTarget t = target_in((uint8_t *)workspace + i * a_slab, m, k, kbs, a_layout, tcs, bn);
+        if ((e = pack(fmt_a, (const uint8_t *)a + i * a_raw, m, k, t, mins, half, stream))) return (int)e;
+        if (!batch.stride_a) break;
     }
     MatmulArgs args;
     args.a.codes = ta.codes; args.a.scales = ta.scales; args.a.extra = mins ? ta.extra : nullptr;
@@ -1501,10 +1515,16 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     args.c_stride = (size_t)batch.stride_c;
     if (few) {
         const int tiles = batch.count * (tb.rows_pad / TILE), grid = tiles < g_mm_sms ? tiles : g_mm_sms;
-        if (bn == 16) fewrows_kernel<16><<<grid, FEW_THREADS, FewCfg<16>::SMEM, stream>>>(args);
-        else if (bn == 32) fewrows_kernel<32><<<grid, FEW_THREADS, FewCfg<32>::SMEM, stream>>>(args);
-        else fewrows_kernel<64><<<grid, FEW_THREADS, FewCfg<64>::SMEM, stream>>>(args);
-        return (int)cudaGetLastError();
+        // launched as a programmatic dependent of A's packing: its prologue and its first copies of B run beside it
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.gridDim = dim3(grid); cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
+        if (bn == 16) { cfg.blockDim = dim3(few_threads<16>()); cfg.dynamicSmemBytes = FewCfg<16>::SMEM; e = cudaLaunchKernelEx(&cfg, fewrows_kernel<16>, args); }
+        else if (bn == 32) { cfg.blockDim = dim3(few_threads<32>()); cfg.dynamicSmemBytes = FewCfg<32>::SMEM; e = cudaLaunchKernelEx(&cfg, fewrows_kernel<32>, args); }
+        else { cfg.blockDim = dim3(few_threads<64>()); cfg.dynamicSmemBytes = FewCfg<64>::SMEM; e = cudaLaunchKernelEx(&cfg, fewrows_kernel<64>, args); }
+        return (int)e;
     }
     const long long total = (long long)args.batch * args.mtiles * args.units;
     const int grid = (int)(total < g_mm_sms ? total : g_mm_sms);
