@@ -1015,7 +1015,10 @@ struct FewCfg {
 // Warps of the few-rows kernel: 0 producer, 1 and 2 issue the tensor instructions of the even and the odd batches (one
 // thread each: an instruction costs its issuer about 60 cycles, whatever its shape, and this kernel's are small), 3 idle,
 // 4 .. the epilogue: four warps (one a quarter of the lanes) for every 32 columns of sums.
-template <int BN> __host__ __device__ constexpr int few_threads() { return 32 * (4 + 4 * (BN > 32 ? BN / 32 : 1)); }
+#ifndef FEW_CW
+#define FEW_CW 16
+#endif
+template <int BN> __host__ __device__ constexpr int few_threads() { return 32 * (4 + 4 * (BN / FEW_CW)); }
 
 // Nothing is emitted: the registers pass through the statement, so that what uses them stays below the wait before it.
 __device__ __forceinline__ void pin16(uint32_t *v)
@@ -1036,7 +1039,7 @@ __global__ void __launch_bounds__(few_threads<BN>(), 1) fewrows_kernel(const Mat
 {
     using G = FewCfg<BN>;
     constexpr int S = G::S, KS = G::KS, BATCH = G::BATCH, NB = G::NB, BPS = KS / BATCH;
-    constexpr int CG = BN > 32 ? BN / 32 : 1, CW = BN / CG;         // column groups of the epilogue, columns a warp
+    constexpr int CG = BN / FEW_CW, CW = FEW_CW;                    // column groups of the epilogue, columns a warp
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = smem_u32(smem);
