@@ -41,7 +41,8 @@ constexpr int TILE = 128;            // rows of A a tile = lanes of tensor memor
 constexpr int BNMAX = 128;           // columns of the widest piece = columns of one accumulator in tensor memory
 constexpr int EPI_WARPS = 16;
 constexpr int GROUP = 8;             // k-blocks a group of B with f16 scales = f16 a 16-byte scale row
-constexpr int MM_THREADS = 32 * (2 + EPI_WARPS);     // warp 0 producer, warp 1 MMA, the rest epilogue
+constexpr int MM_THREADS = 32 * (3 + EPI_WARPS);     // warp 0 producer, warp 1 and the last warp MMA issue, the rest epilogue
+constexpr int MMA2_WARP = 2 + EPI_WARPS;
 constexpr uint32_t MM_HEADER = 1024;
 constexpr uint32_t MM_SMEM_MAX = 232448;           // 227 KB of shared memory a block
 
@@ -648,7 +649,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
             mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, TCS ? 1 : 1 + EPI_WARPS);      // the MMA thread's commit, and the epilogue warps where they read the scales
+            mbar_init(empty0 + 8 * s, TCS ? 2 : 2 + EPI_WARPS);      // the two issuers' commits, and the epilogue warps where they read the scales
         }
         for (int t = 0; t < NT; t++) {
             mbar_init(tfull0 + 8 * t, 1);
@@ -681,6 +682,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
         int tile, u0, w, sc = 0;
         bool alive = true;
         long long w_empty = 0, t_begin = MM_CLOCK();
+        asm volatile("griddepcontrol.wait;" ::: "memory");       // the kernel before this one packed A
         while (alive && pieces.next(tile, u0, w)) {
             const int n0 = u0 * p.unit, bn = w * p.unit, bi = tile / p.mtiles, mt = tile - bi * p.mtiles;
             const uint8_t *a_codes = p.a.codes + bi * p.a_stride, *b_codes = p.b.codes + bi * p.b_stride;
@@ -745,19 +747,23 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                 while (!mbar_try_wait(full0 + 8 * (it % S), (uint32_t)(it / S) & 1u) && clock64() - start < WAIT_CYCLES) { }
             }
         }
-    } else if (warp == 1) {
-        // ---- MMA issue: one thread, whose own instruction stream paces the kernel when it is long (a lone thread issues
-        // a dependent instruction every few cycles): descriptors are formed by one addition a k-block, the waits are a
-        // single poll when the barrier is ready.  Every k-block goes to the next accumulator and is committed to its barrier.
+    } else if (warp == 1 || warp == MMA2_WARP) {
+        // ---- MMA issue: two threads (an instruction costs its issuer about 60 cycles and a commit about 50, a lone thread
+        // issues a dependent instruction every few cycles: one thread's own instruction stream was what paced the kernel).
+        // Thread `role` takes the k-blocks of its parity, i.e. always the same accumulators of tensor memory, and commits
+        // each to its barrier; both wait for every stage and both commit its release.  Descriptors are formed by adding
+        // constants; the waits are a single poll when the barrier is ready.
         if (lane == 0) {
             Pieces pieces(p, wmax);
-            int tile, u0, w, sc = 0, tc = 0;
+            const int role = warp == 1 ? 0 : 1;
+            int tile, u0, w, sc = 0, tc0 = 0;
             bool alive = true;
             long long w_full = 0, w_tempty = 0, c_mma = 0, c_commit = 0, t_begin = MM_CLOCK();
             constexpr uint32_t SBO = KC * 128;
             // the descriptor without its start address: LBO 128, SBO, version
             constexpr uint64_t DESC_HI = (uint64_t)(128u >> 4) << 16 | (uint64_t)(SBO >> 4) << 32 | (uint64_t)1 << 46;
             const uint32_t patch = base + G::O_PATCH;
+            static_assert(NT % 2 == 0, "each issuer owns the accumulators of its parity");
             while (alive && pieces.next(tile, u0, w)) {
                 const uint32_t idesc = idesc_of(KIND, TILE, w * p.unit), idesc_s = idesc_of(1, TILE, w * p.unit);
                 for (int kb0 = 0; kb0 < p.kb && alive; kb0 += KS, sc++) {
@@ -768,14 +774,15 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                     w_full += MM_CLOCK() - w0;
                     tc_fence_after();
                     const uint32_t a_smem = smem_u32(ring + (size_t)s * G::STAGE);
-                    uint64_t a_desc = DESC_HI | (uint64_t)(a_smem >> 4), b_desc = DESC_HI | (uint64_t)((a_smem + G::O_B) >> 4);
-                    // scale rows: the second half of K is the patch of zeros, LBO bytes past the start; a k-block on, the start
-                    // is one slab further and the patch that much nearer
-                    uint64_t sa_desc = smem_desc(a_smem + G::O_SA, patch - (a_smem + G::O_SA), 128), sb_desc = smem_desc(a_smem + G::O_SB, patch - (a_smem + G::O_SB), 128);
+                    const uint64_t a_desc = DESC_HI | (uint64_t)(a_smem >> 4), b_desc = DESC_HI | (uint64_t)((a_smem + G::O_B) >> 4);
+                    // scale rows: the second half of K is the patch of zeros, LBO bytes past the start; a k-block on, A's start is
+                    // one slab further and the patch that much nearer; B's rows hold the group's eight scales, the same for all
+                    const uint64_t sa_desc = smem_desc(a_smem + G::O_SA, patch - (a_smem + G::O_SA), 128), sb_desc = smem_desc(a_smem + G::O_SB, patch - (a_smem + G::O_SB), 128);
                     constexpr uint64_t SA_STEP = (uint64_t)((TILE * 16) >> 4) - ((uint64_t)((TILE * 16) >> 4) << 16);
 #pragma unroll
                     for (int kk = 0; kk < KS; kk++) {
-                        if (kk < nkb) {
+                        const int tc = tc0 + kb0 + kk;
+                        if (kk < nkb && (tc & 1) == role) {
                             const int t = tc % NT;
                             if (tc >= NT) {
                                 const uint32_t par = (uint32_t)(tc / NT - 1) & 1u;
@@ -792,27 +799,22 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                                 const uint32_t a_at = a_smem + kk * G::A_KB, b_at = a_smem + G::O_B + kk * G::B_KB;
                                 mma_issue<KIND>(d, smem_desc(a_at, patch - a_at, 128), smem_desc(b_at, 128, 128), idesc, 0u);
                             } else {
-                                mma_issue<KIND>(d, a_desc, b_desc, idesc, 0u);
-                                if (KC == 4) mma_issue<KIND>(d, a_desc + (256 >> 4), b_desc + (256 >> 4), idesc, 1u);
+                                mma_issue<KIND>(d, a_desc + (uint64_t)kk * (G::A_KB >> 4), b_desc + (uint64_t)kk * (G::B_KB >> 4), idesc, 0u);
+                                if (KC == 4) mma_issue<KIND>(d, a_desc + (uint64_t)kk * (G::A_KB >> 4) + (256 >> 4), b_desc + (uint64_t)kk * (G::B_KB >> 4) + (256 >> 4), idesc, 1u);
                             }
-                            if (TCS && !(MM_PROBE(p) & 8)) {
-                                // the scale products: rows [d, 0 x 7] of A's and B's scales, the other half of K from the zeros
-                                mma_issue<1>(d + BNMAX, sa_desc, sb_desc, idesc_s, 0u);
-                                sa_desc += SA_STEP;      // B's rows hold the group's eight scales: the same rows for every k-block
-                            }
+                            // the scale products: A's rows [0 .., d at k-block % 8, .. 0], B's rows of eight scales, the other half of K zeros
+                            if (TCS && !(MM_PROBE(p) & 8)) mma_issue<1>(d + BNMAX, sa_desc + (uint64_t)kk * SA_STEP, sb_desc, idesc_s, 0u);
                             const long long c1 = MM_CLOCK();
                             mma_commit(tfull0 + 8 * t);
                             c_commit += MM_CLOCK() - c1;
                             c_mma += c1 - c0;
-                            a_desc += G::A_KB >> 4;
-                            b_desc += G::B_KB >> 4;
-                            tc++;
                         }
                     }
-                    if (alive) mma_commit(empty0 + 8 * s);      // the stage is free once these products have run
+                    if (alive) mma_commit(empty0 + 8 * s);      // the stage is free once both issuers' products have run
                 }
+                tc0 += p.kb;
             }
-            MM_TRACE(p, 8, w_full); MM_TRACE(p, 9, w_tempty); MM_TRACE(p, 10, MM_CLOCK() - t_begin); MM_TRACE(p, 11, (long long)tc); MM_TRACE(p, 12, c_mma); MM_TRACE(p, 13, c_commit);
+            if (role == 0) { MM_TRACE(p, 8, w_full); MM_TRACE(p, 9, w_tempty); MM_TRACE(p, 10, MM_CLOCK() - t_begin); MM_TRACE(p, 11, (long long)tc0); MM_TRACE(p, 12, c_mma); MM_TRACE(p, 13, c_commit); }
         }
     } else {
         // ---- epilogue: warp (q, g) owns rows 32 q .. 32 q + 31 of the tile (the tensor-memory lanes a warp may read) and
@@ -1448,7 +1450,15 @@ int matmul_prepack_b(int fmt_b, const void *b, int n, int k, void *packed, cudaS
 template <int KIND, bool SUMS, int VAR>
 static void launch_var(int grid, const MatmulArgs &args, cudaStream_t stream)
 {
-    matmul_kernel<KIND, SUMS, VAR><<<grid, MM_THREADS, Cfg<KIND, VAR == VAR_MINS, VAR == VAR_HALF, VAR == VAR_TCS>::SMEM, stream>>>(args);
+    // a programmatic dependent of A's packing (the launch before it): its prologue runs beside that kernel, its producer
+    // waits for it before the first copy
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(MM_THREADS); cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
+    cfg.dynamicSmemBytes = Cfg<KIND, VAR == VAR_MINS, VAR == VAR_HALF, VAR == VAR_TCS>::SMEM;
+    cudaLaunchKernelEx(&cfg, matmul_kernel<KIND, SUMS, VAR>, args);
 }
 
 template <int KIND, bool SUMS>
