@@ -348,7 +348,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-extra", action="store_true", help="only the headline (profiling runs)")
-    ap.add_argument("--leg", default=None, choices=["c2-chained", "abt"],
+    ap.add_argument("--leg", default=None, choices=["c2-chained", "abt", "abt-few"],
                     help="run one small leg alone and print its record (profiling runs): the Q4_0 8192 x 8192 gemv with calls chained "
                          "through y, or the Q8_0 x Q8_0 A.B^T of configs[2] at M 512")
     args = ap.parse_args()
@@ -381,7 +381,7 @@ def main():
         if args.leg == "c2-chained":
             rec = gemv_record(ops, torch, timer, B.Q4_0, 8192, 8192, 3, 3, peak, chained=True)
         else:
-            rec = abt_record(ops, torch, timer, B.Q8_0, 512, 11008, 4096, tensor_peak(ops, 1965.0)[0])
+            rec = abt_record(ops, torch, timer, B.Q8_0, 512 if args.leg == "abt" else 16, 11008, 4096, tensor_peak(ops, 1965.0)[0])
         if rank == 0:
             print(json.dumps({"leg": args.leg, "record": rec}), flush=True)
         return

@@ -154,6 +154,10 @@ int qb200_gemv_noalloc_status(int *status);
  *   acc = fma(float(D), sA*(d*sc), acc); acc = fma(dmin*m, -(sA*float(sum of qA)), acc).
  *   With fmt_b Q6_K every 16-value sub-block is a k-block with scale d*sc (src/Blocks.cs:167-170).
  *   k whole blocks of both operands (32; 256 with Q4_K / Q6_K); m, n >= 1.
+ *   Block scales must be finite: with Q8_0 / Q4_0 on both sides the products sA*sB are taken by the
+ *   tensor cores together with the zero terms of the neighbouring k-blocks, which an infinite scale
+ *   would turn into NaN (the result is then NaN where the reference gives +-inf or NaN).
+ *   With at most 64 rows of A the rows of B take the lanes of tensor memory instead of A's (same bits).
  *   workspace: device scratch of qb200_matmul_workspace_bytes(...) bytes, 256-byte aligned,
  *   private to the call until it completes on `stream` (the operands are re-laid there for
  *   the tensor cores).  Pass NULL/0 to use one scratch buffer the library keeps and grows: calls
