@@ -247,6 +247,15 @@ int qb200_shard_range(int rows, int world, int rank, int *first, int *count);
 int qb200_shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const qb200_shard_peers_t *peers,
                      unsigned int epoch, void *stream);
 int qb200_shard_wait(const qb200_shard_peers_t *peers, unsigned int epoch, long long limit_cycles, void *stream);
+/* A chain of sharded products, each reading the whole output of the one before it (the layers of a model): as
+ * qb200_shard_gemv, but x is rank `peers->rank`'s copy of the output of the exchange `after`, and the kernel itself waits
+ * (bounded by limit_cycles as qb200_shard_wait is; status bit 2 when it runs out) until every rank's word of after's
+ * local flag array has reached after_epoch (0: counted, as above) before it reads x -- while its copies of the weights
+ * are already running.  No qb200_shard_wait is needed between the two products; the last product of the chain is followed
+ * by one.  `after` and `peers` are two exchanges between the same ranks with buffers of their own (alternate two of them
+ * along the chain): a rank that is a product ahead must not store into the y its peers are still reading. */
+int qb200_shard_gemv_after(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const qb200_shard_peers_t *peers,
+                           unsigned int epoch, const qb200_shard_peers_t *after, unsigned int after_epoch, long long limit_cycles, void *stream);
 /* A device allocation of this process (qb200_malloc) as a 64-byte handle another process on the same box can open
  * (cudaIpcGetMemHandle / cudaIpcOpenMemHandle / cudaIpcCloseMemHandle); opening enables peer access to the owner's GPU. */
 int qb200_ipc_export(const void *ptr, void *handle64);

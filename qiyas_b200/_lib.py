@@ -51,6 +51,7 @@ SIGNATURES = {
     "qb200_shard_range": (_I, [_I, _I, _I, C.POINTER(_I), C.POINTER(_I)]),
     "qb200_shard_gemv": (_I, [_I, _I, _P, _P, _I, _I, C.POINTER(ShardPeers), C.c_uint, _P]),
     "qb200_shard_wait": (_I, [C.POINTER(ShardPeers), C.c_uint, C.c_longlong, _P]),
+    "qb200_shard_gemv_after": (_I, [_I, _I, _P, _P, _I, _I, C.POINTER(ShardPeers), C.c_uint, C.POINTER(ShardPeers), C.c_uint, C.c_longlong, _P]),
     "qb200_ipc_export": (_I, [_P, _P]),
     "qb200_ipc_import": (_I, [_P, C.POINTER(_P)]),
     "qb200_ipc_close": (_I, [_P]),

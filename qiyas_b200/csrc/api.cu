@@ -449,7 +449,20 @@ int qb200_shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, i
     if ((rc = qb200_shard_range(rows_total, peers->world, peers->rank, &first, &count))) return rc;
     // the slice as an ordinary gemv: formats, whole blocks, limits, alignment (a rank without rows has nothing to check but x)
     if ((rc = check_gemv(fmt_a, fmt_x, count ? a_shard : x, x, peers->out[peers->rank] + first, count, cols))) return rc;
-    return finish(qb::shard_gemv(fmt_a, fmt_x, a_shard, x, rows_total, cols, peers, epoch, (cudaStream_t)stream), "shard_gemv");
+    return finish(qb::shard_gemv(fmt_a, fmt_x, a_shard, x, rows_total, cols, peers, epoch, nullptr, 0, 0, (cudaStream_t)stream), "shard_gemv");
+}
+
+int qb200_shard_gemv_after(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const qb200_shard_peers_t *peers,
+                           unsigned int epoch, const qb200_shard_peers_t *after, unsigned int after_epoch, long long limit_cycles, void *stream)
+{
+    int rc = check_peers(peers);
+    if (rc || (rc = check_peers(after))) return rc;
+    if (after->world != peers->world || after->rank != peers->rank) return fail(QB200_E_SHAPE, "the two exchanges must be between the same ranks");
+    int first = 0, count = 0;
+    if ((rc = qb200_shard_range(rows_total, peers->world, peers->rank, &first, &count))) return rc;
+    if ((rc = check_gemv(fmt_a, fmt_x, count ? a_shard : x, x, peers->out[peers->rank] + first, count, cols))) return rc;
+    return finish(qb::shard_gemv(fmt_a, fmt_x, a_shard, x, rows_total, cols, peers, epoch, after, after_epoch, limit_cycles, (cudaStream_t)stream),
+                  "shard_gemv_after");
 }
 
 int qb200_shard_wait(const qb200_shard_peers_t *peers, unsigned int epoch, long long limit_cycles, void *stream)

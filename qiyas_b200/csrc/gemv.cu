@@ -876,6 +876,35 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
     // whatever wrote x (or prepared it) has ended and its writes are visible; skipped when the host has established that
     // the launch before this one (the only one that can still be running) shares no buffer with this call
     if (!p.independent || !p.x) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if constexpr (TAIL == TAIL_PUBLISH) {
+        // x is the output of an earlier exchange: thread w waits (bounded) until rank w's word of this rank's flag array
+        // of that exchange has reached its epoch -- the peers' rows of x have then arrived (the acquire pairs with the
+        // publishers' release; the barrier hands it to the block's other threads).  The launch before this one has
+        // completed (the wait above), so with counted epochs the count of published calls is that exchange's last epoch.
+        // The weights' copies have been running all along.
+        if (p.publish.wait_flags) {
+            if ((int)threadIdx.x < p.publish.world) {
+                const unsigned int *flags = p.publish.wait_flags;
+                const unsigned int epoch = p.publish.wait_epoch ? p.publish.wait_epoch : __ldcg(flags + QB200_SHARD_MAX);
+                if (epoch) {
+                    const long long start = clock64();
+                    for (;;) {
+                        unsigned int v;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
+                        if ((int)(v - epoch) >= 0) break;
+                        if (clock64() - start > p.publish.wait_limit) {
+                            atomicOr(p.status, STATUS_SHARD_WAIT);
+                            break;
+                        }
+                        __nanosleep(50);
+                    }
+                    // the exchange's count of waits follows its count of published calls (one block counts)
+                    if (blockIdx.x == 0 && threadIdx.x == 0 && !p.publish.wait_epoch) atomicAdd((unsigned int *)flags + QB200_SHARD_MAX + 1, 1u);
+                }
+            }
+            named_bar_sync(1, threads);
+        }
+    }
     const uint8_t *xp = p.xprep;
     if (p.x) {
         if (FMT == QB200_Q8_0 || FMT == QB200_Q4_0) prepare_x_in_block<true>(p.x, p.fmt_x, p.cols, smem + p.off_x, threadIdx.x, threads, xbar);
@@ -1318,8 +1347,15 @@ int gemv_launch(int fmt_a, int fmt_x, const void *a, const void *x, float *y, in
     // full order by the launch itself: nothing known, the weights themselves in flight (the producer reads them before
     // any wait), launches side by side that a wait on the newest would not cover, or a history that has no room left
     const bool serial = conflict && (!known || weights_written || !t_hist.settled || t_hist.count == HISTORY);
-    if (publish) t_hist.count = 0;          // nothing is known about what runs beside the next call
-    else if (independent) {
+    if (publish) {
+        // it writes memory this record does not describe, and has itself waited for everything before it (by its launch
+        // or by griddepcontrol.wait after a settled history): the next call waits for it, by griddepcontrol.wait alone
+        memset(&t_hist.at[0], 0, sizeof t_hist.at[0]);
+        t_hist.at[0].everything = true;
+        t_hist.stream = stream;
+        t_hist.count = 1;
+        t_hist.settled = true;
+    } else if (independent) {
         t_hist.at[t_hist.count++] = now;
         t_hist.settled = false;
     } else if (serial) {

@@ -23,6 +23,10 @@ struct GemvPublish {
     unsigned int *epoch_counter;  // this rank's count of published calls (device-local), used when epoch is 0
     int world;
     unsigned int epoch;           // the value stored to the flags; 0: the next value of epoch_counter
+    // optional: x is the output of an earlier exchange; the consumers wait (bounded) for its flags before they read x
+    const unsigned int *wait_flags;   // this rank's flag array of that exchange (null: no wait)
+    unsigned int wait_epoch;          // the epoch to wait for; 0: that exchange's count of published calls
+    long long wait_limit;             // clock cycles
 };
 
 cudaError_t gemv_init(int sm_count, int max_smem, int *status);
@@ -40,8 +44,9 @@ int gemv_noalloc_status(int *value);
 
 // The sharded gemv (shard.cu): rows [first, first + count) of a rows_total-row product on this rank, published to the peers.
 cudaError_t shard_init(int *status);
+// after: optional peers of the exchange that produced x (waited for inside the kernel), with its epoch and limit
 int shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const void *peers, unsigned int epoch,
-               cudaStream_t stream);
+               const void *after, unsigned int after_epoch, long long limit_cycles, cudaStream_t stream);
 int shard_wait(const void *peers, unsigned int epoch, long long limit_cycles, cudaStream_t stream);
 
 int encode_launch(int fmt, const float *lanes, void *blocks, int64_t n, cudaStream_t stream);

@@ -68,9 +68,9 @@ __global__ void shard_wait_kernel(unsigned int *flags, int world, unsigned int e
 }
 
 int shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const void *peers_v, unsigned int epoch,
-               cudaStream_t stream)
+               const void *after_v, unsigned int after_epoch, long long limit_cycles, cudaStream_t stream)
 {
-    const qb200_shard_peers_t *peers = (const qb200_shard_peers_t *)peers_v;
+    const qb200_shard_peers_t *peers = (const qb200_shard_peers_t *)peers_v, *after = (const qb200_shard_peers_t *)after_v;
     int first = 0, count = 0;
     qb200_shard_range(rows_total, peers->world, peers->rank, &first, &count);
     GemvPublish pub;
@@ -83,7 +83,17 @@ int shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int row
         pub.out[w] = w == peers->rank ? nullptr : peers->out[w] + first;
         pub.flag[w] = peers->flags[w] + peers->rank;
     }
+    if (after) {
+        pub.wait_flags = after->flags[after->rank];
+        pub.wait_epoch = after_epoch;
+        pub.wait_limit = limit_cycles > 0 ? limit_cycles : WAIT_CYCLES;
+    }
     if (count == 0) {
+        // a rank without rows: its flag, after the wait its peers' kernels make inside (so that its counters keep step)
+        if (after) {
+            int rc = shard_wait(after_v, after_epoch, limit_cycles, stream);
+            if (rc) return rc;
+        }
         shard_flag_kernel<<<1, 32, 0, stream>>>(pub);
         return (int)cudaGetLastError();
     }

@@ -203,18 +203,27 @@ class PeerExchange:
         self._opened, self._own = [], []
 
 
-def _exchange(self, x, exchange, fmt_x=None, stream=None, limit_cycles=0):
+def _exchange(self, x, exchange, fmt_x=None, stream=None, limit_cycles=0, after=None, wait=True):
     """This rank's slice into every rank's copy of y (stores from inside the gemv kernel), then the bounded wait for the
-    peers' slices: after it, work on `stream` sees the whole y in `exchange.y()`."""
+    peers' slices: after it, work on `stream` sees the whole y in `exchange.y()`.
+
+    A chain of products (each x the whole y of the one before): pass `after` = the exchange whose y this x is and
+    `wait=False` on all but the last; the kernel then waits for that exchange's flags itself, with its weights' copies
+    already running, and no wait kernel stands between the products.  Alternate two exchanges along the chain."""
     import ctypes as C
 
     from .ops import _ptr, _stream
     exchange.epoch += 1
     fx = self.fmt if fmt_x is None else fmt_id(fmt_x)
-    rc = self.ops.lib.qb200_shard_gemv(self.fmt, fx, _ptr(self.w), _ptr(x), self.plan.rows, self.cols, C.byref(exchange.peers), exchange.epoch,
-                                       _stream(stream))
+    if after is None:
+        rc = self.ops.lib.qb200_shard_gemv(self.fmt, fx, _ptr(self.w), _ptr(x), self.plan.rows, self.cols, C.byref(exchange.peers), exchange.epoch,
+                                           _stream(stream))
+    else:
+        rc = self.ops.lib.qb200_shard_gemv_after(self.fmt, fx, _ptr(self.w), _ptr(x), self.plan.rows, self.cols, C.byref(exchange.peers),
+                                                 exchange.epoch, C.byref(after.peers), after.epoch, int(limit_cycles), _stream(stream))
     self.ops.gpu.check(rc, "shard_gemv")
-    self.ops.gpu.check(self.ops.lib.qb200_shard_wait(C.byref(exchange.peers), exchange.epoch, int(limit_cycles), _stream(stream)), "shard_wait")
+    if wait:
+        self.ops.gpu.check(self.ops.lib.qb200_shard_wait(C.byref(exchange.peers), exchange.epoch, int(limit_cycles), _stream(stream)), "shard_wait")
     return exchange.y()
 
 

@@ -55,11 +55,40 @@ def _worker(rank, world, port, rows, cols, m, out):
             torch.cuda.synchronize()
             dist.barrier()
             ex.close()
+        # a chain of products, each reading the whole output of the one before it from the exchange it was published to:
+        # the kernels wait for the flags themselves, two exchanges alternate, one wait at the end
+        if chained_case(rows, cols):
+            wc = B.make_weights(B.Q4_0, rows, rows, 9)
+            sc = torch.from_numpy(plan.slice_weights(rank, B.Q4_0, rows, wc)).to(dev)
+            gc = ShardedGemv(ops, plan, rank, B.Q4_0, rows, sc)
+            ea, eb = PeerExchange(ops, rows, rank, world), PeerExchange(ops, rows, rank, world)
+            try:
+                v = torch.from_numpy(B.make_activations(rows, 70)).to(dev)
+                yv = gc.exchange(v, ea, fmt_x=B.F32, wait=False)
+                for step in range(1, CHAIN):
+                    src, dst = (ea, eb) if step % 2 else (eb, ea)
+                    yv = gc.exchange(yv, dst, fmt_x=B.F32, after=src, wait=step == CHAIN - 1)
+                torch.cuda.synchronize()
+                assert ops.gpu.status() == 0
+                np.save(f"{out}.chain.r{rank}.npy", yv.cpu().numpy())
+            finally:
+                torch.cuda.synchronize()
+                dist.barrier()
+                ea.close()
+                eb.close()
         if rank == 0:
             np.save(out + ".y.npy", y.cpu().numpy())
             np.save(out + ".c.npy", c.cpu().numpy())
     finally:
         dist.destroy_process_group()
+
+
+CHAIN = 4
+
+
+def chained_case(rows, cols):
+    """The chained products (a square matrix of `rows`: every y is the next x) ride on one of the shapes only."""
+    return rows == 4096 and cols == 8192
 
 
 @pytest.mark.parametrize("rows,cols", [(4096, 8192), (4093, 8160)])
@@ -85,6 +114,16 @@ def test_two_ranks_equal_unsharded(oracle, tmp_path, rows, cols):
         for rank in range(world):
             got = np.load(f"{out}.x{epoch}.r{rank}.npy")
             assert np.max(np.abs(got - want)) <= 1e-5 * np.abs(want).max(), (epoch, rank)
+    if chained_case(rows, cols):
+        # the chain on the CPU: every rank must hold the same whole vector, and it must be the oracle's chain (each step
+        # re-encodes its x to Q8_0, where a last-bit difference of an element can move a code: hence the looser bound)
+        wc = B.make_weights(B.Q4_0, rows, rows, 9)
+        v = B.make_activations(rows, 70)
+        for _ in range(CHAIN):
+            v = oracle.gemv_blocks(B.Q4_0, B.F32, wc, v, rows, rows, order=1)
+        got = [np.load(f"{out}.chain.r{rank}.npy") for rank in range(world)]
+        assert np.array_equal(got[0].view(np.uint32), got[1].view(np.uint32))
+        assert np.max(np.abs(got[0] - v)) <= 2e-3 * np.abs(v).max()
 
 
 def _peers(lib, world, rank, ys, flags):
@@ -147,4 +186,70 @@ def test_a_wait_nobody_answers_runs_out():
     assert o.gpu.status() == 0                                                  # read and cleared
     flags[0][:2] = 1
     assert o.lib.qb200_shard_wait(C.byref(p), 1, 2_000_000, None) == 0
+    assert o.gpu.status() == 0
+
+
+@pytest.mark.parametrize("counted", [False, True])
+def test_chained_exchange_kernels_on_one_gpu(oracle, counted):
+    # the chain's kernels (the wait inside the gemv) with every rank's launches in turn on the one GPU: a product's launches
+    # all precede the next product's, so no kernel waits for one that has not been launched
+    import ctypes as C
+    import torch
+
+    from . import helpers as H
+    from qiyas_b200.shard import ShardPlan
+    o = H.ops()
+    rows, world, steps = 1024, 4, 4
+    w = B.make_weights(B.Q4_0, rows, rows, 25)
+    plan = ShardPlan(rows, world)
+    shards = [H.dev(plan.slice_weights(r, B.Q4_0, rows, w)) for r in range(world)]
+    ys = [[torch.zeros(rows, dtype=torch.float32, device="cuda:0") for _ in range(world)] for _ in range(2)]
+    flags = [[torch.zeros(16, dtype=torch.int32, device="cuda:0") for _ in range(world)] for _ in range(2)]
+    x0 = B.make_activations(rows, 26)
+    x = H.dev(x0)
+    epochs = [0, 0]
+    for step in range(steps):
+        dst, src = step % 2, (step + 1) % 2
+        epochs[dst] += 1
+        for r in range(world):
+            pd = _peers(o.lib, world, r, ys[dst], flags[dst])
+            if step == 0:
+                rc = o.lib.qb200_shard_gemv(B.Q4_0, B.F32, shards[r].data_ptr(), x.data_ptr(), rows, rows, C.byref(pd), 0 if counted else epochs[dst], None)
+            else:
+                ps = _peers(o.lib, world, r, ys[src], flags[src])
+                rc = o.lib.qb200_shard_gemv_after(B.Q4_0, B.F32, shards[r].data_ptr(), ys[src][r].data_ptr(), rows, rows, C.byref(pd),
+                                                  0 if counted else epochs[dst], C.byref(ps), 0 if counted else epochs[src], 0, None)
+            assert rc == 0, o.gpu.error()
+    for r in range(world):
+        pd = _peers(o.lib, world, r, ys[(steps - 1) % 2], flags[(steps - 1) % 2])
+        assert o.lib.qb200_shard_wait(C.byref(pd), 0 if counted else epochs[(steps - 1) % 2], 0, None) == 0
+    assert o.gpu.status() == 0
+    v = x0
+    for _ in range(steps):
+        v = oracle.gemv_blocks(B.Q4_0, B.F32, w, v, rows, rows, order=1)
+    for r in range(world):
+        got = ys[(steps - 1) % 2][r].cpu().numpy()
+        assert np.max(np.abs(got - v)) <= 2e-3 * np.abs(v).max(), r
+        assert np.array_equal(got.view(np.uint32), ys[(steps - 1) % 2][0].cpu().numpy().view(np.uint32))
+
+
+def test_a_wait_inside_the_gemv_runs_out():
+    # the exchange x is said to come from never raised its flags: the kernel's own wait gives up after its limit, reports
+    # bit 2, computes on what is there, and the context stays usable
+    import ctypes as C
+    import torch
+
+    from . import helpers as H
+    o = H.ops()
+    rows = 256
+    w = H.dev(B.make_weights(B.Q4_0, rows, rows, 27))
+    ys = [[torch.zeros(rows, dtype=torch.float32, device="cuda:0")] for _ in range(2)]
+    flags = [[torch.zeros(16, dtype=torch.int32, device="cuda:0")] for _ in range(2)]
+    pd, ps = _peers(o.lib, 1, 0, ys[0], flags[0]), _peers(o.lib, 1, 0, ys[1], flags[1])
+    assert o.gpu.status() == 0
+    assert o.lib.qb200_shard_gemv_after(B.Q4_0, B.F32, w.data_ptr(), ys[1][0].data_ptr(), rows, rows, C.byref(pd), 1, C.byref(ps), 7, 2_000_000, None) == 0
+    assert o.gpu.status() == 4
+    assert o.gpu.status() == 0
+    flags[1][0][0] = 7
+    assert o.lib.qb200_shard_gemv_after(B.Q4_0, B.F32, w.data_ptr(), ys[1][0].data_ptr(), rows, rows, C.byref(pd), 2, C.byref(ps), 7, 2_000_000, None) == 0
     assert o.gpu.status() == 0
