@@ -112,6 +112,7 @@ struct MatmulArgs {
     int mtiles;
     int probe;               // tuning build only (see MM_PROBE)
     long long *trace;        // tuning build only: clock stamps of block 0
+    const uint8_t *b_raw;    // few rows of A on raw weights: B's rows as the caller holds them (k in whole groups of eight blocks, 16-byte aligned)
     int batch;               // products: operand sets a_stride / b_stride bytes apart in their packed form (0: the same for all), results c_stride values apart
     size_t a_stride, b_stride, c_stride;
 };
@@ -996,9 +997,18 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
 // the epilogue; NB batches are in flight.  Thread (q, lane) of the four epilogue warps owns row n0 + 32 q + lane of B,
 // i.e. column n of C, and keeps its BN accumulators in registers; a warp's stores of one row of C are 32 consecutive
 // floats.  A shared-memory stage is one group of eight k-blocks: B's slab in one copy (read once from HBM), A's in another.
-template <int BN>
+// RAW: 0 = B comes prepacked (LAY_GROUPED slabs, one copy a stage); 1 + format = B comes as raw Q8_0 / Q4_0 rows and eight
+// converter warps re-lay a tile's group of k-blocks into the stage themselves: coalesced 16-byte loads of the rows' bytes
+// into registers (the next stage's while the current one is converted), through a staging buffer in shared memory, then
+// a thread a (row, block) writes the int8 codes as core matrices and the f16 scale into the scale rows, as the pack
+// kernels would have written them to memory.  The weights are then read once, in their raw form (Q4_0: 4 bits a value),
+// and a call on raw operands needs no packing pass over B.
+template <int BN, int RAW = 0>
 struct FewCfg {
     static constexpr int KS = GROUP;                               // k-blocks a shared-memory stage
+    static constexpr int RAW_BB = RAW == 2 ? 18 : 34;               // bytes a raw block
+    static constexpr int RAW_HALVES = GROUP * RAW_BB / 2, RAW_PITCH = RAW_HALVES + 2;      // halfwords a row's group; an odd number of words a row
+    static constexpr uint32_t STAGING = RAW ? TILE * RAW_PITCH * 2 : 0;
     static constexpr int BATCH = 64 / BN;                          // k-blocks a batch in tensor memory
     static constexpr int BCOLS = 128;                              // its columns: 64 of sums, 64 of scale products
     static constexpr int NB = 512 / BCOLS;                         // batches in flight
@@ -1007,10 +1017,11 @@ struct FewCfg {
     static constexpr uint32_t O_BS = GROUP * B_KB, O_A = B_SLAB, O_AS = O_A + GROUP * A_KB;
     static constexpr uint32_t STAGE = B_SLAB + A_SLAB;
     static constexpr uint32_t PATCH = 2048;
-    static constexpr int S_FIT = (int)((MM_SMEM_MAX - MM_HEADER - PATCH) / STAGE);
+    static constexpr int S_FIT = (int)((MM_SMEM_MAX - MM_HEADER - PATCH - STAGING) / STAGE);
     static constexpr int S = S_FIT > 8 ? 8 : S_FIT;
     static constexpr uint32_t O_PATCH = MM_HEADER + S * STAGE;
-    static constexpr uint32_t SMEM = O_PATCH + PATCH;
+    static constexpr uint32_t O_STAGING = O_PATCH + PATCH;
+    static constexpr uint32_t SMEM = O_STAGING + STAGING;
     static_assert(BN == 16 || BN == 32 || BN == 64, "the batch is 64 columns of sums");
     static_assert(S >= 2 && 2 * S + 2 * NB + 2 <= 64, "barriers fit the header");
 };
@@ -1020,8 +1031,17 @@ struct FewCfg {
 #ifndef FEW_CW
 #define FEW_CW 16
 #endif
-template <int BN> __host__ __device__ constexpr int few_threads() { return 32 * (4 + 4 * (BN / FEW_CW)); }
+constexpr int CONV_WARPS = 8;               // RAW: the warps after the epilogue's
+template <int BN, int RAW = 0> __host__ __device__ constexpr int few_threads() { return 32 * (4 + 4 * (BN / FEW_CW) + (RAW ? CONV_WARPS : 0)); }
 
+// A named barrier of `threads` threads that also tells every one of them whether `mine` held for all.
+__device__ __forceinline__ bool named_bar_and(int id, int threads, bool mine)
+{
+    uint32_t all;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, %3, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(all) : "r"(mine ? 1u : 0u), "r"(id), "r"(threads) : "memory");
+    return all != 0;
+}
 // Nothing is emitted: the registers pass through the statement, so that what uses them stays below the wait before it.
 __device__ __forceinline__ void pin16(uint32_t *v)
 {
@@ -1036,12 +1056,15 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N])
     for (int c = 0; c < N; c += 16) tmem_ld16(taddr + c, *(uint32_t(*)[16])(v + c));
 }
 
-template <int BN>
-__global__ void __launch_bounds__(few_threads<BN>(), 1) fewrows_kernel(const MatmulArgs p)
+template <int BN, int RAW>
+__global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(const MatmulArgs p)
 {
-    using G = FewCfg<BN>;
+    using G = FewCfg<BN, RAW>;
     constexpr int S = G::S, KS = G::KS, BATCH = G::BATCH, NB = G::NB, BPS = KS / BATCH;
     constexpr int CG = BN / FEW_CW, CW = FEW_CW;                    // column groups of the epilogue, columns a warp
+    constexpr int THREADS = few_threads<BN, RAW>(), CONV0 = 4 + 4 * CG;      // the first converter warp
+    // k-blocks of a batch the epilogue reads at once (64 registers of sums and scale products a thread)
+    constexpr int SUB = RAW && BATCH > 2 ? 2 : BATCH;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = smem_u32(smem);
@@ -1054,7 +1077,7 @@ __global__ void __launch_bounds__(few_threads<BN>(), 1) fewrows_kernel(const Mat
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
-            mbar_init(full0 + 8 * s, 1);
+            mbar_init(full0 + 8 * s, RAW ? 1 + CONV_WARPS : 1);     // the producer's copies, and the converter warps
             mbar_init(empty0 + 8 * s, 2);                // both issuers' commits
         }
         for (int t = 0; t < NB; t++) {
@@ -1064,7 +1087,7 @@ __global__ void __launch_bounds__(few_threads<BN>(), 1) fewrows_kernel(const Mat
         *abort_flag = 0;
         mbar_fence_init();
     }
-    for (int i = threadIdx.x; i < (int)G::PATCH / 16; i += few_threads<BN>()) *(uint4 *)(smem + G::O_PATCH + i * 16) = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < (int)G::PATCH / 16; i += THREADS) *(uint4 *)(smem + G::O_PATCH + i * 16) = make_uint4(0, 0, 0, 0);
     fence_proxy_async();
     if (warp == 1) tmem_alloc(holder, 512);
     tc_fence_before();
@@ -1095,8 +1118,8 @@ __global__ void __launch_bounds__(few_threads<BN>(), 1) fewrows_kernel(const Mat
             };
             const int pre = min(S, stages);
             for (int sc = 0; sc < pre; sc++) {
-                mbar_arrive_expect_tx(full0 + 8 * sc, G::B_SLAB + (with_a ? G::A_SLAB : 0u));
-                bulk_g2s(smem_u32(ring + (size_t)sc * G::STAGE), b_src(sc), G::B_SLAB, full0 + 8 * sc);
+                mbar_arrive_expect_tx(full0 + 8 * sc, (RAW ? 0u : G::B_SLAB) + (with_a ? G::A_SLAB : 0u));
+                if (!RAW) bulk_g2s(smem_u32(ring + (size_t)sc * G::STAGE), b_src(sc), G::B_SLAB, full0 + 8 * sc);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int sc = 0; sc < pre && with_a; sc++) bulk_g2s(smem_u32(ring + (size_t)sc * G::STAGE) + G::O_A, a_src(sc), G::A_SLAB, full0 + 8 * sc);
@@ -1107,8 +1130,8 @@ __global__ void __launch_bounds__(few_threads<BN>(), 1) fewrows_kernel(const Mat
                 if (!mm_wait(empty0 + 8 * s, (uint32_t)(sc / S - 1) & 1u, abort_flag, p.status, wmode)) break;
                 w_empty += MM_CLOCK() - w0;
                 const uint32_t dst = smem_u32(ring + (size_t)s * G::STAGE), bar = full0 + 8 * s;
-                mbar_arrive_expect_tx(bar, G::B_SLAB + (with_a ? G::A_SLAB : 0u));
-                bulk_g2s(dst, b_src(sc), G::B_SLAB, bar);
+                mbar_arrive_expect_tx(bar, (RAW ? 0u : G::B_SLAB) + (with_a ? G::A_SLAB : 0u));
+                if (!RAW) bulk_g2s(dst, b_src(sc), G::B_SLAB, bar);
                 if (with_a) bulk_g2s(dst + G::O_A, a_src(sc), G::A_SLAB, bar);
             }
             MM_TRACE(p, 0, w_empty); MM_TRACE(p, 1, MM_CLOCK() - t_begin); MM_TRACE(p, 2, (long long)sc);
@@ -1174,7 +1197,7 @@ __global__ void __launch_bounds__(few_threads<BN>(), 1) fewrows_kernel(const Mat
             }
             MM_TRACE(p, 8 + 4 * (warp - 1), w_full); MM_TRACE(p, 9 + 4 * (warp - 1), w_tempty); MM_TRACE(p, 10 + 4 * (warp - 1), MM_CLOCK() - t_begin);
         }
-    } else if (warp >= 4) {
+    } else if (warp >= 4 && warp < CONV0) {
         // ---- epilogue: warp (q, cg) reads lanes 32 q .. 32 q + 31 and columns cg * CW .. of every k-block's sums
         const int q = warp & 3, cg = (warp - 4) >> 2;
         const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cg * CW);
@@ -1196,26 +1219,31 @@ __global__ void __launch_bounds__(few_threads<BN>(), 1) fewrows_kernel(const Mat
                 w_tfull += w1 - w0;
                 tc_fence_after();
                 const uint32_t at = tlane + (uint32_t)(t * G::BCOLS);
-                uint32_t v[BATCH][CW], x[BATCH][CW];
 #pragma unroll
-                for (int j = 0; j < BATCH; j++) {
-                    tmem_ld_cols<CW>(at + j * BN, v[j]);
-                    tmem_ld_cols<CW>(at + 64 + j * BN, x[j]);
-                }
-                tmem_ld_wait();
-                w_ld += MM_CLOCK() - w1;
+                for (int j0 = 0; j0 < BATCH; j0 += SUB) {
+                    uint32_t v[SUB][CW], x[SUB][CW];
 #pragma unroll
-                for (int j = 0; j < BATCH; j++) {
+                    for (int j = 0; j < SUB; j++) {
+                        tmem_ld_cols<CW>(at + (j0 + j) * BN, v[j]);
+                        tmem_ld_cols<CW>(at + 64 + (j0 + j) * BN, x[j]);
+                    }
+                    tmem_ld_wait();
+                    if (j0 == 0) w_ld += MM_CLOCK() - w1;
 #pragma unroll
-                    for (int c = 0; c < CW; c += 16) { pin16(v[j] + c); pin16(x[j] + c); }
-                }
-                tc_fence_before();
-                if (lane == 0) mbar_arrive(tempty0 + 8 * t);             // the batch has been read (warp-wide reads)
+                    for (int j = 0; j < SUB; j++) {
 #pragma unroll
-                for (int j = 0; j < BATCH; j++) {
-                    if (j < nb && !(MM_PROBE(p) & 4)) {
+                        for (int c = 0; c < CW; c += 16) { pin16(v[j] + c); pin16(x[j] + c); }
+                    }
+                    if (j0 + SUB >= BATCH) {
+                        tc_fence_before();
+                        if (lane == 0) mbar_arrive(tempty0 + 8 * t);         // the batch has been read (warp-wide reads)
+                    }
 #pragma unroll
-                        for (int c = 0; c < CW; c++) acc[c] = __fmaf_rn((float)(int32_t)v[j][c], __uint_as_float(x[j][c]), acc[c]);
+                    for (int j = 0; j < SUB; j++) {
+                        if (j0 + j < nb && !(MM_PROBE(p) & 4)) {
+#pragma unroll
+                            for (int c = 0; c < CW; c++) acc[c] = __fmaf_rn((float)(int32_t)v[j][c], __uint_as_float(x[j][c]), acc[c]);
+                        }
                     }
                 }
             }
@@ -1246,6 +1274,114 @@ __global__ void __launch_bounds__(few_threads<BN>(), 1) fewrows_kernel(const Mat
             }
         }
         if (lane == 0 && warp < 8) { MM_TRACE(p, 16 + 4 * (warp - 4), w_tfull); MM_TRACE(p, 17 + 4 * (warp - 4), MM_CLOCK() - t_begin); MM_TRACE(p, 18 + 4 * (warp - 4), w_ld); }
+    } else if (RAW && warp >= CONV0) {
+        // ---- converters (RAW): the tile's rows of the group, raw, become the stage's codes and scale rows
+        constexpr int BB = G::RAW_BB, VECS = GROUP * BB / 16, PITCH = G::RAW_PITCH, CT = CONV_WARPS * 32, PER = (TILE * VECS + CT - 1) / CT;
+        const int ct = threadIdx.x - CONV0 * 32;
+        uint16_t *staging = (uint16_t *)(smem + G::O_STAGING);
+        const size_t row_bytes = (size_t)p.kb * BB;
+        // 16-byte pieces of the 128 row segments, consecutive threads on consecutive pieces (coalesced); rows past the end
+        // read as zeros.  The next stage's bytes are on their way (in registers) while one is converted; a second stage
+        // ahead changed nothing (the loads of one stage already fill the multiprocessor's queue of pending requests: this
+        // path is bound by that queue and by the conversion's own shared-memory traffic, not by the tensor cores).
+        auto load = [&](int sc, uint4 (&held)[PER]) {
+            if (sc >= stages) return;
+            const int tile = blockIdx.x + (sc / groups) * gridDim.x, n0 = (tile % ntiles) * TILE;
+            const uint8_t *src = p.b_raw + (size_t)(sc % groups) * (GROUP * BB);
+#pragma unroll
+            for (int i = 0; i < PER; i++) {
+                const int idx = ct + i * CT, rr = idx / VECS, c = idx - rr * VECS;
+                held[i] = make_uint4(0, 0, 0, 0);
+                if (idx < TILE * VECS && n0 + rr < p.n) held[i] = __ldg((const uint4 *)(src + (size_t)(n0 + rr) * row_bytes) + c);
+            }
+        };
+        // one stage: its bytes from registers to the staging buffer, the registers refilled with the next stage's, the
+        // conversion into the ring; false when the block gives up
+        const bool load_first = (warp & 1) == 0;
+        long long c_sts = 0, c_bar = 0, c_wait = 0, c_conv = 0, c_and = 0, c_fence = 0, c_load = 0;
+        const long long c_begin = MM_CLOCK();
+        auto step = [&](int sc, uint4 (&held)[PER]) -> bool {
+            const long long q0 = MM_CLOCK();
+#pragma unroll
+            for (int i = 0; i < PER; i++) {
+                const int idx = ct + i * CT, rr = idx / VECS, c = idx - rr * VECS;
+                if (idx < TILE * VECS) {
+                    uint32_t *dst = (uint32_t *)(staging + rr * PITCH) + c * 4;
+                    dst[0] = held[i].x; dst[1] = held[i].y; dst[2] = held[i].z; dst[3] = held[i].w;
+                }
+            }
+            const long long q1 = MM_CLOCK();
+            named_bar_sync(3, CT);                       // the staging buffer holds the stage's raw bytes
+            const long long q2 = MM_CLOCK();
+            // half the warps ask for the next stage's bytes before they convert, the other half after: the loads' issue (the
+            // queue of pending requests) and the conversion (shared memory, integer pipe) then overlap across warps
+            if (load_first) load(sc + 1, held);
+            c_load += MM_CLOCK() - q2;
+            const int s = sc % S;
+            bool ok = true;
+            if (sc >= S) ok = mm_wait(empty0 + 8 * s, (uint32_t)(sc / S - 1) & 1u, abort_flag, p.status, wmode);
+            const long long q3 = MM_CLOCK();
+            c_sts += q1 - q0; c_bar += q2 - q1; c_wait += q3 - q2;
+            if (ok) {
+                uint8_t *stage = ring + (size_t)s * G::STAGE;
+                const int rl = ct & (TILE - 1), half = ct >> 7;
+#pragma unroll
+                for (int jj = 0; jj < GROUP / 2; jj++) {
+                    const int j = half * (GROUP / 2) + jj;
+                    // the block's bytes as 32-bit words: a block starts on a word boundary when j is even (34 j and 18 j are
+                    // then multiples of 4), two bytes past one when j is odd; jj has j's parity (half * 4 is even)
+                    const uint32_t *w32 = (const uint32_t *)(staging + rl * PITCH) + (j * BB) / 4;
+                    uint32_t w[8], d_bits;
+                    if (RAW == 1) {
+                        uint32_t r[9];
+#pragma unroll
+                        for (int i = 0; i < 9; i++) r[i] = w32[i];
+                        if (jj & 1) {
+                            d_bits = r[0] >> 16;
+#pragma unroll
+                            for (int i = 0; i < 8; i++) w[i] = r[i + 1];
+                        } else {
+                            d_bits = r[0] & 0xFFFFu;
+#pragma unroll
+                            for (int i = 0; i < 8; i++) w[i] = __funnelshift_r(r[i], r[i + 1], 16);
+                        }
+                    } else {
+                        // value i in the low nibble of byte i, value i + 16 in the high nibble, each minus 8 (src/MatMulBlocks.cs:282-299)
+                        uint32_t r[5];
+#pragma unroll
+                        for (int i = 0; i < 5; i++) r[i] = w32[i];
+                        d_bits = (jj & 1) ? r[0] >> 16 : r[0] & 0xFFFFu;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const uint32_t nib = (jj & 1) ? r[i + 1] : __funnelshift_r(r[i], r[i + 1], 16);
+                            w[i] = __vsub4(nib & 0x0F0F0F0Fu, 0x08080808u);
+                            w[i + 4] = __vsub4((nib >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+                        }
+                    }
+                    uint8_t *codes = stage + j * G::B_KB + (rl / 8) * 256 + (rl & 7) * 16;
+                    *(uint4 *)codes = make_uint4(w[0], w[1], w[2], w[3]);
+                    *(uint4 *)(codes + 128) = make_uint4(w[4], w[5], w[6], w[7]);
+                    *(uint16_t *)(stage + G::O_BS + rl * 16 + j * 2) = (uint16_t)d_bits;
+                }
+                const long long q5 = MM_CLOCK();
+                fence_proxy_async();                     // the tensor cores read the stage through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + 8 * s);
+                c_fence += MM_CLOCK() - q5;
+            }
+            if (!load_first) load(sc + 1, held);
+            // everybody has read the staging buffer; and everybody goes on, or nobody does
+            const long long q4 = MM_CLOCK();
+            const bool go = named_bar_and(3, CT, ok && !*abort_flag);
+            c_conv += q4 - q3; c_and += MM_CLOCK() - q4;
+            return go;
+        };
+        uint4 held0[PER];
+        load(0, held0);
+        for (int sc = 0; sc < stages; sc++) {
+            if (!step(sc, held0)) break;
+        }
+        if (ct == 0) { MM_TRACE(p, 32, c_sts); MM_TRACE(p, 33, c_bar); MM_TRACE(p, 34, c_wait); MM_TRACE(p, 35, c_conv); MM_TRACE(p, 36, c_and); MM_TRACE(p, 37, MM_CLOCK() - c_begin); MM_TRACE(p, 38, (long long)stages); MM_TRACE(p, 39, c_fence); MM_TRACE(p, 40, c_load); }
     }
     tc_fence_before();
     __syncthreads();
@@ -1321,6 +1457,13 @@ static int g_mm_sms = 0;
 static int g_mm_kind = 0;          // the tensor kind the library packs for and multiplies with
 static int g_mm_tcs = 1;           // scale products of plain f16 scales on the tensor cores
 static int g_mm_few = 64;          // most rows of A the kernel with the operands' sides exchanged takes
+static int g_mm_raw_few = 1;       // that kernel re-lays raw weights itself where it can
+
+template <int BN, int RAW>
+static cudaError_t set_few_attr()
+{
+    return cudaFuncSetAttribute(fewrows_kernel<BN, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewCfg<BN, RAW>::SMEM);
+}
 
 template <int KIND, bool SUMS, int VAR>
 static cudaError_t set_mm_attr_var()
@@ -1348,11 +1491,13 @@ cudaError_t matmul_init(int sm_count, int max_smem, int *status)
     g_mm_tcs = tcs && *tcs ? atoi(tcs) != 0 : 1;
     const char *few = getenv("QB200_MM_FEW");
     g_mm_few = few && *few ? atoi(few) : 64;
+    const char *rawfew = getenv("QB200_MM_RAW_FEW");
+    g_mm_raw_few = rawfew && *rawfew ? atoi(rawfew) != 0 : 1;
 #endif
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(fewrows_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewCfg<16>::SMEM))) return e;
-    if ((e = cudaFuncSetAttribute(fewrows_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewCfg<32>::SMEM))) return e;
-    if ((e = cudaFuncSetAttribute(fewrows_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewCfg<64>::SMEM))) return e;
+    if ((e = set_few_attr<16, 0>()) || (e = set_few_attr<32, 0>()) || (e = set_few_attr<64, 0>())) return e;
+    if ((e = set_few_attr<16, 1>()) || (e = set_few_attr<32, 1>())) return e;
+    if ((e = set_few_attr<16, 2>()) || (e = set_few_attr<32, 2>())) return e;
     if ((e = set_mm_attr<0, false>()) || (e = set_mm_attr<0, true>())) return e;
     if ((e = set_mm_attr<1, false>()) || (e = set_mm_attr<1, true>())) return e;
     return cudaSuccess;
@@ -1447,6 +1592,26 @@ int matmul_prepack_b(int fmt_b, const void *b, int n, int k, void *packed, cudaS
     return (int)pack(fmt_b, b, n, k, t, false, false, stream);
 }
 
+template <int BN, int RAW>
+static cudaError_t launch_few(int grid, const MatmulArgs &args, cudaStream_t stream)
+{
+    // launched as a programmatic dependent of A's packing: its prologue and its first loads of B run beside it
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(few_threads<BN, RAW>()); cfg.dynamicSmemBytes = FewCfg<BN, RAW>::SMEM;
+    cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, fewrows_kernel<BN, RAW>, args);
+}
+template <int RAW>
+static cudaError_t launch_few_rows(int bn, int grid, const MatmulArgs &args, cudaStream_t stream)
+{
+    if (bn == 16) return launch_few<16, RAW>(grid, args, stream);
+    if (bn == 32) return launch_few<32, RAW>(grid, args, stream);
+    if constexpr (RAW == 0) return launch_few<64, 0>(grid, args, stream);
+    else return cudaErrorInvalidValue;         // raw weights: at most 32 rows of A (the converters' registers)
+}
 template <int KIND, bool SUMS, int VAR>
 static void launch_var(int grid, const MatmulArgs &args, cudaStream_t stream)
 {
@@ -1491,7 +1656,9 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     const bool few = tcs && !sums && g_mm_kind == 0 && m <= g_mm_few;
     const int bn = few_bn(m), a_layout = few ? LAY_FEW : LAY_TILE, lay_b = b_layout(fmt_b);
     const size_t a_slab = a_packed_bytes(m, k, kbs, tcs), b_slab = packed_bytes(lay_b, n, k, kbs, false);
-    const int b_sets = b_packed ? 0 : (batch.stride_b ? batch.count : 1);
+    // ... and on raw weights that come in whole groups of eight blocks, 16-byte aligned, the kernel re-lays B itself
+    const bool raw_few = few && m <= 32 && !b_packed && batch.count == 1 && kbs % GROUP == 0 && ((uintptr_t)b & 15) == 0 && g_mm_raw_few;
+    const int b_sets = b_packed || raw_few ? 0 : (batch.stride_b ? batch.count : 1);
     const size_t a_raw = raw_bytes(fmt_a, batch.stride_a), b_raw = raw_bytes(fmt_b, batch.stride_b);
     // B first: A's packing is then the launch right before the product, whose start the few-rows kernel overlaps
     const int a_sets = batch.stride_a ? batch.count : 1;
@@ -1522,21 +1689,15 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     args.unit = 32;          // columns a warp of the epilogue owns: pieces are whole units
     args.units = (n + args.unit - 1) / args.unit;
     args.mtiles = (m + TILE - 1) / TILE;
+    args.b_raw = raw_few ? (const uint8_t *)b : nullptr;
     args.batch = batch.count;
     args.a_stride = batch.stride_a ? a_slab : 0;
     args.b_stride = !b_packed && batch.stride_b ? b_slab : 0;
     args.c_stride = (size_t)batch.stride_c;
     if (few) {
         const int tiles = batch.count * (tb.rows_pad / TILE), grid = tiles < g_mm_sms ? tiles : g_mm_sms;
-        // launched as a programmatic dependent of A's packing: its prologue and its first copies of B run beside it
-        cudaLaunchConfig_t cfg = {};
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr.val.programmaticStreamSerializationAllowed = 1;
-        cfg.gridDim = dim3(grid); cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
-        if (bn == 16) { cfg.blockDim = dim3(few_threads<16>()); cfg.dynamicSmemBytes = FewCfg<16>::SMEM; e = cudaLaunchKernelEx(&cfg, fewrows_kernel<16>, args); }
-        else if (bn == 32) { cfg.blockDim = dim3(few_threads<32>()); cfg.dynamicSmemBytes = FewCfg<32>::SMEM; e = cudaLaunchKernelEx(&cfg, fewrows_kernel<32>, args); }
-        else { cfg.blockDim = dim3(few_threads<64>()); cfg.dynamicSmemBytes = FewCfg<64>::SMEM; e = cudaLaunchKernelEx(&cfg, fewrows_kernel<64>, args); }
+        if (raw_few) e = fmt_b == QB200_Q8_0 ? launch_few_rows<1>(bn, grid, args, stream) : launch_few_rows<2>(bn, grid, args, stream);
+        else e = launch_few_rows<0>(bn, grid, args, stream);
         return (int)e;
     }
     const long long total = (long long)args.batch * args.mtiles * args.units;
