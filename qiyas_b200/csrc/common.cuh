@@ -98,5 +98,13 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
+// A named barrier of `threads` threads that also tells every one of them whether `mine` held for all.
+__device__ __forceinline__ bool named_bar_and(int id, int threads, bool mine)
+{
+    uint32_t all;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, %3, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(all) : "r"(mine ? 1u : 0u), "r"(id), "r"(threads) : "memory");
+    return all != 0;
+}
 
 }  // namespace qb

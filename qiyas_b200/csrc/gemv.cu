@@ -1027,8 +1027,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, 16 / NW) gemv_kernel(const Gemv
         // GPU's copy, a fence orders them before the block's count, and the block that counts last raises the flags.
         // A block that gave up on a wait publishes nothing and does not count: the flags then never show this epoch
         // and the readers' bounded waits report it.
-        named_bar_sync(1, threads);
-        if (!*abort_flag) {
+        // (the barrier also tells every thread whether anyone has given up: all publish, or none does)
+        if (named_bar_and(1, threads, !*abort_flag)) {
             const GemvPublish *pub = &p.publish;
             const int r0 = chunk0 * RW, r1 = min(p.rows, chunk1 * RW), world = pub->world;
             for (int idx = r0 + (int)threadIdx.x; idx < r1; idx += threads) {

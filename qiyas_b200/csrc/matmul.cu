@@ -959,9 +959,9 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
             if (p.cb) {
                 // `Back` for the piece (src/MatMulBlocks.cs:421 -> Ptx.LanesToBlock): once every epilogue warp has stored its
                 // lanes, the epilogue threads encode the piece's blocks of 32 consecutive values (n % 32 == 0, unit 32: a block
-                // lies in one row of one piece).  All warps come here whether or not a wait gave up, then look at the flag.
-                named_bar_sync(2, EPI_WARPS * 32);
-                if (*abort_flag) { alive = false; break; }
+                // lies in one row of one piece).  All warps come here whether or not a wait gave up; the barrier also tells every
+                // thread whether all of them are still going, so that they leave together or not at all.
+                if (!named_bar_and(2, EPI_WARPS * 32, alive && !*abort_flag)) { alive = false; break; }
                 const int bw = w * p.unit / 32, tid = threadIdx.x - 64;
                 const int rows_here = min(TILE, p.m - mt * TILE);
                 for (int idx = tid; idx < rows_here * bw; idx += EPI_WARPS * 32) {
@@ -1034,14 +1034,6 @@ struct FewCfg {
 constexpr int CONV_WARPS = 8;               // RAW: the warps after the epilogue's
 template <int BN, int RAW = 0> __host__ __device__ constexpr int few_threads() { return 32 * (4 + 4 * (BN / FEW_CW) + (RAW ? CONV_WARPS : 0)); }
 
-// A named barrier of `threads` threads that also tells every one of them whether `mine` held for all.
-__device__ __forceinline__ bool named_bar_and(int id, int threads, bool mine)
-{
-    uint32_t all;
-    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, %3, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(all) : "r"(mine ? 1u : 0u), "r"(id), "r"(threads) : "memory");
-    return all != 0;
-}
 // Nothing is emitted: the registers pass through the statement, so that what uses them stays below the wait before it.
 __device__ __forceinline__ void pin16(uint32_t *v)
 {
@@ -1256,8 +1248,8 @@ __global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(co
             if (p.cb) {
                 // `Back` for the tile: once the epilogue warps have stored their lanes, their threads encode the tile's blocks of
                 // 32 consecutive values of a row of C (n % 32 == 0: a block lies inside one warp's columns)
-                named_bar_sync(2, 128 * CG);
-                if (*abort_flag) { alive = false; break; }
+                // (the barrier also tells every thread whether all of them are still going: they leave together or not at all)
+                if (!named_bar_and(2, 128 * CG, alive && !*abort_flag)) { alive = false; break; }
                 const int bw = min(TILE, p.n - n0) / 32, tid = threadIdx.x - 128;
                 for (int idx = tid; idx < p.m * bw; idx += 128 * CG) {
                     const int rr = idx / bw, bc = idx - rr * bw;
