@@ -44,9 +44,10 @@ WEIGHT5 = N5 * (K5 // 32) * 18
 ALGO5 = WEIGHT5 + K5 * 4 + N5 * 4                         # weights once, x, y
 REPLAYS = 100                                             # graph replays a step
 L2_BYTES = 126e6
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the gemv on the 8192 x 8192 Q4_0 matrix (ncu, profiles/):
-# 37 852 160 bytes against 37 814 272 algorithmic, a ratio the larger matrix shares (the kernel reads every byte once)
-TRAFFIC_RATIO = 37852160 / 37814272
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the gemv on the headline matrix (ncu, profiles/): 132 225 536
+# bytes read, nothing written that the kernel caused (y stays in L2), against 132 268 032 algorithmic; a rank's shard at
+# N > 1 is taken at the same ratio (the kernel reads every byte of its rows once; 8192 x 8192: 37 852 928 against 37 814 272)
+TRAFFIC_RATIO = 132225536 / 132268032
 MMA_OPS = 2 * 128 * 128 * 32                              # int8 operations of one tcgen05.mma of the product's shape
 
 
@@ -348,7 +349,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-extra", action="store_true", help="only the headline (profiling runs)")
-    ap.add_argument("--leg", default=None, choices=["c2-chained", "abt", "abt-few"],
+    ap.add_argument("--leg", default=None, choices=["c2", "c2-chained", "abt", "abt-few"],
                     help="run one small leg alone and print its record (profiling runs): the Q4_0 8192 x 8192 gemv with calls chained "
                          "through y, or the Q8_0 x Q8_0 A.B^T of configs[2] at M 512")
     args = ap.parse_args()
@@ -378,8 +379,8 @@ def main():
     timer = Timer(torch, dist, world, dev, side)
     peak, peak_kind = measured_peaks()
     if args.leg:
-        if args.leg == "c2-chained":
-            rec = gemv_record(ops, torch, timer, B.Q4_0, 8192, 8192, 3, 3, peak, chained=True)
+        if args.leg in ("c2", "c2-chained"):
+            rec = gemv_record(ops, torch, timer, B.Q4_0, 8192, 8192, 3, 3, peak, chained=args.leg == "c2-chained")
         else:
             rec = abt_record(ops, torch, timer, B.Q8_0, 512 if args.leg == "abt" else 16, 11008, 4096, tensor_peak(ops, 1965.0)[0])
         if rank == 0:
