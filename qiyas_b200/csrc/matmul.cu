@@ -41,8 +41,14 @@ constexpr int TILE = 128;            // rows of A a tile = lanes of tensor memor
 constexpr int BNMAX = 128;           // columns of the widest piece = columns of one accumulator in tensor memory
 constexpr int EPI_WARPS = 16;
 constexpr int GROUP = 8;             // k-blocks a group of B with f16 scales = f16 a 16-byte scale row
-constexpr int MM_THREADS = 32 * (3 + EPI_WARPS);     // warp 0 producer, warp 1 and the last warp MMA issue, the rest epilogue
-constexpr int MMA2_WARP = 2 + EPI_WARPS;
+// With the scale products on the tensor cores an epilogue warp takes 64 columns instead of 32 (MM_FAT): eight warps,
+// two a scheduler (one of each set of 64 columns), 168 registers a thread; four warps instead of eight have to have read
+// an accumulator before it is released (measured: equal at M 512, 3-4 % faster at M 2048 and on the 28672 x 8192 shape).
+#ifndef MM_FAT
+#define MM_FAT 1
+#endif
+__host__ __device__ constexpr int epi_warps(bool tcs) { return tcs && MM_FAT ? 8 : EPI_WARPS; }
+__host__ __device__ constexpr int mm_threads(bool tcs) { return 32 * (3 + epi_warps(tcs)); }     // warp 0 producer, warp 1 and the last warp MMA issue, the rest epilogue
 constexpr uint32_t MM_HEADER = 1024;
 constexpr uint32_t MM_SMEM_MAX = 232448;           // 227 KB of shared memory a block
 
@@ -464,6 +470,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Nothing is emitted: the registers pass through the statement, so that what uses them stays below the wait before it.
+__device__ __forceinline__ void pin16(uint32_t *v)
+{
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
+                      "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]) :: "memory");
+}
 // The reads issued so far have landed, and nothing that uses v is scheduled above this point (the registers pass through
 // the statement, so their uses depend on it).
 __device__ __forceinline__ void tmem_ld_landed16(uint32_t (&v)[16])
@@ -641,11 +653,12 @@ struct Pieces {
 enum { VAR_PLAIN = 0, VAR_MINS = 1, VAR_HALF = 2, VAR_TCS = 3 };
 
 template <int KIND, bool SUMS, int VAR>
-__global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs p)
+__global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(const MatmulArgs p)
 {
     constexpr bool MINS = VAR == VAR_MINS, HALF = VAR == VAR_HALF, TCS = VAR == VAR_TCS;
     using G = Cfg<KIND, MINS, HALF, TCS>;
-    constexpr int S = G::S, KS = G::KS, KC = G::KC, NT = G::NT, TCOLS = G::TCOLS, THREADS = MM_THREADS;
+    constexpr int EW = epi_warps(TCS), MMA2_WARP = 2 + EW, EC = 128 / (EW / 4);      // epilogue warps, the second issuer's warp, columns a warp
+    constexpr int S = G::S, KS = G::KS, KC = G::KC, NT = G::NT, TCOLS = G::TCOLS, THREADS = mm_threads(TCS);
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = smem_u32(smem);
@@ -660,11 +673,11 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
             mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, TCS ? 2 : 2 + EPI_WARPS);      // the two issuers' commits, and the epilogue warps where they read the scales
+            mbar_init(empty0 + 8 * s, TCS ? 2 : 2 + EW);      // the two issuers' commits, and the epilogue warps where they read the scales
         }
         for (int t = 0; t < NTB; t++) {
             mbar_init(tfull0 + 8 * t, 1);
-            mbar_init(tempty0 + 8 * t, SPLIT2 ? EPI_WARPS / 2 : EPI_WARPS);
+            mbar_init(tempty0 + 8 * t, SPLIT2 ? EW / 2 : EW);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -840,9 +853,9 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
         // the arithmetic: the instruction count of this loop is what bounds the kernel.
         const int q = warp & 3, g = (warp - 2) >> 2;
         // split: the warp's set of 64 columns (its half of tensor memory, its barriers) and its 32 columns inside it
-        const int set = SPLIT2 ? g >> 1 : 0;
+        const int set = SPLIT2 ? g * EC / 64 : 0;
         constexpr int SLOT = SPLIT2 ? 128 : TCOLS, S_OFF = SPLIT2 ? 64 : BNMAX;
-        const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(SPLIT2 ? set * 256 + (g & 1) * 32 : g * 32);
+        const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(SPLIT2 ? set * 256 + (g * EC) % 64 : g * EC);
         const uint32_t tfull_w = tfull0 + 8 * (set * NT), tempty_w = tempty0 + 8 * (set * NT);
         Pieces pieces(p, wmax);
         int tile, u0, w, sc = 0, tc = 0;
@@ -850,17 +863,17 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
         long long w_tfull = 0, t_store = 0, t_begin = MM_CLOCK();
         while (alive && pieces.next(tile, u0, w)) {
             const int n0 = u0 * p.unit, bi = tile / p.mtiles, mt = tile - bi * p.mtiles;
-            const bool active = g * 32 < w * p.unit;                    // this warp has columns in the piece
+            const bool active = g * EC < w * p.unit;                    // this warp has columns in the piece
             const int row = mt * TILE + q * 32 + lane;
             float *c_out = p.c + bi * p.c_stride;
             int32_t *sums_out = SUMS ? p.sums + (size_t)bi * p.m * p.n * p.kb : nullptr;
             // 32 f32 accumulators: as 16 pairs for the packed instructions of the CUDA-core scale path, as 32 scalars for TCS
             uint64_t acc[TCS ? 1 : 16];
-            float accf[TCS ? 32 : 1];
+            float accf[TCS ? EC : 1];
 #pragma unroll
             for (int j = 0; j < (TCS ? 1 : 16); j++) acc[j] = 0ull;
 #pragma unroll
-            for (int j = 0; j < (TCS ? 32 : 1); j++) accf[j] = 0.f;
+            for (int j = 0; j < (TCS ? EC : 1); j++) accf[j] = 0.f;
             int kk = 0;
             // split: a piece the warp's set has no columns in goes by without a wait
             const bool set_active = !SPLIT2 || set * 64 < w * p.unit;
@@ -875,29 +888,39 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                 tc_fence_after();
                 const uint32_t at = tlane + (uint32_t)(t * SLOT);
                 if (TCS) {
-                    // two halves of 16 columns: sums and scale products side by side in registers
+                    // chunks of 16 columns, HG of them a wait: sums and scale products side by side in registers
+                    constexpr int HG = EC / 32;
 #pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        uint32_t v[16], x[16];
-                        if (active && !(MM_PROBE(p) & 2)) {
-                            tmem_ld16(at + 16 * h, v);
-                            tmem_ld16(at + S_OFF + 16 * h, x);
+                    for (int h = 0; h < EC / 16; h += HG) {
+                        uint32_t v[HG][16], x[HG][16];
+#pragma unroll
+                        for (int hh = 0; hh < HG; hh++) {
+                            if (active && !(MM_PROBE(p) & 2)) {
+                                tmem_ld16(at + 16 * (h + hh), v[hh]);
+                                tmem_ld16(at + S_OFF + 16 * (h + hh), x[hh]);
+                            }
                         }
-                        tmem_ld_landed16x2(v, x);
-                        if (h == 1) {
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int hh = 0; hh < HG; hh++) { pin16(v[hh]); pin16(x[hh]); }
+                        if (h + HG == EC / 16) {
                             tc_fence_before();
                             if (lane == 0) mbar_arrive(tempty_w + 8 * t);        // the accumulator has been read (warp-wide reads)
                         }
-                        if (active && !(MM_PROBE(p) & 1)) {
-                            // scalar fma on the registers the reads filled: forming f32x2 pairs would cost a move or two a pair
 #pragma unroll
-                            for (int c = 0; c < 16; c++) accf[16 * h + c] = __fmaf_rn(sum_as_float<KIND>(v[c]), __uint_as_float(x[c]), accf[16 * h + c]);
-                        }
-                        if (SUMS && active && row < p.m) {
+                        for (int hh = 0; hh < HG; hh++) {
+                            if (active && !(MM_PROBE(p) & 1)) {
+                                // scalar fma on the registers the reads filled: forming f32x2 pairs would cost a move or two a pair
 #pragma unroll
-                            for (int c = 0; c < 16; c++) {
-                                const int col = n0 + g * 32 + 16 * h + c;
-                                if (col < p.n) sums_out[((size_t)row * p.n + col) * p.kb + i] = sum_as_int<KIND>(v[c]);
+                                for (int c = 0; c < 16; c++)
+                                    accf[16 * (h + hh) + c] = __fmaf_rn(sum_as_float<KIND>(v[hh][c]), __uint_as_float(x[hh][c]), accf[16 * (h + hh) + c]);
+                            }
+                            if (SUMS && active && row < p.m) {
+#pragma unroll
+                                for (int c = 0; c < 16; c++) {
+                                    const int cc = g * EC + 16 * (h + hh) + c, col = n0 + cc;
+                                    if (col < p.n && cc < w * p.unit) sums_out[((size_t)row * p.n + col) * p.kb + i] = sum_as_int<KIND>(v[hh][c]);
+                                }
                             }
                         }
                     }
@@ -958,22 +981,22 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
             const long long s0 = MM_CLOCK();
             if (alive && active && row < p.m) {
                 const bool vec = (p.n & 3) == 0 && ((uintptr_t)c_out & 15) == 0;
-                const int col0 = n0 + g * 32;
+                const int col0 = n0 + g * EC, col_end = min(p.n, n0 + w * p.unit);        // (a warp of 64 columns may reach past the piece)
                 float *out = c_out + (size_t)row * p.n + col0;
 #pragma unroll
-                for (int c4 = 0; c4 < 8; c4++) {
+                for (int c4 = 0; c4 < EC / 4; c4++) {
                     float f[4];
                     if (TCS) {
 #pragma unroll
                         for (int c = 0; c < 4; c++) f[c] = accf[(TCS ? 4 * c4 : 0) + (TCS ? c : 0)];
                     } else {
-                        unpack2(acc[TCS ? 0 : 2 * c4], f[0], f[1]);
-                        unpack2(acc[TCS ? 0 : 2 * c4 + 1], f[2], f[3]);
+                        unpack2(acc[TCS ? 0 : (2 * c4) % 16], f[0], f[1]);
+                        unpack2(acc[TCS ? 0 : (2 * c4 + 1) % 16], f[2], f[3]);
                     }
-                    if (vec && col0 + 4 * c4 + 4 <= p.n) *(float4 *)(out + 4 * c4) = make_float4(f[0], f[1], f[2], f[3]);
+                    if (vec && col0 + 4 * c4 + 4 <= col_end) *(float4 *)(out + 4 * c4) = make_float4(f[0], f[1], f[2], f[3]);
                     else {
 #pragma unroll
-                        for (int c = 0; c < 4; c++) if (col0 + 4 * c4 + c < p.n) out[4 * c4 + c] = f[c];
+                        for (int c = 0; c < 4; c++) if (col0 + 4 * c4 + c < col_end) out[4 * c4 + c] = f[c];
                     }
                 }
             }
@@ -983,10 +1006,10 @@ __global__ void __launch_bounds__(MM_THREADS, 1) matmul_kernel(const MatmulArgs 
                 // lanes, the epilogue threads encode the piece's blocks of 32 consecutive values (n % 32 == 0, unit 32: a block
                 // lies in one row of one piece).  All warps come here whether or not a wait gave up; the barrier also tells every
                 // thread whether all of them are still going, so that they leave together or not at all.
-                if (!named_bar_and(2, EPI_WARPS * 32, alive && !*abort_flag)) { alive = false; break; }
+                if (!named_bar_and(2, EW * 32, alive && !*abort_flag)) { alive = false; break; }
                 const int bw = w * p.unit / 32, tid = threadIdx.x - 64;
                 const int rows_here = min(TILE, p.m - mt * TILE);
-                for (int idx = tid; idx < rows_here * bw; idx += EPI_WARPS * 32) {
+                for (int idx = tid; idx < rows_here * bw; idx += EW * 32) {
                     const int rr = idx / bw, bc = idx - rr * bw;
                     const size_t first = bi * p.c_stride + (size_t)(mt * TILE + rr) * p.n + n0 + bc * 32;      // c_stride is whole blocks
                     float f[32];
@@ -1056,12 +1079,6 @@ struct FewCfg {
 constexpr int CONV_WARPS = 8;               // RAW: the warps after the epilogue's
 template <int BN, int RAW = 0> __host__ __device__ constexpr int few_threads() { return 32 * (4 + 4 * (BN / FEW_CW) + (RAW ? CONV_WARPS : 0)); }
 
-// Nothing is emitted: the registers pass through the statement, so that what uses them stays below the wait before it.
-__device__ __forceinline__ void pin16(uint32_t *v)
-{
-    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
-                      "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]) :: "memory");
-}
 template <int N>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N])
 {
@@ -1635,7 +1652,7 @@ static void launch_var(int grid, const MatmulArgs &args, cudaStream_t stream)
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
-    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(MM_THREADS); cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(mm_threads(VAR == VAR_TCS)); cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
     cfg.dynamicSmemBytes = Cfg<KIND, VAR == VAR_MINS, VAR == VAR_HALF, VAR == VAR_TCS>::SMEM;
     cudaLaunchKernelEx(&cfg, matmul_kernel<KIND, SUMS, VAR>, args);
 }
