@@ -46,3 +46,22 @@ def test_calls_fail_loudly_without_a_device(library):
     # nothing runs on the CPU instead: the product entry points refuse
     assert library.qb200_gemv_blocks(0, 0, None, None, None, 4, 32, None) == -5
     assert library.qb200_block_product_available() == 0
+
+
+def test_packed_sizes_follow_the_layouts(library):
+    # host arithmetic only: weights with f16 scales are packed in slabs of a 128-row tile and eight k-blocks (eight times
+    # 4 KB of codes and 2 KB of scale rows); a call's workspace has room for A in its few-rows form as well
+    import ctypes as C
+    lib = library
+    lib.qb200_matmul_prepacked_bytes.restype = C.c_size_t
+    lib.qb200_matmul_prepacked_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
+    lib.qb200_matmul_prepacked_workspace_bytes.restype = C.c_size_t
+    lib.qb200_matmul_prepacked_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int]
+    for fmt in (0, 1):
+        for n, k in ((11008, 4096), (129, 64), (1, 32), (300, 8160)):
+            tiles, groups = (n + 127) // 128, (k // 32 + 7) // 8
+            assert lib.qb200_matmul_prepacked_bytes(fmt, n, k) == (tiles * groups * 34816 + 255) // 256 * 256
+    for m, k in ((1, 32), (16, 64), (64, 64), (33, 4096)):
+        bn = 16 if m <= 16 else 32 if m <= 32 else 64
+        few = (k // 32 + 7) // 8 * (8 * bn * 32 + 8 * bn * 16)
+        assert lib.qb200_matmul_prepacked_workspace_bytes(0, 0, m, k) >= few

@@ -97,6 +97,26 @@ def test_few_rows_of_a(oracle, fmt_a, fmt_b, m, n, k):
     assert np.array_equal(c2.view(np.uint32), ref.view(np.uint32))
 
 
+@pytest.mark.parametrize("fmt_b", [B.Q8_0, B.Q4_0])
+@pytest.mark.parametrize("m,n,k,offset", [(8, 300, 512, 0), (8, 300, 512, 2), (32, 129, 256, 0), (19, 1000, 2048, 16), (3, 128, 256, 6)])
+def test_raw_weights_in_the_product_kernel(oracle, fmt_b, m, n, k, offset):
+    # at most 32 rows of A, k in whole groups of eight blocks: the kernel converts the raw rows of B itself when B lies on a
+    # 16-byte boundary, and falls back to the packing pass when it does not; the same bits either way
+    import torch
+    o = H.ops()
+    a, b = operands(oracle, B.Q8_0, fmt_b, m, n, k, 700 + m + offset)
+    buf = torch.zeros(b.size + 64, dtype=torch.uint8, device="cuda:0")
+    base = buf.data_ptr() + (-buf.data_ptr()) % 16 + offset
+    view = buf[base - buf.data_ptr():][:b.size]
+    view.copy_(torch.from_numpy(b))
+    c = H.empty(m * n, torch.float32)
+    c.fill_(float("nan"))
+    o.MatMulBlocks(B.Q8_0, H.dev(a), base, c, m, n, k, fmt_b=fmt_b)
+    assert o.gpu.status() == 0
+    ref = oracle.matmul_blocks(B.Q8_0, fmt_b, a, b, m, n, k, order=1)
+    assert np.array_equal(c.cpu().numpy().reshape(m, n).view(np.uint32), ref.view(np.uint32))
+
+
 def test_caller_workspace(oracle):
     m, n, k = 70, 300, 512
     a, b = operands(oracle, B.Q8_0, B.Q8_0, m, n, k, 3)
