@@ -230,19 +230,23 @@ __device__ __forceinline__ void store_codes16(const PackTarget &t, int r, int kc
 // rows lie on 16-byte boundaries, else 2); then a thread a block assembles its 32 int8 values and its scale.
 // Rows past `rows` (the padding up to rows_pad) are written as zeros.
 // SPLIT (against Q6_K rows, whose scales change every 16 values): a block becomes two k-blocks of 16 values, same scale.
+#ifndef PACK_ROWS
+#define PACK_ROWS 128                    // rows a block of the Q8_0 / Q4_0 pack kernel re-lays at once
+#endif
 template <int FMT, bool SPLIT>
 __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int rows, int kb32, PackTarget t, int want_usums)
 {
     // halfwords a row segment; the pitch is an odd number of 32-bit words, so the 32 rows start in 32 different banks
     constexpr int BB = block_bytes(FMT), HALVES = 8 * BB / 2, PITCH = HALVES + 2, VECS = 8 * BB / 16;
-    __shared__ __align__(16) uint16_t seg[32 * PITCH];
+    __shared__ __align__(16) uint16_t seg[PACK_ROWS * PITCH];
     // a product launched as a programmatic dependent may start its prologue now (it waits for this grid before it reads A)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int r0 = blockIdx.x * 32, b0 = blockIdx.y * 8;
+    const int r0 = blockIdx.x * PACK_ROWS, b0 = blockIdx.y * 8;
     const int nb = min(8, kb32 - b0), halves = nb * BB / 2;
     const size_t row_bytes = (size_t)kb32 * BB;
     if (nb == 8 && (((uintptr_t)raw | row_bytes) & 15) == 0) {
-        for (int idx = threadIdx.x; idx < 32 * VECS; idx += 256) {
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < PACK_ROWS * VECS; idx += 256) {
             const int rr = idx / VECS, c = idx - rr * VECS;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (r0 + rr < rows) v = __ldg((const uint4 *)(raw + (size_t)(r0 + rr) * row_bytes + (size_t)b0 * BB) + c);
@@ -250,7 +254,7 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int 
             dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
         }
     } else {
-        for (int idx = threadIdx.x; idx < 32 * HALVES; idx += 256) {
+        for (int idx = threadIdx.x; idx < PACK_ROWS * HALVES; idx += 256) {
             const int rr = idx / HALVES, h = idx - rr * HALVES;
             uint16_t v = 0;
             if (r0 + rr < rows && h < halves) v = __ldg((const uint16_t *)(raw + ((size_t)(r0 + rr) * kb32 + b0) * BB) + h);
@@ -258,8 +262,12 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int 
         }
     }
     __syncthreads();
-    const int rl = threadIdx.x & 31, bl = threadIdx.x >> 5, r = r0 + rl, b = b0 + bl;
+    const int bl = threadIdx.x >> 5, b = b0 + bl;
     if (b >= kb32) return;
+#pragma unroll
+    for (int rh = 0; rh < PACK_ROWS / 32; rh++) {
+    const int rl = (threadIdx.x & 31) + 32 * rh, r = r0 + rl;
+    if (r >= t.rows_pad) break;
     const uint16_t *p = seg + rl * PITCH + bl * (BB / 2);
     const float d = half_bits_to_float(p[0]);           // zero rows read as scale 0, codes 0 (Q4_0: see below)
     uint32_t w[8];
@@ -285,7 +293,7 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int 
     if (SPLIT) {
         t.scales[scale_offset(t, r, 2 * b)] = d;
         t.scales[scale_offset(t, r, 2 * b + 1)] = d;
-        return;
+        continue;
     }
     store_scale(t, r, b, d, p[0]);
     if (want_usums) {       // against a format with mins: scale * (sum of the codes), the factor of the other operand's min
@@ -293,6 +301,7 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int 
 #pragma unroll
         for (int i = 0; i < 8; i++) asm("dp4a.s32.s32 %0, %1, %2, %0;" : "+r"(sum) : "r"(w[i]), "r"(0x01010101));
         t.extra[scale_offset(t, r, b)] = __fmul_rn(d, (float)sum);
+    }
     }
 }
 
@@ -1602,7 +1611,7 @@ static cudaError_t pack(int fmt, const void *raw, int rows, int k, const PackTar
     if (fmt == QB200_Q4_K) pack_q4_k_kernel<<<dim3(padded / 32, kb32 / 8), 256, 0, stream>>>(r, rows, kb32, t);
     else if (fmt == QB200_Q6_K) pack_q6_k_kernel<<<dim3(padded / 32, k / 256), 256, 0, stream>>>(r, rows, k / 16, t);
     else {
-        const dim3 grid(padded / 32, (kb32 + 7) / 8);
+        const dim3 grid((padded + PACK_ROWS - 1) / PACK_ROWS, (kb32 + 7) / 8);
         const int us = want_usums ? 1 : 0;
         if (fmt == QB200_Q8_0) {
             if (split) pack_rows_kernel<QB200_Q8_0, true><<<grid, 256, 0, stream>>>(r, rows, kb32, t, us);
