@@ -155,6 +155,9 @@ struct PackTarget {
 
 __host__ __device__ inline size_t grouped_slab(int kc) { return (size_t)GROUP * TILE * kc * 16 + TILE * 16; }
 __host__ __device__ inline size_t few_slab(int bn, int kc) { return (size_t)GROUP * bn * kc * 16 + (size_t)GROUP * bn * 16; }
+// the few-rows form of A against weights whose scale products stay on the CUDA cores (Q4_K): codes, then f32 scales
+// [8][bn], then the scaled sums of the codes [8][bn]
+__host__ __device__ inline size_t fewq_slab(int bn, int kc) { return (size_t)GROUP * bn * kc * 16 + 2 * (size_t)GROUP * bn * 4; }
 __host__ __device__ inline int groups_of(int kbs) { return (kbs + GROUP - 1) / GROUP; }
 
 // Byte offset of k-chunk `kci` (counted along the whole row) of row r.
@@ -166,7 +169,7 @@ __device__ __forceinline__ size_t chunk_offset(const PackTarget &t, int r, int k
         return slab + (size_t)(kblock % GROUP) * (TILE * t.kc * 16) + (size_t)(((r % TILE) / 8) * t.kc + kc) * 128 + (size_t)(r & 7) * 16;
     }
     if (t.layout == LAY_FEW) {
-        const size_t slab = (size_t)(kblock / GROUP) * few_slab(t.bn, t.kc);
+        const size_t slab = (size_t)(kblock / GROUP) * (t.tcs ? few_slab(t.bn, t.kc) : fewq_slab(t.bn, t.kc));
         return slab + (size_t)(kblock % GROUP) * (t.bn * t.kc * 16) + (size_t)((r / 8) * t.kc + kc) * 128 + (size_t)(r & 7) * 16;
     }
     size_t group;
@@ -197,10 +200,25 @@ __device__ __forceinline__ void store_scale(const PackTarget &t, int r, int kblo
         if (kblock == t.kbs - 1) for (int z = j + 1; z < GROUP; z++) row[z] = 0;      // positions past the last k-block multiply as zeros
     } else if (t.layout == LAY_FEW) {
         if (r >= t.bn) return;
+        if (!t.tcs) {
+            const size_t slab = (size_t)(kblock / GROUP) * fewq_slab(t.bn, t.kc);
+            *(float *)(t.codes + slab + (size_t)GROUP * t.bn * t.kc * 16 + (size_t)(j * t.bn + r) * 4) = d;
+            return;
+        }
         const size_t slab = (size_t)(kblock / GROUP) * few_slab(t.bn, t.kc);
         *(uint4 *)(t.codes + slab + (size_t)GROUP * t.bn * t.kc * 16 + (size_t)(j * t.bn + r) * 16) = scale_row(d_bits, j);
     } else if (t.tcs) ((uint4 *)t.scales)[scale_offset(t, r, kblock)] = scale_row(d_bits, j);
     else t.scales[scale_offset(t, r, kblock)] = d;
+}
+
+// The extra value of (row, k-block): scale * (sum of the block's codes), the factor of the other operand's min.
+__device__ __forceinline__ void store_extra(const PackTarget &t, int r, int kblock, float value)
+{
+    if (t.layout == LAY_FEW) {
+        if (r >= t.bn) return;
+        const size_t slab = (size_t)(kblock / GROUP) * fewq_slab(t.bn, t.kc);
+        *(float *)(t.codes + slab + (size_t)GROUP * t.bn * t.kc * 16 + (size_t)GROUP * t.bn * 4 + (size_t)((kblock % GROUP) * t.bn + r) * 4) = value;
+    } else t.extra[scale_offset(t, r, kblock)] = value;
 }
 
 // 16 int8 values (four words) as one k-chunk (int8) or two (f16), starting at k-chunk kci0 of row r.
@@ -299,7 +317,7 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int 
         int sum = 0;
 #pragma unroll
         for (int i = 0; i < 8; i++) asm("dp4a.s32.s32 %0, %1, %2, %0;" : "+r"(sum) : "r"(w[i]), "r"(0x01010101));
-        t.extra[scale_offset(t, r, b)] = __fmul_rn(d, (float)sum);
+        store_extra(t, r, b, __fmul_rn(d, (float)sum));
     }
     }
 }
@@ -1427,6 +1445,204 @@ __global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(co
     if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
+// ---------------------------------------------------------------------------------- few rows of A against Q4_K weights
+
+// The few-rows kernel for weights whose scale products stay on the CUDA cores (Q4_K: scales d*sc and mins dmin*m are
+// f32).  Same sides as fewrows_kernel: the 128 rows of a tile of B on the lanes of tensor memory, A's rows (BN = 16 or 32)
+// as columns; a k-block's sums take BN columns and nothing else, so 64 / BN k-blocks form a batch of 64 columns and
+// eight batches are in flight.  Thread (q, lane) owns row n of B: its scale and min of a k-block are two words of shared
+// memory, A's scales and scaled code sums are broadcast reads;
+//     acc = fma(float(D), sA * (d*sc), acc);  acc = fma(dmin*m, -(sA * sum(qA)), acc)      (the 128-row-tile kernel's order).
+// B comes k-block-major (LAY_KBLOCK): three copies a k-block (codes, scales, mins), issued by a lane each; A in its
+// few-rows form with f32 planes (one copy a stage).
+template <int BN>
+struct FewQCfg {
+    static constexpr int KS = GROUP;
+    static constexpr int BATCH = 64 / BN, BCOLS = 64, NB = 512 / BCOLS;
+    static constexpr uint32_t B_KB = TILE * 32, PLANE_KB = TILE * 4, A_KB = BN * 32;
+    static constexpr uint32_t O_SB = KS * B_KB, O_MB = O_SB + KS * PLANE_KB, O_A = O_MB + KS * PLANE_KB;
+    static constexpr uint32_t A_SLAB = GROUP * A_KB + 2 * GROUP * BN * 4, O_SA = O_A + GROUP * A_KB, O_UA = O_SA + GROUP * BN * 4;
+    static constexpr uint32_t STAGE = O_A + A_SLAB;
+    static constexpr int S_FIT = (int)((MM_SMEM_MAX - MM_HEADER) / STAGE);
+    static constexpr int S = S_FIT > 6 ? 6 : S_FIT;
+    static constexpr uint32_t SMEM = MM_HEADER + S * STAGE;
+    static_assert(BN == 16 || BN == 32, "at most 32 rows of A");
+    static_assert(S >= 2 && 2 * S + 2 * NB + 2 <= 64, "barriers fit the header");
+};
+template <int BN> __host__ __device__ constexpr int fewq_threads() { return 32 * (4 + 4 * (BN / 16)); }
+
+template <int BN>
+__global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const MatmulArgs p)
+{
+    using G = FewQCfg<BN>;
+    constexpr int S = G::S, KS = G::KS, BATCH = G::BATCH, NB = G::NB, BPS = KS / BATCH, CG = BN / 16, CW = 16;
+    constexpr int THREADS = fewq_threads<BN>();
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = smem_u32(smem);
+    const uint32_t full0 = base, empty0 = base + 8 * S, tfull0 = base + 16 * S, tempty0 = tfull0 + 8 * NB;
+    const uint32_t holder = tempty0 + 8 * NB;
+    volatile int *abort_flag = (volatile int *)(smem + 768);
+    volatile uint32_t *holder_ptr = (volatile uint32_t *)(smem + (holder - base));
+    constexpr int wmode = MM_WAIT_MODE;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 2 + 4 * CG);       // both issuers' commits, and the epilogue warps, which read the stage's scales
+        }
+        for (int t = 0; t < NB; t++) {
+            mbar_init(tfull0 + 8 * t, 1);
+            mbar_init(tempty0 + 8 * t, 4 * CG);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(holder, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *holder_ptr;
+    uint8_t *ring = smem + MM_HEADER;
+    const int ntiles = p.b.rows_pad / TILE, tiles = p.batch * ntiles, groups = p.b.groups;
+    const int my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0, stages = my_tiles * groups;
+    const int bpt = (p.kb + BATCH - 1) / BATCH;
+    (void)THREADS;
+
+    if (warp == 0) {
+        // ---- producer: lanes 0 .. 23 copy B's codes, scales and mins of the stage's k-blocks, lane 24 A's slab
+        asm volatile("griddepcontrol.wait;" ::: "memory");       // the kernel before this one packed A
+        bool alive = true;
+        for (int sc = 0; sc < stages && alive; sc++) {
+            const int s = sc % S, g = sc % groups, tile = blockIdx.x + (sc / groups) * gridDim.x, bi = tile / ntiles, n0 = (tile - bi * ntiles) * TILE;
+            const int nkb = min(KS, p.kb - g * KS);
+            int ok = 1;
+            if (lane == 0 && sc >= S) ok = mm_wait(empty0 + 8 * s, (uint32_t)(sc / S - 1) & 1u, abort_flag, p.status, wmode) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { alive = false; break; }
+            const uint32_t dst = smem_u32(ring + (size_t)s * G::STAGE), bar = full0 + 8 * s;
+            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)nkb * (G::B_KB + 2 * G::PLANE_KB) + G::A_SLAB);
+            __syncwarp();
+            const int kk = lane / 3, what = lane - kk * 3;
+            if (lane < 24 && kk < nkb) {
+                const size_t kb = (size_t)(g * KS + kk);
+                const uint8_t *bb = p.b.codes + bi * p.b_stride, *bs = (const uint8_t *)p.b.scales + bi * p.b_stride, *bm = (const uint8_t *)p.b.extra + bi * p.b_stride;
+                if (what == 0) bulk_g2s(dst + kk * G::B_KB, bb + (kb * (p.b.rows_pad / 8) + n0 / 8) * 256, G::B_KB, bar);
+                else if (what == 1) bulk_g2s(dst + G::O_SB + kk * G::PLANE_KB, bs + (kb * p.b.rows_pad + n0) * 4, G::PLANE_KB, bar);
+                else bulk_g2s(dst + G::O_MB + kk * G::PLANE_KB, bm + (kb * p.b.rows_pad + n0) * 4, G::PLANE_KB, bar);
+            } else if (lane == 24) bulk_g2s(dst + G::O_A, p.a.codes + bi * p.a_stride + (size_t)g * G::A_SLAB, G::A_SLAB, bar);
+        }
+        if (*abort_flag && lane == 0) {          // let the copies still in flight land before the block exits
+            for (int it = max(0, stages - S); it < stages; it++) {
+                long long start = clock64();
+                while (!mbar_try_wait(full0 + 8 * (it % S), (uint32_t)(it / S) & 1u) && clock64() - start < WAIT_CYCLES) { }
+            }
+        }
+    } else if (warp == 1 || warp == 2) {
+        // ---- MMA issue: the batches of this warp's parity; per k-block the sums (kind::i8, M 128, N BN, K 32), one commit a batch
+        if (lane == 0) {
+            bool alive = true;
+            const int role = warp - 1;
+            constexpr uint64_t DESC_HI = (uint64_t)(128u >> 4) << 16 | (uint64_t)(256u >> 4) << 32 | (uint64_t)1 << 46;
+            constexpr uint32_t idesc = idesc_of(0, TILE, BN);
+            for (int sc = 0; sc < stages && alive; sc++) {
+                const int s = sc % S, g = sc % groups, nkb = min(KS, p.kb - g * KS);
+                const int tc0 = (sc / groups) * bpt + g * BPS;
+                if (!mm_poll(full0 + 8 * s, (uint32_t)(sc / S) & 1u, wmode & 3) &&
+                    !mm_wait(full0 + 8 * s, (uint32_t)(sc / S) & 1u, abort_flag, p.status, wmode)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t st = smem_u32(ring + (size_t)s * G::STAGE);
+                const uint64_t bc = DESC_HI | (uint64_t)(st >> 4), ac = DESC_HI | (uint64_t)((st + G::O_A) >> 4);
+#pragma unroll
+                for (int b = 0; b < BPS; b++) {
+                    const int tc = tc0 + b;
+                    if (b * BATCH < nkb && (tc & 1) == role) {
+                        const int slot = tc & (NB - 1);
+                        if (tc >= NB) {
+                            const uint32_t par = (uint32_t)(tc / NB - 1) & 1u;
+                            if (!mm_poll(tempty0 + 8 * slot, par, wmode & 3) && !mm_wait(tempty0 + 8 * slot, par, abort_flag, p.status, wmode)) { alive = false; break; }
+                            tc_fence_after();
+                        }
+                        const uint32_t d = tmem + (uint32_t)(slot * G::BCOLS);
+#pragma unroll
+                        for (int j = 0; j < BATCH; j++) {
+                            const int kk = b * BATCH + j;
+                            if (kk < nkb) mma_issue<0>(d + j * BN, bc + (uint64_t)kk * (G::B_KB >> 4), ac + (uint64_t)kk * (G::A_KB >> 4), idesc, 0u);
+                        }
+                        mma_commit(tfull0 + 8 * slot);
+                    }
+                }
+                if (alive) mma_commit(empty0 + 8 * s);
+            }
+        }
+    } else if (warp >= 4) {
+        // ---- epilogue: warp (q, cg) reads lanes 32 q .. and columns cg * 16 .. of every k-block's sums
+        const int q = warp & 3, cg = (warp - 4) >> 2;
+        const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cg * CW);
+        int tc = 0, sc = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
+            const int bi = tile / ntiles, n0 = (tile - bi * ntiles) * TILE;
+            float acc[CW];
+#pragma unroll
+            for (int c = 0; c < CW; c++) acc[c] = 0.f;
+            for (int i = 0; i < p.kb && alive; i += BATCH, tc++) {
+                const int t = tc & (NB - 1), nb = min(BATCH, p.kb - i), s = sc % S, kk0 = i % KS;
+                const uint32_t bar = tfull0 + 8 * t, par = (uint32_t)(tc / NB) & 1u;
+                if (!mm_poll(bar, par, wmode & 3) && !mm_wait_lanes(bar, par, abort_flag, p.status, wmode)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t at = tlane + (uint32_t)(t * G::BCOLS);
+                uint32_t v[BATCH][CW];
+#pragma unroll
+                for (int j = 0; j < BATCH; j++) tmem_ld_cols<CW>(at + j * BN, v[j]);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < BATCH; j++) pin16(v[j]);
+                tc_fence_before();
+                if (lane == 0) mbar_arrive(tempty0 + 8 * t);
+                // the stage's planes (complete long since: the products that filled the batch read the same stage; the poll is
+                // this thread's own sight of the copies)
+                if (kk0 == 0 && !mm_poll(full0 + 8 * s, (uint32_t)(sc / S) & 1u, wmode & 3) &&
+                    !mm_wait_lanes(full0 + 8 * s, (uint32_t)(sc / S) & 1u, abort_flag, p.status, wmode)) { alive = false; break; }
+                const uint8_t *stage = ring + (size_t)s * G::STAGE;
+#pragma unroll
+                for (int j = 0; j < BATCH; j++) {
+                    if (j < nb) {
+                        const int kk = kk0 + j;
+                        const float sb = ((const float *)(stage + G::O_SB))[kk * TILE + q * 32 + lane];
+                        const float wb = ((const float *)(stage + G::O_MB))[kk * TILE + q * 32 + lane];
+                        const float4 *sa4 = (const float4 *)(stage + G::O_SA) + (kk * BN + cg * CW) / 4;
+                        const float4 *ua4 = (const float4 *)(stage + G::O_UA) + (kk * BN + cg * CW) / 4;
+#pragma unroll
+                        for (int c4 = 0; c4 < CW / 4; c4++) {
+                            const float4 sa = sa4[c4], ua = ua4[c4];
+                            const float sav[4] = { sa.x, sa.y, sa.z, sa.w }, uav[4] = { ua.x, ua.y, ua.z, ua.w };
+#pragma unroll
+                            for (int c = 0; c < 4; c++) {
+                                float a1 = __fmaf_rn((float)(int32_t)v[j][4 * c4 + c], __fmul_rn(sav[c], sb), acc[4 * c4 + c]);
+                                acc[4 * c4 + c] = __fmaf_rn(wb, -uav[c], a1);
+                            }
+                        }
+                    }
+                }
+                if (kk0 + BATCH >= KS || i + BATCH >= p.kb) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty0 + 8 * s);          // this warp has read the stage's planes
+                    sc++;
+                }
+            }
+            const int col = n0 + q * 32 + lane;
+            float *c_out = p.c + bi * p.c_stride;
+            if (alive && col < p.n) {
+#pragma unroll
+                for (int r = 0; r < CW; r++) if (cg * CW + r < p.m) c_out[(size_t)(cg * CW + r) * p.n + col] = acc[r];
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
 // ---------------------------------------------------------------------------------- the tensor pipe's own rate
 
 // One thread of one block issues `iters` x 4 tcgen05.mma kind::i8 (M 128, N 128, K 32, the product's instruction) on
@@ -1537,6 +1753,8 @@ cudaError_t matmul_init(int sm_count, int max_smem, int *status)
     if ((e = set_few_attr<16, 0>()) || (e = set_few_attr<32, 0>()) || (e = set_few_attr<64, 0>())) return e;
     if ((e = set_few_attr<16, 1>()) || (e = set_few_attr<32, 1>())) return e;
     if ((e = set_few_attr<16, 2>()) || (e = set_few_attr<32, 2>())) return e;
+    if ((e = cudaFuncSetAttribute(fewq_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<16>::SMEM))) return e;
+    if ((e = cudaFuncSetAttribute(fewq_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<32>::SMEM))) return e;
     if ((e = set_mm_attr<0, false>()) || (e = set_mm_attr<0, true>())) return e;
     if ((e = set_mm_attr<1, false>()) || (e = set_mm_attr<1, true>())) return e;
     return cudaSuccess;
@@ -1565,7 +1783,8 @@ static int few_bn(int m) { return m <= 16 ? 16 : m <= 32 ? 32 : 64; }
 static size_t a_packed_bytes(int m, int k, int kbs, bool tcs)
 {
     const size_t tile = packed_bytes(LAY_TILE, m, k, kbs, tcs);
-    const size_t few = tcs && m <= 64 ? align256((size_t)groups_of(kbs) * few_slab(few_bn(m), kc_of(k, kbs))) : 0;
+    const size_t few = tcs && m <= 64 ? align256((size_t)groups_of(kbs) * few_slab(few_bn(m), kc_of(k, kbs))) :
+                       !tcs && m <= 32 ? align256((size_t)groups_of(kbs) * fewq_slab(few_bn(m), kc_of(k, kbs))) : 0;
     return tile > few ? tile : few;
 }
 // B with plain f16 scales is grouped for the tensor cores' scale product, any other B is k-block-major with f32 planes
@@ -1694,7 +1913,9 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     const bool tcs = use_tcs(fmt_b);
     // few rows of A: B's rows become the lanes of tensor memory (fewrows_kernel), A is packed for that
     const bool few = tcs && !sums && g_mm_kind == 0 && m <= g_mm_few;
-    const int bn = few_bn(m), a_layout = few ? LAY_FEW : LAY_TILE, lay_b = b_layout(fmt_b);
+    // ... and against Q4_K weights (scale products on the CUDA cores) with at most 32 rows, lanes only
+    const bool fewq = mins && !sums && !c_blocks && g_mm_kind == 0 && m <= 32 && m <= g_mm_few;
+    const int bn = few_bn(m), a_layout = few || fewq ? LAY_FEW : LAY_TILE, lay_b = b_layout(fmt_b);
     const size_t a_slab = a_packed_bytes(m, k, kbs, tcs), b_slab = packed_bytes(lay_b, n, k, kbs, false);
     // ... and on raw weights that come in whole groups of eight blocks, 16-byte aligned, the kernel re-lays B itself
     const bool raw_few = few && m <= 32 && !b_packed && batch.count == 1 && kbs % GROUP == 0 && ((uintptr_t)b & 15) == 0 && g_mm_raw_few;
@@ -1734,6 +1955,17 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     args.a_stride = batch.stride_a ? a_slab : 0;
     args.b_stride = !b_packed && batch.stride_b ? b_slab : 0;
     args.c_stride = (size_t)batch.stride_c;
+    if (fewq) {
+        const int tiles = batch.count * (tb.rows_pad / TILE), grid = tiles < g_mm_sms ? tiles : g_mm_sms;
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.gridDim = dim3(grid); cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
+        if (bn == 16) { cfg.blockDim = dim3(fewq_threads<16>()); cfg.dynamicSmemBytes = FewQCfg<16>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<16>, args); }
+        else { cfg.blockDim = dim3(fewq_threads<32>()); cfg.dynamicSmemBytes = FewQCfg<32>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<32>, args); }
+        return (int)e;
+    }
     if (few) {
         const int tiles = batch.count * (tb.rows_pad / TILE), grid = tiles < g_mm_sms ? tiles : g_mm_sms;
         if (raw_few) e = fmt_b == QB200_Q8_0 ? launch_few_rows<1>(bn, grid, args, stream) : launch_few_rows<2>(bn, grid, args, stream);

@@ -329,7 +329,7 @@ def check_k(oracle, fmt_a, fmt_b, m, n, k, seed):
 
 @pytest.mark.parametrize("fmt_b", [B.Q4_K, B.Q6_K])
 @pytest.mark.parametrize("fmt_a", [B.Q8_0, B.Q4_0])
-@pytest.mark.parametrize("m,n,k", [(1, 1, 256), (37, 29, 512), (129, 127, 1280), (16, 257, 4096)])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 256), (37, 29, 512), (129, 127, 1280), (16, 257, 4096), (24, 300, 1024), (32, 129, 768), (5, 1000, 2304)])
 def test_k_quant_weights(oracle, fmt_a, fmt_b, m, n, k):
     check_k(oracle, fmt_a, fmt_b, m, n, k, 500 + m)
 
