@@ -308,8 +308,8 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int 
     store_codes16(t, r, 2 * b * per16, w[0], w[1], w[2], w[3]);
     store_codes16(t, r, (2 * b + 1) * per16, w[4], w[5], w[6], w[7]);
     if (SPLIT) {
-        t.scales[scale_offset(t, r, 2 * b)] = d;
-        t.scales[scale_offset(t, r, 2 * b + 1)] = d;
+        store_scale(t, r, 2 * b, d, p[0]);
+        store_scale(t, r, 2 * b + 1, d, p[0]);
         continue;
     }
     store_scale(t, r, b, d, p[0]);
@@ -1455,26 +1455,31 @@ __global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(co
 //     acc = fma(float(D), sA * (d*sc), acc);  acc = fma(dmin*m, -(sA * sum(qA)), acc)      (the 128-row-tile kernel's order).
 // B comes k-block-major (LAY_KBLOCK): three copies a k-block (codes, scales, mins), issued by a lane each; A in its
 // few-rows form with f32 planes (one copy a stage).
-template <int BN>
+// HALFQ: Q6_K weights, k-blocks of 16 values (the other half of the instruction's K comes from a patch of zeros on B's
+// side; A's may then be anything), no min term.
+template <int BN, bool HALFQ>
 struct FewQCfg {
     static constexpr int KS = GROUP;
     static constexpr int BATCH = 64 / BN, BCOLS = 64, NB = 512 / BCOLS;
-    static constexpr uint32_t B_KB = TILE * 32, PLANE_KB = TILE * 4, A_KB = BN * 32;
-    static constexpr uint32_t O_SB = KS * B_KB, O_MB = O_SB + KS * PLANE_KB, O_A = O_MB + KS * PLANE_KB;
+    static constexpr int KC = HALFQ ? 1 : 2;
+    static constexpr uint32_t B_KB = TILE * KC * 16, PLANE_KB = TILE * 4, A_KB = BN * KC * 16;
+    static constexpr uint32_t O_SB = KS * B_KB, O_MB = O_SB + KS * PLANE_KB, O_A = O_MB + (HALFQ ? 0 : KS * PLANE_KB);
     static constexpr uint32_t A_SLAB = GROUP * A_KB + 2 * GROUP * BN * 4, O_SA = O_A + GROUP * A_KB, O_UA = O_SA + GROUP * BN * 4;
     static constexpr uint32_t STAGE = O_A + A_SLAB;
-    static constexpr int S_FIT = (int)((MM_SMEM_MAX - MM_HEADER) / STAGE);
+    static constexpr uint32_t PATCH = HALFQ ? 2048 : 0;
+    static constexpr int S_FIT = (int)((MM_SMEM_MAX - MM_HEADER - PATCH) / STAGE);
     static constexpr int S = S_FIT > 6 ? 6 : S_FIT;
-    static constexpr uint32_t SMEM = MM_HEADER + S * STAGE;
+    static constexpr uint32_t O_PATCH = MM_HEADER + S * STAGE;
+    static constexpr uint32_t SMEM = O_PATCH + PATCH;
     static_assert(BN == 16 || BN == 32, "at most 32 rows of A");
     static_assert(S >= 2 && 2 * S + 2 * NB + 2 <= 64, "barriers fit the header");
 };
 template <int BN> __host__ __device__ constexpr int fewq_threads() { return 32 * (4 + 4 * (BN / 16)); }
 
-template <int BN>
+template <int BN, bool HALFQ>
 __global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const MatmulArgs p)
 {
-    using G = FewQCfg<BN>;
+    using G = FewQCfg<BN, HALFQ>;
     constexpr int S = G::S, KS = G::KS, BATCH = G::BATCH, NB = G::NB, BPS = KS / BATCH, CG = BN / 16, CW = 16;
     constexpr int THREADS = fewq_threads<BN>();
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -1497,6 +1502,10 @@ __global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const Matmu
         *abort_flag = 0;
         mbar_fence_init();
     }
+    if (G::PATCH) {
+        for (int i = threadIdx.x; i < (int)G::PATCH / 16; i += THREADS) *(uint4 *)(smem + G::O_PATCH + i * 16) = make_uint4(0, 0, 0, 0);
+        fence_proxy_async();
+    }
     if (warp == 1) tmem_alloc(holder, 512);
     tc_fence_before();
     __syncthreads();
@@ -1506,7 +1515,6 @@ __global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const Matmu
     const int ntiles = p.b.rows_pad / TILE, tiles = p.batch * ntiles, groups = p.b.groups;
     const int my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0, stages = my_tiles * groups;
     const int bpt = (p.kb + BATCH - 1) / BATCH;
-    (void)THREADS;
 
     if (warp == 0) {
         // ---- producer: lanes 0 .. 23 copy B's codes, scales and mins of the stage's k-blocks, lane 24 A's slab
@@ -1520,13 +1528,13 @@ __global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const Matmu
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { alive = false; break; }
             const uint32_t dst = smem_u32(ring + (size_t)s * G::STAGE), bar = full0 + 8 * s;
-            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)nkb * (G::B_KB + 2 * G::PLANE_KB) + G::A_SLAB);
+            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)nkb * (G::B_KB + (HALFQ ? 1 : 2) * G::PLANE_KB) + G::A_SLAB);
             __syncwarp();
             const int kk = lane / 3, what = lane - kk * 3;
-            if (lane < 24 && kk < nkb) {
+            if (lane < 24 && kk < nkb && !(HALFQ && what == 2)) {
                 const size_t kb = (size_t)(g * KS + kk);
                 const uint8_t *bb = p.b.codes + bi * p.b_stride, *bs = (const uint8_t *)p.b.scales + bi * p.b_stride, *bm = (const uint8_t *)p.b.extra + bi * p.b_stride;
-                if (what == 0) bulk_g2s(dst + kk * G::B_KB, bb + (kb * (p.b.rows_pad / 8) + n0 / 8) * 256, G::B_KB, bar);
+                if (what == 0) bulk_g2s(dst + kk * G::B_KB, bb + (kb * (p.b.rows_pad / 8) + n0 / 8) * (G::KC * 128), G::B_KB, bar);
                 else if (what == 1) bulk_g2s(dst + G::O_SB + kk * G::PLANE_KB, bs + (kb * p.b.rows_pad + n0) * 4, G::PLANE_KB, bar);
                 else bulk_g2s(dst + G::O_MB + kk * G::PLANE_KB, bm + (kb * p.b.rows_pad + n0) * 4, G::PLANE_KB, bar);
             } else if (lane == 24) bulk_g2s(dst + G::O_A, p.a.codes + bi * p.a_stride + (size_t)g * G::A_SLAB, G::A_SLAB, bar);
@@ -1542,8 +1550,9 @@ __global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const Matmu
         if (lane == 0) {
             bool alive = true;
             const int role = warp - 1;
-            constexpr uint64_t DESC_HI = (uint64_t)(128u >> 4) << 16 | (uint64_t)(256u >> 4) << 32 | (uint64_t)1 << 46;
+            constexpr uint64_t DESC_HI = (uint64_t)(128u >> 4) << 16 | (uint64_t)((G::KC * 128u) >> 4) << 32 | (uint64_t)1 << 46;
             constexpr uint32_t idesc = idesc_of(0, TILE, BN);
+            const uint32_t patch = base + G::O_PATCH;
             for (int sc = 0; sc < stages && alive; sc++) {
                 const int s = sc % S, g = sc % groups, nkb = min(KS, p.kb - g * KS);
                 const int tc0 = (sc / groups) * bpt + g * BPS;
@@ -1566,7 +1575,13 @@ __global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const Matmu
 #pragma unroll
                         for (int j = 0; j < BATCH; j++) {
                             const int kk = b * BATCH + j;
-                            if (kk < nkb) mma_issue<0>(d + j * BN, bc + (uint64_t)kk * (G::B_KB >> 4), ac + (uint64_t)kk * (G::A_KB >> 4), idesc, 0u);
+                            if (kk < nkb) {
+                                if (HALFQ) {
+                                    // the second 16-byte k-chunk of every row of B is the patch of zeros; A's may then be anything
+                                    const uint32_t b_at = st + kk * G::B_KB, a_at = st + G::O_A + kk * G::A_KB;
+                                    mma_issue<0>(d + j * BN, smem_desc(b_at, patch - b_at, 128), smem_desc(a_at, 128, 128), idesc, 0u);
+                                } else mma_issue<0>(d + j * BN, bc + (uint64_t)kk * (G::B_KB >> 4), ac + (uint64_t)kk * (G::A_KB >> 4), idesc, 0u);
+                            }
                         }
                         mma_commit(tfull0 + 8 * slot);
                     }
@@ -1609,7 +1624,7 @@ __global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const Matmu
                     if (j < nb) {
                         const int kk = kk0 + j;
                         const float sb = ((const float *)(stage + G::O_SB))[kk * TILE + q * 32 + lane];
-                        const float wb = ((const float *)(stage + G::O_MB))[kk * TILE + q * 32 + lane];
+                        const float wb = HALFQ ? 0.f : ((const float *)(stage + G::O_MB))[kk * TILE + q * 32 + lane];
                         const float4 *sa4 = (const float4 *)(stage + G::O_SA) + (kk * BN + cg * CW) / 4;
                         const float4 *ua4 = (const float4 *)(stage + G::O_UA) + (kk * BN + cg * CW) / 4;
 #pragma unroll
@@ -1619,7 +1634,7 @@ __global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const Matmu
 #pragma unroll
                             for (int c = 0; c < 4; c++) {
                                 float a1 = __fmaf_rn((float)(int32_t)v[j][4 * c4 + c], __fmul_rn(sav[c], sb), acc[4 * c4 + c]);
-                                acc[4 * c4 + c] = __fmaf_rn(wb, -uav[c], a1);
+                                acc[4 * c4 + c] = HALFQ ? a1 : __fmaf_rn(wb, -uav[c], a1);
                             }
                         }
                     }
@@ -1753,8 +1768,10 @@ cudaError_t matmul_init(int sm_count, int max_smem, int *status)
     if ((e = set_few_attr<16, 0>()) || (e = set_few_attr<32, 0>()) || (e = set_few_attr<64, 0>())) return e;
     if ((e = set_few_attr<16, 1>()) || (e = set_few_attr<32, 1>())) return e;
     if ((e = set_few_attr<16, 2>()) || (e = set_few_attr<32, 2>())) return e;
-    if ((e = cudaFuncSetAttribute(fewq_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<16>::SMEM))) return e;
-    if ((e = cudaFuncSetAttribute(fewq_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<32>::SMEM))) return e;
+    if ((e = cudaFuncSetAttribute(fewq_kernel<16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<16, false>::SMEM))) return e;
+    if ((e = cudaFuncSetAttribute(fewq_kernel<32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<32, false>::SMEM))) return e;
+    if ((e = cudaFuncSetAttribute(fewq_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<16, true>::SMEM))) return e;
+    if ((e = cudaFuncSetAttribute(fewq_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<32, true>::SMEM))) return e;
     if ((e = set_mm_attr<0, false>()) || (e = set_mm_attr<0, true>())) return e;
     if ((e = set_mm_attr<1, false>()) || (e = set_mm_attr<1, true>())) return e;
     return cudaSuccess;
@@ -1914,7 +1931,7 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     // few rows of A: B's rows become the lanes of tensor memory (fewrows_kernel), A is packed for that
     const bool few = tcs && !sums && g_mm_kind == 0 && m <= g_mm_few;
     // ... and against Q4_K weights (scale products on the CUDA cores) with at most 32 rows, lanes only
-    const bool fewq = mins && !sums && !c_blocks && g_mm_kind == 0 && m <= 32 && m <= g_mm_few;
+    const bool fewq = (mins || half) && !sums && !c_blocks && g_mm_kind == 0 && m <= 32 && m <= g_mm_few;
     const int bn = few_bn(m), a_layout = few || fewq ? LAY_FEW : LAY_TILE, lay_b = b_layout(fmt_b);
     const size_t a_slab = a_packed_bytes(m, k, kbs, tcs), b_slab = packed_bytes(lay_b, n, k, kbs, false);
     // ... and on raw weights that come in whole groups of eight blocks, 16-byte aligned, the kernel re-lays B itself
@@ -1962,8 +1979,14 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
         attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr.val.programmaticStreamSerializationAllowed = 1;
         cfg.gridDim = dim3(grid); cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
-        if (bn == 16) { cfg.blockDim = dim3(fewq_threads<16>()); cfg.dynamicSmemBytes = FewQCfg<16>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<16>, args); }
-        else { cfg.blockDim = dim3(fewq_threads<32>()); cfg.dynamicSmemBytes = FewQCfg<32>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<32>, args); }
+        cfg.blockDim = dim3(bn == 16 ? fewq_threads<16>() : fewq_threads<32>());
+        if (half) {
+            if (bn == 16) { cfg.dynamicSmemBytes = FewQCfg<16, true>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<16, true>, args); }
+            else { cfg.dynamicSmemBytes = FewQCfg<32, true>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<32, true>, args); }
+        } else {
+            if (bn == 16) { cfg.dynamicSmemBytes = FewQCfg<16, false>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<16, false>, args); }
+            else { cfg.dynamicSmemBytes = FewQCfg<32, false>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<32, false>, args); }
+        }
         return (int)e;
     }
     if (few) {
