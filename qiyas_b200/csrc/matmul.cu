@@ -1448,7 +1448,7 @@ __global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(co
 // ---------------------------------------------------------------------------------- few rows of A against Q4_K weights
 
 // The few-rows kernel for weights whose scale products stay on the CUDA cores (Q4_K: scales d*sc and mins dmin*m are
-// f32).  Same sides as fewrows_kernel: the 128 rows of a tile of B on the lanes of tensor memory, A's rows (BN = 16 or 32)
+// f32).  Same sides as fewrows_kernel: the 128 rows of a tile of B on the lanes of tensor memory, A's rows (BN = 16, 32 or 64)
 // as columns; a k-block's sums take BN columns and nothing else, so 64 / BN k-blocks form a batch of 64 columns and
 // eight batches are in flight.  Thread (q, lane) owns row n of B: its scale and min of a k-block are two words of shared
 // memory, A's scales and scaled code sums are broadcast reads;
@@ -1471,7 +1471,7 @@ struct FewQCfg {
     static constexpr int S = S_FIT > 6 ? 6 : S_FIT;
     static constexpr uint32_t O_PATCH = MM_HEADER + S * STAGE;
     static constexpr uint32_t SMEM = O_PATCH + PATCH;
-    static_assert(BN == 16 || BN == 32, "at most 32 rows of A");
+    static_assert(BN == 16 || BN == 32 || BN == 64, "at most 64 rows of A");
     static_assert(S >= 2 && 2 * S + 2 * NB + 2 <= 64, "barriers fit the header");
 };
 template <int BN> __host__ __device__ constexpr int fewq_threads() { return 32 * (4 + 4 * (BN / 16)); }
@@ -1772,6 +1772,8 @@ cudaError_t matmul_init(int sm_count, int max_smem, int *status)
     if ((e = cudaFuncSetAttribute(fewq_kernel<32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<32, false>::SMEM))) return e;
     if ((e = cudaFuncSetAttribute(fewq_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<16, true>::SMEM))) return e;
     if ((e = cudaFuncSetAttribute(fewq_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<32, true>::SMEM))) return e;
+    if ((e = cudaFuncSetAttribute(fewq_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<64, false>::SMEM))) return e;
+    if ((e = cudaFuncSetAttribute(fewq_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<64, true>::SMEM))) return e;
     if ((e = set_mm_attr<0, false>()) || (e = set_mm_attr<0, true>())) return e;
     if ((e = set_mm_attr<1, false>()) || (e = set_mm_attr<1, true>())) return e;
     return cudaSuccess;
@@ -1801,7 +1803,7 @@ static size_t a_packed_bytes(int m, int k, int kbs, bool tcs)
 {
     const size_t tile = packed_bytes(LAY_TILE, m, k, kbs, tcs);
     const size_t few = tcs && m <= 64 ? align256((size_t)groups_of(kbs) * few_slab(few_bn(m), kc_of(k, kbs))) :
-                       !tcs && m <= 32 ? align256((size_t)groups_of(kbs) * fewq_slab(few_bn(m), kc_of(k, kbs))) : 0;
+                       !tcs && m <= 64 ? align256((size_t)groups_of(kbs) * fewq_slab(few_bn(m), kc_of(k, kbs))) : 0;
     return tile > few ? tile : few;
 }
 // B with plain f16 scales is grouped for the tensor cores' scale product, any other B is k-block-major with f32 planes
@@ -1931,7 +1933,7 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     // few rows of A: B's rows become the lanes of tensor memory (fewrows_kernel), A is packed for that
     const bool few = tcs && !sums && g_mm_kind == 0 && m <= g_mm_few;
     // ... and against Q4_K weights (scale products on the CUDA cores) with at most 32 rows, lanes only
-    const bool fewq = (mins || half) && !sums && !c_blocks && g_mm_kind == 0 && m <= 32 && m <= g_mm_few;
+    const bool fewq = (mins || half) && !sums && !c_blocks && g_mm_kind == 0 && m <= 64 && m <= g_mm_few;
     const int bn = few_bn(m), a_layout = few || fewq ? LAY_FEW : LAY_TILE, lay_b = b_layout(fmt_b);
     const size_t a_slab = a_packed_bytes(m, k, kbs, tcs), b_slab = packed_bytes(lay_b, n, k, kbs, false);
     // ... and on raw weights that come in whole groups of eight blocks, 16-byte aligned, the kernel re-lays B itself
@@ -1979,13 +1981,15 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
         attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr.val.programmaticStreamSerializationAllowed = 1;
         cfg.gridDim = dim3(grid); cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
-        cfg.blockDim = dim3(bn == 16 ? fewq_threads<16>() : fewq_threads<32>());
+        cfg.blockDim = dim3(bn == 16 ? fewq_threads<16>() : bn == 32 ? fewq_threads<32>() : fewq_threads<64>());
         if (half) {
             if (bn == 16) { cfg.dynamicSmemBytes = FewQCfg<16, true>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<16, true>, args); }
-            else { cfg.dynamicSmemBytes = FewQCfg<32, true>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<32, true>, args); }
+            else if (bn == 32) { cfg.dynamicSmemBytes = FewQCfg<32, true>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<32, true>, args); }
+            else { cfg.dynamicSmemBytes = FewQCfg<64, true>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<64, true>, args); }
         } else {
             if (bn == 16) { cfg.dynamicSmemBytes = FewQCfg<16, false>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<16, false>, args); }
-            else { cfg.dynamicSmemBytes = FewQCfg<32, false>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<32, false>, args); }
+            else if (bn == 32) { cfg.dynamicSmemBytes = FewQCfg<32, false>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<32, false>, args); }
+            else { cfg.dynamicSmemBytes = FewQCfg<64, false>::SMEM; e = cudaLaunchKernelEx(&cfg, fewq_kernel<64, false>, args); }
         }
         return (int)e;
     }
