@@ -326,14 +326,16 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(const uint8_t *raw, int 
 // eight k-blocks.  Sub-block j (32 values): codes q = the low (j even) or high nibbles of qs[32 (j/2) ..], kept as
 // 0..15; scale d * sc and min dmin * m, each rounded to f32 as DecodeQ4_K rounds them, with sc and m unpacked as ScaleMin
 // does (src/Blocks.cs:73-77).  value = (d*sc)*q - dmin*m, so a k-block contributes sA*(d*sc)*sum(qA*q) - (dmin*m)*sA*sum(qA).
+template <int PR>       // rows a block: 128 for a whole weight matrix (more loads in flight a thread), 32 for a small one
 __global__ void __launch_bounds__(256) pack_q4_k_kernel(const uint8_t *raw, int rows, int kb32, PackTarget t)
 {
     constexpr int PITCH = 37;                           // words a row of 144 bytes (36 words): odd, so rows start in different banks
-    __shared__ uint32_t seg[32 * PITCH];
-    const int r0 = blockIdx.x * 32, sb = blockIdx.y;
+    __shared__ uint32_t seg[PR * PITCH];
+    const int r0 = blockIdx.x * PR, sb = blockIdx.y;
     const size_t row_bytes = (size_t)(kb32 / 8) * 144;
     if ((((uintptr_t)raw | row_bytes) & 15) == 0) {
-        for (int idx = threadIdx.x; idx < 32 * 9; idx += 256) {
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < PR * 9; idx += 256) {
             const int rr = idx / 9, c = idx - rr * 9;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (r0 + rr < rows) v = __ldg((const uint4 *)(raw + (size_t)(r0 + rr) * row_bytes + (size_t)sb * 144) + c);
@@ -341,7 +343,7 @@ __global__ void __launch_bounds__(256) pack_q4_k_kernel(const uint8_t *raw, int 
             dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
         }
     } else {
-        for (int idx = threadIdx.x; idx < 32 * 72; idx += 256) {
+        for (int idx = threadIdx.x; idx < PR * 72; idx += 256) {
             const int rr = idx / 72, h = idx - rr * 72;
             uint16_t v = 0;
             if (r0 + rr < rows) v = __ldg((const uint16_t *)(raw + (size_t)(r0 + rr) * row_bytes + (size_t)sb * 144) + h);
@@ -349,7 +351,9 @@ __global__ void __launch_bounds__(256) pack_q4_k_kernel(const uint8_t *raw, int 
         }
     }
     __syncthreads();
-    const int rl = threadIdx.x & 31, j = threadIdx.x >> 5, r = r0 + rl, b = sb * 8 + j;
+#pragma unroll
+    for (int rh = 0; rh < PR / 32; rh++) {
+    const int rl = (threadIdx.x & 31) + 32 * rh, j = threadIdx.x >> 5, r = r0 + rl, b = sb * 8 + j;
     const uint32_t *row = seg + rl * PITCH;
     const uint8_t *sc12 = (const uint8_t *)(row + 1);
     const float d = half_bits_to_float(row[0] & 0xFFFFu), dmin = half_bits_to_float(row[0] >> 16);
@@ -367,6 +371,7 @@ __global__ void __launch_bounds__(256) pack_q4_k_kernel(const uint8_t *raw, int 
     store_codes16(t, r, (2 * b + 1) * per16, w[4], w[5], w[6], w[7]);
     t.scales[scale_offset(t, r, b)] = __fmul_rn(d, (float)sc);       // rows past the end read as zeros throughout
     t.extra[scale_offset(t, r, b)] = __fmul_rn(dmin, (float)m);
+    }
 }
 
 // Q6_K rows as an operand: a block of 256 threads re-lays 32 rows x one super-block (210 bytes, src/Blocks.cs:157-171)
@@ -1845,7 +1850,10 @@ static cudaError_t pack(int fmt, const void *raw, int rows, int k, const PackTar
 {
     const int kb32 = k / 32, padded = t.rows_pad;
     const uint8_t *r = (const uint8_t *)raw;
-    if (fmt == QB200_Q4_K) pack_q4_k_kernel<<<dim3(padded / 32, kb32 / 8), 256, 0, stream>>>(r, rows, kb32, t);
+    if (fmt == QB200_Q4_K) {
+        if ((long long)(padded / 128) * (kb32 / 8) >= 2ll * g_mm_sms) pack_q4_k_kernel<128><<<dim3(padded / 128, kb32 / 8), 256, 0, stream>>>(r, rows, kb32, t);
+        else pack_q4_k_kernel<32><<<dim3(padded / 32, kb32 / 8), 256, 0, stream>>>(r, rows, kb32, t);
+    }
     else if (fmt == QB200_Q6_K) pack_q6_k_kernel<<<dim3(padded / 32, k / 256), 256, 0, stream>>>(r, rows, k / 16, t);
     else {
         const int us = want_usums ? 1 : 0, kgroups = (kb32 + 7) / 8;
