@@ -31,6 +31,7 @@
 // KIND selects the tensor instruction: 0 = kind::i8 (codes as int8, s32 sums, converted to f32 in the epilogue),
 // 1 = kind::f16 (codes as f16: every product and every sum of 32 products is an integer below 2^24, so the f32 sums
 // are exact and need no conversion; twice the operand bytes).
+#include <cuda.h>                 // CUtensorMap (types only: the encoder is fetched through the runtime)
 #include "common.cuh"
 #include "encode_blocks.cuh"
 #include "launch.h"
@@ -1082,9 +1083,15 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(c
 template <int BN, int RAW = 0>
 struct FewCfg {
     static constexpr int KS = GROUP;                               // k-blocks a shared-memory stage
-    static constexpr int RAW_BB = RAW == 2 ? 18 : 34;               // bytes a raw block
+    // RAW 3, 4: as 1, 2 with the rows' bytes fetched by the TMA unit (one 2-D tile copy a stage from a tensor map over B's
+    // rows, into a ring of RAWS raw stages) instead of by the converters' own loads
+    static constexpr bool TMA = RAW >= 3;
+    static constexpr int RFMT = TMA ? RAW - 2 : RAW;
+    static constexpr int RAW_BB = RFMT == 2 ? 18 : 34;              // bytes a raw block
     static constexpr int RAW_HALVES = GROUP * RAW_BB / 2, RAW_PITCH = RAW_HALVES + 2;      // halfwords a row's group; an odd number of words a row
-    static constexpr uint32_t STAGING = RAW ? TILE * RAW_PITCH * 2 : 0;
+    static constexpr int RAWS = TMA ? 3 : 0;
+    static constexpr uint32_t RAW_ROW = GROUP * RAW_BB, RAW_STAGE = TILE * RAW_ROW;
+    static constexpr uint32_t STAGING = TMA ? RAWS * RAW_STAGE : RAW ? TILE * RAW_PITCH * 2 : 0;
     static constexpr int BATCH = 64 / BN;                          // k-blocks a batch in tensor memory
     static constexpr int BCOLS = 128;                              // its columns: 64 of sums, 64 of scale products
     static constexpr int NB = 512 / BCOLS;                         // batches in flight
@@ -1099,7 +1106,7 @@ struct FewCfg {
     static constexpr uint32_t O_STAGING = O_PATCH + PATCH;
     static constexpr uint32_t SMEM = O_STAGING + STAGING;
     static_assert(BN == 16 || BN == 32 || BN == 64, "the batch is 64 columns of sums");
-    static_assert(S >= 2 && 2 * S + 2 * NB + 2 <= 64, "barriers fit the header");
+    static_assert(S >= 2 && 2 * S + 2 * NB + 2 * RAWS + 2 <= 64, "barriers fit the header");
 };
 // Warps of the few-rows kernel: 0 producer, 1 and 2 issue the tensor instructions of the even and the odd batches (one
 // thread each: an instruction costs its issuer about 60 cycles, whatever its shape, and this kernel's are small), 3 idle,
@@ -1119,9 +1126,11 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N])
 }
 
 template <int BN, int RAW>
-__global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(const MatmulArgs p)
+__global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(const MatmulArgs p, const __grid_constant__ CUtensorMap bmap)
 {
     using G = FewCfg<BN, RAW>;
+    constexpr bool TMA = G::TMA;
+    constexpr int RFMT = G::RFMT, RAWS = G::RAWS;
     constexpr int S = G::S, KS = G::KS, BATCH = G::BATCH, NB = G::NB, BPS = KS / BATCH;
     constexpr int CG = BN / FEW_CW, CW = FEW_CW;                    // column groups of the epilogue, columns a warp
     constexpr int THREADS = few_threads<BN, RAW>(), CONV0 = 4 + 4 * CG;      // the first converter warp
@@ -1131,7 +1140,8 @@ __global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = smem_u32(smem);
     const uint32_t full0 = base, empty0 = base + 8 * S, tfull0 = base + 16 * S, tempty0 = tfull0 + 8 * NB;
-    const uint32_t holder = tempty0 + 8 * NB;
+    const uint32_t rawfull0 = tempty0 + 8 * NB, rawempty0 = rawfull0 + 8 * RAWS;         // the raw stages' barriers (TMA)
+    const uint32_t holder = rawempty0 + 8 * RAWS;
     volatile int *abort_flag = (volatile int *)(smem + 768);
     volatile uint32_t *holder_ptr = (volatile uint32_t *)(smem + (holder - base));
     constexpr int wmode = MM_WAIT_MODE;
@@ -1145,6 +1155,10 @@ __global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(co
         for (int t = 0; t < NB; t++) {
             mbar_init(tfull0 + 8 * t, 1);
             mbar_init(tempty0 + 8 * t, 4 * CG);
+        }
+        for (int r = 0; r < RAWS; r++) {
+            mbar_init(rawfull0 + 8 * r, 1);
+            mbar_init(rawempty0 + 8 * r, CONV_WARPS);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -1259,6 +1273,26 @@ __global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(co
             }
             MM_TRACE(p, 8 + 4 * (warp - 1), w_full); MM_TRACE(p, 9 + 4 * (warp - 1), w_tempty); MM_TRACE(p, 10 + 4 * (warp - 1), MM_CLOCK() - t_begin);
         }
+    } else if (TMA && warp == 3) {
+        // ---- the raw rows' producer (one thread): per stage one 2-D tile copy, the tile's 128 rows x the group's bytes, into
+        // the ring of raw stages (rows past the matrix come as zeros).  B does not depend on the kernel before this one.
+        if (lane == 0) {
+            for (int sc = 0; sc < stages; sc++) {
+                const int r = sc % RAWS, tile = blockIdx.x + (sc / groups) * gridDim.x, n0 = (tile % ntiles) * TILE;
+                if (sc >= RAWS && !mm_wait(rawempty0 + 8 * r, (uint32_t)(sc / RAWS - 1) & 1u, abort_flag, p.status, wmode)) break;
+                mbar_arrive_expect_tx(rawfull0 + 8 * r, G::RAW_STAGE);
+                const uint32_t dst = base + G::O_STAGING + (uint32_t)r * G::RAW_STAGE;
+                const int x = (sc % groups) * (int)(G::RAW_ROW / 2);            // in 16-bit elements: a multiple of 16 bytes
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             :: "r"(dst), "l"((uint64_t)&bmap), "r"(x), "r"(n0), "r"(rawfull0 + 8 * r) : "memory");
+            }
+            if (*abort_flag) {          // let the copies still in flight land before the block exits
+                for (int r = 0; r < RAWS; r++) {
+                    long long start = clock64();
+                    while (!mbar_try_wait(rawfull0 + 8 * r, 0u) && !mbar_try_wait(rawfull0 + 8 * r, 1u) && clock64() - start < WAIT_CYCLES / 64) { }
+                }
+            }
+        }
     } else if (warp >= 4 && warp < CONV0) {
         // ---- epilogue: warp (q, cg) reads lanes 32 q .. 32 q + 31 and columns cg * CW .. of every k-block's sums
         const int q = warp & 3, cg = (warp - 4) >> 2;
@@ -1336,6 +1370,56 @@ __global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(co
             }
         }
         if (lane == 0 && warp < 8) { MM_TRACE(p, 16 + 4 * (warp - 4), w_tfull); MM_TRACE(p, 17 + 4 * (warp - 4), MM_CLOCK() - t_begin); MM_TRACE(p, 18 + 4 * (warp - 4), w_ld); }
+    } else if (TMA && warp >= CONV0) {
+        // ---- converters on raw stages the TMA unit filled: lane = 8 rows x 4 blocks (rows 272 or 144 bytes apart: eight rows
+        // start in eight different banks; reads of different blocks then collide two ways at most, and the eight lanes of a
+        // 16-byte store write one core matrix's 128 contiguous bytes); a warp takes four (row group, half of the blocks) pairs
+        constexpr int BB = G::RAW_BB;
+        const int cw = warp - CONV0, rsub = lane & 7, jsub = lane >> 3;
+        for (int sc = 0; sc < stages; sc++) {
+            const int r = sc % RAWS, s = sc % S;
+            if (!mm_wait(rawfull0 + 8 * r, (uint32_t)(sc / RAWS) & 1u, abort_flag, p.status, wmode)) break;
+            if (sc >= S && !mm_wait(empty0 + 8 * s, (uint32_t)(sc / S - 1) & 1u, abort_flag, p.status, wmode)) break;
+            const uint8_t *raw = smem + G::O_STAGING + (size_t)r * G::RAW_STAGE;
+            uint8_t *stage = ring + (size_t)s * G::STAGE;
+#pragma unroll
+            for (int i4 = 0; i4 < 4; i4++) {
+                const int pair = cw * 4 + i4, rg = pair >> 1, j = (pair & 1) * 4 + jsub, row = rg * 8 + rsub;
+                const uint32_t *w32 = (const uint32_t *)(raw + (size_t)row * G::RAW_ROW) + (j * BB) / 4;
+                const uint32_t shift = (j & 1) ? 32u : 16u;             // an odd block starts two bytes past a word boundary
+                uint32_t w[8], d_bits;
+                if (RFMT == 1) {
+                    uint32_t v[9];
+#pragma unroll
+                    for (int i = 0; i < 9; i++) v[i] = w32[i];
+                    d_bits = (j & 1) ? v[0] >> 16 : v[0] & 0xFFFFu;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) w[i] = __funnelshift_rc(v[i], v[i + 1], shift);
+                } else {
+                    // value i in the low nibble of byte i, value i + 16 in the high nibble, each minus 8 (src/MatMulBlocks.cs:282-299)
+                    uint32_t v[5];
+#pragma unroll
+                    for (int i = 0; i < 5; i++) v[i] = w32[i];
+                    d_bits = (j & 1) ? v[0] >> 16 : v[0] & 0xFFFFu;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const uint32_t nib = __funnelshift_rc(v[i], v[i + 1], shift);
+                        w[i] = __vsub4(nib & 0x0F0F0F0Fu, 0x08080808u);
+                        w[i + 4] = __vsub4((nib >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+                    }
+                }
+                uint8_t *codes = stage + j * G::B_KB + rg * 256 + rsub * 16;
+                *(uint4 *)codes = make_uint4(w[0], w[1], w[2], w[3]);
+                *(uint4 *)(codes + 128) = make_uint4(w[4], w[5], w[6], w[7]);
+                *(uint16_t *)(stage + G::O_BS + row * 16 + j * 2) = (uint16_t)d_bits;
+            }
+            fence_proxy_async();                         // the tensor cores read the stage through the async proxy
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(full0 + 8 * s);
+                mbar_arrive(rawempty0 + 8 * r);          // the raw stage has been read
+            }
+        }
     } else if (RAW && warp >= CONV0) {
         // ---- converters (RAW): the tile's rows of the group, raw, become the stage's codes and scale rows
         constexpr int BB = G::RAW_BB, VECS = GROUP * BB / 16, PITCH = G::RAW_PITCH, CT = CONV_WARPS * 32, PER = (TILE * VECS + CT - 1) / CT;
@@ -1394,7 +1478,7 @@ __global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(co
                     // then multiples of 4), two bytes past one when j is odd; jj has j's parity (half * 4 is even)
                     const uint32_t *w32 = (const uint32_t *)(staging + rl * PITCH) + (j * BB) / 4;
                     uint32_t w[8], d_bits;
-                    if (RAW == 1) {
+                    if (RFMT == 1) {
                         uint32_t r[9];
 #pragma unroll
                         for (int i = 0; i < 9; i++) r[i] = w32[i];
@@ -1733,6 +1817,12 @@ static int g_mm_kind = 0;          // the tensor kind the library packs for and 
 static int g_mm_tcs = 1;           // scale products of plain f16 scales on the tensor cores
 static int g_mm_few = 64;          // most rows of A the kernel with the operands' sides exchanged takes
 static int g_mm_raw_few = 1;       // that kernel re-lays raw weights itself where it can
+static int g_mm_raw_tma = 1;       // ... fetching the raw rows by 2-D TMA tile copies
+// cuTensorMapEncodeTiled, fetched through the runtime (the library does not link the driver); null when it is not there
+typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiled g_encode_tiled = nullptr;
+
 
 template <int BN, int RAW>
 static cudaError_t set_few_attr()
@@ -1768,11 +1858,22 @@ cudaError_t matmul_init(int sm_count, int max_smem, int *status)
     g_mm_few = few && *few ? atoi(few) : 64;
     const char *rawfew = getenv("QB200_MM_RAW_FEW");
     g_mm_raw_few = rawfew && *rawfew ? atoi(rawfew) != 0 : 1;
+    const char *rawtma = getenv("QB200_MM_RAW_TMA");
+    g_mm_raw_tma = rawtma && *rawtma ? atoi(rawtma) != 0 : 1;
 #endif
     cudaError_t e;
     if ((e = set_few_attr<16, 0>()) || (e = set_few_attr<32, 0>()) || (e = set_few_attr<64, 0>())) return e;
     if ((e = set_few_attr<16, 1>()) || (e = set_few_attr<32, 1>())) return e;
     if ((e = set_few_attr<16, 2>()) || (e = set_few_attr<32, 2>())) return e;
+    if ((e = set_few_attr<16, 3>()) || (e = set_few_attr<32, 3>())) return e;
+    if ((e = set_few_attr<16, 4>()) || (e = set_few_attr<32, 4>())) return e;
+    {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) == cudaSuccess && found == cudaDriverEntryPointSuccess)
+            g_encode_tiled = (EncodeTiled)fn;
+        else (void)cudaGetLastError();
+    }
     if ((e = cudaFuncSetAttribute(fewq_kernel<16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<16, false>::SMEM))) return e;
     if ((e = cudaFuncSetAttribute(fewq_kernel<32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<32, false>::SMEM))) return e;
     if ((e = cudaFuncSetAttribute(fewq_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<16, true>::SMEM))) return e;
@@ -1879,7 +1980,7 @@ int matmul_prepack_b(int fmt_b, const void *b, int n, int k, void *packed, cudaS
 }
 
 template <int BN, int RAW>
-static cudaError_t launch_few(int grid, const MatmulArgs &args, cudaStream_t stream)
+static cudaError_t launch_few(int grid, const MatmulArgs &args, const CUtensorMap &bmap, cudaStream_t stream)
 {
     // launched as a programmatic dependent of A's packing: its prologue and its first loads of B run beside it
     cudaLaunchConfig_t cfg = {};
@@ -1888,15 +1989,26 @@ static cudaError_t launch_few(int grid, const MatmulArgs &args, cudaStream_t str
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(few_threads<BN, RAW>()); cfg.dynamicSmemBytes = FewCfg<BN, RAW>::SMEM;
     cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, fewrows_kernel<BN, RAW>, args);
+    return cudaLaunchKernelEx(&cfg, fewrows_kernel<BN, RAW>, args, bmap);
 }
 template <int RAW>
-static cudaError_t launch_few_rows(int bn, int grid, const MatmulArgs &args, cudaStream_t stream)
+static cudaError_t launch_few_rows(int bn, int grid, const MatmulArgs &args, const CUtensorMap &bmap, cudaStream_t stream)
 {
-    if (bn == 16) return launch_few<16, RAW>(grid, args, stream);
-    if (bn == 32) return launch_few<32, RAW>(grid, args, stream);
-    if constexpr (RAW == 0) return launch_few<64, 0>(grid, args, stream);
+    if (bn == 16) return launch_few<16, RAW>(grid, args, bmap, stream);
+    if (bn == 32) return launch_few<32, RAW>(grid, args, bmap, stream);
+    if constexpr (RAW == 0) return launch_few<64, 0>(grid, args, bmap, stream);
     else return cudaErrorInvalidValue;         // raw weights: at most 32 rows of A (the converters' registers)
+}
+
+// A tensor map over B's raw rows as 16-bit elements: tiles of 128 rows x one group of eight blocks; rows past n read as zeros.
+static bool raw_rows_map(CUtensorMap &map, const void *b, int fmt_b, int n, int kbs)
+{
+    if (!g_encode_tiled) return false;
+    const cuuint64_t row_bytes = (cuuint64_t)kbs * block_bytes(fmt_b);
+    const cuuint64_t dims[2] = { row_bytes / 2, (cuuint64_t)n }, strides[1] = { row_bytes };
+    const cuuint32_t box[2] = { (cuuint32_t)(GROUP * block_bytes(fmt_b) / 2), (cuuint32_t)TILE }, estr[2] = { 1, 1 };
+    return g_encode_tiled(&map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(b), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 template <int KIND, bool SUMS, int VAR>
 static void launch_var(int grid, const MatmulArgs &args, cudaStream_t stream)
@@ -2003,8 +2115,12 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     }
     if (few) {
         const int tiles = batch.count * (tb.rows_pad / TILE), grid = tiles < g_mm_sms ? tiles : g_mm_sms;
-        if (raw_few) e = fmt_b == QB200_Q8_0 ? launch_few_rows<1>(bn, grid, args, stream) : launch_few_rows<2>(bn, grid, args, stream);
-        else e = launch_few_rows<0>(bn, grid, args, stream);
+        CUtensorMap bmap;
+        memset(&bmap, 0, sizeof bmap);
+        if (raw_few && g_mm_raw_tma && raw_rows_map(bmap, b, fmt_b, n, kbs))
+            e = fmt_b == QB200_Q8_0 ? launch_few_rows<3>(bn, grid, args, bmap, stream) : launch_few_rows<4>(bn, grid, args, bmap, stream);
+        else if (raw_few) e = fmt_b == QB200_Q8_0 ? launch_few_rows<1>(bn, grid, args, bmap, stream) : launch_few_rows<2>(bn, grid, args, bmap, stream);
+        else e = launch_few_rows<0>(bn, grid, args, bmap, stream);
         return (int)e;
     }
     const long long total = (long long)args.batch * args.mtiles * args.units;
