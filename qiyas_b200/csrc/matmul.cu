@@ -1865,8 +1865,8 @@ cudaError_t matmul_init(int sm_count, int max_smem, int *status)
     if ((e = set_few_attr<16, 0>()) || (e = set_few_attr<32, 0>()) || (e = set_few_attr<64, 0>())) return e;
     if ((e = set_few_attr<16, 1>()) || (e = set_few_attr<32, 1>())) return e;
     if ((e = set_few_attr<16, 2>()) || (e = set_few_attr<32, 2>())) return e;
-    if ((e = set_few_attr<16, 3>()) || (e = set_few_attr<32, 3>())) return e;
-    if ((e = set_few_attr<16, 4>()) || (e = set_few_attr<32, 4>())) return e;
+    if ((e = set_few_attr<16, 3>()) || (e = set_few_attr<32, 3>()) || (e = set_few_attr<64, 3>())) return e;
+    if ((e = set_few_attr<16, 4>()) || (e = set_few_attr<32, 4>()) || (e = set_few_attr<64, 4>())) return e;
     {
         void *fn = nullptr;
         cudaDriverEntryPointQueryResult found;
@@ -1996,8 +1996,8 @@ static cudaError_t launch_few_rows(int bn, int grid, const MatmulArgs &args, con
 {
     if (bn == 16) return launch_few<16, RAW>(grid, args, bmap, stream);
     if (bn == 32) return launch_few<32, RAW>(grid, args, bmap, stream);
-    if constexpr (RAW == 0) return launch_few<64, 0>(grid, args, bmap, stream);
-    else return cudaErrorInvalidValue;         // raw weights: at most 32 rows of A (the converters' registers)
+    if constexpr (RAW == 0 || RAW >= 3) return launch_few<64, RAW>(grid, args, bmap, stream);
+    else return cudaErrorInvalidValue;         // raw weights by the converters' own loads: at most 32 rows of A (their registers)
 }
 
 // A tensor map over B's raw rows as 16-bit elements: tiles of 128 rows x one group of eight blocks; rows past n read as zeros.
@@ -2057,7 +2057,12 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     const int bn = few_bn(m), a_layout = few || fewq ? LAY_FEW : LAY_TILE, lay_b = b_layout(fmt_b);
     const size_t a_slab = a_packed_bytes(m, k, kbs, tcs), b_slab = packed_bytes(lay_b, n, k, kbs, false);
     // ... and on raw weights that come in whole groups of eight blocks, 16-byte aligned, the kernel re-lays B itself
-    const bool raw_few = few && m <= 32 && !b_packed && batch.count == 1 && kbs % GROUP == 0 && ((uintptr_t)b & 15) == 0 && g_mm_raw_few;
+    // (its rows fetched by the TMA unit where a tensor map over them can be made; else by the converters' own loads, at most 32 rows of A)
+    const bool raw_able = few && !b_packed && batch.count == 1 && kbs % GROUP == 0 && ((uintptr_t)b & 15) == 0 && g_mm_raw_few;
+    CUtensorMap bmap;
+    memset(&bmap, 0, sizeof bmap);
+    const bool raw_tma = raw_able && g_mm_raw_tma && raw_rows_map(bmap, b, fmt_b, n, kbs);
+    const bool raw_few = raw_tma || (raw_able && m <= 32);
     const int b_sets = b_packed || raw_few ? 0 : (batch.stride_b ? batch.count : 1);
     const size_t a_raw = raw_bytes(fmt_a, batch.stride_a), b_raw = raw_bytes(fmt_b, batch.stride_b);
     // B first: A's packing is then the launch right before the product, whose start the few-rows kernel overlaps
@@ -2115,9 +2120,7 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     }
     if (few) {
         const int tiles = batch.count * (tb.rows_pad / TILE), grid = tiles < g_mm_sms ? tiles : g_mm_sms;
-        CUtensorMap bmap;
-        memset(&bmap, 0, sizeof bmap);
-        if (raw_few && g_mm_raw_tma && raw_rows_map(bmap, b, fmt_b, n, kbs))
+        if (raw_tma)
             e = fmt_b == QB200_Q8_0 ? launch_few_rows<3>(bn, grid, args, bmap, stream) : launch_few_rows<4>(bn, grid, args, bmap, stream);
         else if (raw_few) e = fmt_b == QB200_Q8_0 ? launch_few_rows<1>(bn, grid, args, bmap, stream) : launch_few_rows<2>(bn, grid, args, bmap, stream);
         else e = launch_few_rows<0>(bn, grid, args, bmap, stream);
