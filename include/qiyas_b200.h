@@ -158,8 +158,9 @@ int qb200_gemv_noalloc_status(int *status);
  *   tensor cores together with the zero terms of the neighbouring k-blocks, which an infinite scale
  *   would turn into NaN (the result is then NaN where the reference gives +-inf or NaN).
  *   With at most 64 rows of A the rows of B take the lanes of tensor memory instead of A's (same bits);
- *   with at most 32, k a multiple of 256 and b on a 16-byte boundary, Q8_0 / Q4_0 weights are not re-laid in
- *   memory at all: the product kernel converts the raw blocks as it streams them (same bits again).
+ *   with k a multiple of 256 and b on a 16-byte boundary as well, Q8_0 / Q4_0 weights are not re-laid in
+ *   memory at all: the product kernel fetches the raw blocks by TMA tile copies and converts them as it
+ *   streams them (same bits again; at most 32 rows of A where the driver offers no tensor-map encoder).
  *   workspace: device scratch of qb200_matmul_workspace_bytes(...) bytes, 256-byte aligned,
  *   private to the call until it completes on `stream` (the operands are re-laid there for
  *   the tensor cores).  Pass NULL/0 to use one scratch buffer the library keeps and grows: calls
