@@ -250,6 +250,14 @@ int qb200_shard_range(int rows, int world, int rank, int *first, int *count);
 int qb200_shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const qb200_shard_peers_t *peers,
                      unsigned int epoch, void *stream);
 int qb200_shard_wait(const qb200_shard_peers_t *peers, unsigned int epoch, long long limit_cycles, void *stream);
+/* The sharded A.B^T.  B's rows are C's columns: rank r keeps rows [first, first + count) of B (qb200_shard_range over
+ * n_total) and computes that column block of the m x n_total C; peers->out[w] is rank w's copy of the whole C
+ * (row-major, m * n_total floats), and the product kernel's epilogue stores the block, row stride n_total, into every
+ * copy (plain peer stores), then raises the flags as qb200_shard_gemv does; qb200_shard_wait completes it in the same way.
+ * b_shard: the rank's rows as raw blocks, or NULL when b_shard_packed (qb200_matmul_prepack of those rows) is given.
+ * workspace: as qb200_matmul_blocks / _prepacked for an m x count x k product.  Lanes only (no sums, no `Back`). */
+int qb200_shard_matmul(int fmt_a, int fmt_b, const void *a, const void *b_shard, const void *b_shard_packed, int m, int n_total, int k,
+                       const qb200_shard_peers_t *peers, unsigned int epoch, void *workspace, size_t workspace_bytes, void *stream);
 /* A chain of sharded products, each reading the whole output of the one before it (the layers of a model): as
  * qb200_shard_gemv, but x is rank `peers->rank`'s copy of the output of the exchange `after`, and the kernel itself waits
  * (bounded by limit_cycles as qb200_shard_wait is; status bit 2 when it runs out) until every rank's word of after's

@@ -50,6 +50,7 @@ SIGNATURES = {
     "qb200_matmul_block_sums": (_I, [_I, _I, _P, _P, _P, _P, _I, _I, _I, _P]),
     "qb200_shard_range": (_I, [_I, _I, _I, C.POINTER(_I), C.POINTER(_I)]),
     "qb200_shard_gemv": (_I, [_I, _I, _P, _P, _I, _I, C.POINTER(ShardPeers), C.c_uint, _P]),
+    "qb200_shard_matmul": (_I, [_I, _I, _P, _P, _P, _I, _I, _I, C.POINTER(ShardPeers), C.c_uint, _P, _Z, _P]),
     "qb200_shard_wait": (_I, [C.POINTER(ShardPeers), C.c_uint, C.c_longlong, _P]),
     "qb200_shard_gemv_after": (_I, [_I, _I, _P, _P, _I, _I, C.POINTER(ShardPeers), C.c_uint, C.POINTER(ShardPeers), C.c_uint, C.c_longlong, _P]),
     "qb200_ipc_export": (_I, [_P, _P]),

@@ -452,6 +452,23 @@ int qb200_shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, i
     return finish(qb::shard_gemv(fmt_a, fmt_x, a_shard, x, rows_total, cols, peers, epoch, nullptr, 0, 0, (cudaStream_t)stream), "shard_gemv");
 }
 
+int qb200_shard_matmul(int fmt_a, int fmt_b, const void *a, const void *b_shard, const void *b_shard_packed, int m, int n_total, int k,
+                       const qb200_shard_peers_t *peers, unsigned int epoch, void *workspace, size_t workspace_bytes, void *stream)
+{
+    int rc = check_peers(peers);
+    if (rc) return rc;
+    int first = 0, count = 0;
+    if ((rc = qb200_shard_range(n_total, peers->world, peers->rank, &first, &count))) return rc;
+    if (count) {
+        // the column block as an ordinary product: formats, whole blocks, limits, alignment
+        const void *b = b_shard_packed ? b_shard_packed : b_shard;
+        if ((rc = check_matmul(fmt_a, fmt_b, a, b, peers->out[peers->rank] + first, m, count, k))) return rc;
+        if ((uintptr_t)b_shard_packed & 255) return fail(QB200_E_WORKSPACE, "the packed operand is 256-byte aligned");
+        if ((rc = take_workspace(workspace, workspace_bytes, qb::matmul_workspace_bytes(fmt_b, m, count, k, ONE, b_shard_packed != nullptr)))) return rc;
+    }
+    return finish(qb::shard_matmul(fmt_a, fmt_b, a, b_shard, b_shard_packed, m, n_total, k, peers, epoch, workspace, (cudaStream_t)stream), "shard_matmul");
+}
+
 int qb200_shard_gemv_after(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const qb200_shard_peers_t *peers,
                            unsigned int epoch, const qb200_shard_peers_t *after, unsigned int after_epoch, long long limit_cycles, void *stream)
 {

@@ -48,6 +48,10 @@ cudaError_t shard_init(int *status);
 int shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const void *peers, unsigned int epoch,
                const void *after, unsigned int after_epoch, long long limit_cycles, cudaStream_t stream);
 int shard_wait(const void *peers, unsigned int epoch, long long limit_cycles, cudaStream_t stream);
+// The sharded A.B^T: rows [first, first + count) of B on this rank give columns [first, first + count) of the m x n_total C,
+// stored into every rank's copy (peers->out[w] = rank w's C).  b_packed: null, or the shard as matmul_prepack_b left it.
+int shard_matmul(int fmt_a, int fmt_b, const void *a, const void *b_shard, const void *b_packed, int m, int n_total, int k, const void *peers,
+                 unsigned int epoch, void *workspace, cudaStream_t stream);
 
 int encode_launch(int fmt, const float *lanes, void *blocks, int64_t n, cudaStream_t stream);
 int decode_launch(int fmt, const void *blocks, float *lanes, int64_t n, cudaStream_t stream);
@@ -62,8 +66,11 @@ size_t matmul_workspace_bytes(int fmt_b, int m, int n, int k, const MatmulBatch 
 size_t matmul_prepacked_bytes(int fmt_b, int n, int k);
 int matmul_prepack_b(int fmt_b, const void *b, int n, int k, void *packed, cudaStream_t stream);
 // b_packed: null, or B as matmul_prepack_b left it (then `b` is not read); c_blocks: null, or C again as blocks of fmt_c
+// ldc: values from a row of C to the next (0: n); publish (optional, one product, lanes only) = a GemvPublish whose out[w]
+// is where this call's C starts in rank w's copy of a wider matrix of the same ldc: the launch stores C there as well
 int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void *b_packed, float *c, int32_t *sums, int fmt_c,
-                  void *c_blocks, int m, int n, int k, const MatmulBatch &batch, void *workspace, cudaStream_t stream);
+                  void *c_blocks, int m, int n, int k, const MatmulBatch &batch, void *workspace, cudaStream_t stream, int ldc = 0,
+                  const void *publish = nullptr);
 
 // clock cycles a tcgen05.mma kind::i8 (M 128, N 128, K 32) takes on one multiprocessor, measured now
 int matmul_mma_rate(double *cycles_per_mma, cudaStream_t stream);

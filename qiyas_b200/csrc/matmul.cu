@@ -105,6 +105,12 @@ struct PackedB {             // LAY_KBLOCK (codes, scales, extra) or LAY_GROUPED
     int groups;              // LAY_GROUPED: groups of eight k-blocks a tile
 };
 
+// (tuning builds compile the sharded product's exchange out with -DMM_PUBLISH=0)
+#ifndef MM_PUBLISH
+#define MM_PUBLISH 1
+#endif
+#define MM_WORLD(p) (MM_PUBLISH ? (p).pub.world : 0)
+
 struct MatmulArgs {
     PackedA a;
     PackedB b;
@@ -120,6 +126,8 @@ struct MatmulArgs {
     int probe;               // tuning build only (see MM_PROBE)
     long long *trace;        // tuning build only: clock stamps of block 0
     const uint8_t *b_raw;    // few rows of A on raw weights: B's rows as the caller holds them (k in whole groups of eight blocks, 16-byte aligned)
+    int ldc;                 // values from a row of C to the next (n, unless C is a column block of a wider matrix: the sharded product)
+    GemvPublish pub;         // the sharded product's exchange: where C's column block goes besides c (world 0: nowhere), and the flags
     int batch;               // products: operand sets a_stride / b_stride bytes apart in their packed form (0: the same for all), results c_stride values apart
     size_t a_stride, b_stride, c_stride;
 };
@@ -503,6 +511,35 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // Nothing is emitted: the registers pass through the statement, so that what uses them stays below the wait before it.
+// The sharded product's exchange.  Every block stores its part of C into the other GPUs' copies beside its own (plain
+// stores through peer-mapped pointers); at its end, after the barrier that makes the block's stores thread 0's to order,
+// thread 0 fences and counts the block in, and the block that counts last fences at system scope and raises this rank's
+// flag in every rank's flag array.  When a bounded wait gave up in any block the flags are not raised: they then never
+// show this epoch and the readers' own bounded waits report it.
+__device__ __forceinline__ bool peers_aligned(const GemvPublish &pub)
+{
+    uintptr_t bits = 0;
+    for (int w = 0; w < pub.world; w++) bits |= (uintptr_t)pub.out[w];
+    return (bits & 15) == 0;
+}
+__device__ __noinline__ void publish_count(const GemvPublish &pub, bool ok)
+{
+    // (a block that gave up counts all the same, with a mark in the upper half of the word, so that the counter returns to
+    // zero for the next call)
+    __threadfence();
+    const unsigned int before = atomicAdd(pub.counter, ok ? 1u : 0x10001u);
+    if ((before & 0xffffu) != gridDim.x - 1) return;
+    *pub.counter = 0u;
+    if (!ok || (before >> 16)) return;
+    __threadfence_system();
+    // epoch 0: the call's number is counted on the device (a captured graph replays the same arguments)
+    const unsigned int epoch = pub.epoch ? pub.epoch : atomicAdd(pub.epoch_counter, 1u) + 1u;
+    for (int w = 0; w < pub.world; w++) {
+        unsigned int *f = pub.flag[w];
+        if (f) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+    }
+}
+
 __device__ __forceinline__ void pin16(uint32_t *v)
 {
     asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
@@ -684,9 +721,11 @@ struct Pieces {
 // MINS: the same with Q4_K's min term; HALF: Q6_K's k-blocks of 16 values; TCS: scale products from the tensor cores.
 enum { VAR_PLAIN = 0, VAR_MINS = 1, VAR_HALF = 2, VAR_TCS = 3 };
 
-template <int KIND, bool SUMS, int VAR>
-__global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(const MatmulArgs p)
+template <int KIND, int OUT, int VAR>
+__global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(const __grid_constant__ MatmulArgs p)
 {
+    // OUT: 0 lanes, 1 lanes and the blocks' integer sums, 2 lanes into the other GPUs' copies of C as well (the sharded product)
+    constexpr bool SUMS = OUT == 1, PUB = OUT == 2;
     constexpr bool MINS = VAR == VAR_MINS, HALF = VAR == VAR_HALF, TCS = VAR == VAR_TCS;
     using G = Cfg<KIND, MINS, HALF, TCS>;
     constexpr int EW = epi_warps(TCS), MMA2_WARP = 2 + EW, EC = 128 / (EW / 4);      // epilogue warps, the second issuer's warp, columns a warp
@@ -1012,9 +1051,14 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(c
             tmem_ld_wait();
             const long long s0 = MM_CLOCK();
             if (alive && active && row < p.m) {
-                const bool vec = (p.n & 3) == 0 && ((uintptr_t)c_out & 15) == 0;
+                const bool vec = (p.ldc & 3) == 0 && ((uintptr_t)c_out & 15) == 0 && (!PUB || peers_aligned(p.pub));
                 const int col0 = n0 + g * EC, col_end = min(p.n, n0 + w * p.unit);        // (a warp of 64 columns may reach past the piece)
-                float *out = c_out + (size_t)row * p.n + col0;
+                const size_t at = (size_t)row * p.ldc + col0;
+                // (the sharded product: the same values into the other GPUs' copies of C as well, by plain peer stores)
+                for (int pw = -1; pw < (PUB ? MM_WORLD(p) : 0); pw++) {
+                float *dst = pw < 0 ? c_out : p.pub.out[pw];
+                if (!dst) continue;
+                float *out = dst + at;
 #pragma unroll
                 for (int c4 = 0; c4 < EC / 4; c4++) {
                     float f[4];
@@ -1031,6 +1075,7 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(c
                         for (int c = 0; c < 4; c++) if (col0 + 4 * c4 + c < col_end) out[4 * c4 + c] = f[c];
                     }
                 }
+                }
             }
             t_store += MM_CLOCK() - s0;
             if (p.cb) {
@@ -1043,7 +1088,7 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(c
                 const int rows_here = min(TILE, p.m - mt * TILE);
                 for (int idx = tid; idx < rows_here * bw; idx += EW * 32) {
                     const int rr = idx / bw, bc = idx - rr * bw;
-                    const size_t first = bi * p.c_stride + (size_t)(mt * TILE + rr) * p.n + n0 + bc * 32;      // c_stride is whole blocks
+                    const size_t first = bi * p.c_stride + (size_t)(mt * TILE + rr) * p.n + n0 + bc * 32;      // c_stride is whole blocks (ldc = n with `Back`)
                     float f[32];
 #pragma unroll
                     for (int c = 0; c < 8; c++) {
@@ -1060,6 +1105,7 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(c
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, 512);
+    if (PUB && MM_WORLD(p) > 0 && threadIdx.x == 0) publish_count(p.pub, !*abort_flag);
 }
 
 // ---------------------------------------------------------------------------------- few rows of A: the operands change sides
@@ -1126,7 +1172,7 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N])
 }
 
 template <int BN, int RAW>
-__global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(const MatmulArgs p, const __grid_constant__ CUtensorMap bmap)
+__global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(const __grid_constant__ MatmulArgs p, const __grid_constant__ CUtensorMap bmap)
 {
     using G = FewCfg<BN, RAW>;
     constexpr bool TMA = G::TMA;
@@ -1347,7 +1393,13 @@ __global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(co
             float *c_out = p.c + bi * p.c_stride;
             if (alive && col < p.n) {
 #pragma unroll
-                for (int r = 0; r < CW; r++) if (cg * CW + r < p.m) c_out[(size_t)(cg * CW + r) * p.n + col] = acc[r];
+                for (int r = 0; r < CW; r++) if (cg * CW + r < p.m) c_out[(size_t)(cg * CW + r) * p.ldc + col] = acc[r];
+                for (int pw = 0; pw < MM_WORLD(p); pw++) {          // the sharded product: into the other GPUs' copies of C
+                    float *peer = p.pub.out[pw];
+                    if (!peer) continue;
+#pragma unroll
+                    for (int r = 0; r < CW; r++) if (cg * CW + r < p.m) peer[(size_t)(cg * CW + r) * p.ldc + col] = acc[r];
+                }
             }
             if (p.cb) {
                 // `Back` for the tile: once the epilogue warps have stored their lanes, their threads encode the tile's blocks of
@@ -1532,6 +1584,7 @@ __global__ void __launch_bounds__((few_threads<BN, RAW>()), 1) fewrows_kernel(co
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, 512);
+    if (MM_WORLD(p) > 0 && threadIdx.x == 0) publish_count(p.pub, !*abort_flag);
 }
 
 // ---------------------------------------------------------------------------------- few rows of A against Q4_K weights
@@ -1566,7 +1619,7 @@ struct FewQCfg {
 template <int BN> __host__ __device__ constexpr int fewq_threads() { return 32 * (4 + 4 * (BN / 16)); }
 
 template <int BN, bool HALFQ>
-__global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const MatmulArgs p)
+__global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const __grid_constant__ MatmulArgs p)
 {
     using G = FewQCfg<BN, HALFQ>;
     constexpr int S = G::S, KS = G::KS, BATCH = G::BATCH, NB = G::NB, BPS = KS / BATCH, CG = BN / 16, CW = 16;
@@ -1738,13 +1791,20 @@ __global__ void __launch_bounds__(fewq_threads<BN>(), 1) fewq_kernel(const Matmu
             float *c_out = p.c + bi * p.c_stride;
             if (alive && col < p.n) {
 #pragma unroll
-                for (int r = 0; r < CW; r++) if (cg * CW + r < p.m) c_out[(size_t)(cg * CW + r) * p.n + col] = acc[r];
+                for (int r = 0; r < CW; r++) if (cg * CW + r < p.m) c_out[(size_t)(cg * CW + r) * p.ldc + col] = acc[r];
+                for (int pw = 0; pw < MM_WORLD(p); pw++) {          // the sharded product: into the other GPUs' copies of C
+                    float *peer = p.pub.out[pw];
+                    if (!peer) continue;
+#pragma unroll
+                    for (int r = 0; r < CW; r++) if (cg * CW + r < p.m) peer[(size_t)(cg * CW + r) * p.ldc + col] = acc[r];
+                }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, 512);
+    if (MM_WORLD(p) > 0 && threadIdx.x == 0) publish_count(p.pub, !*abort_flag);
 }
 
 // ---------------------------------------------------------------------------------- the tensor pipe's own rate
@@ -1830,13 +1890,13 @@ static cudaError_t set_few_attr()
     return cudaFuncSetAttribute(fewrows_kernel<BN, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewCfg<BN, RAW>::SMEM);
 }
 
-template <int KIND, bool SUMS, int VAR>
+template <int KIND, int SUMS, int VAR>
 static cudaError_t set_mm_attr_var()
 {
     return cudaFuncSetAttribute(matmul_kernel<KIND, SUMS, VAR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)Cfg<KIND, VAR == VAR_MINS, VAR == VAR_HALF, VAR == VAR_TCS>::SMEM);
 }
-template <int KIND, bool SUMS>
+template <int KIND, int SUMS>
 static cudaError_t set_mm_attr()
 {
     cudaError_t e;
@@ -1880,8 +1940,8 @@ cudaError_t matmul_init(int sm_count, int max_smem, int *status)
     if ((e = cudaFuncSetAttribute(fewq_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<32, true>::SMEM))) return e;
     if ((e = cudaFuncSetAttribute(fewq_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<64, false>::SMEM))) return e;
     if ((e = cudaFuncSetAttribute(fewq_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FewQCfg<64, true>::SMEM))) return e;
-    if ((e = set_mm_attr<0, false>()) || (e = set_mm_attr<0, true>())) return e;
-    if ((e = set_mm_attr<1, false>()) || (e = set_mm_attr<1, true>())) return e;
+    if ((e = set_mm_attr<0, 0>()) || (e = set_mm_attr<0, 1>()) || (e = set_mm_attr<0, 2>())) return e;
+    if ((e = set_mm_attr<1, 0>()) || (e = set_mm_attr<1, 1>())) return e;
     return cudaSuccess;
 }
 
@@ -2010,7 +2070,7 @@ static bool raw_rows_map(CUtensorMap &map, const void *b, int fmt_b, int n, int 
     return g_encode_tiled(&map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(b), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
-template <int KIND, bool SUMS, int VAR>
+template <int KIND, int SUMS, int VAR>
 static void launch_var(int grid, const MatmulArgs &args, cudaStream_t stream)
 {
     // a programmatic dependent of A's packing (the launch before it): its prologue runs beside that kernel, its producer
@@ -2024,7 +2084,7 @@ static void launch_var(int grid, const MatmulArgs &args, cudaStream_t stream)
     cudaLaunchKernelEx(&cfg, matmul_kernel<KIND, SUMS, VAR>, args);
 }
 
-template <int KIND, bool SUMS>
+template <int KIND, int SUMS>
 static void launch_product(int var, int grid, const MatmulArgs &args, cudaStream_t stream)
 {
     if (var == VAR_MINS) launch_var<KIND, SUMS, VAR_MINS>(grid, args, stream);
@@ -2036,15 +2096,16 @@ static void launch_product(int var, int grid, const MatmulArgs &args, cudaStream
 template <int KIND>
 static void launch_kind(bool sums, int var, int grid, const MatmulArgs &args, cudaStream_t stream)
 {
-    if (sums) launch_product<KIND, true>(var, grid, args, stream);
-    else launch_product<KIND, false>(var, grid, args, stream);
+    if (sums) launch_product<KIND, 1>(var, grid, args, stream);
+    else launch_product<KIND, 0>(var, grid, args, stream);
 }
 
 // fmt_a: Q8_0 / Q4_0; fmt_b: Q8_0 / Q4_0 / Q4_K / Q6_K (k then in whole super-blocks of 256).  `b_packed`: B as
 // matmul_prepack_b left it, or null to pack `b` into the workspace now.  `c_blocks`: optional `Back` of C as fmt_c.
 int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void *b_packed, float *c, int32_t *sums, int fmt_c,
-                  void *c_blocks, int m, int n, int k, const MatmulBatch &batch, void *workspace, cudaStream_t stream)
+                  void *c_blocks, int m, int n, int k, const MatmulBatch &batch, void *workspace, cudaStream_t stream, int ldc, const void *publish)
 {
+    if (publish && (sums || c_blocks || batch.count != 1)) return QB200_E_SHAPE;
     const bool mins = fmt_b == QB200_Q4_K, half = fmt_b == QB200_Q6_K;
     const int kbs = k_blocks(fmt_b, k);
     cudaError_t e;
@@ -2085,6 +2146,9 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     args.c = c; args.sums = sums; args.status = g_mm_status;
     args.cb = (uint8_t *)c_blocks; args.fmt_c = fmt_c;
     args.m = m; args.n = n; args.kb = kbs;
+    args.ldc = ldc > 0 ? ldc : n;
+    if (publish) args.pub = *(const GemvPublish *)publish;
+    else memset(&args.pub, 0, sizeof args.pub);
     args.probe = 0;
     args.trace = nullptr;
 #ifdef QB_MM_TUNING
@@ -2129,7 +2193,8 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     const long long total = (long long)args.batch * args.mtiles * args.units;
     const int grid = (int)(total < g_mm_sms ? total : g_mm_sms);
     const int var = mins ? VAR_MINS : half ? VAR_HALF : tcs ? VAR_TCS : VAR_PLAIN;
-    if (g_mm_kind) launch_kind<1>(sums != nullptr, var, grid, args, stream);
+    if (publish) launch_product<0, 2>(var, grid, args, stream);       // (the exchange: integer sums on the tensor cores only)
+    else if (g_mm_kind) launch_kind<1>(sums != nullptr, var, grid, args, stream);
     else launch_kind<0>(sums != nullptr, var, grid, args, stream);
     return (int)cudaGetLastError();
 }

@@ -100,6 +100,34 @@ int shard_gemv(int fmt_a, int fmt_x, const void *a_shard, const void *x, int row
     return gemv_launch(fmt_a, fmt_x, a_shard, x, peers->out[peers->rank] + first, nullptr, 0, nullptr, count, cols, stream, &pub);
 }
 
+// The sharded A.B^T.  C's columns are B's rows, so rank r computes the column block [first, first + count) of the m x
+// n_total C and the product kernel's epilogue stores it, row stride n_total, into every rank's copy of C; the flags and
+// the wait are the gemv's.
+int shard_matmul(int fmt_a, int fmt_b, const void *a, const void *b_shard, const void *b_packed, int m, int n_total, int k, const void *peers_v,
+                 unsigned int epoch, void *workspace, cudaStream_t stream)
+{
+    const qb200_shard_peers_t *peers = (const qb200_shard_peers_t *)peers_v;
+    int first = 0, count = 0;
+    qb200_shard_range(n_total, peers->world, peers->rank, &first, &count);
+    GemvPublish pub;
+    memset(&pub, 0, sizeof pub);
+    pub.world = peers->world;
+    pub.epoch = epoch;
+    pub.counter = g_publish_counter_ptr;
+    pub.epoch_counter = peers->flags[peers->rank] + QB200_SHARD_MAX;
+    for (int w = 0; w < peers->world; w++) {
+        pub.out[w] = w == peers->rank ? nullptr : peers->out[w] + first;
+        pub.flag[w] = peers->flags[w] + peers->rank;
+    }
+    if (count == 0) {
+        shard_flag_kernel<<<1, 32, 0, stream>>>(pub);
+        return (int)cudaGetLastError();
+    }
+    const MatmulBatch one = {1, 0, 0, 0};
+    return matmul_launch(fmt_a, fmt_b, a, b_shard, b_packed, peers->out[peers->rank] + first, nullptr, 0, nullptr, m, count, k, one, workspace, stream,
+                         n_total, &pub);
+}
+
 int shard_wait(const void *peers_v, unsigned int epoch, long long limit_cycles, cudaStream_t stream)
 {
     const qb200_shard_peers_t *peers = (const qb200_shard_peers_t *)peers_v;

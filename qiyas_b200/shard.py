@@ -228,3 +228,23 @@ def _exchange(self, x, exchange, fmt_x=None, stream=None, limit_cycles=0, after=
 
 
 ShardedGemv.exchange = _exchange
+
+
+def _exchange_columns(self, fmt_a, a, m, exchange, b_packed=None, stream=None, limit_cycles=0, wait=True):
+    """This rank's column block into every rank's copy of C (stores from inside the product kernel's epilogue), then the
+    bounded wait for the peers' blocks: after it, work on `stream` sees the whole m x n C in `exchange.y()`
+    (`exchange` = a PeerExchange over m * n values).  `b_packed`: the shard as `Prepack` left it, instead of the raw rows."""
+    import ctypes as C
+
+    from .ops import _ptr, _stream
+    exchange.epoch += 1
+    rc = self.ops.lib.qb200_shard_matmul(fmt_id(fmt_a), self.fmt_b, _ptr(a), None if b_packed is not None else _ptr(self.b),
+                                         None if b_packed is None else _ptr(b_packed), int(m), self.plan.rows, self.k, C.byref(exchange.peers),
+                                         exchange.epoch, None, 0, _stream(stream))
+    self.ops.gpu.check(rc, "shard_matmul")
+    if wait:
+        self.ops.gpu.check(self.ops.lib.qb200_shard_wait(C.byref(exchange.peers), exchange.epoch, int(limit_cycles), _stream(stream)), "shard_wait")
+    return exchange.y().view(int(m), self.plan.rows)
+
+
+ShardedMatMul.exchange = _exchange_columns

@@ -76,6 +76,19 @@ def _worker(rank, world, port, rows, cols, m, out):
                 dist.barrier()
                 ea.close()
                 eb.close()
+        # the same C by the exchange inside the product kernel's epilogue, twice (m rows, then fewer: another kernel)
+        ec = PeerExchange(ops, m * rows, rank, world)
+        try:
+            for epoch, rows_a in enumerate((m, 5)):
+                got = mm.exchange(B.Q8_0, a, rows_a, ec)
+                torch.cuda.synchronize()
+                assert ops.gpu.status() == 0
+                np.save(f"{out}.cx{epoch}.r{rank}.npy", got.reshape(-1)[:rows_a * rows].cpu().numpy())
+                dist.barrier()
+        finally:
+            torch.cuda.synchronize()
+            dist.barrier()
+            ec.close()
         if rank == 0:
             np.save(out + ".y.npy", y.cpu().numpy())
             np.save(out + ".c.npy", c.cpu().numpy())
@@ -109,6 +122,10 @@ def test_two_ranks_equal_unsharded(oracle, tmp_path, rows, cols):
     a = oracle.encode(B.Q8_0, B.make_activations(m * cols, 7))
     want_c = oracle.matmul_blocks(B.Q8_0, B.Q4_0, a, w, m, rows, cols, order=1)
     assert np.array_equal(np.load(out + ".c.npy").view(np.uint32), want_c.view(np.uint32))
+    for epoch, rows_a in enumerate((m, 5)):
+        for rank in range(world):
+            got = np.load(f"{out}.cx{epoch}.r{rank}.npy")
+            assert np.array_equal(got.view(np.uint32), want_c[:rows_a].reshape(-1).view(np.uint32)), (epoch, rank)
     for epoch in range(3):
         want = oracle.gemv_blocks(B.Q4_0, B.F32, w, B.make_activations(cols, 60 + epoch), rows, cols, order=1)
         for rank in range(world):
@@ -167,6 +184,49 @@ def test_exchange_kernels_on_one_gpu(oracle, rows, world, counted):
             got = ys[r].cpu().numpy()
             assert np.max(np.abs(got[:rows] - want)) <= 1e-5 * np.abs(want).max(), (epoch, r)
             assert np.isnan(got[rows:]).all()                       # nothing stored past the vector
+            assert (flags[r].cpu().numpy()[:world] == epoch).all()
+
+
+@pytest.mark.parametrize("m,n,k,world,fmt_b,prepacked", [(37, 300, 512, 2, B.Q8_0, False), (130, 517, 256, 4, B.Q8_0, False),
+                                                         (200, 256, 320, 2, B.Q4_0, True), (8, 1000, 256, 2, B.Q4_K, False),
+                                                         (64, 640, 256, 3, B.Q4_0, True), (5, 3, 64, 8, B.Q8_0, False)])
+def test_product_exchange_kernels_on_one_gpu(oracle, m, n, k, world, fmt_b, prepacked):
+    # the sharded A.B^T: every rank's product in turn on the one GPU, each storing its column block into every rank's copy
+    # of C (each copy with its own flags); then every rank's wait.  Bit for bit the unsharded oracle product in every copy.
+    import ctypes as C
+    import torch
+
+    from . import helpers as H
+    from qiyas_b200.shard import ShardPlan
+    o = H.ops()
+    b = B.make_weights(fmt_b, n, k, 25)
+    a_raw = oracle.encode(B.Q8_0, B.make_activations(m * k, 26))
+    a = H.dev(a_raw)
+    plan = ShardPlan(n, world)
+    shards = [H.dev(plan.slice_weights(r, fmt_b, k, b)) if plan.count(r) else None for r in range(world)]
+    packed = [o.Prepack(fmt_b, s, plan.count(r), k) if prepacked and s is not None else None for r, s in enumerate(shards)]
+    cs = [torch.full((m * n + 8,), float("nan"), dtype=torch.float32, device="cuda:0") for _ in range(world)]
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda:0") for _ in range(world)]
+    if fmt_b == B.Q4_K:
+        want = oracle.matmul_q4_k(B.Q8_0, a_raw, b, m, n, k).reshape(-1)
+    else:
+        want = oracle.matmul_blocks(B.Q8_0, fmt_b, a_raw, b, m, n, k, order=1).reshape(-1)
+    for epoch in (1, 2):
+        for c in cs:
+            c.fill_(float("nan"))
+        for r in range(world):
+            p = _peers(o.lib, world, r, cs, flags)
+            raw = shards[r].data_ptr() if shards[r] is not None and packed[r] is None else None
+            pk = packed[r].data_ptr() if packed[r] is not None else None
+            assert o.lib.qb200_shard_matmul(B.Q8_0, fmt_b, a.data_ptr(), raw, pk, m, n, k, C.byref(p), epoch, None, 0, None) == 0, o.gpu.error()
+        for r in range(world):
+            p = _peers(o.lib, world, r, cs, flags)
+            assert o.lib.qb200_shard_wait(C.byref(p), epoch, 0, None) == 0
+        assert o.gpu.status() == 0
+        for r in range(world):
+            got = cs[r].cpu().numpy()
+            assert np.array_equal(got[:m * n].view(np.uint32), want.view(np.uint32)), (epoch, r)
+            assert np.isnan(got[m * n:]).all()                      # nothing stored past the matrix
             assert (flags[r].cpu().numpy()[:world] == epoch).all()
 
 
