@@ -17,7 +17,9 @@ fastest and slowest step.
 Beside the headline the JSON line carries: `local` (the same sharded product without the exchange) and, at N > 1,
 `with_allgather` (slices joined by NCCL instead); `c2` (BASELINE configs[1], Q4_0 8192 x 8192, every rank its own
 matrices: calls independent of one another and calls chained through y); `configs` (the other gemv configurations, N = 1);
-`abt` (the Q8_0 x Q8_0 A.B^T of configs[2] and the Q4_0-weight product of configs[4], N = 1); `e2e` (the headline product
+`abt` (the Q8_0 x Q8_0 A.B^T of configs[2] and the Q4_0-weight product of configs[4], N = 1); `abt_sharded` (N > 1: the
+configs[4] A.B^T with B's rows over the ranks: column blocks alone, with the exchange inside the product kernel, with an NCCL
+all-gather); `e2e` (the headline product
 through the host-buffer C-ABI call: pinned host operands, H2D + kernel + D2H every call); `roofline`; `cpu_baseline` (the C
 restatement of the reference's CPU gemv on this machine's host cores).  `--impl reference` times only that CPU
 restatement (the reference itself is C#/.NET and cannot run here).
@@ -321,6 +323,58 @@ def abt_record(ops, torch, timer, fmt_b, m, n, k, peak_measured):
             "frac_of_measured_mma_rate": ops_count / pre / 1e12 / peak_measured if peak_measured else None}
 
 
+def abt_sharded_record(ops, torch, dist, timer, plan, rank, world, dev, shard, m):
+    """The sharded A.B^T of the headline matrix at N > 1: rank r's rows of B give its column block of C.  Timed three ways
+    (host-launched calls between events, barrier on both sides, max over ranks): the column block alone; with the exchange
+    inside the product kernel (every rank ends with the whole C); and joined by an NCCL all-gather instead."""
+    from qiyas_b200.shard import PeerExchange, ShardedMatMul, all_gather_columns
+    n_local = plan.count(rank)
+    a = torch.from_numpy(B.make_weights(B.Q8_0, m, K5, 4100 + m)).to(dev)
+    mm = ShardedMatMul(ops, plan, rank, FMT_A, K5, shard)
+    packed = ops.Prepack(FMT_A, shard, n_local, K5)
+    c_slice = torch.empty(m * max(n_local, 1), dtype=torch.float32, device=dev)
+    ex = PeerExchange(ops, m * N5, rank, world)
+    try:
+        def local():
+            ops.MatMulBlocksPrepacked(B.Q8_0, a, packed, c_slice, m, n_local, K5, fmt_b=FMT_A)
+
+        def fused():
+            return mm.exchange(B.Q8_0, a, m, ex, b_packed=packed)
+
+        def gathered():
+            local()
+            return all_gather_columns(plan, rank, c_slice, m)
+        whole = fused()
+        joined = gathered()
+        torch.cuda.synchronize()
+        if ops.gpu.status() != 0 or not torch.equal(whole.view(torch.int32), joined.view(torch.int32)):
+            raise SystemExit(f"sharded A.B^T check failed on rank {rank}: C after the exchange differs from the gathered column blocks")
+        rec = {"shape": f"Q8_0 x {B.NAMES[FMT_A]}  M {m} N {N5} K {K5}, B's rows over {world} ranks (weights prepacked)"}
+        for name, fn, reps in (("local", local, 20), ("with_exchange", fused, 20), ("with_allgather", gathered, 10)):
+            for _ in range(3):
+                fn()
+            timer.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            timer.barrier()
+            t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item()) * 1e3 / reps
+            rec[name] = {"us": us, "int8_TOPS": 2.0 * m * N5 * K5 / us / 1e6}
+        if ops.gpu.status() != 0:
+            raise SystemExit("a kernel gave up on a bounded wait: the timing is void")
+        rec["exchange"] = "peer stores from the product kernel's epilogue + flags + bounded wait"
+        rec["c_bytes_stored_to_each_peer"] = m * n_local * 4
+        return rec
+    finally:
+        torch.cuda.synchronize()
+        dist.barrier()
+        ex.close()
+
+
 def abt_cpu_baseline(seconds=8.0):
     """The reference's CPU tile product (src/MatMulBlocks.cs:28-36, 84-169) as restated in oracle/, on a reduced configs[2]."""
     from oracle import qiyas_oracle as O
@@ -537,6 +591,10 @@ def main():
             if not args.no_cpu:
                 abt["cpu_baseline"] = abt_cpu_baseline()
 
+    abt_sharded = None
+    if world > 1 and not args.no_extra:
+        abt_sharded = [abt_sharded_record(ops, torch, dist, timer, plan, rank, world, dev, shards[0], m) for m in (512, 2048)]
+
     if rank != 0:
         exchange.close()
         if world > 1:
@@ -571,6 +629,8 @@ def main():
         line["configs"] = configs
     if abt is not None:
         line["abt"] = abt
+    if abt_sharded is not None:
+        line["abt_sharded"] = abt_sharded
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"], _ = cpu_gemv(10.0, layers)
     print(json.dumps(line), flush=True)

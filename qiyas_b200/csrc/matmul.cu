@@ -1051,14 +1051,10 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(c
             tmem_ld_wait();
             const long long s0 = MM_CLOCK();
             if (alive && active && row < p.m) {
-                const bool vec = (p.ldc & 3) == 0 && ((uintptr_t)c_out & 15) == 0 && (!PUB || peers_aligned(p.pub));
+                const bool vec = (p.ldc & 3) == 0 && ((uintptr_t)c_out & 15) == 0;
                 const int col0 = n0 + g * EC, col_end = min(p.n, n0 + w * p.unit);        // (a warp of 64 columns may reach past the piece)
                 const size_t at = (size_t)row * p.ldc + col0;
-                // (the sharded product: the same values into the other GPUs' copies of C as well, by plain peer stores)
-                for (int pw = -1; pw < (PUB ? MM_WORLD(p) : 0); pw++) {
-                float *dst = pw < 0 ? c_out : p.pub.out[pw];
-                if (!dst) continue;
-                float *out = dst + at;
+                float *out = c_out + at;
 #pragma unroll
                 for (int c4 = 0; c4 < EC / 4; c4++) {
                     float f[4];
@@ -1075,9 +1071,39 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(c
                         for (int c = 0; c < 4; c++) if (col0 + 4 * c4 + c < col_end) out[4 * c4 + c] = f[c];
                     }
                 }
-                }
             }
             t_store += MM_CLOCK() - s0;
+            if (PUB && MM_WORLD(p) > 0) {
+                // The sharded product: once every epilogue warp has stored its lanes into this GPU's C, the epilogue threads
+                // re-read the piece row by row (it is still in the L2) and store it into the other GPUs' copies of C, a warp a
+                // row's 512 contiguous bytes: peer stores of whole lines, where the lane-a-row stores above would cross
+                // NVLink as 16-byte fragments.  (The barrier also tells every thread whether all of them are still going.)
+                if (!named_bar_and(2, EW * 32, alive && !*abort_flag)) { alive = false; break; }
+                const int tid = threadIdx.x - 64, rows_here = min(TILE, p.m - mt * TILE), wcols = min(p.n, n0 + w * p.unit) - n0;
+                const float *own = c_out + (size_t)(mt * TILE) * p.ldc + n0;
+                if ((p.ldc & 3) == 0 && ((uintptr_t)c_out & 15) == 0 && peers_aligned(p.pub) && (wcols & 3) == 0) {
+                    const int v4 = wcols >> 2;
+                    for (int idx = tid; idx < rows_here * v4; idx += EW * 32) {
+                        const int rr = idx / v4, c = idx - rr * v4;
+                        const size_t off = (size_t)rr * p.ldc + 4 * c;
+                        const float4 x = __ldcg((const float4 *)(own + off));
+                        for (int pw = 0; pw < p.pub.world; pw++) {
+                            float *peer = p.pub.out[pw];
+                            if (peer) *(float4 *)(peer + (own - c_out) + off) = x;
+                        }
+                    }
+                } else {
+                    for (int idx = tid; idx < rows_here * wcols; idx += EW * 32) {
+                        const int rr = idx / wcols, c = idx - rr * wcols;
+                        const size_t off = (size_t)rr * p.ldc + c;
+                        const float x = __ldcg(own + off);
+                        for (int pw = 0; pw < p.pub.world; pw++) {
+                            float *peer = p.pub.out[pw];
+                            if (peer) peer[(own - c_out) + off] = x;
+                        }
+                    }
+                }
+            }
             if (p.cb) {
                 // `Back` for the piece (src/MatMulBlocks.cs:421 -> Ptx.LanesToBlock): once every epilogue warp has stored its
                 // lanes, the epilogue threads encode the piece's blocks of 32 consecutive values (n % 32 == 0, unit 32: a block

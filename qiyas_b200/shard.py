@@ -244,7 +244,7 @@ def _exchange_columns(self, fmt_a, a, m, exchange, b_packed=None, stream=None, l
     self.ops.gpu.check(rc, "shard_matmul")
     if wait:
         self.ops.gpu.check(self.ops.lib.qb200_shard_wait(C.byref(exchange.peers), exchange.epoch, int(limit_cycles), _stream(stream)), "shard_wait")
-    return exchange.y().view(int(m), self.plan.rows)
+    return exchange.y()[:int(m) * self.plan.rows].view(int(m), self.plan.rows)
 
 
 ShardedMatMul.exchange = _exchange_columns

@@ -77,10 +77,12 @@ def _worker(rank, world, port, rows, cols, m, out):
                 ea.close()
                 eb.close()
         # the same C by the exchange inside the product kernel's epilogue, twice (m rows, then fewer: another kernel)
-        ec = PeerExchange(ops, m * rows, rank, world)
+        # (a third time with more than 64 rows: the 128-row-tile kernel)
+        a_tall = torch.from_numpy(O.encode(B.Q8_0, B.make_activations(M_TALL * cols, 8))).to(dev)
+        ec = PeerExchange(ops, M_TALL * rows, rank, world)
         try:
-            for epoch, rows_a in enumerate((m, 5)):
-                got = mm.exchange(B.Q8_0, a, rows_a, ec)
+            for epoch, rows_a in enumerate((m, 5, M_TALL)):
+                got = mm.exchange(B.Q8_0, a_tall if rows_a == M_TALL else a, rows_a, ec)
                 torch.cuda.synchronize()
                 assert ops.gpu.status() == 0
                 np.save(f"{out}.cx{epoch}.r{rank}.npy", got.reshape(-1)[:rows_a * rows].cpu().numpy())
@@ -97,6 +99,7 @@ def _worker(rank, world, port, rows, cols, m, out):
 
 
 CHAIN = 4
+M_TALL = 130
 
 
 def chained_case(rows, cols):
@@ -122,10 +125,13 @@ def test_two_ranks_equal_unsharded(oracle, tmp_path, rows, cols):
     a = oracle.encode(B.Q8_0, B.make_activations(m * cols, 7))
     want_c = oracle.matmul_blocks(B.Q8_0, B.Q4_0, a, w, m, rows, cols, order=1)
     assert np.array_equal(np.load(out + ".c.npy").view(np.uint32), want_c.view(np.uint32))
-    for epoch, rows_a in enumerate((m, 5)):
+    a_tall = oracle.encode(B.Q8_0, B.make_activations(M_TALL * cols, 8))
+    want_tall = oracle.matmul_blocks(B.Q8_0, B.Q4_0, a_tall, w, M_TALL, rows, cols, order=1)
+    for epoch, rows_a in enumerate((m, 5, M_TALL)):
         for rank in range(world):
             got = np.load(f"{out}.cx{epoch}.r{rank}.npy")
-            assert np.array_equal(got.view(np.uint32), want_c[:rows_a].reshape(-1).view(np.uint32)), (epoch, rank)
+            want = want_tall if rows_a == M_TALL else want_c[:rows_a]
+            assert np.array_equal(got.view(np.uint32), want.reshape(-1).view(np.uint32)), (epoch, rank)
     for epoch in range(3):
         want = oracle.gemv_blocks(B.Q4_0, B.F32, w, B.make_activations(cols, 60 + epoch), rows, cols, order=1)
         for rank in range(world):
