@@ -722,13 +722,13 @@ struct Pieces {
 enum { VAR_PLAIN = 0, VAR_MINS = 1, VAR_HALF = 2, VAR_TCS = 3 };
 
 template <int KIND, int OUT, int VAR>
-__global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(const __grid_constant__ MatmulArgs p)
+__global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS) + (OUT == 2 ? 32 : 0), 1) matmul_kernel(const __grid_constant__ MatmulArgs p)
 {
     // OUT: 0 lanes, 1 lanes and the blocks' integer sums, 2 lanes into the other GPUs' copies of C as well (the sharded product)
     constexpr bool SUMS = OUT == 1, PUB = OUT == 2;
     constexpr bool MINS = VAR == VAR_MINS, HALF = VAR == VAR_HALF, TCS = VAR == VAR_TCS;
     using G = Cfg<KIND, MINS, HALF, TCS>;
-    constexpr int EW = epi_warps(TCS), MMA2_WARP = 2 + EW, EC = 128 / (EW / 4);      // epilogue warps, the second issuer's warp, columns a warp
+    constexpr int EW = epi_warps(TCS), MMA2_WARP = 2 + EW, PUB_WARP = MMA2_WARP + 1, EC = 128 / (EW / 4);      // epilogue warps, the second issuer's warp, columns a warp
     constexpr int S = G::S, KS = G::KS, KC = G::KC, NT = G::NT, TCOLS = G::TCOLS, THREADS = mm_threads(TCS);
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -751,6 +751,7 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(c
             mbar_init(tempty0 + 8 * t, SPLIT2 ? EW / 2 : EW);
         }
         *abort_flag = 0;
+        for (int i = 0; i < EW; i++) *(volatile int *)(smem + 772 + 4 * i) = 0;          // pieces each epilogue warp has stored (the sharded product)
         mbar_fence_init();
     }
     if (G::PATCH) {
@@ -917,6 +918,71 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(c
             }
             if (role == 0) { MM_TRACE(p, 8, w_full); MM_TRACE(p, 9, w_tempty); MM_TRACE(p, 10, MM_CLOCK() - t_begin); MM_TRACE(p, 11, (long long)tc0); MM_TRACE(p, 12, c_mma); MM_TRACE(p, 13, c_commit); }
         }
+    } else if (PUB && warp == PUB_WARP) {
+        // ---- the sharded product's publisher (PUB: one more warp): it carries the finished pieces of C into the other GPUs'
+        // copies.  Once the epilogue warps have all stored a piece (their words), the piece is re-read row by row from this
+        // GPU's C (still in the L2) and stored to the peers, a warp a row's contiguous bytes: the peer stores cross NVLink as
+        // whole lines, and where they wait for the link only this warp waits with them.
+        Pieces pub_pieces(p, wmax);
+        int pub_tile = 0, pub_u0 = 0, pub_w = 0, pub_count = 0, pub_off = 0;
+        bool pub_has = false, pub_stored = false, pub_end = !(PUB && MM_WORLD(p) > 0);
+        auto publish_some = [&](int rounds) {
+            constexpr int UNR = 8;
+            while (rounds-- > 0 && !pub_end) {
+                if (!pub_has) {
+                    if (!pub_pieces.next(pub_tile, pub_u0, pub_w)) { pub_end = true; return; }
+                    pub_has = true; pub_stored = false; pub_off = 0;
+                }
+                if (!pub_stored) {
+                    const int ready = lane >= EW || *(volatile int *)(smem + 772 + 4 * lane) > pub_count;
+                    if (!__all_sync(0xffffffffu, ready)) return;
+                    __threadfence();
+                    pub_stored = true;
+                }
+                const int n0 = pub_u0 * p.unit, mt = pub_tile % p.mtiles;
+                const int rows_here = min(TILE, p.m - mt * TILE), wcols = min(p.n, n0 + pub_w * p.unit) - n0;
+                const size_t origin = (size_t)(mt * TILE) * p.ldc + n0;
+                const bool vec = (p.ldc & 3) == 0 && ((uintptr_t)p.c & 15) == 0 && peers_aligned(p.pub) && (wcols & 3) == 0;
+                const int upr = vec ? wcols >> 2 : wcols, total = rows_here * upr;         // units (float4 or float) a row, and in the piece
+                float4 x[UNR];
+                size_t off[UNR];
+#pragma unroll
+                for (int u = 0; u < UNR; u++) {
+                    const int idx = pub_off + u * 32 + lane, rr = idx / upr, c = idx - rr * upr;
+                    off[u] = origin + (size_t)rr * p.ldc + (vec ? 4 * c : c);
+                    if (idx < total) {
+                        if (vec) x[u] = __ldcg((const float4 *)(p.c + off[u]));
+                        else x[u].x = __ldcg(p.c + off[u]);
+                    }
+                }
+                for (int pw = 0; pw < p.pub.world; pw++) {
+                    float *peer = p.pub.out[pw];
+                    if (!peer) continue;
+#pragma unroll
+                    for (int u = 0; u < UNR; u++) {
+                        if (pub_off + u * 32 + lane < total) {
+                            if (vec) *(float4 *)(peer + off[u]) = x[u];
+                            else peer[off[u]] = x[u].x;
+                        }
+                    }
+                }
+                pub_off += UNR * 32;
+                if (pub_off >= total) { pub_has = false; pub_count++; }
+            }
+        };
+        const long long start = clock64();
+        while (!pub_end) {
+            publish_some(1 << 20);
+            if (pub_end) break;
+            int stop = *abort_flag != 0;
+            if (!stop && clock64() - start > 4 * WAIT_CYCLES) {           // (the whole kernel's time, not one handshake's)
+                *abort_flag = 1;
+                atomicOr(p.status, STATUS_MATMUL_WAIT);
+                stop = 1;
+            }
+            if (__any_sync(0xffffffffu, stop)) break;
+            __nanosleep(500);
+        }
     } else {
         // ---- epilogue: warp (q, g) owns rows 32 q .. 32 q + 31 of the tile (the tensor-memory lanes a warp may read) and
         // columns 32 g .. 32 g + 31 of the piece (none when the piece is narrower); the four warps of a q share a scheduler.
@@ -929,7 +995,7 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(c
         const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(SPLIT2 ? set * 256 + (g * EC) % 64 : g * EC);
         const uint32_t tfull_w = tfull0 + 8 * (set * NT), tempty_w = tempty0 + 8 * (set * NT);
         Pieces pieces(p, wmax);
-        int tile, u0, w, sc = 0, tc = 0;
+        int tile, u0, w, sc = 0, tc = 0, pieces_done = 0;
         bool alive = true;
         long long w_tfull = 0, t_store = 0, t_begin = MM_CLOCK();
         while (alive && pieces.next(tile, u0, w)) {
@@ -1074,34 +1140,13 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS), 1) matmul_kernel(c
             }
             t_store += MM_CLOCK() - s0;
             if (PUB && MM_WORLD(p) > 0) {
-                // The sharded product: once every epilogue warp has stored its lanes into this GPU's C, the epilogue threads
-                // re-read the piece row by row (it is still in the L2) and store it into the other GPUs' copies of C, a warp a
-                // row's 512 contiguous bytes: peer stores of whole lines, where the lane-a-row stores above would cross
-                // NVLink as 16-byte fragments.  (The barrier also tells every thread whether all of them are still going.)
-                if (!named_bar_and(2, EW * 32, alive && !*abort_flag)) { alive = false; break; }
-                const int tid = threadIdx.x - 64, rows_here = min(TILE, p.m - mt * TILE), wcols = min(p.n, n0 + w * p.unit) - n0;
-                const float *own = c_out + (size_t)(mt * TILE) * p.ldc + n0;
-                if ((p.ldc & 3) == 0 && ((uintptr_t)c_out & 15) == 0 && peers_aligned(p.pub) && (wcols & 3) == 0) {
-                    const int v4 = wcols >> 2;
-                    for (int idx = tid; idx < rows_here * v4; idx += EW * 32) {
-                        const int rr = idx / v4, c = idx - rr * v4;
-                        const size_t off = (size_t)rr * p.ldc + 4 * c;
-                        const float4 x = __ldcg((const float4 *)(own + off));
-                        for (int pw = 0; pw < p.pub.world; pw++) {
-                            float *peer = p.pub.out[pw];
-                            if (peer) *(float4 *)(peer + (own - c_out) + off) = x;
-                        }
-                    }
-                } else {
-                    for (int idx = tid; idx < rows_here * wcols; idx += EW * 32) {
-                        const int rr = idx / wcols, c = idx - rr * wcols;
-                        const size_t off = (size_t)rr * p.ldc + c;
-                        const float x = __ldcg(own + off);
-                        for (int pw = 0; pw < p.pub.world; pw++) {
-                            float *peer = p.pub.out[pw];
-                            if (peer) peer[(own - c_out) + off] = x;
-                        }
-                    }
+                // the sharded product: this warp's lanes of the piece are in this GPU's C; it says so in its own word (the
+                // pieces it has finished), which the publisher warp reads: a warp without columns in a narrow piece may be a
+                // piece ahead of the others, so the words are kept apart
+                __syncwarp();
+                if (lane == 0) {
+                    __threadfence();
+                    *(volatile int *)(smem + 772 + 4 * (warp - 2)) = ++pieces_done;
                 }
             }
             if (p.cb) {
@@ -2105,7 +2150,7 @@ static void launch_var(int grid, const MatmulArgs &args, cudaStream_t stream)
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
-    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(mm_threads(VAR == VAR_TCS)); cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(mm_threads(VAR == VAR_TCS) + (SUMS == 2 ? 32 : 0)); cfg.stream = stream; cfg.attrs = &attr; cfg.numAttrs = 1;
     cfg.dynamicSmemBytes = Cfg<KIND, VAR == VAR_MINS, VAR == VAR_HALF, VAR == VAR_TCS>::SMEM;
     cudaLaunchKernelEx(&cfg, matmul_kernel<KIND, SUMS, VAR>, args);
 }
