@@ -45,6 +45,14 @@ int finish(int rc, const char *what)
     return 0;
 }
 
+// A launch that is not a gemv: the gemv's record of launches in flight (which lets an unrelated gemv start beside its
+// predecessors) does not describe what this one touches, so the next gemv on the stream orders itself after everything.
+int finish_other(int rc, const char *what, void *stream)
+{
+    if (rc == 0) qb::gemv_history_everything((cudaStream_t)stream);
+    return finish(rc, what);
+}
+
 const char *fmt_name(int fmt)
 {
     switch (fmt) {
@@ -291,7 +299,7 @@ int qb200_matmul_blocks(int fmt_a, int fmt_b, const void *a, const void *b, floa
     if (rc) return rc;
     // a few rows of A: the weights stream once past activations held on the chip, no re-laying, no tensor tile of padding
     if ((rc = take_workspace(workspace, workspace_bytes, qb::matmul_workspace_bytes(fmt_b, m, n, k, ONE, false)))) return rc;
-    return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c, nullptr, 0, nullptr, m, n, k, ONE, workspace, (cudaStream_t)stream), "matmul_blocks");
+    return finish_other(qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c, nullptr, 0, nullptr, m, n, k, ONE, workspace, (cudaStream_t)stream), "matmul_blocks", stream);
 }
 
 // GpuOps.MatMulViewBlocks<TN> (reference src/MatMulBlocks.cs:414-424) in one product launch: the f32 lanes and their `Back`.
@@ -309,7 +317,7 @@ int qb200_matmul_blocks_back(int fmt_a, int fmt_b, const void *a, const void *b,
     const bool fused = n % 32 == 0 && ((uintptr_t)c_lanes & 15) == 0;
     rc = qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c_lanes, nullptr, fmt_c, fused ? c_blocks : nullptr, m, n, k, ONE, workspace, (cudaStream_t)stream);
     if (rc == 0 && !fused) rc = qb::encode_launch(fmt_c, c_lanes, c_blocks, (int64_t)m * n, (cudaStream_t)stream);
-    return finish(rc, "matmul_blocks_back");
+    return finish_other(rc, "matmul_blocks_back", stream);
 }
 
 size_t qb200_matmul_prepacked_bytes(int fmt_b, int n, int k)
@@ -327,7 +335,7 @@ int qb200_matmul_prepack(int fmt_b, const void *b, int n, int k, void *packed, s
     if (!packed || ((uintptr_t)packed & 255)) return fail(QB200_E_WORKSPACE, "the packed operand needs a 256-byte aligned buffer");
     const size_t need = qb::matmul_prepacked_bytes(fmt_b, n, k);
     if (packed_bytes < need) return fail(QB200_E_WORKSPACE, "packed buffer of %zu bytes, %zu needed", packed_bytes, need);
-    return finish(qb::matmul_prepack_b(fmt_b, b, n, k, packed, (cudaStream_t)stream), "matmul_prepack");
+    return finish_other(qb::matmul_prepack_b(fmt_b, b, n, k, packed, (cudaStream_t)stream), "matmul_prepack", stream);
 }
 
 size_t qb200_matmul_prepacked_workspace_bytes(int fmt_a, int fmt_b, int m, int k)
@@ -344,8 +352,8 @@ int qb200_matmul_blocks_prepacked(int fmt_a, int fmt_b, const void *a, const voi
     if (rc) return rc;
     if ((uintptr_t)b_packed & 255) return fail(QB200_E_WORKSPACE, "the packed operand is 256-byte aligned");
     if ((rc = take_workspace(workspace, workspace_bytes, qb::matmul_workspace_bytes(fmt_b, m, n, k, ONE, true)))) return rc;
-    return finish(qb::matmul_launch(fmt_a, fmt_b, a, nullptr, b_packed, c, nullptr, 0, nullptr, m, n, k, ONE, workspace, (cudaStream_t)stream),
-                  "matmul_blocks_prepacked");
+    return finish_other(qb::matmul_launch(fmt_a, fmt_b, a, nullptr, b_packed, c, nullptr, 0, nullptr, m, n, k, ONE, workspace, (cudaStream_t)stream),
+                  "matmul_blocks_prepacked", stream);
 }
 
 static int check_batch(int fmt_a, int fmt_b, int m, int n, int k, int batch, int64_t stride_a, int64_t stride_b, int64_t stride_c)
@@ -376,8 +384,8 @@ int qb200_matmul_blocks_batched(int fmt_a, int fmt_b, const void *a, const void 
     if ((rc = check_batch(fmt_a, fmt_b, m, n, k, batch, stride_a, stride_b, stride_c))) return rc;
     const qb::MatmulBatch bt = { batch, batch > 1 ? stride_a : 0, batch > 1 ? stride_b : 0, batch > 1 ? stride_c : 0 };
     if ((rc = take_workspace(workspace, workspace_bytes, qb::matmul_workspace_bytes(fmt_b, m, n, k, bt, false)))) return rc;
-    return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c, nullptr, 0, nullptr, m, n, k, bt, workspace, (cudaStream_t)stream),
-                  "matmul_blocks_batched");
+    return finish_other(qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c, nullptr, 0, nullptr, m, n, k, bt, workspace, (cudaStream_t)stream),
+                  "matmul_blocks_batched", stream);
 }
 
 int qb200_matmul_block_sums(int fmt_a, int fmt_b, const void *a, const void *b, float *c, int32_t *sums, int m, int n, int k, void *stream)
@@ -388,7 +396,7 @@ int qb200_matmul_block_sums(int fmt_a, int fmt_b, const void *a, const void *b, 
     const int per = fmt_b == QB200_Q6_K ? 16 : 32;
     if ((int64_t)m * n * (k / per) > (1 << 24)) return fail(QB200_E_LIMIT, "block sums are for small shapes: m*n*(k/%d) at most 2^24", per);
     if ((rc = keep(g_scratch, qb::matmul_workspace_bytes(fmt_b, m, n, k, ONE, false)))) return rc;
-    return finish(qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c, sums, 0, nullptr, m, n, k, ONE, g_scratch.ptr, (cudaStream_t)stream), "matmul_block_sums");
+    return finish_other(qb::matmul_launch(fmt_a, fmt_b, a, b, nullptr, c, sums, 0, nullptr, m, n, k, ONE, g_scratch.ptr, (cudaStream_t)stream), "matmul_block_sums", stream);
 }
 
 int qb200_tensor_rate(double *cycles_per_mma)
@@ -405,7 +413,7 @@ int qb200_encode(int fmt, const float *lanes, void *blocks, int64_t n, void *str
     if (!qb::block_values(fmt)) return fail(QB200_E_FORMAT, "%s: not a block format", fmt_name(fmt));
     if (n < 0 || n > 2147483647LL) return fail(QB200_E_SHAPE, "count %lld", (long long)n);
     if (n && (!lanes || !blocks || ((uintptr_t)lanes & 3))) return fail(QB200_E_POINTER, "null or misaligned operand");
-    return finish(qb::encode_launch(fmt, lanes, blocks, n, (cudaStream_t)stream), "encode");
+    return finish_other(qb::encode_launch(fmt, lanes, blocks, n, (cudaStream_t)stream), "encode", stream);
 }
 
 int qb200_decode(int fmt, const void *blocks, float *lanes, int64_t n, void *stream)
@@ -414,7 +422,7 @@ int qb200_decode(int fmt, const void *blocks, float *lanes, int64_t n, void *str
     if (!qb::block_values(fmt)) return fail(QB200_E_FORMAT, "%s: not a block format", fmt_name(fmt));
     if (n < 0 || n > 2147483647LL) return fail(QB200_E_SHAPE, "count %lld", (long long)n);
     if (n && (!lanes || !blocks || ((uintptr_t)lanes & 3))) return fail(QB200_E_POINTER, "null or misaligned operand");
-    return finish(qb::decode_launch(fmt, blocks, lanes, n, (cudaStream_t)stream), "decode");
+    return finish_other(qb::decode_launch(fmt, blocks, lanes, n, (cudaStream_t)stream), "decode", stream);
 }
 
 int qb200_shard_range(int rows, int world, int rank, int *first, int *count)
@@ -466,7 +474,7 @@ int qb200_shard_matmul(int fmt_a, int fmt_b, const void *a, const void *b_shard,
         if ((uintptr_t)b_shard_packed & 255) return fail(QB200_E_WORKSPACE, "the packed operand is 256-byte aligned");
         if ((rc = take_workspace(workspace, workspace_bytes, qb::matmul_workspace_bytes(fmt_b, m, count, k, ONE, b_shard_packed != nullptr)))) return rc;
     }
-    return finish(qb::shard_matmul(fmt_a, fmt_b, a, b_shard, b_shard_packed, m, n_total, k, peers, epoch, workspace, (cudaStream_t)stream), "shard_matmul");
+    return finish_other(qb::shard_matmul(fmt_a, fmt_b, a, b_shard, b_shard_packed, m, n_total, k, peers, epoch, workspace, (cudaStream_t)stream), "shard_matmul", stream);
 }
 
 int qb200_shard_gemv_after(int fmt_a, int fmt_x, const void *a_shard, const void *x, int rows_total, int cols, const qb200_shard_peers_t *peers,

@@ -931,6 +931,7 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS) + (OUT == 2 ? 32 : 
             while (rounds-- > 0 && !pub_end) {
                 if (!pub_has) {
                     if (!pub_pieces.next(pub_tile, pub_u0, pub_w)) { pub_end = true; return; }
+                    if (pub_pieces.at >= pub_pieces.hi) { pub_end = true; return; }      // the block's last piece is the epilogue warps' own
                     pub_has = true; pub_stored = false; pub_off = 0;
                 }
                 if (!pub_stored) {
@@ -1143,10 +1144,46 @@ __global__ void __launch_bounds__(mm_threads(VAR == VAR_TCS) + (OUT == 2 ? 32 : 
                 // the sharded product: this warp's lanes of the piece are in this GPU's C; it says so in its own word (the
                 // pieces it has finished), which the publisher warp reads: a warp without columns in a narrow piece may be a
                 // piece ahead of the others, so the words are kept apart
-                __syncwarp();
-                if (lane == 0) {
-                    __threadfence();
-                    *(volatile int *)(smem + 772 + 4 * (warp - 2)) = ++pieces_done;
+                if (pieces.at < pieces.hi) {
+                    __syncwarp();
+                    if (lane == 0) {
+                        __threadfence();
+                        *(volatile int *)(smem + 772 + 4 * (warp - 2)) = ++pieces_done;
+                    }
+                } else {
+                    // the block's last piece: no arithmetic is left to hide its transfer behind, so all the epilogue warps carry
+                    // it, the same way (once every warp has stored its lanes: the barrier, which also tells every thread
+                    // whether all of them are still going)
+                    if (!named_bar_and(2, EW * 32, alive && !*abort_flag)) { alive = false; break; }
+                    constexpr int T = EW * 32, UNR = 2;
+                    const int tid = threadIdx.x - 64, rows_here = min(TILE, p.m - mt * TILE), wcols = min(p.n, n0 + w * p.unit) - n0;
+                    const size_t origin = (size_t)(mt * TILE) * p.ldc + n0;
+                    const bool vec4 = (p.ldc & 3) == 0 && ((uintptr_t)p.c & 15) == 0 && peers_aligned(p.pub) && (wcols & 3) == 0;
+                    const int upr = vec4 ? wcols >> 2 : wcols, total = rows_here * upr;
+                    for (int i0 = tid; i0 < total; i0 += UNR * T) {
+                        float4 x[UNR];
+                        size_t off[UNR];
+#pragma unroll
+                        for (int u = 0; u < UNR; u++) {
+                            const int idx = i0 + u * T, rr = idx / upr, c = idx - rr * upr;
+                            off[u] = origin + (size_t)rr * p.ldc + (vec4 ? 4 * c : c);
+                            if (idx < total) {
+                                if (vec4) x[u] = __ldcg((const float4 *)(p.c + off[u]));
+                                else x[u].x = __ldcg(p.c + off[u]);
+                            }
+                        }
+                        for (int pw = 0; pw < p.pub.world; pw++) {
+                            float *peer = p.pub.out[pw];
+                            if (!peer) continue;
+#pragma unroll
+                            for (int u = 0; u < UNR; u++) {
+                                if (i0 + u * T < total) {
+                                    if (vec4) *(float4 *)(peer + off[u]) = x[u];
+                                    else peer[off[u]] = x[u].x;
+                                }
+                            }
+                        }
+                    }
                 }
             }
             if (p.cb) {

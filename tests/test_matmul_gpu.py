@@ -346,3 +346,29 @@ def test_k_quant_weights_prefill_shape(oracle, fmt_b):
     ref = oracle_k(oracle, fmt_b)(B.Q8_0, a_rows, b, len(pick), n, k)
     assert np.array_equal(c[pick].view(np.uint32), ref.view(np.uint32))
     assert np.isfinite(c).all()
+
+
+def test_a_gemv_after_a_product_reads_its_output(oracle):
+    # the gemv's record of launches in flight knows gemv launches only: a product (or a codec) between two gemvs must make
+    # the second one order itself after everything, or it could start beside the product whose C it reads as x
+    import torch
+    o = H.ops()
+    n, k, rows = 2048, 1024, 96
+    b = B.make_weights(B.Q8_0, n, k, 31)
+    a_raw = oracle.encode(B.Q8_0, B.make_activations(k, 32))
+    w = B.make_weights(B.Q8_0, rows, n, 33)
+    bd, ad, wd, x0 = H.dev(b), H.dev(a_raw), H.dev(w), H.dev(B.make_activations(n, 34))
+    c = torch.empty(n, dtype=torch.float32, device="cuda:0")
+    y0, y = torch.empty(rows, dtype=torch.float32, device="cuda:0"), torch.empty(rows, dtype=torch.float32, device="cuda:0")
+    want_c = oracle.matmul_blocks(B.Q8_0, B.Q8_0, a_raw, b, 1, n, k, order=1).reshape(-1)
+    want_y = oracle.gemv_blocks(B.Q8_0, B.F32, w, want_c, rows, n, order=1)
+    for _ in range(3):
+        c.fill_(float("nan"))
+        y.fill_(float("nan"))
+        o.GemvBlocks(B.Q8_0, wd, x0, y0, rows, n, fmt_x=B.F32)         # a launch the record knows, unrelated to what follows
+        o.MatMulBlocks(B.Q8_0, ad, bd, c, 1, n, k)
+        o.GemvBlocks(B.Q8_0, wd, c, y, rows, n, fmt_x=B.F32)
+        torch.cuda.synchronize()
+        assert o.gpu.status() == 0
+        assert np.array_equal(c.cpu().numpy().view(np.uint32), want_c.view(np.uint32))
+        assert np.max(np.abs(y.cpu().numpy() - want_y)) <= 1e-5 * np.abs(want_y).max()
