@@ -593,7 +593,7 @@ def main():
 
     abt_sharded = None
     if world > 1 and not args.no_extra:
-        abt_sharded = [abt_sharded_record(ops, torch, dist, timer, plan, rank, world, dev, shards[0], m) for m in (512, 2048)]
+        abt_sharded = [abt_sharded_record(ops, torch, dist, timer, plan, rank, world, dev, shards[0], m) for m in (8, 64, 512, 2048)]
 
     if rank != 0:
         exchange.close()
