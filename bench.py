@@ -325,7 +325,7 @@ def abt_record(ops, torch, timer, fmt_b, m, n, k, peak_measured):
 
 def abt_sharded_record(ops, torch, dist, timer, plan, rank, world, dev, shard, m):
     """The sharded A.B^T of the headline matrix at N > 1: rank r's rows of B give its column block of C.  Timed three ways
-    (host-launched calls between events, barrier on both sides, max over ranks): the column block alone; with the exchange
+    (CUDA events around the calls, barrier on both sides, max over ranks; the first two as replayed CUDA graphs): the column block alone; with the exchange
     inside the product kernel (every rank ends with the whole C); and joined by an NCCL all-gather instead."""
     from qiyas_b200.shard import PeerExchange, ShardedMatMul, all_gather_columns
     n_local = plan.count(rank)
@@ -333,13 +333,20 @@ def abt_sharded_record(ops, torch, dist, timer, plan, rank, world, dev, shard, m
     mm = ShardedMatMul(ops, plan, rank, FMT_A, K5, shard)
     packed = ops.Prepack(FMT_A, shard, n_local, K5)
     c_slice = torch.empty(m * max(n_local, 1), dtype=torch.float32, device=dev)
-    ex = PeerExchange(ops, m * N5, rank, world)
+    ex, exg = PeerExchange(ops, m * N5, rank, world), PeerExchange(ops, m * N5, rank, world)
     try:
         def local():
             ops.MatMulBlocksPrepacked(B.Q8_0, a, packed, c_slice, m, n_local, K5, fmt_b=FMT_A)
 
         def fused():
             return mm.exchange(B.Q8_0, a, m, ex, b_packed=packed)
+
+        def fused_counted(stream):
+            # epochs counted on the device (0): the form a captured graph can replay
+            rc = ops.lib.qb200_shard_matmul(B.Q8_0, FMT_A, a.data_ptr(), None, packed.data_ptr(), m, N5, K5, C.byref(exg.peers), 0, None, 0,
+                                            stream.cuda_stream)
+            ops.gpu.check(rc, "shard_matmul")
+            ops.gpu.check(ops.lib.qb200_shard_wait(C.byref(exg.peers), 0, 0, stream.cuda_stream), "shard_wait")
 
         def gathered():
             local()
@@ -350,20 +357,44 @@ def abt_sharded_record(ops, torch, dist, timer, plan, rank, world, dev, shard, m
         if ops.gpu.status() != 0 or not torch.equal(whole.view(torch.int32), joined.view(torch.int32)):
             raise SystemExit(f"sharded A.B^T check failed on rank {rank}: C after the exchange differs from the gathered column blocks")
         rec = {"shape": f"Q8_0 x {B.NAMES[FMT_A]}  M {m} N {N5} K {K5}, B's rows over {world} ranks (weights prepacked)"}
+        # each form as a CUDA graph of one product where it can be captured (small products are otherwise timed at the rate
+        # the host can launch them), replayed on the side stream; the all-gather form is host-launched.  The captured
+        # exchange counts its epochs on the device, so it has an exchange of its own (the two numberings do not mix).
+        side = timer.stream
+        graphs = {}
+        try:
+            graphs["local"] = capture(torch, side, lambda st: ops.MatMulBlocksPrepacked(B.Q8_0, a, packed, c_slice, m, n_local, K5, fmt_b=FMT_A, stream=st))
+            graphs["with_exchange"] = capture(torch, side, fused_counted)
+        except Exception as e:                     # noqa: BLE001 (a failed capture leaves the host-launched loop)
+            graphs = {}
+            rec["capture"] = f"not captured: {type(e).__name__}"
+        torch.cuda.synchronize()
+        dist.barrier()
+        rec["launch"] = {k: ("one CUDA graph of a product, replayed" if k in graphs else "host-launched") for k in ("local", "with_exchange", "with_allgather")}
         for name, fn, reps in (("local", local, 20), ("with_exchange", fused, 20), ("with_allgather", gathered, 10)):
-            for _ in range(3):
-                fn()
+            graph = graphs.get(name)
+            stream = side if graph is not None else torch.cuda.current_stream()
+            if graph is not None:
+                fn, reps = graph.replay, 40
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    fn()
             timer.barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(reps):
-                fn()
-            e1.record()
+            with torch.cuda.stream(stream):
+                e0.record()
+                for _ in range(reps):
+                    fn()
+                e1.record()
             timer.barrier()
             t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             us = float(t.item()) * 1e3 / reps
             rec[name] = {"us": us, "int8_TOPS": 2.0 * m * N5 * K5 / us / 1e6}
+        if graphs:
+            torch.cuda.synchronize()
+            if not torch.equal(exg.y()[:m * N5].view(torch.int32), joined.reshape(-1).view(torch.int32)):
+                raise SystemExit(f"sharded A.B^T check failed on rank {rank}: C after the replayed exchange differs from the gathered column blocks")
         if ops.gpu.status() != 0:
             raise SystemExit("a kernel gave up on a bounded wait: the timing is void")
         rec["exchange"] = "peer stores from the product kernel's epilogue + flags + bounded wait"
@@ -373,6 +404,7 @@ def abt_sharded_record(ops, torch, dist, timer, plan, rank, world, dev, shard, m
         torch.cuda.synchronize()
         dist.barrier()
         ex.close()
+        exg.close()
 
 
 def abt_cpu_baseline(seconds=8.0):
