@@ -9,7 +9,8 @@ NVLink unless a full output vector is wanted, in which case the f32 slices are j
 For the gemv, whose slices are a few kilobytes, the all-gather's launch latency is several times the product's own
 time.  `PeerExchange` is the alternative on one box: every rank maps every other rank's output vector (CUDA IPC) and
 the gemv kernel itself stores its rows into all of them, followed by a flag a rank; `ShardedGemv.exchange` is that call
-plus the bounded wait for the peers' flags (qb200_shard_gemv / qb200_shard_wait).
+plus the bounded wait for the peers' flags (qb200_shard_gemv / qb200_shard_wait).  `ShardedMatMul.exchange` does the same
+for A.B^T: the product kernel stores its column block of C into every rank's copy of C (qb200_shard_matmul).
 """
 from dataclasses import dataclass
 
