@@ -12,13 +12,18 @@
 //     unswizzled shared-memory layout of tcgen05), so that the rows a tile needs for one k-block are one contiguous run
 //     of bytes.  A (activations) is packed on every call, tile-major; B (weights) is packed k-block-major and can be
 //     packed once and kept by the caller (matmul_prepack_b): the layout does not depend on m.
-//  2. matmul_kernel: a persistent grid, one block a multiprocessor.  The output is cut into units of 16 (or 32)
-//     columns of one 128-row tile of A; block b takes a contiguous, equal share of the units and walks it in pieces of
-//     up to BNMAX columns.  A producer warp brings codes and scales into a ring of shared-memory stages with untiled
-//     TMA bulk copies; one thread issues the tcgen05.mma of every k-block (M 128, N = the piece's width, accumulation
-//     off) into one of NT accumulators in tensor memory and commits it to an mbarrier; sixteen epilogue warps read the
-//     sums back with tcgen05.ld, eight columns a chunk, scale them in f32 (packed f32x2 instructions) and add them to
-//     register accumulators while the products of the next k-blocks run.
+//  2. matmul_kernel (more than 64 rows of A): a persistent grid, one block a multiprocessor.  The output is cut into
+//     units of 32 columns of one 128-row tile of A; block b takes a contiguous, equal share of the units and walks it in
+//     pieces of up to BNMAX columns.  A producer warp brings codes and scales into a ring of shared-memory stages with
+//     untiled TMA bulk copies; two threads issue the tcgen05.mma of the k-blocks (M 128, N = the piece's width or its
+//     half, accumulation off) into accumulators in tensor memory and commit each to an mbarrier; the epilogue warps
+//     (eight of 64 columns with the scale products on the tensor cores, sixteen of 32 otherwise) read the sums back
+//     with tcgen05.ld, scale them in f32 and add them to register accumulators while the products of the next k-blocks
+//     run.  Optional tails: C again as blocks (`Back`), or C into the other GPUs' copies (the sharded product: a
+//     publisher warp).
+//  3. fewrows_kernel / fewq_kernel (at most 64 rows of A): the operands change sides, B's 128 rows on the lanes of tensor
+//     memory and A's rows as N = 16 / 32 / 64; fewrows_kernel can also take Q8_0 / Q4_0 weights as raw blocks, fetched
+//     by 2-D TMA tile copies and re-laid by converter warps inside the kernel.
 //
 // Where both operands carry plain f16 block scales (Q8_0 / Q4_0 against Q8_0 / Q4_0) the scale products sA*sB are taken
 // by the tensor cores as well (TCS): a second instruction a k-block, kind::f16 with K = 16, multiplies the 128 x 1 column
@@ -2221,7 +2226,7 @@ int matmul_launch(int fmt_a, int fmt_b, const void *a, const void *b, const void
     const bool tcs = use_tcs(fmt_b);
     // few rows of A: B's rows become the lanes of tensor memory (fewrows_kernel), A is packed for that
     const bool few = tcs && !sums && g_mm_kind == 0 && m <= g_mm_few;
-    // ... and against Q4_K weights (scale products on the CUDA cores) with at most 32 rows, lanes only
+    // ... and against Q4_K weights (scale products on the CUDA cores) with at most 64 rows, lanes only
     const bool fewq = (mins || half) && !sums && !c_blocks && g_mm_kind == 0 && m <= 64 && m <= g_mm_few;
     const int bn = few_bn(m), a_layout = few || fewq ? LAY_FEW : LAY_TILE, lay_b = b_layout(fmt_b);
     const size_t a_slab = a_packed_bytes(m, k, kbs, tcs), b_slab = packed_bytes(lay_b, n, k, kbs, false);
