@@ -45,6 +45,14 @@ def test_calls_fail_loudly_without_a_device(library):
     assert library.qb200_last_error()
     # nothing runs on the CPU instead: the product entry points refuse
     assert library.qb200_gemv_blocks(0, 0, None, None, None, 4, 32, None) == -5
+    assert library.qb200_matmul_blocks(0, 0, None, None, None, 4, 4, 32, None, 0, None) == -5
+    # ... and so do the sharded ones, before they look at their peers
+    from qiyas_b200 import _lib
+    peers = _lib.ShardPeers()
+    peers.world, peers.rank = 2, 0
+    assert library.qb200_shard_gemv(0, 0, None, None, 8, 32, ctypes.byref(peers), 1, None) == -5
+    assert library.qb200_shard_matmul(0, 0, None, None, None, 4, 8, 32, ctypes.byref(peers), 1, None, 0, None) == -5
+    assert library.qb200_shard_wait(ctypes.byref(peers), 1, 0, None) == -5
     assert library.qb200_block_product_available() == 0
 
 
