@@ -99,7 +99,7 @@ def test_few_rows_of_a(oracle, fmt_a, fmt_b, m, n, k):
 
 @pytest.mark.parametrize("fmt_b", [B.Q8_0, B.Q4_0])
 @pytest.mark.parametrize("m,n,k,offset", [(8, 300, 512, 0), (8, 300, 512, 2), (32, 129, 256, 0), (19, 1000, 2048, 16), (3, 128, 256, 6), (64, 257, 1024, 0),
-                                            (40, 1000, 4096, 32)])
+                                            (40, 1000, 4096, 32), (8, 100, 256, 0), (50, 5, 512, 0)])
 def test_raw_weights_in_the_product_kernel(oracle, fmt_b, m, n, k, offset):
     # at most 64 rows of A, k in whole groups of eight blocks: the kernel converts the raw rows of B itself when B lies on a
     # 16-byte boundary, and falls back to the packing pass when it does not; the same bits either way
